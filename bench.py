@@ -1,0 +1,304 @@
+"""Benchmark of the mixture-evaluation hot path: evaluate_inversed forward + backward, 3D, fp32.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one forward + backward pass over one batch of the 3D evaluation configuration
+(B=32 per GPU, L=16, G=512 components, N=16384 query points: 2^32 Gaussian-point pairs per GPU and step).
+With N > 1 (launched under torch.distributed.run, one rank per GPU) every rank owns its own batch shard
+(weak scaling); the only inter-GPU traffic is an NCCL all-gather of the forward outputs, enqueued on a side
+stream so that it overlaps the backward kernel. Rank 0 prints one JSON line.
+
+--impl reference times the reference's CPU algorithm (the oracle restatement of its OpenMP path, fp32) on the
+host cores for the same metric, on a bounded batch slice of the same workload.
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+PKG = os.path.join(ROOT, "gaussian-mixture-convolution-networks_b200")
+for _p in (ROOT, PKG):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+METRIC = "gaussian_point_evals_per_s_fwd_bwd_3d"
+UNIT = "pair-evals/s"
+L, G, N, D = 16, 512, 16384, 3
+B_PER_GPU = 32
+FLOP_FWD, FLOP_BWD = 27, 52          # algorithmic FP32 flop per (Gaussian, point) pair, 3D
+N_SM_LANES = 128                      # FP32 lanes per SM
+
+
+def _args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-batch", type=int, default=4, help="batch slice timed on the host cores")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def _measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "sm_max_mhz": 1965.0}, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        self.index = index
+        self.samples = []
+        self.reasons = set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nvml = None
+
+    def _run(self):
+        nv = self.nvml
+        names = {}
+        for n in dir(nv):
+            if n.startswith("nvmlClocksEventReason") or n.startswith("nvmlClocksThrottleReason"):
+                v = getattr(nv, n)
+                if isinstance(v, int) and v != 0:
+                    names.setdefault(v, n.replace("nvmlClocksEventReason", "").replace("nvmlClocksThrottleReason", ""))
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                for bit, name in names.items():
+                    if mask & bit and bin(bit).count("1") == 1:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.02)
+
+    def start(self):
+        if self.nvml is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": ["unsampled"]}
+        s = sorted(self.samples)
+        reasons = sorted(r for r in self.reasons if r not in ("None", "GpuIdle", "ApplicationsClocksSetting"))
+        return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": reasons, "samples": len(s)}
+
+
+def _cpu_baseline(cpu_batch):
+    """Reference CPU algorithm (oracle restatement, fp32, OpenMP over query points) on a batch slice."""
+    from gmc import synthetic
+    from oracle import cpu_oracle
+    m, x, g = synthetic.config1(n_batch=cpu_batch)
+    m, x, g = m.numpy(), x.numpy(), g.numpy()
+    cpu_oracle.eval_forward(m[:1, :1], x[:1, :1])   # page in / thread pool warm-up
+    t0 = time.perf_counter()
+    cpu_oracle.eval_forward(m, x)
+    cpu_oracle.eval_backward(g, m, x)
+    dt = time.perf_counter() - t0
+    pairs = cpu_batch * L * G * N
+    return {"value": pairs / dt, "unit": UNIT, "cores": cpu_oracle.num_threads(), "kind": "port",
+            "sample": f"batch slice B={cpu_batch} of the same workload ({pairs} pairs, one fwd+bwd, {dt:.2f} s); "
+                      "fp32, OpenMP over query points"}, dt
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    times = []
+    base = None
+    for i in range(args.warmup + args.steps):
+        base, dt = _cpu_baseline(args.cpu_batch)
+        if i >= args.warmup:
+            times.append(dt)
+        if sum(times) > 120:     # keep the whole run within a few minutes
+            break
+    steps = len(times)
+    pairs = args.cpu_batch * L * G * N
+    value = pairs * steps / sum(times)
+    base["value"] = value
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+            "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"config1 slice: 3D evaluate_inversed fwd+bwd, B={args.cpu_batch} L={L} G={G} N={N}"},
+            "cpu_baseline": base,
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    import gmc.mixture as gm
+    from gmc import synthetic, sharding
+    import gmc.cpp.extensions.evaluate_inversed.evaluate_inversed as ev
+
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+
+    # every rank owns its own batch shard (different seed per rank)
+    m_h, x_h, g_h = synthetic.config1(n_batch=B_PER_GPU, seed=1001 + rank)
+    m_h, x_h, g_h = m_h.pin_memory(), x_h.pin_memory(), g_h.pin_memory()
+    m, x, g = m_h.to(dev), x_h.to(dev), g_h.to(dev)
+    pairs_rank = B_PER_GPU * L * G * N
+    gather = sharding.OutputGatherer(world, dev) if world > 1 else None
+
+    def step(record=None):
+        out = ev.parallel_forward(m, x)[0]
+        if record is not None:
+            record[1].record()
+        if gather is not None:
+            gather.start(out)          # side stream, overlaps the backward kernel
+        gm_, gx_ = ev.parallel_backward(g, m, x, None, True, True)
+        if gather is not None:
+            gather.finish()
+        if record is not None:
+            record[2].record()
+        return out, gm_, gx_
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else local_rank)
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    for i in range(args.steps):
+        evs[i][0].record()
+        step(evs[i])
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    clocks = sampler.stop()
+    total_ms = evs[0][0].elapsed_time(evs[-1][2])
+    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in evs) / args.steps
+    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in evs) / args.steps
+
+    # ---- end to end through the public API with host buffers ----
+    out_h = torch.empty((B_PER_GPU, L, N), dtype=torch.float32).pin_memory()
+    gm_h = torch.empty_like(m_h).pin_memory()
+    gx_h = torch.empty_like(x_h).pin_memory()
+    e2e_steps = max(3, min(args.steps, 20))
+
+    def e2e_step():
+        md = m_h.to(dev, non_blocking=True).requires_grad_(True)
+        xd = x_h.to(dev, non_blocking=True).requires_grad_(True)
+        gd = g_h.to(dev, non_blocking=True)
+        out = gm.evaluate_inversed(md, xd)
+        out.backward(gd)
+        out_h.copy_(out.detach(), non_blocking=True)
+        gm_h.copy_(md.grad, non_blocking=True)
+        gx_h.copy_(xd.grad, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+
+    t = torch.tensor([total_ms, fwd_ms, bwd_ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, fwd_ms, bwd_ms, e2e_ms = t.tolist()
+    if rank != 0:
+        return
+
+    peaks, peaks_kind = _measured_peaks()
+    n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
+    sm_max_mhz = float(peaks.get("sm_max_mhz", 1965.0))
+    fp32_peak_tflops = n_sm * N_SM_LANES * 2 * sm_max_mhz * 1e6 / 1e12     # nominal: no measured FP32 entry exists
+    ms_per_step = total_ms / args.steps
+    value = world * pairs_rank / (ms_per_step * 1e-3)
+    ach_bwd = FLOP_BWD * pairs_rank / (bwd_ms * 1e-3) / 1e12
+    ach_fwd = FLOP_FWD * pairs_rank / (fwd_ms * 1e-3) / 1e12
+    ach_all = (FLOP_FWD + FLOP_BWD) * pairs_rank / ((fwd_ms + bwd_ms) * 1e-3) / 1e12
+    h2d = (m_h.numel() + x_h.numel() + g_h.numel()) * 4
+    d2h = (out_h.numel() + gm_h.numel() + gx_h.numel()) * 4
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"config1: 3D evaluate_inversed fwd+bwd, B={B_PER_GPU}/GPU L={L} G={G} N={N} "
+                               f"({pairs_rank} pairs per GPU and step)",
+                   "l2": "inputs (148 MB per step) are larger than L2 (126 MB); no explicit flush",
+                   "sharding": f"batch over {world} rank(s), all-gather of forward outputs overlapped with backward"},
+        "roofline": {"bound": "fp32", "kernel": "eval_backward_kernel<3,4>", "achieved": ach_bwd,
+                     "peak": fp32_peak_tflops, "unit": "TFLOP/s", "frac": ach_bwd / fp32_peak_tflops,
+                     "traffic": None,
+                     "peak_source": f"nominal {n_sm} SMs x 128 lanes x 2 flop x {sm_max_mhz:.0f} MHz "
+                                    f"(sm_max_mhz from {peaks_kind} MEASURED_PEAKS.json; it has no FP32 entry)",
+                     "algorithmic_flop_per_pair": FLOP_BWD, "ms_per_launch": bwd_ms},
+        "roofline_forward": {"bound": "fp32", "kernel": "eval_forward_kernel<3,4>", "achieved": ach_fwd,
+                             "peak": fp32_peak_tflops, "unit": "TFLOP/s", "frac": ach_fwd / fp32_peak_tflops,
+                             "algorithmic_flop_per_pair": FLOP_FWD, "ms_per_launch": fwd_ms},
+        "roofline_fwd_bwd": {"bound": "fp32", "achieved": ach_all, "peak": fp32_peak_tflops, "unit": "TFLOP/s",
+                             "frac": ach_all / fp32_peak_tflops, "algorithmic_flop_per_pair": FLOP_FWD + FLOP_BWD},
+        "e2e": {"value": world * pairs_rank / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps},
+        "gpu_launches": 2 * args.steps,
+        "clocks": clocks,
+    }
+    if not args.no_cpu_baseline and world == 1:
+        line["cpu_baseline"], _ = _cpu_baseline(args.cpu_batch)
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    args = _args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,76 @@
+"""Builds libgmc_b200.so (the C-ABI library) from csrc/*.cu with nvcc for sm_100a.
+
+Run as a script or call build(). Objects are compiled in parallel and only when a source or header
+is newer than the object; the shared object lands next to the Python package in gmc/_lib/.
+"""
+import concurrent.futures
+import os
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+INCLUDE = os.path.join(os.path.dirname(HERE), "include")
+OUT_DIR = os.path.join(HERE, "gmc", "_lib")
+BUILD_DIR = os.path.join(HERE, "build")
+LIB_PATH = os.path.join(OUT_DIR, "libgmc_b200.so")
+
+NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
+COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-I", INCLUDE, "-I", CSRC]
+# Fast-math is applied per file: kernels whose integer results must be bit-exact (Morton codes) are
+# compiled with IEEE arithmetic and without FMA contraction.
+FAST_MATH = ["--use_fast_math"]
+IEEE_FILES = {"lbvh.cu", "convolution_fitting.cu"}
+
+
+def _sources():
+    return sorted(f for f in os.listdir(CSRC) if f.endswith(".cu"))
+
+
+def _headers_mtime():
+    newest = 0.0
+    for d in (CSRC, INCLUDE):
+        for f in os.listdir(d):
+            if f.endswith((".cuh", ".h")):
+                newest = max(newest, os.path.getmtime(os.path.join(d, f)))
+    return newest
+
+
+def _compile(src, verbose):
+    obj = os.path.join(BUILD_DIR, src[:-3] + ".o")
+    src_path = os.path.join(CSRC, src)
+    if os.path.exists(obj) and os.path.getmtime(obj) >= max(os.path.getmtime(src_path), _headers_mtime()):
+        return obj
+    flags = list(COMMON_FLAGS)
+    if src in IEEE_FILES:
+        flags += ["--fmad=false"]
+    else:
+        flags += FAST_MATH
+    if verbose:
+        flags += ["-Xptxas", "-v"]
+    cmd = [NVCC] + ARCH_FLAGS + flags + ["-c", src_path, "-o", obj]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"nvcc failed for {src}:\n{res.stdout}\n{res.stderr}")
+    if verbose:
+        print(res.stderr)
+    return obj
+
+
+def build(verbose: bool = False) -> str:
+    os.makedirs(OUT_DIR, exist_ok=True)
+    os.makedirs(BUILD_DIR, exist_ok=True)
+    srcs = _sources()
+    with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as pool:
+        objs = list(pool.map(lambda s: _compile(s, verbose), srcs))
+    if (not os.path.exists(LIB_PATH)) or any(os.path.getmtime(o) > os.path.getmtime(LIB_PATH) for o in objs):
+        cmd = [NVCC] + ARCH_FLAGS + ["-shared", "-o", LIB_PATH] + objs + ["-lcudart"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+    return LIB_PATH
+
+
+if __name__ == "__main__":
+    print(build(verbose="-v" in sys.argv))

@@ -1,0 +1,43 @@
+// Status strings, the per-thread CUDA error message and the device check word reader.
+#include "common.cuh"
+
+namespace gmc {
+namespace {
+thread_local cudaError_t t_last_error = cudaSuccess;
+}
+void set_last_cuda_error(cudaError_t e) { t_last_error = e; }
+}  // namespace gmc
+
+// one reader per translation unit that owns kernels
+int gmc_tu_check_eval_inversed(int* word);
+int gmc_tu_check_small_ops(int* word);
+
+extern "C" const char* gmc_status_string(int status) {
+    switch (status) {
+        case GMC_OK: return "ok";
+        case GMC_ERR_BAD_DIMS: return "bad dimensions: D must be 2 or 3 and every extent positive and within its limit";
+        case GMC_ERR_BAD_BROADCAST: return "xes must have a batch and layer extent of one or equal to the mixture's";
+        case GMC_ERR_NULL_POINTER: return "a required pointer is NULL";
+        case GMC_ERR_UNSUPPORTED: return "unsupported parameter value";
+        case GMC_ERR_WORKSPACE: return "scratch buffer too small";
+        case GMC_ERR_CUDA: return "CUDA runtime error";
+        case GMC_ERR_DEVICE_CHECK: return "a device-side check failed";
+        case GMC_ERR_ALIGNMENT: return "pointer not aligned";
+        default: return "unknown status";
+    }
+}
+
+extern "C" const char* gmc_last_cuda_error(void) {
+    return gmc::t_last_error == cudaSuccess ? "" : cudaGetErrorString(gmc::t_last_error);
+}
+
+extern "C" const char* gmc_version(void) { return "0.1"; }
+
+extern "C" int gmc_device_check_word(int* word_out) {
+    if (!word_out) return GMC_ERR_NULL_POINTER;
+    *word_out = 0;
+    GMC_CUDA_TRY(cudaDeviceSynchronize());
+    if (int s = gmc_tu_check_eval_inversed(word_out)) return s;
+    if (int s = gmc_tu_check_small_ops(word_out)) return s;
+    return GMC_OK;
+}

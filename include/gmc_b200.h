@@ -1,0 +1,98 @@
+/*
+ * gmc_b200.h -- C ABI of the B200 (sm_100a) Gaussian-mixture operator library.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as void*,
+ * nullptr = the legacy default stream) and returns an int status (GMC_OK == 0). The library
+ * allocates nothing: outputs and scratch are owned by the caller. All kernels are enqueued on
+ * the given stream and the call returns without synchronising. There is no CPU code path: a
+ * call on a machine without a CUDA device returns GMC_ERR_CUDA.
+ *
+ * Data layout (identical to the reference's packed mixtures, src/gmc/mixture.py:37-67 and
+ * src/gmc/cpp/extensions/util/gaussian.h:14-46): a mixture is a contiguous fp32 array
+ * [n_batch, n_layers, n_components, 1 + D + D*D] = [weight | position(D) | matrix(DxD, row major)],
+ * D in {2, 3}. "layers" are feature channels.
+ *
+ * The reference binds each operator through pybind11 functions that take torch::Tensor; the
+ * comment above each declaration names the reference function it replaces.
+ */
+#ifndef GMC_B200_H
+#define GMC_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum gmc_status {
+    GMC_OK = 0,
+    GMC_ERR_BAD_DIMS = 1,        /* D not in {2,3} or a size is <= 0 / exceeds a documented limit     */
+    GMC_ERR_BAD_BROADCAST = 2,   /* xes batch/layer extent is neither 1 nor the mixture's             */
+    GMC_ERR_NULL_POINTER = 3,    /* a required pointer is NULL                                        */
+    GMC_ERR_UNSUPPORTED = 4,     /* e.g. reduction_n not in {2,4}                                     */
+    GMC_ERR_WORKSPACE = 5,       /* caller-provided scratch is too small                              */
+    GMC_ERR_CUDA = 6,            /* a CUDA runtime call failed (see gmc_last_cuda_error)              */
+    GMC_ERR_DEVICE_CHECK = 7,    /* a kernel-side bounded wait or self check gave up                  */
+    GMC_ERR_ALIGNMENT = 8        /* a pointer is not aligned to sizeof(float)                         */
+};
+
+/* Human-readable text for a status code (static storage, never NULL). */
+const char* gmc_status_string(int status);
+/* cudaGetErrorString of the last CUDA error this library saw on the calling thread ("" if none). */
+const char* gmc_last_cuda_error(void);
+/* Library version, "major.minor". */
+const char* gmc_version(void);
+/* Reads and clears the device-side check word of the current device (synchronises the device).
+ * 0 = no kernel reported a problem since the last call. */
+int gmc_device_check_word(int* word_out);
+
+/* ------------------------------------------------------------------------------------------------
+ * Mixture evaluation with the matrix slot holding the INVERSE covariance S:
+ *   out[b,l,n] = sum_g w * (2 pi)^(-D/2) * sqrt(det S_g) * exp(-1/2 (x - mu_g)^T S_g (x - mu_g))
+ * xes is [n_batch_xes, n_layers_xes, n_xes, D] with n_batch_xes in {1, n_batch} and n_layers_xes in
+ * {1, n_layers} (broadcast). out is [n_batch, n_layers, n_xes] and is fully overwritten.
+ *
+ * Replaces evaluate_inversed::parallel_forward
+ *   (src/gmc/cpp/extensions/evaluate_inversed/evaluate_inversed.cpp:11-20,
+ *    parallel_implementation_optimised_forward.cu:59-98; math util/gaussian.h:82-95).
+ * ---------------------------------------------------------------------------------------------- */
+int gmc_eval_inversed_forward(const float* mixture, const float* xes, float* out,
+                              int n_batch, int n_layers, int n_components, int n_dims,
+                              int n_batch_xes, int n_layers_xes, int n_xes, void* stream);
+
+/* Gradients of the evaluation above for an incoming grad_out [n_batch, n_layers, n_xes].
+ * grad_mixture ([n_batch, n_layers, n_components, 1+D+D*D], full DxD matrix gradient) and grad_xes
+ * (same shape as xes; summed over the broadcast axes) may each be NULL, which skips that gradient.
+ * Non-NULL outputs are fully overwritten (the library zeroes them before accumulating).
+ *
+ * Replaces evaluate_inversed::parallel_backward
+ *   (evaluate_inversed.cpp:22-34, parallel_implementation_optimised_backward.cu:111-169;
+ *    math util/grad/gaussian.h:19-66).
+ * ---------------------------------------------------------------------------------------------- */
+int gmc_eval_inversed_backward(const float* grad_out, const float* mixture, const float* xes,
+                               float* grad_mixture, float* grad_xes,
+                               int n_batch, int n_layers, int n_components, int n_dims,
+                               int n_batch_xes, int n_layers_xes, int n_xes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Batched inverse of n_matrices contiguous row-major DxD matrices (D in {2,3}); `inverses` holds the
+ * mathematical inverse in the same layout. In-place (inverses == matrices) is allowed.
+ *
+ * Replaces matrix_inverse_cuda.forward (src/gmc/cpp/extensions/math/matrix_inverse_cuda.cu:18-63,
+ * Python wrapper math/matrix_inverse.py:14-36) and pieces_bindings.matrix_inverse
+ * (src/gmc/cpp/extensions/pieces/matrix_inverse.cu:23-73).
+ * ---------------------------------------------------------------------------------------------- */
+int gmc_matrix_inverse(const float* matrices, float* inverses, long long n_matrices, int n_dims, void* stream);
+
+/* Integral of each mixture = sum of its weights (weights are integrals, not amplitudes).
+ * mixture is [n_mixtures, n_components, 1+D+D*D], integrals is [n_mixtures].
+ * Replaces gm.integrate (src/gmc/mixture.py:87-91), which the reference computes with a torch reduction.
+ * ---------------------------------------------------------------------------------------------- */
+int gmc_integrate(const float* mixture, float* integrals, long long n_mixtures, int n_components, int n_dims,
+                  void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GMC_B200_H */

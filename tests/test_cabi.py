@@ -1,0 +1,55 @@
+"""CPU: the C-ABI library loads and exports every function that include/gmc_b200.h declares; host-side
+argument checks answer with status codes (no GPU work is issued)."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+from conftest import ROOT
+
+
+def _declared_functions():
+    text = open(os.path.join(ROOT, "include", "gmc_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(gmc_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported():
+    from gmc import _native
+    names = _declared_functions()
+    assert "gmc_eval_inversed_forward" in names and "gmc_eval_inversed_backward" in names
+    for n in names:
+        assert hasattr(_native.lib, n), f"{n} declared in gmc_b200.h but not exported"
+
+
+def test_status_strings():
+    from gmc import _native
+    assert _native.lib.gmc_status_string(0) == b"ok"
+    for s in range(1, 9):
+        assert len(_native.lib.gmc_status_string(s)) > 0
+    assert _native.lib.gmc_version().decode().count(".") == 1
+
+
+def test_argument_checks_return_status_without_gpu():
+    from gmc import _native
+    null = ctypes.c_void_p(0)
+    one = ctypes.c_void_p(16)  # never dereferenced: argument checks come first
+    f = _native.lib.gmc_eval_inversed_forward
+    assert f(one, one, one, 1, 1, 1, 4, 1, 1, 1, null) == 1   # D = 4
+    assert f(one, one, one, 2, 1, 1, 2, 3, 1, 1, null) == 2   # batch broadcast mismatch
+    assert f(null, one, one, 1, 1, 1, 2, 1, 1, 1, null) == 3  # NULL mixture
+    b = _native.lib.gmc_eval_inversed_backward
+    assert b(one, one, one, one, one, 1, 1, 0, 2, 1, 1, 1, null) == 1
+    assert b(null, one, one, one, one, 1, 1, 1, 2, 1, 1, 1, null) == 3
+
+
+def test_cpu_tensors_are_rejected_loudly():
+    import gmc.cpp.extensions.evaluate_inversed.evaluate_inversed as ev
+    with pytest.raises(RuntimeError, match="no CPU implementation"):
+        ev.apply(torch.zeros(1, 1, 1, 7), torch.zeros(1, 1, 1, 2))
+    with pytest.raises(RuntimeError, match="last dimension"):
+        ev.apply(torch.zeros(1, 1, 1, 8), torch.zeros(1, 1, 1, 2))
+    with pytest.raises(RuntimeError, match="batch dimension"):
+        ev.apply(torch.zeros(2, 1, 1, 7), torch.zeros(3, 1, 1, 2))

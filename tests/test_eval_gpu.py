@@ -1,0 +1,151 @@
+"""GPU parity of evaluate_inversed forward/backward (CUDA through the C-ABI) against the fp64 CPU oracle and the
+golden vectors from the reference's Python. Tolerance: relative 1e-4 per output tensor (||a-b||inf / ||ref||inf),
+with the reference's own criterion (RMSE rounds to 0 at 4 places, src/gmc/test_cpp_eval.py:15-22) checked beside it."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import rel_inf
+from oracle import cpu_oracle
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-4
+
+
+def _gpu_eval(mixture: np.ndarray, xes: np.ndarray, grad_out: np.ndarray):
+    import gmc.cpp.extensions.evaluate_inversed.evaluate_inversed as ev
+    m = torch.from_numpy(mixture).cuda().requires_grad_(True)
+    x = torch.from_numpy(xes).cuda().requires_grad_(True)
+    out = ev.apply(m, x)
+    out.backward(torch.from_numpy(grad_out).cuda())
+    return out.detach().cpu().numpy(), m.grad.cpu().numpy(), x.grad.cpu().numpy()
+
+
+def _check(mixture, xes, grad_out, ref=None, what=""):
+    out, gm, gx = _gpu_eval(mixture, xes, grad_out)
+    if ref is None:
+        m64, x64, g64 = (a.astype(np.float64) for a in (mixture, xes, grad_out))
+        ref_out = cpu_oracle.eval_forward(m64, x64)
+        ref_gm, ref_gx = cpu_oracle.eval_backward(g64, m64, x64)
+    else:
+        ref_out, ref_gm, ref_gx = ref
+    assert out.shape == ref_out.shape and gm.shape == ref_gm.shape and gx.shape == ref_gx.shape
+    for name, a, r in (("out", out, ref_out), ("grad_mixture", gm, ref_gm), ("grad_xes", gx, ref_gx)):
+        assert np.isfinite(a).all(), f"{what} {name} not finite"
+        assert rel_inf(a, r) < TOL, f"{what} {name}: rel {rel_inf(a, r):.3e}"
+    # grad_mixture per field (weight / position / matrix have different magnitudes)
+    D = xes.shape[-1]
+    for name, sl in (("w", slice(0, 1)), ("pos", slice(1, 1 + D)), ("mat", slice(1 + D, None))):
+        assert rel_inf(gm[..., sl], ref_gm[..., sl]) < TOL, f"{what} grad_mixture[{name}]"
+
+
+def test_golden_vectors(golden_eval):
+    cases = sorted({k.rsplit("_mixture", 1)[0] for k in golden_eval if k.endswith("_mixture") and "grad" not in k})
+    for c in cases:
+        ref = (golden_eval[c + "_out"], golden_eval[c + "_grad_mixture"], golden_eval[c + "_grad_xes"])
+        _check(golden_eval[c + "_mixture"], golden_eval[c + "_xes"], golden_eval[c + "_grad_out"], ref, c)
+        out, _, _ = _gpu_eval(golden_eval[c + "_mixture"], golden_eval[c + "_xes"], golden_eval[c + "_grad_out"])
+        rmse = float(np.sqrt(((out - golden_eval[c + "_out_f32ref"]) ** 2).mean()))
+        assert round(rmse, 4) == 0
+
+
+def _random_case(rng, B, L, G, N, D, bx, lx, radius=10.0):
+    w = rng.uniform(-1, 1, (B, L, G)).astype(np.float32)
+    p = rng.uniform(-radius, radius, (B, L, G, D)).astype(np.float32)
+    A = rng.uniform(-1, 1, (B, L, G, D, D))
+    cov = (A @ np.swapaxes(A, -1, -2) + np.eye(D) * 0.01) * radius
+    inv = np.linalg.inv(cov)
+    inv = 0.5 * (inv + np.swapaxes(inv, -1, -2))
+    mixture = np.concatenate((w[..., None], p, inv.reshape(B, L, G, D * D).astype(np.float32)), -1)
+    xes = rng.uniform(-radius, radius, (B if bx else 1, L if lx else 1, N, D)).astype(np.float32)
+    grad_out = rng.standard_normal((B, L, N)).astype(np.float32)
+    return np.ascontiguousarray(mixture), xes, grad_out
+
+
+def test_shape_sweep_of_the_reference_test():
+    # the sweep of src/gmc/test_cpp_eval.py:30-44 / 68-95 (per-layer and broadcast xes)
+    rng = np.random.default_rng(7)
+    for B in (1, 5):
+        for L in (1, 4, 7):
+            for G in (1, 6, 17, 50):
+                for N in (1, 8, 23, 50):
+                    for D in (2, 3):
+                        for bx, lx in ((True, True), (False, False)):
+                            m, x, g = _random_case(rng, B, L, G, N, D, bx, lx)
+                            _check(m, x, g, what=f"B{B} L{L} G{G} N{N} D{D} bx{bx}")
+
+
+@pytest.mark.parametrize("D", [2, 3])
+@pytest.mark.parametrize("G,N", [(64, 700), (130, 513), (300, 1500), (700, 600), (1100, 530)])
+def test_every_kernel_variant(D, G, N):
+    # covers 1/2/4 Gaussians per thread, several Gaussian chunks, several point tiles, ragged edges,
+    # and the unaligned (non-bulk) staging path (G not a multiple of 4)
+    rng = np.random.default_rng(G * 7 + N + D)
+    for bx, lx in ((True, True), (True, False), (False, False)):
+        m, x, g = _random_case(rng, 2, 3, G, N, D, bx, lx, radius=1.0)
+        _check(m, x, g, what=f"G{G} N{N} D{D} bx{bx} lx{lx}")
+
+
+def test_large_n_uses_the_four_points_per_thread_forward():
+    rng = np.random.default_rng(5)
+    for D in (2, 3):
+        m, x, g = _random_case(rng, 4, 8, 33, 9601, D, True, True, radius=1.0)
+        _check(m, x, g, what=f"large N D{D}")
+
+
+def test_config0():
+    from gmc import synthetic
+    m, x, g = synthetic.config0()
+    _check(m.numpy(), x.numpy(), g.numpy(), what="config0")
+
+
+def test_only_requested_gradients():
+    import gmc.cpp.extensions.evaluate_inversed.evaluate_inversed as ev
+    rng = np.random.default_rng(3)
+    m, x, g = _random_case(rng, 2, 2, 40, 100, 3, True, True, radius=1.0)
+    mt, xt, gt = (torch.from_numpy(a).cuda() for a in (m, x, g))
+    gm_full, gx_full = ev.parallel_backward(gt, mt, xt, None, True, True)
+    gm_only, gx_zero = ev.parallel_backward(gt, mt, xt, None, True, False)
+    gm_zero, gx_only = ev.parallel_backward(gt, mt, xt, None, False, True)
+    assert gx_zero.abs().max().item() == 0 and gm_zero.abs().max().item() == 0
+    assert rel_inf(gm_only.cpu().numpy(), gm_full.cpu().numpy()) < 1e-5
+    assert rel_inf(gx_only.cpu().numpy(), gx_full.cpu().numpy()) < 1e-5
+
+
+def test_forward_is_deterministic_and_does_not_touch_inputs():
+    import gmc.cpp.extensions.evaluate_inversed.evaluate_inversed as ev
+    rng = np.random.default_rng(11)
+    m, x, _ = _random_case(rng, 2, 3, 257, 1000, 3, True, True, radius=1.0)
+    mt, xt = torch.from_numpy(m).cuda(), torch.from_numpy(x).cuda()
+    a = ev.apply(mt, xt)
+    b = ev.apply(mt, xt)
+    assert torch.equal(a, b)
+    assert torch.equal(mt.cpu(), torch.from_numpy(m)) and torch.equal(xt.cpu(), torch.from_numpy(x))
+
+
+def test_config1_full_size_identities():
+    """Full benchmark size (2^32 pairs). The output is linear in the weights, so
+    sum_n grad_out[n] out[n] == sum_g w_g dL/dw_g for every (batch, layer); a CPU oracle slice pins values."""
+    import gmc.cpp.extensions.evaluate_inversed.evaluate_inversed as ev
+    from gmc import synthetic
+    m, x, g = synthetic.config1()
+    mt = m.cuda().requires_grad_(True)
+    xt = x.cuda().requires_grad_(True)
+    gt = g.cuda()
+    out = ev.apply(mt, xt)
+    out.backward(gt)
+    lhs = (out.detach().double() * gt.double()).sum(-1)
+    rhs = (mt.grad[..., 0].double() * mt.detach()[..., 0].double()).sum(-1)
+    assert rel_inf(rhs.cpu().numpy(), lhs.cpu().numpy()) < TOL
+    # translation identity: sum_n dL/dx_n == - sum_g dL/dmu_g
+    sx = xt.grad.double().sum(2)
+    sm = mt.grad[..., 1:4].double().sum(2)
+    assert rel_inf((-sm).cpu().numpy(), sx.cpu().numpy()) < 1e-3
+    # one (batch, layer) slice against the fp64 oracle, 2048 points
+    b, l = 3, 5
+    ms = m[b:b + 1, l:l + 1].numpy().astype(np.float64)
+    xs = x[b:b + 1, l:l + 1, :2048].numpy().astype(np.float64)
+    ref = cpu_oracle.eval_forward(ms, xs)
+    assert rel_inf(out[b, l, :2048].detach().cpu().numpy(), ref[0, 0]) < TOL
+    assert torch.isfinite(mt.grad).all() and torch.isfinite(xt.grad).all()
