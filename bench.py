@@ -40,6 +40,9 @@ def _args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-batch", type=int, default=4, help="batch slice timed on the host cores")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batch", type=int, default=B_PER_GPU,
+                    help="batch per GPU (default: the configuration's 32; smaller values are for profiler captures)")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiler captures)")
     return ap.parse_args()
 
 
@@ -162,6 +165,7 @@ def run_ours(args, rank, world, local_rank):
     dev = torch.device("cuda", local_rank)
 
     # every rank owns its own batch shard (different seed per rank)
+    B_PER_GPU = args.batch
     m_h, x_h, g_h = synthetic.config1(n_batch=B_PER_GPU, seed=1001 + rank)
     m_h, x_h, g_h = m_h.pin_memory(), x_h.pin_memory(), g_h.pin_memory()
     m, x, g = m_h.to(dev), x_h.to(dev), g_h.to(dev)
@@ -218,18 +222,20 @@ def run_ours(args, rank, world, local_rank):
         gm_h.copy_(md.grad, non_blocking=True)
         gx_h.copy_(xd.grad, non_blocking=True)
 
-    for _ in range(3):
-        e2e_step()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    e1.record()
-    torch.cuda.synchronize()
-    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    e2e_ms = float("nan")
+    if not args.no_e2e:
+        for _ in range(3):
+            e2e_step()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(e2e_steps):
+            e2e_step()
+        e1.record()
+        torch.cuda.synchronize()
+        e2e_ms = e0.elapsed_time(e1) / e2e_steps
 
     t = torch.tensor([total_ms, fwd_ms, bwd_ms, e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:
@@ -255,20 +261,24 @@ def run_ours(args, rank, world, local_rank):
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": f"config1: 3D evaluate_inversed fwd+bwd, B={B_PER_GPU}/GPU L={L} G={G} N={N} "
                                f"({pairs_rank} pairs per GPU and step)",
-                   "l2": "inputs (148 MB per step) are larger than L2 (126 MB); no explicit flush",
+                   "l2": f"inputs ({(m_h.numel() + x_h.numel() + g_h.numel()) * 4 / 1e6:.0f} MB per step) "
+                         "are larger than L2 (126 MB) at the default batch; no explicit flush",
                    "sharding": f"batch over {world} rank(s), all-gather of forward outputs overlapped with backward"},
-        "roofline": {"bound": "fp32", "kernel": "eval_backward_kernel<3,4>", "achieved": ach_bwd,
+        "roofline": {"bound": "fp32", "kernel": "eval_backward_kernel<3,2>", "achieved": ach_bwd,
                      "peak": fp32_peak_tflops, "unit": "TFLOP/s", "frac": ach_bwd / fp32_peak_tflops,
-                     "traffic": None,
+                     # dram__bytes_read+write of one launch: 32.79 MB captured by ncu at B=4 (profiles/), scaled by B/4
+                     # because every byte of traffic belongs to one (batch, layer) mixture
+                     "traffic": 32.79e6 * B_PER_GPU / 4, "traffic_unit": "bytes (ncu capture at B=4, scaled by B/4)",
                      "peak_source": f"nominal {n_sm} SMs x 128 lanes x 2 flop x {sm_max_mhz:.0f} MHz "
                                     f"(sm_max_mhz from {peaks_kind} MEASURED_PEAKS.json; it has no FP32 entry)",
                      "algorithmic_flop_per_pair": FLOP_BWD, "ms_per_launch": bwd_ms},
-        "roofline_forward": {"bound": "fp32", "kernel": "eval_forward_kernel<3,4>", "achieved": ach_fwd,
+        "roofline_forward": {"bound": "fp32", "kernel": "eval_forward_kernel<3,8>", "achieved": ach_fwd,
                              "peak": fp32_peak_tflops, "unit": "TFLOP/s", "frac": ach_fwd / fp32_peak_tflops,
                              "algorithmic_flop_per_pair": FLOP_FWD, "ms_per_launch": fwd_ms},
         "roofline_fwd_bwd": {"bound": "fp32", "achieved": ach_all, "peak": fp32_peak_tflops, "unit": "TFLOP/s",
                              "frac": ach_all / fp32_peak_tflops, "algorithmic_flop_per_pair": FLOP_FWD + FLOP_BWD},
-        "e2e": {"value": world * pairs_rank / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
+        "e2e": None if args.no_e2e else
+               {"value": world * pairs_rank / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps},
         "gpu_launches": 2 * args.steps,
         "clocks": clocks,

@@ -22,8 +22,22 @@
 namespace gmc {
 namespace {
 
+// Tuning constants (overridable at compile time for experiments).
+#ifndef GMC_FWD_CHUNK
+#define GMC_FWD_CHUNK 256
+#endif
+#ifndef GMC_FWD_P
+#define GMC_FWD_P 8
+#endif
+#ifndef GMC_BWD_PPI
+#define GMC_BWD_PPI 2
+#endif
+#ifndef GMC_BWD_MINB
+#define GMC_BWD_MINB 4
+#endif
 constexpr int kFwdThreads = 128;
-constexpr int kFwdChunk = 256;   // Gaussians staged per shared-memory chunk
+constexpr int kFwdChunk = GMC_FWD_CHUNK;   // Gaussians staged per shared-memory chunk
+constexpr int kFwdPoints = GMC_FWD_P;      // query points per thread in the large-problem variant
 
 template <int D>
 struct Raw {
@@ -31,10 +45,16 @@ struct Raw {
 };
 
 // ---------------------------------------------------------------------------------------------
-// "ready" records: 2D = float4 (mx, my, c, a00) + float2 (a01, a11);
-//                  3D = float4 (mx, my, mz, c) + float4 (a00, a01, a02, a11) + float2 (a12, a22),
-// with a_ij = k (S_ij + S_ji) for i != j, a_ii = k S_ii, k = -1/2 log2(e).
+// Packed fp32x2 arithmetic. sm_100 executes one packed instruction on two fp32 lanes of a 64-bit register
+// pair, so a pair loop written on float2 needs half the issue slots of the scalar form; the two halves
+// always belong to two different Gaussians evaluated at the same query point.
 // ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 ex2_2(float2 q) { return make_float2(ex2_approx(q.x), ex2_approx(q.y)); }
+
 constexpr float kExpScale = -0.5f * kLog2e;
 
 __device__ __forceinline__ float det2(const float* S) { return S[0] * S[3] - S[1] * S[2]; }
@@ -43,30 +63,42 @@ __device__ __forceinline__ float det3(const float* S) {
            S[2] * (S[3] * S[7] - S[4] * S[6]);
 }
 
-__device__ __forceinline__ void make_ready(const float* r, float4& a, float2& b) {
-    const float* S = r + 3;
-    const float c = r[0] * kInv2Pi * sqrtf(det2(S));
-    a = make_float4(r[1], r[2], c, kExpScale * S[0]);
-    b = make_float2(kExpScale * (S[1] + S[2]), kExpScale * S[3]);
-}
-__device__ __forceinline__ void make_ready(const float* r, float4& a, float4& b, float2& c2) {
-    const float* S = r + 4;
-    const float c = r[0] * kInv2Pi15 * sqrtf(det3(S));
-    a = make_float4(r[1], r[2], r[3], c);
-    b = make_float4(kExpScale * S[0], kExpScale * (S[1] + S[3]), kExpScale * (S[2] + S[6]), kExpScale * S[4]);
-    c2 = make_float2(kExpScale * (S[5] + S[7]), kExpScale * S[8]);
+// "ready" form of one Gaussian for the forward pair loop:
+//   nm = -mu, c = w (2 pi)^(-D/2) sqrt(det S), a_ii = k S_ii, a_ij = k (S_ij + S_ji) (i < j), k = -1/2 log2(e)
+// 2D: nm0 nm1 c a00 a01 a11 (6 values); 3D: nm0 nm1 nm2 c a00 a01 a02 a11 a12 a22 (10 values).
+template <int D>
+struct ReadyCount {
+    static constexpr int value = D == 2 ? 6 : 10;
+};
+
+template <int D>
+__device__ __forceinline__ void make_ready(const float* r, float* out) {
+    if constexpr (D == 2) {
+        const float* S = r + 3;
+        out[0] = -r[1]; out[1] = -r[2];
+        out[2] = r[0] * kInv2Pi * sqrtf(det2(S));
+        out[3] = kExpScale * S[0]; out[4] = kExpScale * (S[1] + S[2]); out[5] = kExpScale * S[3];
+    } else {
+        const float* S = r + 4;
+        out[0] = -r[1]; out[1] = -r[2]; out[2] = -r[3];
+        out[3] = r[0] * kInv2Pi15 * sqrtf(det3(S));
+        out[4] = kExpScale * S[0]; out[5] = kExpScale * (S[1] + S[3]); out[6] = kExpScale * (S[2] + S[6]);
+        out[7] = kExpScale * S[4]; out[8] = kExpScale * (S[5] + S[7]); out[9] = kExpScale * S[8];
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
 // forward
 // ---------------------------------------------------------------------------------------------
+// Shared layout of the ready records: Gaussians 2j and 2j+1 are interleaved value by value,
+//   pair j = [v0(2j) v0(2j+1) v1(2j) v1(2j+1) ...], 2 * ReadyCount floats = 3 (2D) or 5 (3D) float4,
+// so one broadcast float4 load delivers two packed operands.
 template <int D, int P>
 struct FwdSmem {
     static constexpr int kTile = kFwdThreads * P;
+    static constexpr int kPairFloats = 2 * ReadyCount<D>::value;
     alignas(16) float raw[kFwdChunk * Raw<D>::kFloats];
-    alignas(16) float4 ra[kFwdChunk];
-    alignas(16) float4 rb[D == 3 ? kFwdChunk : 1];
-    alignas(16) float2 rc[kFwdChunk];
+    alignas(16) float ready[(kFwdChunk / 2) * kPairFloats];
     alignas(16) float xs[kTile * D];
     alignas(8) uint64_t bar;
 };
@@ -77,6 +109,8 @@ eval_forward_kernel(const float* __restrict__ mixture, const float* __restrict__
                     int n_layers, int n_components, int n_batch_xes, int n_layers_xes, int n_xes,
                     int tiles_per_mixture) {
     constexpr int RF = Raw<D>::kFloats;
+    constexpr int RC = ReadyCount<D>::value;
+    constexpr int PF = 2 * RC;
     constexpr int TILE = kFwdThreads * P;
     extern __shared__ __align__(16) unsigned char smem_bytes[];
     FwdSmem<D, P>& sm = *reinterpret_cast<FwdSmem<D, P>*>(smem_bytes);
@@ -112,20 +146,23 @@ eval_forward_kernel(const float* __restrict__ mixture, const float* __restrict__
     }
     __syncthreads();
 
-    float x[P][D];
-    float acc[P];
+    float2 x[P][D];    // every coordinate duplicated into both halves
+    float2 acc[P];
 #pragma unroll
     for (int p = 0; p < P; ++p) {
 #pragma unroll
-        for (int d = 0; d < D; ++d) x[p][d] = sm.xs[(tid + p * kFwdThreads) * D + d];
-        acc[p] = 0.f;
+        for (int d = 0; d < D; ++d) {
+            const float v = sm.xs[(tid + p * kFwdThreads) * D + d];
+            x[p][d] = f2(v, v);
+        }
+        acc[p] = f2(0.f, 0.f);
     }
 
     const float* mix = mixture + size_t(bl) * n_components * RF;
     unsigned phase = 0;
-    bool ok = true;
     for (int g0 = 0; g0 < n_components; g0 += kFwdChunk) {
         const int gc = min(kFwdChunk, n_components - g0);
+        const int gc_even = (gc + 1) & ~1;
         const float* chunk = mix + size_t(g0) * RF;
         const unsigned bytes = unsigned(gc) * RF * 4u;
         const bool bulk = ((reinterpret_cast<uintptr_t>(chunk) & 15u) == 0) && ((bytes & 15u) == 0);
@@ -136,56 +173,65 @@ eval_forward_kernel(const float* __restrict__ mixture, const float* __restrict__
                 mbar_arrive_expect_tx(&sm.bar, bytes);
                 bulk_copy_g2s(sm.raw, chunk, bytes, &sm.bar);
             }
-            ok = mbar_wait_bounded(&sm.bar, phase);
+            const bool ok = mbar_wait_bounded(&sm.bar, phase);
             phase ^= 1u;
-            // a CTA-wide decision keeps the barriers below convergent
-            if (__syncthreads_or(!ok)) return;
-            for (int g = tid; g < gc; g += kFwdThreads) {
-                if constexpr (D == 2) make_ready(sm.raw + g * RF, sm.ra[g], sm.rc[g]);
-                else make_ready(sm.raw + g * RF, sm.ra[g], sm.rb[g], sm.rc[g]);
-            }
-        } else {
-            for (int g = tid; g < gc; g += kFwdThreads) {
+            if (__syncthreads_or(!ok)) return;   // CTA-wide decision, nothing else is in flight
+        }
+        for (int g = tid; g < gc_even; g += kFwdThreads) {
+            float rdy[RC];
+            if (g < gc) {
                 float r[RF];
+                if (bulk) {
 #pragma unroll
-                for (int i = 0; i < RF; ++i) r[i] = __ldg(chunk + g * RF + i);
-                if constexpr (D == 2) make_ready(r, sm.ra[g], sm.rc[g]);
-                else make_ready(r, sm.ra[g], sm.rb[g], sm.rc[g]);
+                    for (int i = 0; i < RF; ++i) r[i] = sm.raw[g * RF + i];
+                } else {
+#pragma unroll
+                    for (int i = 0; i < RF; ++i) r[i] = __ldg(chunk + g * RF + i);
+                }
+                make_ready<D>(r, rdy);
+            } else {
+#pragma unroll
+                for (int i = 0; i < RC; ++i) rdy[i] = 0.f;   // padding Gaussian: c = 0
             }
+            float* dst = sm.ready + (g >> 1) * PF + (g & 1);
+#pragma unroll
+            for (int i = 0; i < RC; ++i) dst[2 * i] = rdy[i];
         }
         __syncthreads();
 
+        const float4* rp = reinterpret_cast<const float4*>(sm.ready);
+        const int n_pairs = gc_even >> 1;
         if constexpr (D == 3) {
 #pragma unroll 2
-            for (int g = 0; g < gc; ++g) {
-                const float4 ga = sm.ra[g];
-                const float4 gb = sm.rb[g];
-                const float2 gcv = sm.rc[g];
+            for (int j = 0; j < n_pairs; ++j) {
+                const float4 v0 = rp[j * 5 + 0], v1 = rp[j * 5 + 1], v2 = rp[j * 5 + 2], v3 = rp[j * 5 + 3],
+                             v4 = rp[j * 5 + 4];
+                const float2 nm0 = f2(v0.x, v0.y), nm1 = f2(v0.z, v0.w), nm2 = f2(v1.x, v1.y), c = f2(v1.z, v1.w);
+                const float2 a00 = f2(v2.x, v2.y), a01 = f2(v2.z, v2.w), a02 = f2(v3.x, v3.y), a11 = f2(v3.z, v3.w);
+                const float2 a12 = f2(v4.x, v4.y), a22 = f2(v4.z, v4.w);
 #pragma unroll
                 for (int p = 0; p < P; ++p) {
-                    const float t0 = x[p][0] - ga.x;
-                    const float t1 = x[p][1] - ga.y;
-                    const float t2 = x[p][2] - ga.z;
-                    const float r0 = fmaf(gb.z, t2, fmaf(gb.y, t1, gb.x * t0));
-                    const float r1 = fmaf(gcv.x, t2, gb.w * t1);
-                    const float r2 = gcv.y * t2;
-                    const float q = fmaf(t2, r2, fmaf(t1, r1, t0 * r0));
-                    acc[p] = fmaf(ga.w, ex2_approx(q), acc[p]);
+                    const float2 t0 = add2(x[p][0], nm0), t1 = add2(x[p][1], nm1), t2 = add2(x[p][2], nm2);
+                    const float2 r0 = fma2(a02, t2, fma2(a01, t1, mul2(a00, t0)));
+                    const float2 r1 = fma2(a12, t2, mul2(a11, t1));
+                    const float2 r2 = mul2(a22, t2);
+                    const float2 q = fma2(t2, r2, fma2(t1, r1, mul2(t0, r0)));
+                    acc[p] = fma2(c, ex2_2(q), acc[p]);
                 }
             }
         } else {
 #pragma unroll 2
-            for (int g = 0; g < gc; ++g) {
-                const float4 ga = sm.ra[g];
-                const float2 gb = sm.rc[g];
+            for (int j = 0; j < n_pairs; ++j) {
+                const float4 v0 = rp[j * 3 + 0], v1 = rp[j * 3 + 1], v2 = rp[j * 3 + 2];
+                const float2 nm0 = f2(v0.x, v0.y), nm1 = f2(v0.z, v0.w), c = f2(v1.x, v1.y), a00 = f2(v1.z, v1.w);
+                const float2 a01 = f2(v2.x, v2.y), a11 = f2(v2.z, v2.w);
 #pragma unroll
                 for (int p = 0; p < P; ++p) {
-                    const float t0 = x[p][0] - ga.x;
-                    const float t1 = x[p][1] - ga.y;
-                    const float r0 = fmaf(gb.x, t1, ga.w * t0);
-                    const float r1 = gb.y * t1;
-                    const float q = fmaf(t1, r1, t0 * r0);
-                    acc[p] = fmaf(ga.z, ex2_approx(q), acc[p]);
+                    const float2 t0 = add2(x[p][0], nm0), t1 = add2(x[p][1], nm1);
+                    const float2 r0 = fma2(a01, t1, mul2(a00, t0));
+                    const float2 r1 = mul2(a11, t1);
+                    const float2 q = fma2(t1, r1, mul2(t0, r0));
+                    acc[p] = fma2(c, ex2_2(q), acc[p]);
                 }
             }
         }
@@ -195,7 +241,7 @@ eval_forward_kernel(const float* __restrict__ mixture, const float* __restrict__
 #pragma unroll
     for (int p = 0; p < P; ++p) {
         const int i = tid + p * kFwdThreads;
-        if (i < n_here) o[i] = acc[p];
+        if (i < n_here) o[i] = acc[p].x + acc[p].y;
     }
 }
 
@@ -208,12 +254,13 @@ constexpr int kBwdTilePoints = 512;    // points per CTA
 
 template <int D>
 struct BwdSmem {
-    alignas(16) float4 pts[kBwdTilePoints];                                // x, y, (z), grad_out
+    alignas(16) float4 pts[kBwdTilePoints * 2];                            // (x,x,y,y) (z,z,g,g) per point
     alignas(16) float partial[kBwdPointChunk * D * (kBwdThreads + 4)];      // [point][dim][thread] (+pad)
 };
 
-template <int D, int GQ>
-__global__ void __launch_bounds__(kBwdThreads)
+// GP = packed Gaussian pairs per thread (a thread owns 2 * GP Gaussians: g = base + tg + (2 q + h) * TG).
+template <int D, int GP>
+__global__ void __launch_bounds__(kBwdThreads, GMC_BWD_MINB)
 eval_backward_kernel(const float* __restrict__ grad_out, const float* __restrict__ mixture,
                      const float* __restrict__ xes, float* __restrict__ grad_mixture,
                      float* __restrict__ grad_xes, int n_layers, int n_components, int n_batch_xes,
@@ -244,110 +291,134 @@ eval_backward_kernel(const float* __restrict__ grad_out, const float* __restrict
     const int n_here = min(kBwdTilePoints, n_xes - n0);
     const size_t xes_row = (size_t(bx) * n_layers_xes + lx) * size_t(n_xes);
 
-    // ---- stage points: (x, grad_out) ----
+    // ---- stage points: (x, grad_out), every value duplicated for the packed pair loop ----
     for (int i = tid; i < kBwdTilePoints; i += kBwdThreads) {
-        float4 p = make_float4(0.f, 0.f, 0.f, 0.f);
+        float px = 0.f, py = 0.f, pz = 0.f, go = 0.f;
         if (i < n_here) {
             const float* xp = xes + (xes_row + n0 + i) * D;
-            const float go = __ldg(grad_out + size_t(bl) * n_xes + n0 + i);
-            if constexpr (D == 3) p = make_float4(__ldg(xp), __ldg(xp + 1), __ldg(xp + 2), go);
-            else p = make_float4(__ldg(xp), __ldg(xp + 1), 0.f, go);
+            go = __ldg(grad_out + size_t(bl) * n_xes + n0 + i);
+            px = __ldg(xp);
+            py = __ldg(xp + 1);
+            if constexpr (D == 3) pz = __ldg(xp + 2);
         }
-        sm.pts[i] = p;
+        sm.pts[2 * i] = make_float4(px, px, py, py);
+        sm.pts[2 * i + 1] = make_float4(pz, pz, go, go);
     }
 
     // ---- my Gaussians, in ready form for the backward pair loop ----
-    float mu[GQ][D], A[GQ][NS], cw2[GQ];
-    float sa[GQ], U[GQ][D], M[GQ][NS];
+    float2 nmu[GP][D], A[GP][NS], cw2[GP];
+    float2 sa[GP], U[GP][D], M[GP][NS];
     const float* mix = mixture + size_t(bl) * n_components * RF;
-    const int gbase = gchunk * TG * GQ;
+    const int gbase = gchunk * TG * GP * 2;
 #pragma unroll
-    for (int q = 0; q < GQ; ++q) {
-        const int g = gbase + tg + q * TG;
-        sa[q] = 0.f;
+    for (int q = 0; q < GP; ++q) {
+        float v[2][D + NS + 1];
 #pragma unroll
-        for (int d = 0; d < D; ++d) { U[q][d] = 0.f; mu[q][d] = 0.f; }
+        for (int h = 0; h < 2; ++h) {
 #pragma unroll
-        for (int s = 0; s < NS; ++s) { M[q][s] = 0.f; A[q][s] = 0.f; }
-        cw2[q] = 0.f;
-        if (g < n_components) {
-            const float* r = mix + size_t(g) * RF;
-            const float w = __ldg(r);
+            for (int i = 0; i < D + NS + 1; ++i) v[h][i] = 0.f;
+            const int g = gbase + tg + (2 * q + h) * TG;
+            if (g < n_components) {
+                const float* r = mix + size_t(g) * RF;
+                const float w = __ldg(r);
 #pragma unroll
-            for (int d = 0; d < D; ++d) mu[q][d] = __ldg(r + 1 + d);
-            float S[D * D];
+                for (int d = 0; d < D; ++d) v[h][d] = -__ldg(r + 1 + d);
+                float S[D * D];
 #pragma unroll
-            for (int i = 0; i < D * D; ++i) S[i] = __ldg(r + 1 + D + i);
-            float det;
-            if constexpr (D == 2) {
-                det = det2(S);
-                A[q][0] = kExpScale * S[0];
-                A[q][1] = kExpScale * 0.5f * (S[1] + S[2]);
-                A[q][2] = kExpScale * S[3];
-            } else {
-                det = det3(S);
-                A[q][0] = kExpScale * S[0];
-                A[q][1] = kExpScale * 0.5f * (S[1] + S[3]);
-                A[q][2] = kExpScale * 0.5f * (S[2] + S[6]);
-                A[q][3] = kExpScale * S[4];
-                A[q][4] = kExpScale * 0.5f * (S[5] + S[7]);
-                A[q][5] = kExpScale * S[8];
+                for (int i = 0; i < D * D; ++i) S[i] = __ldg(r + 1 + D + i);
+                float det;
+                if constexpr (D == 2) {
+                    det = det2(S);
+                    v[h][D + 0] = kExpScale * S[0];
+                    v[h][D + 1] = kExpScale * 0.5f * (S[1] + S[2]);
+                    v[h][D + 2] = kExpScale * S[3];
+                } else {
+                    det = det3(S);
+                    v[h][D + 0] = kExpScale * S[0];
+                    v[h][D + 1] = kExpScale * 0.5f * (S[1] + S[3]);
+                    v[h][D + 2] = kExpScale * 0.5f * (S[2] + S[6]);
+                    v[h][D + 3] = kExpScale * S[4];
+                    v[h][D + 4] = kExpScale * 0.5f * (S[5] + S[7]);
+                    v[h][D + 5] = kExpScale * S[8];
+                }
+                // c2 = w * norm * (2 ln 2): folds the 1/k of "S t = (A t) / k" and the sign of d/dx
+                v[h][D + NS] = w * gauss_norm_factor<D>() * sqrtf(det) * (2.f * kLn2);
             }
-            // c2 = w * norm * (2 ln 2): folds the 1/k of "S t = (A t) / k" and the sign of d/dx
-            cw2[q] = w * gauss_norm_factor<D>() * sqrtf(det) * (2.f * kLn2);
         }
+#pragma unroll
+        for (int d = 0; d < D; ++d) { nmu[q][d] = f2(v[0][d], v[1][d]); U[q][d] = f2(0.f, 0.f); }
+#pragma unroll
+        for (int s = 0; s < NS; ++s) { A[q][s] = f2(v[0][D + s], v[1][D + s]); M[q][s] = f2(0.f, 0.f); }
+        cw2[q] = f2(v[0][D + NS], v[1][D + NS]);
+        sa[q] = f2(0.f, 0.f);
     }
     __syncthreads();
 
     const bool need_gx = grad_xes != nullptr;
+    constexpr int PPI = GMC_BWD_PPI;   // points in flight per loop iteration (independent dependency chains)
     for (int c0 = 0; c0 < n_here; c0 += kBwdPointChunk) {
-        for (int pp = slice; pp < kBwdPointChunk; pp += TP) {
-            const float4 pt = sm.pts[c0 + pp];
-            float dx[D];
+        for (int pp0 = slice * PPI; pp0 < kBwdPointChunk; pp0 += TP * PPI) {
+            float2 X[PPI][3], GO[PPI], dx[PPI][D];
 #pragma unroll
-            for (int d = 0; d < D; ++d) dx[d] = 0.f;
+            for (int k = 0; k < PPI; ++k) {
+                const float4 pa = sm.pts[2 * (c0 + pp0 + k)];
+                const float4 pb = sm.pts[2 * (c0 + pp0 + k) + 1];
+                X[k][0] = f2(pa.x, pa.y); X[k][1] = f2(pa.z, pa.w); X[k][2] = f2(pb.x, pb.y);
+                GO[k] = f2(pb.z, pb.w);
 #pragma unroll
-            for (int q = 0; q < GQ; ++q) {
-                if constexpr (D == 3) {
-                    const float t0 = pt.x - mu[q][0], t1 = pt.y - mu[q][1], t2 = pt.z - mu[q][2];
-                    const float r0 = fmaf(A[q][2], t2, fmaf(A[q][1], t1, A[q][0] * t0));
-                    const float r1 = fmaf(A[q][4], t2, fmaf(A[q][3], t1, A[q][1] * t0));
-                    const float r2 = fmaf(A[q][5], t2, fmaf(A[q][4], t1, A[q][2] * t0));
-                    const float qq = fmaf(t2, r2, fmaf(t1, r1, t0 * r0));
-                    const float a = ex2_approx(qq) * pt.w;
-                    sa[q] += a;
-                    const float c2 = a * cw2[q];
-                    dx[0] = fmaf(c2, r0, dx[0]);
-                    dx[1] = fmaf(c2, r1, dx[1]);
-                    dx[2] = fmaf(c2, r2, dx[2]);
-                    const float u0 = c2 * t0, u1 = c2 * t1, u2 = c2 * t2;
-                    U[q][0] += u0; U[q][1] += u1; U[q][2] += u2;
-                    M[q][0] = fmaf(u0, t0, M[q][0]);
-                    M[q][1] = fmaf(u0, t1, M[q][1]);
-                    M[q][2] = fmaf(u0, t2, M[q][2]);
-                    M[q][3] = fmaf(u1, t1, M[q][3]);
-                    M[q][4] = fmaf(u1, t2, M[q][4]);
-                    M[q][5] = fmaf(u2, t2, M[q][5]);
-                } else {
-                    const float t0 = pt.x - mu[q][0], t1 = pt.y - mu[q][1];
-                    const float r0 = fmaf(A[q][1], t1, A[q][0] * t0);
-                    const float r1 = fmaf(A[q][2], t1, A[q][1] * t0);
-                    const float qq = fmaf(t1, r1, t0 * r0);
-                    const float a = ex2_approx(qq) * pt.w;
-                    sa[q] += a;
-                    const float c2 = a * cw2[q];
-                    dx[0] = fmaf(c2, r0, dx[0]);
-                    dx[1] = fmaf(c2, r1, dx[1]);
-                    const float u0 = c2 * t0, u1 = c2 * t1;
-                    U[q][0] += u0; U[q][1] += u1;
-                    M[q][0] = fmaf(u0, t0, M[q][0]);
-                    M[q][1] = fmaf(u0, t1, M[q][1]);
-                    M[q][2] = fmaf(u1, t1, M[q][2]);
+                for (int d = 0; d < D; ++d) dx[k][d] = f2(0.f, 0.f);
+            }
+#pragma unroll
+            for (int q = 0; q < GP; ++q) {
+#pragma unroll
+                for (int k = 0; k < PPI; ++k) {
+                    if constexpr (D == 3) {
+                        const float2 t0 = add2(X[k][0], nmu[q][0]), t1 = add2(X[k][1], nmu[q][1]),
+                                     t2 = add2(X[k][2], nmu[q][2]);
+                        const float2 r0 = fma2(A[q][2], t2, fma2(A[q][1], t1, mul2(A[q][0], t0)));
+                        const float2 r1 = fma2(A[q][4], t2, fma2(A[q][3], t1, mul2(A[q][1], t0)));
+                        const float2 r2 = fma2(A[q][5], t2, fma2(A[q][4], t1, mul2(A[q][2], t0)));
+                        const float2 qq = fma2(t2, r2, fma2(t1, r1, mul2(t0, r0)));
+                        const float2 a = mul2(ex2_2(qq), GO[k]);
+                        sa[q] = add2(sa[q], a);
+                        const float2 c2 = mul2(a, cw2[q]);
+                        dx[k][0] = fma2(c2, r0, dx[k][0]);
+                        dx[k][1] = fma2(c2, r1, dx[k][1]);
+                        dx[k][2] = fma2(c2, r2, dx[k][2]);
+                        const float2 u0 = mul2(c2, t0), u1 = mul2(c2, t1), u2 = mul2(c2, t2);
+                        U[q][0] = add2(U[q][0], u0);
+                        U[q][1] = add2(U[q][1], u1);
+                        U[q][2] = add2(U[q][2], u2);
+                        M[q][0] = fma2(u0, t0, M[q][0]);
+                        M[q][1] = fma2(u0, t1, M[q][1]);
+                        M[q][2] = fma2(u0, t2, M[q][2]);
+                        M[q][3] = fma2(u1, t1, M[q][3]);
+                        M[q][4] = fma2(u1, t2, M[q][4]);
+                        M[q][5] = fma2(u2, t2, M[q][5]);
+                    } else {
+                        const float2 t0 = add2(X[k][0], nmu[q][0]), t1 = add2(X[k][1], nmu[q][1]);
+                        const float2 r0 = fma2(A[q][1], t1, mul2(A[q][0], t0));
+                        const float2 r1 = fma2(A[q][2], t1, mul2(A[q][1], t0));
+                        const float2 qq = fma2(t1, r1, mul2(t0, r0));
+                        const float2 a = mul2(ex2_2(qq), GO[k]);
+                        sa[q] = add2(sa[q], a);
+                        const float2 c2 = mul2(a, cw2[q]);
+                        dx[k][0] = fma2(c2, r0, dx[k][0]);
+                        dx[k][1] = fma2(c2, r1, dx[k][1]);
+                        const float2 u0 = mul2(c2, t0), u1 = mul2(c2, t1);
+                        U[q][0] = add2(U[q][0], u0);
+                        U[q][1] = add2(U[q][1], u1);
+                        M[q][0] = fma2(u0, t0, M[q][0]);
+                        M[q][1] = fma2(u0, t1, M[q][1]);
+                        M[q][2] = fma2(u1, t1, M[q][2]);
+                    }
                 }
             }
             if (need_gx) {
 #pragma unroll
-                for (int d = 0; d < D; ++d) sm.partial[(pp * D + d) * TGP + tg] = dx[d];
+                for (int k = 0; k < PPI; ++k)
+#pragma unroll
+                    for (int d = 0; d < D; ++d) sm.partial[((pp0 + k) * D + d) * TGP + tg] = dx[k][d].x + dx[k][d].y;
             }
         }
         if (need_gx) {
@@ -375,63 +446,69 @@ eval_backward_kernel(const float* __restrict__ grad_out, const float* __restrict
 
     if (grad_mixture == nullptr) return;
 
-    // ---- fold point slices, finish the per-Gaussian gradient, one atomic per value ----
-    // (slices > 1 only when the mixture is small; their partial sums simply issue separate atomics.)
+    // ---- finish the per-Gaussian gradient, one atomic per value (point slices issue separate atomics) ----
 #pragma unroll
-    for (int q = 0; q < GQ; ++q) {
-        const int g = gbase + tg + q * TG;
-        if (g >= n_components) continue;
-        const float* r = mix + size_t(g) * RF;
-        const float w = __ldg(r);
-        float S[D * D];
+    for (int q = 0; q < GP; ++q) {
 #pragma unroll
-        for (int i = 0; i < D * D; ++i) S[i] = __ldg(r + 1 + D + i);
-        float* go = grad_mixture + (size_t(bl) * n_components + g) * RF;
-        constexpr float inv2ln2 = 1.f / (2.f * kLn2);
-        float det, cof[D * D];
-        if constexpr (D == 2) {
-            det = det2(S);
-            cof[0] = S[3]; cof[1] = -S[2]; cof[2] = -S[1]; cof[3] = S[0];
-        } else {
-            det = det3(S);
-            cof[0] = S[4] * S[8] - S[5] * S[7];
-            cof[1] = -(S[3] * S[8] - S[5] * S[6]);
-            cof[2] = S[3] * S[7] - S[4] * S[6];
-            cof[3] = -(S[1] * S[8] - S[2] * S[7]);
-            cof[4] = S[0] * S[8] - S[2] * S[6];
-            cof[5] = -(S[0] * S[7] - S[1] * S[6]);
-            cof[6] = S[1] * S[5] - S[2] * S[4];
-            cof[7] = -(S[0] * S[5] - S[2] * S[3]);
-            cof[8] = S[0] * S[4] - S[1] * S[3];
-        }
-        const float root = sqrtf(det);
-        const float norm = gauss_norm_factor<D>() * root;
-        atomicAdd(go, norm * sa[q]);
-        // d/d mu = S * sum(c t);  U holds sum(c2 t) with c2 = c * 2 ln 2
-        float Uc[D];
+        for (int h = 0; h < 2; ++h) {
+            const int g = gbase + tg + (2 * q + h) * TG;
+            if (g >= n_components) continue;
+            const float sa_h = h ? sa[q].y : sa[q].x;
+            float Uh[D], Mh[NS];
 #pragma unroll
-        for (int d = 0; d < D; ++d) Uc[d] = U[q][d] * inv2ln2;
+            for (int d = 0; d < D; ++d) Uh[d] = h ? U[q][d].y : U[q][d].x;
 #pragma unroll
-        for (int i = 0; i < D; ++i) {
-            float s = 0.f;
+            for (int s = 0; s < NS; ++s) Mh[s] = h ? M[q][s].y : M[q][s].x;
+            const float* r = mix + size_t(g) * RF;
+            const float w = __ldg(r);
+            float S[D * D];
 #pragma unroll
-            for (int j = 0; j < D; ++j) s = fmaf(0.5f * (S[i * D + j] + S[j * D + i]), Uc[j], s);
-            atomicAdd(go + 1 + i, s);
-        }
-        // d/d S = -1/2 sum(c t t^T) + (w sum(a) factor / (2 sqrt(det))) cof(S)
-        const float gdet = w * sa[q] * gauss_norm_factor<D>() / (2.f * root);
-        int s_idx = 0;
-        float Mfull[D * D];
-#pragma unroll
-        for (int i = 0; i < D; ++i)
-#pragma unroll
-            for (int j = i; j < D; ++j) {
-                Mfull[i * D + j] = M[q][s_idx];
-                Mfull[j * D + i] = M[q][s_idx];
-                ++s_idx;
+            for (int i = 0; i < D * D; ++i) S[i] = __ldg(r + 1 + D + i);
+            float* go = grad_mixture + (size_t(bl) * n_components + g) * RF;
+            constexpr float inv2ln2 = 1.f / (2.f * kLn2);
+            float det, cof[D * D];
+            if constexpr (D == 2) {
+                det = det2(S);
+                cof[0] = S[3]; cof[1] = -S[2]; cof[2] = -S[1]; cof[3] = S[0];
+            } else {
+                det = det3(S);
+                cof[0] = S[4] * S[8] - S[5] * S[7];
+                cof[1] = -(S[3] * S[8] - S[5] * S[6]);
+                cof[2] = S[3] * S[7] - S[4] * S[6];
+                cof[3] = -(S[1] * S[8] - S[2] * S[7]);
+                cof[4] = S[0] * S[8] - S[2] * S[6];
+                cof[5] = -(S[0] * S[7] - S[1] * S[6]);
+                cof[6] = S[1] * S[5] - S[2] * S[4];
+                cof[7] = -(S[0] * S[5] - S[2] * S[3]);
+                cof[8] = S[0] * S[4] - S[1] * S[3];
             }
+            const float root = sqrtf(det);
+            const float norm = gauss_norm_factor<D>() * root;
+            atomicAdd(go, norm * sa_h);
+            // d/d mu = S * sum(c t);  U holds sum(c2 t) with c2 = c * 2 ln 2
 #pragma unroll
-        for (int i = 0; i < D * D; ++i) atomicAdd(go + 1 + D + i, fmaf(-0.5f * inv2ln2, Mfull[i], gdet * cof[i]));
+            for (int i = 0; i < D; ++i) {
+                float s = 0.f;
+#pragma unroll
+                for (int j = 0; j < D; ++j) s = fmaf(0.5f * (S[i * D + j] + S[j * D + i]), Uh[j] * inv2ln2, s);
+                atomicAdd(go + 1 + i, s);
+            }
+            // d/d S = -1/2 sum(c t t^T) + (w sum(a) factor / (2 sqrt(det))) cof(S)
+            const float gdet = w * sa_h * gauss_norm_factor<D>() / (2.f * root);
+            int s_idx = 0;
+            float Mfull[D * D];
+#pragma unroll
+            for (int i = 0; i < D; ++i)
+#pragma unroll
+                for (int j = i; j < D; ++j) {
+                    Mfull[i * D + j] = Mh[s_idx];
+                    Mfull[j * D + i] = Mh[s_idx];
+                    ++s_idx;
+                }
+#pragma unroll
+            for (int i = 0; i < D * D; ++i)
+                atomicAdd(go + 1 + D + i, fmaf(-0.5f * inv2ln2, Mfull[i], gdet * cof[i]));
+        }
     }
 }
 
@@ -466,15 +543,15 @@ int launch_forward(const float* mixture, const float* xes, float* out, int n_bat
     return GMC_OK;
 }
 
-template <int D, int GQ>
+template <int D, int GP>
 int launch_backward(const float* grad_out, const float* mixture, const float* xes, float* grad_mixture,
                     float* grad_xes, int n_batch, int n_layers, int n_components, int n_batch_xes, int n_layers_xes,
                     int n_xes, int tg, cudaStream_t stream) {
     const long long ptiles = (n_xes + kBwdTilePoints - 1) / kBwdTilePoints;
-    const long long gchunks = (n_components + tg * GQ - 1) / (tg * GQ);
+    const long long gchunks = (n_components + tg * GP * 2 - 1) / (tg * GP * 2);
     const long long blocks = ptiles * gchunks * n_batch * n_layers;
     if (blocks > 0x7fffffffLL) return GMC_ERR_BAD_DIMS;
-    auto kernel = eval_backward_kernel<D, GQ>;
+    auto kernel = eval_backward_kernel<D, GP>;
     const size_t smem = sizeof(BwdSmem<D>);
     if (int s = set_smem(kernel, smem)) return s;
     kernel<<<unsigned(blocks), kBwdThreads, smem, stream>>>(grad_out, mixture, xes, grad_mixture, grad_xes, n_layers,
@@ -498,13 +575,13 @@ extern "C" int gmc_eval_inversed_forward(const float* mixture, const float* xes,
     cudaStream_t st = as_stream(stream);
     // points per thread: keep enough CTAs in flight for small problems
     const long long pairs_rows = (long long)n_batch * n_layers * n_xes;
-    const bool small = pairs_rows < 148LL * 4 * kFwdThreads * 4;
+    const bool small = pairs_rows < 148LL * 4 * kFwdThreads * kFwdPoints;
     if (n_dims == 2) {
         return small ? launch_forward<2, 1>(mixture, xes, out, n_batch, n_layers, n_components, n_batch_xes, n_layers_xes, n_xes, st)
-                     : launch_forward<2, 4>(mixture, xes, out, n_batch, n_layers, n_components, n_batch_xes, n_layers_xes, n_xes, st);
+                     : launch_forward<2, kFwdPoints>(mixture, xes, out, n_batch, n_layers, n_components, n_batch_xes, n_layers_xes, n_xes, st);
     }
     return small ? launch_forward<3, 1>(mixture, xes, out, n_batch, n_layers, n_components, n_batch_xes, n_layers_xes, n_xes, st)
-                 : launch_forward<3, 4>(mixture, xes, out, n_batch, n_layers, n_components, n_batch_xes, n_layers_xes, n_xes, st);
+                 : launch_forward<3, kFwdPoints>(mixture, xes, out, n_batch, n_layers, n_components, n_batch_xes, n_layers_xes, n_xes, st);
 }
 
 extern "C" int gmc_eval_inversed_backward(const float* grad_out, const float* mixture, const float* xes,
@@ -522,16 +599,15 @@ extern "C" int gmc_eval_inversed_backward(const float* grad_out, const float* mi
         GMC_CUDA_TRY(cudaMemsetAsync(grad_xes, 0, sizeof(float) * size_t(n_batch_xes) * n_layers_xes * n_xes * n_dims, st));
     if (!grad_mixture && !grad_xes) return GMC_OK;
 
-    // Gaussians per thread and threads along the Gaussian axis
-    int gq, tg;
-    if (n_components >= 512) { gq = 4; tg = 128; }
-    else if (n_components >= 256) { gq = 2; tg = 128; }
-    else if (n_components > 64) { gq = 1; tg = 128; }
-    else if (n_components > 32) { gq = 1; tg = 64; }
-    else { gq = 1; tg = 32; }
-#define GMC_BWD(D_, GQ_) launch_backward<D_, GQ_>(grad_out, mixture, xes, grad_mixture, grad_xes, n_batch, n_layers, \
+    // packed Gaussian pairs per thread (2 or 4 Gaussians) and threads along the Gaussian axis
+    int gp, tg;
+    if (n_components >= 384) { gp = 2; tg = 128; }
+    else if (n_components > 128) { gp = 1; tg = 128; }
+    else if (n_components > 64) { gp = 1; tg = 64; }
+    else { gp = 1; tg = 32; }
+#define GMC_BWD(D_, GP_) launch_backward<D_, GP_>(grad_out, mixture, xes, grad_mixture, grad_xes, n_batch, n_layers, \
                                                   n_components, n_batch_xes, n_layers_xes, n_xes, tg, st)
-    if (n_dims == 2) return gq == 4 ? GMC_BWD(2, 4) : (gq == 2 ? GMC_BWD(2, 2) : GMC_BWD(2, 1));
-    return gq == 4 ? GMC_BWD(3, 4) : (gq == 2 ? GMC_BWD(3, 2) : GMC_BWD(3, 1));
+    if (n_dims == 2) return gp == 2 ? GMC_BWD(2, 2) : GMC_BWD(2, 1);
+    return gp == 2 ? GMC_BWD(3, 2) : GMC_BWD(3, 1);
 #undef GMC_BWD
 }

@@ -8,7 +8,9 @@ import os
 
 import torch
 
-_LIB_PATH = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_lib", "libgmc_b200.so")
+# GMC_B200_LIB selects another build of the same library (for example one compiled with different tuning macros).
+_LIB_PATH = os.environ.get("GMC_B200_LIB") or os.path.join(os.path.dirname(os.path.abspath(__file__)), "_lib",
+                                                            "libgmc_b200.so")
 
 if not os.path.exists(_LIB_PATH):
     raise ImportError(
