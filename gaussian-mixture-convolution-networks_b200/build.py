@@ -21,7 +21,7 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-I", I
 # Fast-math is applied per file: kernels whose integer results must be bit-exact (Morton codes) are
 # compiled with IEEE arithmetic and without FMA contraction.
 FAST_MATH = ["--use_fast_math"]
-IEEE_FILES = {"lbvh.cu", "convolution_fitting.cu"}
+IEEE_FILES = {"lbvh.cu", "mhem_fit.cu", "convolution_fitting.cu"}
 
 
 def _sources():

@@ -1,0 +1,115 @@
+// Device-side building blocks of the linear BVH (Karras 2012) shared by the BVH-MHEM fit and the convolution fit:
+// Morton quantisation, a CTA-wide bitonic sort of 64-bit keys in shared memory, and the range / split search.
+// Semantics follow the reference's lbvh/morton_code.h:77-85, 145-156 and lbvh/building.h:11-103 (and the
+// convolution_fitting/building.h variant that replaces the low 32 key bits by the sorted position).
+// Everything that feeds integer results is written with explicit IEEE intrinsics so that fast-math or FMA
+// contraction of the surrounding file cannot change a Morton code.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace gmc {
+namespace lbvh {
+
+__device__ __forceinline__ uint32_t expand_bits3(uint32_t v) {
+    v = (v * 0x00010001u) & 0xFF0000FFu;
+    v = (v * 0x00000101u) & 0x0F00F00Fu;
+    v = (v * 0x00000011u) & 0xC30C30C3u;
+    v = (v * 0x00000005u) & 0x49249249u;
+    return v;
+}
+
+// 10-bit cell of `pos` inside [lower, upper]; an empty extent (0/0 in the reference) gives cell 0.
+__device__ __forceinline__ uint32_t quantise(float pos, float lower, float upper) {
+    const float extent = __fsub_rn(upper, lower);
+    if (!(extent > 0.0f)) return 0u;
+    const float p = __fdiv_rn(__fsub_rn(pos, lower), extent);
+    const float scaled = __fmul_rn(p, 1024.0f);
+    const uint32_t q = scaled > 0.0f ? __float2uint_rz(scaled) : 0u;
+    return min(q, 1023u);
+}
+
+__device__ __forceinline__ uint32_t morton30(uint32_t qx, uint32_t qy, uint32_t qz) {
+    return (expand_bits3(qx) << 2) + (expand_bits3(qy) << 1) + expand_bits3(qz);
+}
+
+// Sorts keys[0 .. n_pow2) ascending; n_pow2 is a power of two, entries beyond the real count hold ~0ull.
+// All threads of the CTA must call it.
+__device__ __forceinline__ void bitonic_sort_shared(uint64_t* keys, int n_pow2) {
+    for (int k = 2; k <= n_pow2; k <<= 1) {
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int t = threadIdx.x; t < (n_pow2 >> 1); t += blockDim.x) {
+                // t-th pair of this stage: insert a zero bit at position log2(j)
+                const int i = ((t & ~(j - 1)) << 1) | (t & (j - 1));
+                const int p = i | j;
+                const uint64_t a = keys[i], b = keys[p];
+                const bool ascending = (i & k) == 0;
+                if ((a > b) == ascending) {
+                    keys[i] = b;
+                    keys[p] = a;
+                }
+            }
+            __syncthreads();
+        }
+    }
+}
+
+__device__ __forceinline__ int common_upper_bits(uint64_t a, uint64_t b) { return __clzll(int64_t(a ^ b)); }
+
+// Code functor: plain key (BVH fit) or (key & high 32 bits) + sorted position (convolution fit).
+struct PlainCode {
+    const uint64_t* keys;
+    __device__ __forceinline__ uint64_t operator()(int idx) const { return keys[idx]; }
+};
+struct PositionTieBreakCode {
+    const uint64_t* keys;
+    __device__ __forceinline__ uint64_t operator()(int idx) const {
+        return (keys[idx] & 0xFFFFFFFF00000000ull) + uint64_t(uint32_t(idx));
+    }
+};
+
+template <typename Code>
+__device__ __forceinline__ int2 determine_range(const Code& code, int num_leaves, int idx) {
+    if (idx == 0) return make_int2(0, num_leaves - 1);
+    const uint64_t self = code(idx);
+    const int l_delta = common_upper_bits(self, code(idx - 1));
+    const int r_delta = common_upper_bits(self, code(idx + 1));
+    const int d = (r_delta > l_delta) ? 1 : -1;
+    const int delta_min = min(l_delta, r_delta);
+    auto delta_at = [&](long long i) -> int {
+        return (i >= 0 && i < num_leaves) ? common_upper_bits(self, code(int(i))) : -1;
+    };
+    int l_max = 2;
+    while (delta_at((long long)idx + (long long)d * l_max) > delta_min) l_max <<= 1;
+    int l = 0;
+    for (int t = l_max >> 1; t > 0; t >>= 1) {
+        if (delta_at((long long)idx + (long long)(l + t) * d) > delta_min) l += t;
+    }
+    const int jdx = idx + l * d;
+    return d < 0 ? make_int2(jdx, idx) : make_int2(idx, jdx);
+}
+
+template <typename Code>
+__device__ __forceinline__ int find_split(const Code& code, int first, int last) {
+    const uint64_t first_code = code(first), last_code = code(last);
+    if (first_code == last_code) return (first + last) >> 1;
+    const int delta_node = common_upper_bits(first_code, last_code);
+    int split = first;
+    int stride = last - first;
+    do {
+        stride = (stride + 1) >> 1;
+        const int middle = split + stride;
+        if (middle < last && common_upper_bits(first_code, code(middle)) > delta_node) split = middle;
+    } while (stride > 1);
+    return split;
+}
+
+__host__ __device__ __forceinline__ int next_pow2(int v) {
+    int p = 1;
+    while (p < v) p <<= 1;
+    return p;
+}
+
+}  // namespace lbvh
+}  // namespace gmc

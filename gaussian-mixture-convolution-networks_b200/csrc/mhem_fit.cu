@@ -1,0 +1,501 @@
+// BVH-MHEM reduction of a mixture of G Gaussians to K Gaussians (forward).
+//
+// Algorithm (same decisions as the reference's bvh_mhem_fit/implementation_forward.h:35-484): over the LBVH of the
+// component means, every internal node gathers the Gaussians of its two children (left first, |w| < 1e-7 dropped) and,
+// if there are more than R, replaces them by R Gaussians with one hierarchical-EM step (initial representatives by
+// single-linkage clustering of the centres, KL-gated responsibilities, moment matching); afterwards nodes are selected
+// greedily from the root by |integral| until about K Gaussians are collected.
+//
+// Organisation on the GPU: one CTA per mixture. Tree levels (height above the leaves) are computed in shared memory
+// with the "second arriver continues" pass; levels are then processed in order, one warp per node, with the 2R x R
+// likelihood / KL / responsibility matrices spread one entry per lane. The heap-driven clustering of fit_initial is
+// sequential by nature and runs on lane 0. Node results live in a global attribute array that is also what the
+// backward pass reads: per internal node R Gaussians, the integral, the Gaussian count, the R initial indices.
+#include "common.cuh"
+#include "lbvh_device.cuh"
+
+namespace gmc {
+
+int lbvh_build_launch(const float* mixture, long long n_mixtures, int n_components, int n_dims, uint64_t* sorted_keys,
+                      uint16_t* nodes, cudaStream_t stream);
+
+namespace {
+
+constexpr int kThreads = 128;
+constexpr int kWarps = kThreads / 32;
+constexpr int kMaxLevels = 72;
+constexpr float kEpsSmall = 0.0000000000001f;
+constexpr float kEpsLarge = 0.0000001f;
+constexpr float kKlThreshold = 0.5f;
+
+__device__ __forceinline__ float clip(float v) { return fmaxf(v, kEpsSmall); }
+__device__ __forceinline__ int sign_of(float v) { return v >= 0.f ? 1 : -1; }
+
+template <int D> __device__ __forceinline__ float det(const float* m);
+template <> __device__ __forceinline__ float det<2>(const float* m) { return m[0] * m[3] - m[1] * m[2]; }
+template <> __device__ __forceinline__ float det<3>(const float* m) {
+    return m[0] * (m[4] * m[8] - m[5] * m[7]) - m[1] * (m[3] * m[8] - m[5] * m[6]) + m[2] * (m[3] * m[7] - m[4] * m[6]);
+}
+template <int D> __device__ __forceinline__ void inverse(const float* m, float* o);
+template <> __device__ __forceinline__ void inverse<2>(const float* m, float* o) {
+    const float r = 1.f / det<2>(m);
+    o[0] = m[3] * r; o[1] = -m[1] * r; o[2] = -m[2] * r; o[3] = m[0] * r;
+}
+template <> __device__ __forceinline__ void inverse<3>(const float* m, float* o) {
+    const float r = 1.f / det<3>(m);
+    o[0] = (m[4] * m[8] - m[5] * m[7]) * r; o[1] = -(m[1] * m[8] - m[2] * m[7]) * r; o[2] = (m[1] * m[5] - m[2] * m[4]) * r;
+    o[3] = -(m[3] * m[8] - m[5] * m[6]) * r; o[4] = (m[0] * m[8] - m[2] * m[6]) * r; o[5] = -(m[0] * m[5] - m[2] * m[3]) * r;
+    o[6] = (m[3] * m[7] - m[4] * m[6]) * r; o[7] = -(m[0] * m[7] - m[1] * m[6]) * r; o[8] = (m[0] * m[4] - m[1] * m[3]) * r;
+}
+
+// Attribute record of an internal node: [R * RF floats | integral | count | initial indices (4 x uint8) | reserved]
+template <int D, int R>
+struct Attr {
+    static constexpr int RF = 1 + D + D * D;
+    static constexpr int kFloats = R * RF + 4;
+};
+
+// Per-warp scratch in shared memory.
+template <int D, int R>
+struct WarpScratch {
+    static constexpr int RF = 1 + D + D * D;
+    static constexpr int NT = 2 * R;
+    static constexpr int NH = (NT * NT - NT) / 2;
+    float tgt[NT][RF];
+    float heap_d[NH];
+    unsigned char heap_a[NH], heap_b[NH];
+    int idx[R];
+    float r3[NT][R];
+    float fw[R];
+    float outp[R][D];
+    float outc[R][D * D];
+};
+
+// ---- the sequential part of fit_initial, run by one lane ----
+template <int D, int R>
+__device__ void cluster_and_select(WarpScratch<D, R>& ws, int n_valid) {
+    constexpr int NT = 2 * R;
+    constexpr int NH = (NT * NT - NT) / 2;
+    // heap primitives (min-heap on the disparity, ties resolved as in the reference's ArrayHeap)
+    auto two_children = [](unsigned i) { return i < unsigned((NH - 1) / 2); };
+    auto is_leaf = [](unsigned i) { return i >= unsigned(NH / 2); };
+    auto replace_element = [&](float vd, unsigned char va, unsigned char vb, unsigned index, float& rd, unsigned char& ra,
+                               unsigned char& rb) {
+        rd = ws.heap_d[index]; ra = ws.heap_a[index]; rb = ws.heap_b[index];
+        unsigned cur = index;
+        while (two_children(cur)) {
+            const unsigned l = cur * 2 + 1, r = cur * 2 + 2;
+            const float ld = ws.heap_d[l], rdv = ws.heap_d[r];
+            if (vd <= ld && vd <= rdv) break;
+            if (ld <= rdv) { ws.heap_d[cur] = ld; ws.heap_a[cur] = ws.heap_a[l]; ws.heap_b[cur] = ws.heap_b[l]; cur = l; }
+            else { ws.heap_d[cur] = rdv; ws.heap_a[cur] = ws.heap_a[r]; ws.heap_b[cur] = ws.heap_b[r]; cur = r; }
+        }
+        if (!is_leaf(cur)) {
+            const unsigned l = cur * 2 + 1;
+            const float ld = ws.heap_d[l];
+            if (ld <= vd) { ws.heap_d[cur] = ld; ws.heap_a[cur] = ws.heap_a[l]; ws.heap_b[cur] = ws.heap_b[l]; cur = l; }
+        }
+        ws.heap_d[cur] = vd; ws.heap_a[cur] = va; ws.heap_b[cur] = vb;
+    };
+    float rd; unsigned char ra, rb;
+    for (unsigned i = (NH - 2) / 2; i < unsigned(NH); --i) {
+        const float vd = ws.heap_d[i];
+        const unsigned char va = ws.heap_a[i], vb = ws.heap_b[i];
+        replace_element(vd, va, vb, i, rd, ra, rb);
+    }
+    // sub-graph label per Gaussian (valid Gaussians are 0 .. n_valid-1); merging relabels the higher into the lower,
+    // member order inside a sub-graph (needed for the first-max rule) is kept in `order`.
+    unsigned char members[NT][NT];
+    int n_members[NT];
+    for (int i = 0; i < NT; ++i) { members[i][0] = (unsigned char)i; n_members[i] = i < n_valid ? 1 : 0; }
+    int n_subgraphs = n_valid;
+    auto subgraph_of = [&](unsigned char id) {
+        for (int i = 0; i < n_valid; ++i)
+            for (int j = 0; j < n_members[i]; ++j)
+                if (members[i][j] == id) return i;
+        return -1;
+    };
+    while (n_subgraphs > R) {
+        replace_element(INFINITY, 255, 255, 0, rd, ra, rb);
+        if (!(rd < INFINITY)) break;
+        const int sa = subgraph_of(ra), sb = subgraph_of(rb);
+        if (sa != sb && sa >= 0 && sb >= 0) {
+            const int lo = min(sa, sb), hi = max(sa, sb);
+            for (int j = 0; j < n_members[hi]; ++j) members[lo][n_members[lo]++] = members[hi][j];
+            n_members[hi] = 0;
+            --n_subgraphs;
+        }
+    }
+    int sg = -1;
+    for (int i = 0; i < R; ++i) {
+        do { ++sg; } while (sg < n_valid && n_members[sg] == 0);
+        int selected = 255;
+        float max_abs = 0.f;
+        if (sg < n_valid) {
+            for (int j = 0; j < n_members[sg]; ++j) {
+                const int gid = members[sg][j];
+                const float aw = fabsf(ws.tgt[gid][0]);
+                if (aw > max_abs) { max_abs = aw; selected = gid; }
+            }
+        }
+        ws.idx[i] = selected;
+    }
+}
+
+// ---- one hierarchical-EM step on the padded targets in ws.tgt; result goes to `out` (R * RF floats) ----
+template <int D, int R>
+__device__ void fit_em_warp(WarpScratch<D, R>& ws, int n_target, float* __restrict__ out, int* initial_packed) {
+    constexpr int RF = 1 + D + D * D;
+    constexpr int NT = 2 * R;
+    constexpr int NH = (NT * NT - NT) / 2;
+    constexpr int NE = NT * R;   // matrix entries: 32 (R = 4) or 8 (R = 2)
+    const int lane = threadIdx.x & 31;
+
+    float target_integral = 0.f;
+#pragma unroll
+    for (int i = 0; i < NT; ++i) target_integral += ws.tgt[i][0];
+    const float target_clipped = clip(target_integral);
+
+    // pairwise centre distances in the reference's heap fill order: all pairs i < j of the n_target valid
+    // Gaussians (they are compacted in front), row major; the rest of the heap array is +inf padding
+    {
+        int i = 0, rem = lane < NH ? lane : 0;
+        while (rem >= NT - 1 - i) { rem -= NT - 1 - i; ++i; }
+        const int j = i + 1 + rem;
+        const bool real_pair = lane < NH && j < n_target;
+        float d = INFINITY;
+        if (real_pair) {
+            const float wa = ws.tgt[i][0], wb = ws.tgt[j][0];
+            d = 0.f;
+#pragma unroll
+            for (int k = 0; k < D; ++k) { const float tt = ws.tgt[i][1 + k] - ws.tgt[j][1 + k]; d += tt * tt; }
+            if (sign_of(wa) != sign_of(wb) || fabsf(wa) < kEpsLarge || fabsf(wb) < kEpsLarge) d = INFINITY;
+        }
+        if (lane < NH) { ws.heap_d[lane] = INFINITY; ws.heap_a[lane] = 255; ws.heap_b[lane] = 255; }
+        __syncwarp();
+        if (real_pair) {
+            const int pos = i * n_target - (i * (i + 1)) / 2 + (j - i - 1);
+            ws.heap_d[pos] = d; ws.heap_a[pos] = (unsigned char)i; ws.heap_b[pos] = (unsigned char)j;
+        }
+        __syncwarp();
+    }
+    if (lane == 0) cluster_and_select<D, R>(ws, n_target);
+    __syncwarp();
+
+    float initial_integral = 0.f;
+#pragma unroll
+    for (int s = 0; s < R; ++s) initial_integral += ws.tgt[ws.idx[s] < NT ? ws.idx[s] : 0][0];
+    const float initial_clipped = clip(initial_integral);
+
+    // ---- lane (t, s): likelihood, KL, gate ----
+    const int e = lane < NE ? lane : NE - 1;
+    const int t = e / R, s = e - t * R;
+    const int fi = ws.idx[s] < NT ? ws.idx[s] : 0;
+    const float tw = ws.tgt[t][0] / target_clipped;        // target weight scaled to integral 1
+    const float iw = ws.tgt[fi][0] / initial_clipped;      // initial weight scaled to integral 1
+    float lik, kl;
+    {
+        float inv[D * D], diff[D];
+        inverse<D>(&ws.tgt[fi][1 + D], inv);
+#pragma unroll
+        for (int k = 0; k < D; ++k) diff[k] = ws.tgt[t][1 + k] - ws.tgt[fi][1 + k];
+        float maha = 0.f;
+#pragma unroll
+        for (int i = 0; i < D; ++i) {
+            float acc = 0.f;
+#pragma unroll
+            for (int j = 0; j < D; ++j) acc += inv[i * D + j] * diff[j];
+            maha += diff[i] * acc;
+        }
+        float tr = 0.f;
+#pragma unroll
+        for (int i = 0; i < D; ++i)
+#pragma unroll
+            for (int j = 0; j < D; ++j) tr += inv[i * D + j] * ws.tgt[t][1 + D + j * D + i];
+        const float a = sqrtf(det<D>(inv)) * gauss_norm_factor<D>() * expf(-0.5f * maha);
+        const float b = expf(-0.5f * tr);
+        lik = powf(clip(a * b), 4.f * tw);
+        const float lg = logf(det<D>(&ws.tgt[t][1 + D]) / det<D>(&ws.tgt[fi][1 + D]));
+        kl = sign_of(iw) == sign_of(tw) ? 0.5f * (maha + tr - float(D) - lg) : 0.f;
+    }
+    float gate = kl < kKlThreshold ? 1.f : 0.f;
+    // per target: the component with the smallest KL is always gated in (first strict minimum)
+    const int row_base = t * R;
+    {
+        int best = -1;
+        float smallest = INFINITY;
+#pragma unroll
+        for (int s2 = 0; s2 < R; ++s2) {
+            const float v = __shfl_sync(0xffffffffu, kl, row_base + s2);
+            if (v < smallest) { smallest = v; best = s2; }
+        }
+        if (best == s) gate = 1.f;
+    }
+    const float wl = clip(iw * lik) * gate;
+    float row_sum = 0.f;
+#pragma unroll
+    for (int s2 = 0; s2 < R; ++s2) row_sum += __shfl_sync(0xffffffffu, wl, row_base + s2);
+    const float r2 = (wl / row_sum) * tw;
+    float fw = 0.f;
+#pragma unroll
+    for (int t2 = 0; t2 < NT; ++t2) fw += __shfl_sync(0xffffffffu, r2, t2 * R + s);
+    if (lane < NE) {
+        ws.r3[t][s] = r2 / clip(fw);
+        if (t == 0) ws.fw[s] = fw;
+    }
+    __syncwarp();
+
+    // ---- moment matching ----
+    for (int o = lane; o < R * D; o += 32) {
+        const int so = o / D, d = o - so * D;
+        float acc = 0.f;
+#pragma unroll
+        for (int t2 = 0; t2 < NT; ++t2) acc += ws.r3[t2][so] * ws.tgt[t2][1 + d];
+        ws.outp[so][d] = acc;
+    }
+    __syncwarp();
+    for (int o = lane; o < R * D * D; o += 32) {
+        const int so = o / (D * D), ij = o - so * D * D, i = ij / D, j = ij - i * D;
+        float acc = 0.f;
+#pragma unroll
+        for (int t2 = 0; t2 < NT; ++t2) {
+            const float di = ws.tgt[t2][1 + i] - ws.outp[so][i], dj = ws.tgt[t2][1 + j] - ws.outp[so][j];
+            acc += ws.r3[t2][so] * (di * dj + ws.tgt[t2][1 + D + ij]);
+        }
+        if (ws.fw[so] < kEpsLarge) acc = (i == j) ? 1.f : 0.f;
+        ws.outc[so][ij] = acc;
+    }
+    __syncwarp();
+    for (int o = lane; o < R * RF; o += 32) {
+        const int so = o / RF, f = o - so * RF;
+        float v;
+        if (f == 0) v = ws.fw[so] * target_clipped;
+        else if (f <= D) v = ws.outp[so][f - 1];
+        else v = ws.outc[so][f - 1 - D];
+        out[o] = v;
+    }
+    if (lane == 0) {
+        int packed = 0;
+#pragma unroll
+        for (int s2 = 0; s2 < R; ++s2) packed |= (ws.idx[s2] & 0xFF) << (8 * s2);
+        *initial_packed = packed;
+    }
+    __syncwarp();
+}
+
+template <int D, int R>
+struct FitSmem {
+    WarpScratch<D, R> warp[kWarps];
+    int level_start_dummy;
+};
+
+// Shared layout: [FitSmem][level bytes: 2G-1 rounded up][selection: K ints + K floats + K ints]
+template <int D, int R>
+__global__ void __launch_bounds__(kThreads)
+mhem_fit_forward_kernel(const float* __restrict__ mixture, const uint16_t* __restrict__ nodes_all, float* __restrict__ attrs_all,
+                        float* __restrict__ out_all, int n_components, int n_fitting) {
+    constexpr int RF = 1 + D + D * D;
+    constexpr int AF = Attr<D, R>::kFloats;
+    extern __shared__ __align__(16) unsigned char smem_bytes[];
+    FitSmem<D, R>& sm = *reinterpret_cast<FitSmem<D, R>*>(smem_bytes);
+    const int G = n_components, K = n_fitting;
+    const int n_internal = G - 1, n_nodes = 2 * G - 1;
+    unsigned char* level = smem_bytes + sizeof(FitSmem<D, R>);
+    int* arrive = reinterpret_cast<int*>(level + ((n_nodes + 15) & ~15));
+    const int sel_cap = K > 1024 ? K : 1024;   // capacity of the selection list (the reference holds 1024 entries)
+    int* sel_node = arrive + n_internal;
+    float* sel_rating = reinterpret_cast<float*>(sel_node + sel_cap);
+    int* sel_offset = reinterpret_cast<int*>(sel_rating + sel_cap);
+    __shared__ int s_max_level, s_n_selected_nodes, s_written;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* mix = mixture + size_t(blockIdx.x) * G * RF;
+    const uint16_t* nodes = nodes_all + size_t(blockIdx.x) * n_nodes * 4;
+    float* attrs = attrs_all + size_t(blockIdx.x) * n_internal * AF;
+    float* out = out_all + size_t(blockIdx.x) * K * RF;
+
+    // ---- levels: leaves are 0, an internal node is 1 + max(children); second arriver computes ----
+    for (int i = tid; i < n_internal; i += kThreads) arrive[i] = 0;
+    for (int i = tid; i < n_nodes; i += kThreads) level[i] = 0;
+    if (tid == 0) s_max_level = 0;
+    __syncthreads();
+    for (int leaf = tid; leaf < G; leaf += kThreads) {
+        int id = n_internal + leaf;
+        int parent = nodes[size_t(id) * 4];
+        for (int guard = 0; guard < kMaxLevels && parent != 0xFFFF; ++guard) {
+            __threadfence_block();
+            if (atomicAdd(&arrive[parent], 1) == 0) break;
+            __threadfence_block();
+            const int l = nodes[size_t(parent) * 4 + 1], r = nodes[size_t(parent) * 4 + 2];
+            const int lv = 1 + max(int(((volatile unsigned char*)level)[l]), int(((volatile unsigned char*)level)[r]));
+            ((volatile unsigned char*)level)[parent] = (unsigned char)lv;
+            atomicMax(&s_max_level, lv);
+            parent = nodes[size_t(parent) * 4];
+        }
+    }
+    __syncthreads();
+    const int max_level = s_max_level;
+
+    auto child_count = [&](int id) -> int { return id >= n_internal ? 1 : __float_as_int(attrs[size_t(id) * AF + R * RF + 1]); };
+    auto child_integral = [&](int id) -> float {
+        return id >= n_internal ? mix[size_t(nodes[size_t(id) * 4 + 3]) * RF] : attrs[size_t(id) * AF + R * RF];
+    };
+
+    // ---- bottom-up, level by level, one warp per node ----
+    WarpScratch<D, R>& ws = sm.warp[warp];
+    for (int lv = 1; lv <= max_level; ++lv) {
+        for (int base = warp * 32; base < n_internal; base += kWarps * 32) {
+            const int cand = base + lane;
+            const unsigned todo = __ballot_sync(0xffffffffu, cand < n_internal && level[cand] == lv);
+            for (unsigned bits = todo; bits; bits &= bits - 1) {
+                const int id = base + __ffs(bits) - 1;
+                const int l = nodes[size_t(id) * 4 + 1], r = nodes[size_t(id) * 4 + 2];
+                // gather: lane j < R reads the left child's j-th Gaussian, lane R + j the right child's
+                const int cl = child_count(l), cr = child_count(r);
+                const int which = lane < R ? l : r;
+                const int j = lane < R ? lane : lane - R;
+                const bool in_range = lane < 2 * R && j < (lane < R ? cl : cr);
+                const float* src = nullptr;
+                if (in_range) src = which >= n_internal ? mix + size_t(nodes[size_t(which) * 4 + 3]) * RF
+                                                        : attrs + size_t(which) * AF + size_t(j) * RF;
+                const bool valid = in_range && fabsf(src[0]) >= kEpsLarge;
+                const unsigned vmask = __ballot_sync(0xffffffffu, valid);
+                const int n_target = __popc(vmask);
+                if (valid) {
+                    const int pos = __popc(vmask & ((1u << lane) - 1u));
+#pragma unroll
+                    for (int f = 0; f < RF; ++f) ws.tgt[pos][f] = src[f];
+                }
+                if (lane >= n_target && lane < 2 * R) {
+                    ws.tgt[lane][0] = 0.f;
+#pragma unroll
+                    for (int f = 0; f < D; ++f) ws.tgt[lane][1 + f] = 0.f;
+#pragma unroll
+                    for (int f = 0; f < D * D; ++f) ws.tgt[lane][1 + D + f] = (f / D == f % D) ? 1.f : 0.f;
+                }
+                __syncwarp();
+                float* rec = attrs + size_t(id) * AF;
+                if (lane == 0) {
+                    rec[R * RF] = child_integral(l) + child_integral(r);
+                    rec[R * RF + 1] = __int_as_float(n_target > R ? R : n_target);
+                    rec[R * RF + 3] = 0.f;
+                }
+                if (n_target > R) {
+                    fit_em_warp<D, R>(ws, n_target, rec, reinterpret_cast<int*>(rec + R * RF + 2));
+                } else {
+                    for (int o = lane; o < R * RF; o += 32) {
+                        const int so = o / RF, f = o - so * RF;
+                        rec[o] = so < n_target ? ws.tgt[so][f] : 0.f;
+                    }
+                    if (lane == 0) rec[R * RF + 2] = __int_as_float(-1);
+                    __syncwarp();
+                }
+            }
+        }
+        __threadfence_block();
+        __syncthreads();
+    }
+
+    // ---- greedy selection from the root (warp 0) ----
+    if (warp == 0) {
+        auto rating_of = [&](int id) -> float { return child_count(id) < R ? -2.f : fabsf(child_integral(id)); };
+        if (lane == 0) { sel_node[0] = 0; sel_rating[0] = rating_of(0); }
+        __syncwarp();
+        int n_list = 1;
+        int n_selected = child_count(0);
+        while (n_selected < K - R && n_list < sel_cap) {
+            float best_rating = -1.f;
+            int best = 0x7fffffff;
+            for (int i = lane; i < n_list; i += 32)
+                if (sel_rating[i] > best_rating) { best_rating = sel_rating[i]; best = i; }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float orat = __shfl_xor_sync(0xffffffffu, best_rating, o);
+                const int oidx = __shfl_xor_sync(0xffffffffu, best, o);
+                if (orat > best_rating || (orat == best_rating && oidx < best)) { best_rating = orat; best = oidx; }
+            }
+            if (best == 0x7fffffff) break;   // no full node left
+            const int id = sel_node[best];
+            const int l = nodes[size_t(id) * 4 + 1], r = nodes[size_t(id) * 4 + 2];
+            __syncwarp();
+            if (lane == 0) {
+                sel_node[best] = l; sel_rating[best] = rating_of(l);
+                sel_node[n_list] = r; sel_rating[n_list] = rating_of(r);
+            }
+            n_selected = n_selected - R + child_count(l) + child_count(r);
+            ++n_list;
+            __syncwarp();
+        }
+        if (lane == 0) {
+            int w = 0;
+            for (int i = 0; i < n_list; ++i) { sel_offset[i] = w; w += child_count(sel_node[i]); }
+            s_n_selected_nodes = n_list;
+            s_written = w;
+        }
+    }
+    __syncthreads();
+    const int n_list = s_n_selected_nodes;
+    const int written = min(s_written, K);
+    for (int i = warp; i < n_list; i += kWarps) {
+        const int id = sel_node[i];
+        const int cnt = child_count(id);
+        const float* src = id >= n_internal ? mix + size_t(nodes[size_t(id) * 4 + 3]) * RF : attrs + size_t(id) * AF;
+        for (int o = lane; o < cnt * RF; o += 32) {
+            const int slot = sel_offset[i] + o / RF;
+            if (slot < K) out[size_t(sel_offset[i]) * RF + o] = src[o];
+        }
+    }
+    for (int o = written * RF + tid; o < K * RF; o += kThreads) {
+        const int f = o % RF;
+        float v = 0.f;
+        if (f > D && ((f - 1 - D) / D == (f - 1 - D) % D)) v = 1.f;
+        out[o] = v;
+    }
+}
+
+template <int D, int R>
+size_t fit_smem_bytes(int G, int K) {
+    const int n_nodes = 2 * G - 1;
+    return sizeof(FitSmem<D, R>) + size_t((n_nodes + 15) & ~15) + sizeof(int) * size_t(G - 1) + size_t(K > 1024 ? K : 1024) * 12;
+}
+
+template <int D, int R>
+int launch_fit(const float* mixture, long long n_mixtures, int G, int K, const uint16_t* nodes, float* attrs, float* out,
+               cudaStream_t stream) {
+    auto kernel = mhem_fit_forward_kernel<D, R>;
+    const size_t smem = fit_smem_bytes<D, R>(G, K);
+    if (smem > 200 * 1024) return GMC_ERR_BAD_DIMS;
+    if (smem > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    kernel<<<unsigned(n_mixtures), kThreads, smem, stream>>>(mixture, nodes, attrs, out, G, K);
+    GMC_LAUNCH_CHECK();
+    return GMC_OK;
+}
+
+}  // namespace
+}  // namespace gmc
+
+GMC_DEFINE_TU_CHECK_READER(mhem_fit)
+
+extern "C" size_t gmc_mhem_fit_attribute_floats(int n_components, int n_dims, int reduction_n) {
+    if (n_components < 2 || (n_dims != 2 && n_dims != 3) || (reduction_n != 2 && reduction_n != 4)) return 0;
+    return size_t(n_components - 1) * size_t(reduction_n * (1 + n_dims + n_dims * n_dims) + 4);
+}
+
+extern "C" int gmc_mhem_fit_forward(const float* mixture, long long n_mixtures, int n_components, int n_dims,
+                                    int n_components_fitting, int reduction_n, float* fitting, int16_t* bvh_nodes,
+                                    float* bvh_attributes, uint64_t* scratch_keys, void* stream) {
+    using namespace gmc;
+    if (n_dims != 2 && n_dims != 3) return GMC_ERR_BAD_DIMS;
+    if (reduction_n != 2 && reduction_n != 4) return GMC_ERR_UNSUPPORTED;
+    if (n_components_fitting <= 0 || n_components_fitting % reduction_n != 0 || n_components_fitting > 4096) return GMC_ERR_BAD_DIMS;
+    if (n_mixtures < 0 || n_components < 2) return GMC_ERR_BAD_DIMS;
+    if (n_mixtures == 0) return GMC_OK;
+    if (!mixture || !fitting || !bvh_nodes || !bvh_attributes || !scratch_keys) return GMC_ERR_NULL_POINTER;
+    cudaStream_t st = as_stream(stream);
+    uint16_t* nodes = reinterpret_cast<uint16_t*>(bvh_nodes);
+    if (int s = lbvh_build_launch(mixture, n_mixtures, n_components, n_dims, scratch_keys, nodes, st)) return s;
+#define GMC_FIT(D_, R_) launch_fit<D_, R_>(mixture, n_mixtures, n_components, n_components_fitting, nodes, bvh_attributes, fitting, st)
+    if (n_dims == 2) return reduction_n == 2 ? GMC_FIT(2, 2) : GMC_FIT(2, 4);
+    return reduction_n == 2 ? GMC_FIT(3, 2) : GMC_FIT(3, 4);
+#undef GMC_FIT
+}

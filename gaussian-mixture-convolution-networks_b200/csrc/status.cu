@@ -11,6 +11,8 @@ void set_last_cuda_error(cudaError_t e) { t_last_error = e; }
 // one reader per translation unit that owns kernels
 int gmc_tu_check_eval_inversed(int* word);
 int gmc_tu_check_small_ops(int* word);
+int gmc_tu_check_lbvh(int* word);
+int gmc_tu_check_mhem_fit(int* word);
 
 extern "C" const char* gmc_status_string(int status) {
     switch (status) {
@@ -39,5 +41,7 @@ extern "C" int gmc_device_check_word(int* word_out) {
     GMC_CUDA_TRY(cudaDeviceSynchronize());
     if (int s = gmc_tu_check_eval_inversed(word_out)) return s;
     if (int s = gmc_tu_check_small_ops(word_out)) return s;
+    if (int s = gmc_tu_check_lbvh(word_out)) return s;
+    if (int s = gmc_tu_check_mhem_fit(word_out)) return s;
     return GMC_OK;
 }

@@ -92,6 +92,40 @@ int gmc_matrix_inverse(const float* matrices, float* inverses, long long n_matri
 int gmc_integrate(const float* mixture, float* integrals, long long n_mixtures, int n_components, int n_dims,
                   void* stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * Linear BVH over the component means of each mixture (the tree of the BVH-MHEM fit).
+ *   key      = (30-bit Morton code of the mean inside the mixture's own min/max box) << 16 | component id
+ *   sorted_keys [n_mixtures, n_components] uint64, ascending per mixture
+ *   nodes    [n_mixtures, 2*n_components-1, 4] uint16 {parent, left, right, object}: internal nodes first
+ *            (root = 0, object = own id), leaves at n_components-1 .. in sorted order (object = component id);
+ *            fields without a value hold 0xFFFF.
+ * 2 <= n_components <= 8192. Integer results are bit-identical to an IEEE fp32 evaluation of the reference
+ * formulas; a box axis with zero extent (always z in 2D) contributes Morton cell 0.
+ *
+ * Replaces lbvh::Bvh<D,float>::construct with make_aabbs=false
+ * (src/gmc/cpp/extensions/lbvh/bvh.cu:23-144, 241-299, 373-458; lbvh/morton_code.h; lbvh/building.h).
+ * ---------------------------------------------------------------------------------------------- */
+int gmc_lbvh_build(const float* mixture, long long n_mixtures, int n_components, int n_dims,
+                   uint64_t* sorted_keys, int16_t* nodes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * BVH-MHEM reduction: fits n_components_fitting (K, a multiple of reduction_n) Gaussians to each covariance-form
+ * mixture of n_components Gaussians (2 <= n_components <= 8192, reduction_n R in {2,4}).
+ *   fitting        [n_mixtures, K, 1+D+D*D]            out; unused slots are (0, 0, identity)
+ *   bvh_nodes      [n_mixtures, 2*n_components-1, 4]   out; as gmc_lbvh_build
+ *   bvh_attributes [n_mixtures, gmc_mhem_fit_attribute_floats(...)] fp32, out; per internal node
+ *                  [R Gaussians | integral | count | R initial indices (uint8) | reserved]; input of the backward
+ *   scratch_keys   [n_mixtures, n_components] uint64   scratch (sorted Morton keys on return)
+ * Weights are expected non-negative (the network applies the fit after the ReLU fixed-point step).
+ *
+ * Replaces bvh_mhem_fit_forward (src/gmc/cpp/extensions/bvh_mhem_fit/bindings.cpp:11-22,
+ * implementation_forward.h:490-560).
+ * ---------------------------------------------------------------------------------------------- */
+size_t gmc_mhem_fit_attribute_floats(int n_components, int n_dims, int reduction_n);
+int gmc_mhem_fit_forward(const float* mixture, long long n_mixtures, int n_components, int n_dims,
+                         int n_components_fitting, int reduction_n, float* fitting, int16_t* bvh_nodes,
+                         float* bvh_attributes, uint64_t* scratch_keys, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -17,7 +17,7 @@ LIB_PATH = os.path.join(OUT_DIR, "liboracle.so")
 # (src/gmc/cpp/extensions/compile_flags.py:15); the Morton stage is compiled without them.
 FAST = ["-O3", "-march=x86-64-v3", "-fopenmp", "-fPIC", "-ffast-math", "-fno-finite-math-only"]
 IEEE = ["-O2", "-march=x86-64-v3", "-fopenmp", "-fPIC", "-ffp-contract=off"]
-IEEE_FILES = {"lbvh.cpp", "convolution_fitting.cpp"}
+IEEE_FILES = {"lbvh.cpp", "mhem_fit.cpp", "convolution_fitting.cpp"}
 
 
 def build(force: bool = False) -> str:

@@ -62,3 +62,74 @@ def eval_backward(grad_out: np.ndarray, mixture: np.ndarray, xes: np.ndarray):
     fn = lib().oracle_eval_backward_f32 if dt == np.float32 else lib().oracle_eval_backward_f64
     fn(_p(grad_out), _p(mixture), _p(xes), _p(gm), _p(gx), *[ctypes.c_int(d) for d in dims])
     return gm, gx
+
+
+def _flat_mixtures(mixture: np.ndarray):
+    mixture = np.ascontiguousarray(mixture, dtype=np.float32)
+    RF = mixture.shape[-1]
+    D = {7: 2, 13: 3}[RF]
+    G = mixture.shape[-2]
+    return mixture.reshape(-1, G, RF), G, D
+
+
+def lbvh_build(mixture: np.ndarray):
+    """Restated LBVH build over the means: mixture [..., G, 7|13] -> (sorted keys uint64 [n, G], nodes uint16 [n, 2G-1, 4])."""
+    flat, G, D = _flat_mixtures(mixture)
+    n = flat.shape[0]
+    keys = np.empty((n, G), dtype=np.uint64)
+    nodes = np.empty((n, 2 * G - 1, 4), dtype=np.uint16)
+    lib().oracle_lbvh_build(_p(flat), ctypes.c_int(n), ctypes.c_int(G), ctypes.c_int(D), _p(keys), _p(nodes))
+    return keys, nodes
+
+
+def mhem_fit_forward(mixture: np.ndarray, K: int, R: int, nodes: np.ndarray = None, dump: bool = False):
+    """Restated BVH-MHEM fit: mixture [..., G, V] (covariance form) -> fitting [n, K, V]
+    (+ per-node Gaussians / counts / integrals / initial indices when dump=True)."""
+    flat, G, D = _flat_mixtures(mixture)
+    n = flat.shape[0]
+    RF = flat.shape[-1]
+    if nodes is None:
+        _, nodes = lbvh_build(flat)
+    nodes = np.ascontiguousarray(nodes.reshape(n, 2 * G - 1, 4), dtype=np.uint16)
+    out = np.empty((n, K, RF), dtype=np.float32)
+    ng = np.empty((n, 2 * G - 1, R, RF), dtype=np.float32) if dump else None
+    nc = np.empty((n, 2 * G - 1), dtype=np.int32) if dump else None
+    ni = np.empty((n, 2 * G - 1), dtype=np.float32) if dump else None
+    nn = np.empty((n, 2 * G - 1, R), dtype=np.uint8) if dump else None
+    rc = lib().oracle_mhem_fit_forward(_p(flat), ctypes.c_int(n), ctypes.c_int(G), ctypes.c_int(D), _p(nodes),
+                                       ctypes.c_int(K), ctypes.c_int(R), _p(out), _p(ng), _p(nc), _p(ni), _p(nn))
+    assert rc == 0
+    if dump:
+        return out, dict(gaussians=ng, counts=nc, integrals=ni, initial=nn, nodes=nodes)
+    return out
+
+
+def density_grid(mixtures: np.ndarray, lo: np.ndarray, hi: np.ndarray, res: int = 64) -> np.ndarray:
+    """fp64 density of covariance-form mixtures [n, G, V] on a res^D grid spanning [lo, hi] per mixture -> [n, res^D]."""
+    mixtures = np.asarray(mixtures, dtype=np.float64)
+    n, G, RF = mixtures.shape
+    D = {7: 2, 13: 3}[RF]
+    cov = mixtures[..., 1 + D:].reshape(n, G, D, D)
+    inv = np.linalg.inv(cov)
+    inv = 0.5 * (inv + np.swapaxes(inv, -1, -2))
+    packed = np.concatenate((mixtures[..., :1 + D], inv.reshape(n, G, D * D)), -1).reshape(n, 1, G, RF)
+    axes = [np.linspace(0.0, 1.0, res) for _ in range(D)]
+    unit = np.stack(np.meshgrid(*axes, indexing="ij"), -1).reshape(-1, D)
+    xes = lo[:, None, :] + unit[None] * (hi - lo)[:, None, :]
+    return eval_forward(np.ascontiguousarray(packed), np.ascontiguousarray(xes.reshape(n, 1, -1, D)))[:, 0]
+
+
+def density_rel_l2(fit_a: np.ndarray, fit_b: np.ndarray, target: np.ndarray, res: int = 64) -> np.ndarray:
+    """Relative L2 distance of the densities of two fitted mixtures per mixture, ||a - b|| / ||b||, on a res^D grid
+    spanning [min mu - 3 sigma_max, max mu + 3 sigma_max] of the target mixture."""
+    target = np.asarray(target, dtype=np.float64)
+    n, G, RF = target.shape
+    D = {7: 2, 13: 3}[RF]
+    mu = target[..., 1:1 + D]
+    cov = target[..., 1 + D:].reshape(n, G, D, D)
+    sigma_max = np.sqrt(np.linalg.eigvalsh(cov).max(axis=(1, 2)))
+    lo = mu.min(1) - 3 * sigma_max[:, None]
+    hi = mu.max(1) + 3 * sigma_max[:, None]
+    da = density_grid(fit_a, lo, hi, res)
+    db = density_grid(fit_b, lo, hi, res)
+    return np.linalg.norm(da - db, axis=1) / np.maximum(np.linalg.norm(db, axis=1), 1e-300)

@@ -1,0 +1,107 @@
+"""GPU parity of the LBVH build (bit-exact keys / permutation / topology) and of the BVH-MHEM fit forward (node
+level and relative L2 density error <= 1e-3 on a 64^D grid) against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import cpu_oracle
+from gmc import synthetic
+
+pytestmark = pytest.mark.gpu
+
+
+def _positive(m):
+    m = m.clone()
+    m[..., 0] = m[..., 0].abs() + 0.01
+    return m
+
+
+def _mixture(D, B, L, G, seed):
+    if D == 2:
+        return _positive(synthetic.fit_target_2d(B, L, G, seed))
+    g = torch.Generator().manual_seed(seed)
+    w = torch.rand(B, L, G, generator=g) * 0.8 + 0.2
+    p = torch.rand(B, L, G, 3, generator=g) * 2 - 1
+    cov, _ = synthetic.covariances_and_inverses((B, L, G), 3, 0.03, 0.15, g)
+    return synthetic.pack(w, p, cov)
+
+
+@pytest.mark.parametrize("D,G", [(2, 2), (2, 3), (2, 37), (2, 1024), (3, 64), (3, 500), (2, 5120)])
+def test_lbvh_bit_exact(D, G):
+    from gmc import lbvh
+    m = _mixture(D, 3, 2, G, 100 + G)
+    keys, nodes = lbvh.build(m.cuda())
+    ref_keys, ref_nodes = cpu_oracle.lbvh_build(m.numpy())
+    assert np.array_equal(keys.cpu().numpy().view(np.uint64).reshape(-1, G), ref_keys)
+    assert np.array_equal(nodes.cpu().numpy().view(np.uint16).reshape(-1, 2 * G - 1, 4), ref_nodes)
+    keys2, nodes2 = lbvh.build(m.cuda())
+    assert torch.equal(keys, keys2) and torch.equal(nodes, nodes2)      # deterministic
+
+
+def test_lbvh_degenerate_axes_and_duplicate_positions():
+    from gmc import lbvh
+    m = _mixture(2, 1, 2, 33, 5)
+    m[0, 0, :, 1] = 0.25          # zero extent in x
+    m[0, 1, 5:9, 1:3] = m[0, 1, 4:5, 1:3]   # duplicate means: equal Morton cells, ids break the tie
+    keys, nodes = lbvh.build(m.cuda())
+    ref_keys, ref_nodes = cpu_oracle.lbvh_build(m.numpy())
+    assert np.array_equal(keys.cpu().numpy().view(np.uint64).reshape(-1, 33), ref_keys)
+    assert np.array_equal(nodes.cpu().numpy().view(np.uint16).reshape(-1, 65, 4), ref_nodes)
+
+
+def _unpack_attrs(attribs, G, R, RF):
+    a = attribs.cpu().numpy().reshape(attribs.shape[0], G - 1, R * RF + 4)
+    gaussians = a[..., :R * RF].reshape(a.shape[0], G - 1, R, RF)
+    integrals = a[..., R * RF]
+    counts = a[..., R * RF + 1].view(np.int32)
+    initial = a[..., R * RF + 2].copy().view(np.uint8).reshape(a.shape[0], G - 1, 4)[..., :R]
+    return gaussians, integrals, counts, initial
+
+
+@pytest.mark.parametrize("D,G,K,R", [(2, 64, 16, 4), (2, 1024, 64, 4), (2, 100, 32, 2), (3, 64, 32, 4), (3, 333, 16, 2),
+                                     (2, 8, 8, 4), (2, 2, 4, 4)])
+def test_fit_forward_matches_oracle(D, G, K, R):
+    import gmc.cpp.extensions.bvh_mhem_fit.binding as fit
+    m = _mixture(D, 4, 3, G, 7 * G + K)
+    RF = m.shape[-1]
+    fitting, nodes, attribs = fit.forward(m.cuda(), K, R)
+    flat = m.numpy().reshape(-1, G, RF)
+    ref, dump = cpu_oracle.mhem_fit_forward(flat, K, R, dump=True)
+    assert np.array_equal(nodes.cpu().numpy().view(np.uint16).reshape(-1, 2 * G - 1, 4), dump["nodes"])
+    gaussians, integrals, counts, initial = _unpack_attrs(attribs, G, R, RF)
+    assert np.array_equal(counts, dump["counts"][:, :G - 1])
+    np.testing.assert_allclose(integrals, dump["integrals"][:, :G - 1], rtol=1e-6, atol=1e-7)
+    fitted = dump["initial"][:, :G - 1, 0] != 255
+    assert np.array_equal(initial[fitted], dump["initial"][:, :G - 1][fitted])
+    np.testing.assert_allclose(gaussians, dump["gaussians"][:, :G - 1], rtol=2e-3, atol=1e-5)
+    out = fitting.cpu().numpy().reshape(-1, K, RF)
+    assert np.isfinite(out).all()
+    err = cpu_oracle.density_rel_l2(out, ref, flat)
+    assert err.max() <= 1e-3, f"relative L2 density error {err.max():.3e}"
+    # slots agree one to one as well (same selection order), and unused slots are (0, 0, I)
+    np.testing.assert_allclose(out, ref, rtol=5e-3, atol=1e-5)
+
+
+def test_fit_large_k_returns_the_input_set():
+    import gmc.cpp.extensions.bvh_mhem_fit.binding as fit
+    G, R = 48, 4
+    m = _mixture(2, 2, 2, G, 77)
+    fitting, _, _ = fit.forward(m.cuda(), G + R, R)
+    out = fitting.cpu().numpy().reshape(-1, G + R, 7)
+    flat = m.numpy().reshape(-1, G, 7)
+    for i in range(flat.shape[0]):
+        a = out[i][out[i][:, 0] != 0]
+        assert a.shape[0] == G
+        assert np.array_equal(a[np.lexsort(a.T[::-1])], flat[i][np.lexsort(flat[i].T[::-1])])
+        np.testing.assert_array_equal(out[i][G:], np.tile(np.array([0, 0, 0, 1, 0, 0, 1], np.float32), (R, 1)))
+
+
+def test_fit_rejects_bad_arguments():
+    import gmc.cpp.extensions.bvh_mhem_fit.binding as fit
+    m = _mixture(2, 1, 1, 16, 1).cuda()
+    with pytest.raises(RuntimeError):
+        fit.forward(m, 10, 4)          # K not a multiple of R
+    with pytest.raises(RuntimeError):
+        fit.forward(m, 8, 3)           # unsupported R
+    with pytest.raises(RuntimeError):
+        fit.forward(m[:, :, :1], 4, 4)  # a single component
