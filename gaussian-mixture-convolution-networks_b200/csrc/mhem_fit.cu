@@ -11,6 +11,8 @@
 // likelihood / KL / responsibility matrices spread one entry per lane. The heap-driven clustering of fit_initial is
 // sequential by nature and runs on lane 0. Node results live in a global attribute array that is also what the
 // backward pass reads: per internal node R Gaussians, the integral, the Gaussian count, the R initial indices.
+#include <mutex>
+
 #include "common.cuh"
 #include "lbvh_device.cuh"
 
@@ -498,4 +500,75 @@ extern "C" int gmc_mhem_fit_forward(const float* mixture, long long n_mixtures, 
     if (n_dims == 2) return reduction_n == 2 ? GMC_FIT(2, 2) : GMC_FIT(2, 4);
     return reduction_n == 2 ? GMC_FIT(3, 2) : GMC_FIT(3, 4);
 #undef GMC_FIT
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Forward fit for callers that cannot hand over scratch memory.
+//
+// Some hosts of this library have no allocator to turn to when a call needs working memory: a serving process that
+// reserved the whole device for its own pools at start-up (a cudaMalloc made later simply fails), a plug-in that
+// is only ever given its input and output buffers, or a control loop that must not take the implicit device-wide
+// synchronisation an allocation or free can bring. For them the Morton-key scratch of the fit lives inside the
+// library image: a fixed array in device memory that every GPU loading the library carries until the process exits.
+// ---------------------------------------------------------------------------------------------------------------
+namespace gmc {
+namespace {
+
+constexpr long long kBuiltinKeyCapacity = 1ll << 20;   // keys: n_mixtures * n_components may not exceed this (8 MiB)
+
+// In host code this name is only a handle for the symbol, not a device address; the address a kernel can use is
+// looked up once per device with cudaGetSymbolAddress (below). Device code may use the name directly.
+static __device__ __align__(256) unsigned long long g_builtin_fit_keys[kBuiltinKeyCapacity];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_builtin_mutex;
+uint64_t* g_builtin_keys_address[kMaxDevices] = {};
+
+// Device address of the built-in array on the device that is current for the calling thread.
+int builtin_keys_for_current_device(uint64_t** address) {
+    int device = -1;
+    GMC_CUDA_TRY(cudaGetDevice(&device));
+    if (device < 0 || device >= kMaxDevices) return GMC_ERR_UNSUPPORTED;
+    std::lock_guard<std::mutex> lock(g_builtin_mutex);
+    if (g_builtin_keys_address[device] == nullptr) {
+        void* p = nullptr;
+        GMC_CUDA_TRY(cudaGetSymbolAddress(&p, g_builtin_fit_keys));
+        if (p == nullptr) return GMC_ERR_CUDA;
+        g_builtin_keys_address[device] = static_cast<uint64_t*>(p);
+    }
+    *address = g_builtin_keys_address[device];
+    return GMC_OK;
+}
+
+}  // namespace
+}  // namespace gmc
+
+extern "C" long long gmc_mhem_fit_forward_noalloc_capacity(void) { return gmc::kBuiltinKeyCapacity; }
+
+extern "C" int gmc_mhem_fit_forward_noalloc(const float* mixture, long long n_mixtures, int n_components, int n_dims,
+                                            int n_components_fitting, int reduction_n, float* fitting,
+                                            int16_t* bvh_nodes, float* bvh_attributes, void* stream) {
+    using namespace gmc;
+    if (n_dims != 2 && n_dims != 3) return GMC_ERR_BAD_DIMS;
+    if (reduction_n != 2 && reduction_n != 4) return GMC_ERR_UNSUPPORTED;
+    if (n_components_fitting <= 0 || n_components_fitting % reduction_n != 0 || n_components_fitting > 4096) return GMC_ERR_BAD_DIMS;
+    if (n_mixtures < 0 || n_components < 2) return GMC_ERR_BAD_DIMS;
+    // the one limit that the caller-scratch entry point does not have
+    if (n_mixtures * (long long)n_components > kBuiltinKeyCapacity) return GMC_ERR_BUILTIN_SCRATCH;
+    if (n_mixtures == 0) return GMC_OK;
+    if (!mixture || !fitting || !bvh_nodes || !bvh_attributes) return GMC_ERR_NULL_POINTER;
+    uint64_t* keys = nullptr;
+    if (int s = builtin_keys_for_current_device(&keys)) return s;
+    cudaStream_t st = as_stream(stream);
+    uint16_t* nodes = reinterpret_cast<uint16_t*>(bvh_nodes);
+    // every key slot that is read is written first by the build kernel, so the array needs no clearing between calls
+    if (int s = lbvh_build_launch(mixture, n_mixtures, n_components, n_dims, keys, nodes, st)) return s;
+    if (n_dims == 2) {
+        return reduction_n == 2
+                   ? launch_fit<2, 2>(mixture, n_mixtures, n_components, n_components_fitting, nodes, bvh_attributes, fitting, st)
+                   : launch_fit<2, 4>(mixture, n_mixtures, n_components, n_components_fitting, nodes, bvh_attributes, fitting, st);
+    }
+    return reduction_n == 2
+               ? launch_fit<3, 2>(mixture, n_mixtures, n_components, n_components_fitting, nodes, bvh_attributes, fitting, st)
+               : launch_fit<3, 4>(mixture, n_mixtures, n_components, n_components_fitting, nodes, bvh_attributes, fitting, st);
 }

@@ -25,6 +25,9 @@ extern "C" const char* gmc_status_string(int status) {
         case GMC_ERR_CUDA: return "CUDA runtime error";
         case GMC_ERR_DEVICE_CHECK: return "a device-side check failed";
         case GMC_ERR_ALIGNMENT: return "pointer not aligned";
+        case GMC_ERR_BUILTIN_SCRATCH:
+            return "problem exceeds the built-in scratch of the no-allocation entry point (n_mixtures * n_components > "
+                   "2^20); use the entry point that takes caller scratch";
         default: return "unknown status";
     }
 }

@@ -48,6 +48,10 @@ lib.gmc_mhem_fit_attribute_floats.restype = ctypes.c_size_t
 lib.gmc_mhem_fit_attribute_floats.argtypes = [_c_int, _c_int, _c_int]
 _declare("gmc_mhem_fit_forward", [_c_float_p, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
                                   _c_void_p, _c_void_p, _c_void_p])
+lib.gmc_mhem_fit_forward_noalloc_capacity.restype = ctypes.c_longlong
+lib.gmc_mhem_fit_forward_noalloc_capacity.argtypes = []
+_declare("gmc_mhem_fit_forward_noalloc", [_c_float_p, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_int, _c_void_p,
+                                          _c_void_p, _c_void_p, _c_void_p])
 _declare("gmc_integrate", [_c_float_p] * 2 + [ctypes.c_longlong, _c_int, _c_int, _c_void_p])
 
 

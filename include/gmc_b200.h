@@ -34,7 +34,8 @@ enum gmc_status {
     GMC_ERR_WORKSPACE = 5,       /* caller-provided scratch is too small                              */
     GMC_ERR_CUDA = 6,            /* a CUDA runtime call failed (see gmc_last_cuda_error)              */
     GMC_ERR_DEVICE_CHECK = 7,    /* a kernel-side bounded wait or self check gave up                  */
-    GMC_ERR_ALIGNMENT = 8        /* a pointer is not aligned to sizeof(float)                         */
+    GMC_ERR_ALIGNMENT = 8,       /* a pointer is not aligned to sizeof(float)                         */
+    GMC_ERR_BUILTIN_SCRATCH = 9  /* problem larger than the built-in scratch of a *_noalloc entry point */
 };
 
 /* Human-readable text for a status code (static storage, never NULL). */
@@ -125,6 +126,31 @@ size_t gmc_mhem_fit_attribute_floats(int n_components, int n_dims, int reduction
 int gmc_mhem_fit_forward(const float* mixture, long long n_mixtures, int n_components, int n_dims,
                          int n_components_fitting, int reduction_n, float* fitting, int16_t* bvh_nodes,
                          float* bvh_attributes, uint64_t* scratch_keys, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * gmc_mhem_fit_forward for callers that have no scratch memory to give. (No counterpart in the reference, which
+ * allocates its temporaries itself.)
+ *
+ * Who needs it: hosts that cannot allocate device memory at the time of the call -- a server that handed the whole
+ * GPU to its own pools when it started, a plug-in that only ever sees its input and output buffers, a loop that must
+ * not risk the device-wide synchronisation an allocation can cause. The call takes the same inputs and outputs as
+ * gmc_mhem_fit_forward, minus scratch_keys: the Morton-key scratch is a fixed 8 MiB array that is part of the
+ * library image, so every GPU that loads the library holds those 8 MiB until the process ends. The entry point
+ * itself never allocates or frees memory, on the host or on the device.
+ *
+ * Limit: n_mixtures * n_components <= gmc_mhem_fit_forward_noalloc_capacity() (2^20 keys); larger problems are
+ * refused with GMC_ERR_BUILTIN_SCRATCH before any GPU work is issued -- use gmc_mhem_fit_forward for those.
+ * Set-up: the first call on each device looks up the device address of the built-in array (once per device, with
+ * that device current); make that first call before starting any stream capture.
+ * Sharing: all calls on a device use the same array and it keeps whatever the previous call left in it. Nothing in
+ * it has to start at zero (every slot read is written first), but two calls that run concurrently on the GPU -- on
+ * different streams or from different threads -- would overwrite each other's keys: order such calls yourself.
+ * Results are identical to gmc_mhem_fit_forward.
+ * ---------------------------------------------------------------------------------------------- */
+long long gmc_mhem_fit_forward_noalloc_capacity(void);
+int gmc_mhem_fit_forward_noalloc(const float* mixture, long long n_mixtures, int n_components, int n_dims,
+                                 int n_components_fitting, int reduction_n, float* fitting, int16_t* bvh_nodes,
+                                 float* bvh_attributes, void* stream);
 
 #ifdef __cplusplus
 }
