@@ -1,0 +1,393 @@
+// Fused convolution + reduction to K Gaussians per (batch, output channel), forward.
+//
+// The T = Cin * G * Gk product Gaussians (w_d w_k, mu_d + mu_k, C_d + C_k) of an output channel are never
+// materialised. One CTA per (batch, output channel) tree keeps everything but the inputs and the saved outputs in
+// shared memory:
+//   keys        (w_d w_k > 0) << 62 | 30-bit Morton code of mu_d + mu_k in the tree's bounding box << 32 | product index
+//   sort        ascending (bitonic, in shared memory)
+//   tree        Karras nodes over (key high word + sorted position); leaves = sorted products
+//   mass        per node, children summed in tree order (levels above the leaves processed in order)
+//   selection   K - 1 greedy splits of the selected internal node with the largest |mass|
+//   aggregation per selected subtree the weighted mean / scatter of the product centres and the weighted mean of
+//               the product covariances; one warp per output Gaussian, lanes hold partial aggregates that are
+//               merged pairwise (the reference walks the leaves sequentially in one thread)
+// Same decisions as the reference's convolution_fitting/Tree.cu:63-408 and implementation_forward.h:19-124.
+#include "common.cuh"
+#include "lbvh_device.cuh"
+
+namespace gmc {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = kThreads / 32;
+constexpr int kMaxProducts = 8192;
+constexpr int kMaxLevels = 72;
+
+struct Dims {
+    int n_batch, n_channels_in, n_components, n_channels_out, n_kernel_components, n_fitting;
+};
+
+template <int D>
+struct Agg {            // weighted mean / scatter of positions, weighted mean of covariances
+    float w;            // sum of weights
+    float m[D];         // mean position
+    float C[D * D];     // sum w (p - m)(p - m)^T
+    float cm[D * D];    // weighted mean covariance
+};
+
+template <int D>
+__device__ __forceinline__ void agg_add(Agg<D>& a, float w, const float* p, const float* cov) {
+    a.w += w;
+    if (w == 0.f) return;
+    const float f = w / a.w;
+    float d1[D], d2[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) { d1[i] = p[i] - a.m[i]; a.m[i] += f * d1[i]; d2[i] = p[i] - a.m[i]; }
+#pragma unroll
+    for (int i = 0; i < D; ++i)
+#pragma unroll
+        for (int j = 0; j < D; ++j) a.C[i * D + j] += w * (d1[j] * d2[i]);
+#pragma unroll
+    for (int e = 0; e < D * D; ++e) a.cm[e] += f * (cov[e] - a.cm[e]);
+}
+
+// merges b into a (b comes later in leaf order)
+template <int D>
+__device__ __forceinline__ void agg_merge(Agg<D>& a, const Agg<D>& b) {
+    const float w = a.w + b.w;
+    if (b.w == 0.f && a.w != 0.f) return;   // nothing to add (keeps a's moments untouched)
+    if (w == 0.f) {                         // both empty, or weights that cancel exactly: no defined mean
+        if (a.w == 0.f && b.w == 0.f) return;
+    }
+    const float f = (w != 0.f) ? b.w / w : 0.f;
+    float delta[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) delta[i] = b.m[i] - a.m[i];
+    const float cross = a.w * f;
+#pragma unroll
+    for (int i = 0; i < D; ++i)
+#pragma unroll
+        for (int j = 0; j < D; ++j) a.C[i * D + j] += b.C[i * D + j] + cross * delta[i] * delta[j];
+#pragma unroll
+    for (int i = 0; i < D; ++i) a.m[i] += f * delta[i];
+#pragma unroll
+    for (int e = 0; e < D * D; ++e) a.cm[e] += f * (b.cm[e] - a.cm[e]);
+    a.w = w;
+}
+
+template <int D>
+__device__ __forceinline__ Agg<D> agg_shfl_down(const Agg<D>& a, int offset) {
+    Agg<D> r;
+    r.w = __shfl_down_sync(0xffffffffu, a.w, offset);
+#pragma unroll
+    for (int i = 0; i < D; ++i) r.m[i] = __shfl_down_sync(0xffffffffu, a.m[i], offset);
+#pragma unroll
+    for (int e = 0; e < D * D; ++e) {
+        r.C[e] = __shfl_down_sync(0xffffffffu, a.C[e], offset);
+        r.cm[e] = __shfl_down_sync(0xffffffffu, a.cm[e], offset);
+    }
+    return r;
+}
+
+template <int D>
+__global__ void __launch_bounds__(kThreads)
+convolution_fitting_forward_kernel(const float* __restrict__ data, const float* __restrict__ kernels, Dims n,
+                                   float* __restrict__ fitting, float* __restrict__ cached_pos_covs,
+                                   int* __restrict__ nodesobjs_all, int* __restrict__ subtrees_all) {
+    constexpr int RF = 1 + D + D * D;
+    extern __shared__ __align__(16) unsigned char smem_bytes[];
+    const int Cin = n.n_channels_in, G = n.n_components, Gk = n.n_kernel_components, K = n.n_fitting;
+    const int T = Cin * G * Gk;
+    const int n_internal = T - 1, n_nodes = 2 * T - 1;
+    const int P = lbvh::next_pow2(T);
+    // shared layout
+    uint64_t* keys = reinterpret_cast<uint64_t*>(smem_bytes);                 // P keys; later reused as mass[n_nodes]
+    float* mass = reinterpret_cast<float*>(smem_bytes);
+    uint16_t* parent = reinterpret_cast<uint16_t*>(smem_bytes + size_t(P) * 8);   // n_nodes
+    uint16_t* left = parent + ((n_nodes + 7) & ~7);                               // n_internal
+    uint16_t* right = left + ((n_internal + 7) & ~7);                             // n_internal
+    unsigned char* level = reinterpret_cast<unsigned char*>(right + ((n_internal + 7) & ~7));   // n_nodes
+    unsigned* arrive_bits = reinterpret_cast<unsigned*>(level + ((n_nodes + 15) & ~15));        // ceil(n_internal / 32)
+    int* sel_node = reinterpret_cast<int*>(arrive_bits + ((n_internal + 31) / 32 + 3 & ~3));     // K
+    float* sel_rating = reinterpret_cast<float*>(sel_node + K);                                  // K
+    __shared__ float s_hi[kWarps][D], s_lo[kWarps][D], box_hi[D], box_lo[D];
+    __shared__ int s_max_level, s_n_selected;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int b = blockIdx.x / n.n_channels_out, o = blockIdx.x - b * n.n_channels_out;
+    const float* data_b = data + size_t(b) * Cin * G * RF;
+    const float* kernels_o = kernels + size_t(o) * Cin * Gk * RF;
+    int* nodesobjs = nodesobjs_all + size_t(blockIdx.x) * T;
+    int* subtrees = subtrees_all + size_t(blockIdx.x) * 2 * K;
+
+    // ---- bounding box: max over channels of (data max + kernel max), min likewise ----
+    {
+        float hi[D], lo[D];
+#pragma unroll
+        for (int d = 0; d < D; ++d) { hi[d] = -INFINITY; lo[d] = INFINITY; }
+        for (int ci = warp; ci < Cin; ci += kWarps) {
+            float dh[D], dl[D], kh[D], kl[D];
+#pragma unroll
+            for (int d = 0; d < D; ++d) { dh[d] = kh[d] = -INFINITY; dl[d] = kl[d] = INFINITY; }
+            for (int g = lane; g < G; g += 32)
+#pragma unroll
+                for (int d = 0; d < D; ++d) {
+                    const float v = __ldg(data_b + (size_t(ci) * G + g) * RF + 1 + d);
+                    dh[d] = fmaxf(dh[d], v); dl[d] = fminf(dl[d], v);
+                }
+            for (int g = lane; g < Gk; g += 32)
+#pragma unroll
+                for (int d = 0; d < D; ++d) {
+                    const float v = __ldg(kernels_o + (size_t(ci) * Gk + g) * RF + 1 + d);
+                    kh[d] = fmaxf(kh[d], v); kl[d] = fminf(kl[d], v);
+                }
+#pragma unroll
+            for (int d = 0; d < D; ++d) {
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) {
+                    dh[d] = fmaxf(dh[d], __shfl_xor_sync(0xffffffffu, dh[d], off));
+                    dl[d] = fminf(dl[d], __shfl_xor_sync(0xffffffffu, dl[d], off));
+                    kh[d] = fmaxf(kh[d], __shfl_xor_sync(0xffffffffu, kh[d], off));
+                    kl[d] = fminf(kl[d], __shfl_xor_sync(0xffffffffu, kl[d], off));
+                }
+                hi[d] = fmaxf(hi[d], __fadd_rn(dh[d], kh[d]));
+                lo[d] = fminf(lo[d], __fadd_rn(dl[d], kl[d]));
+            }
+        }
+        if (lane == 0) {
+#pragma unroll
+            for (int d = 0; d < D; ++d) { s_hi[warp][d] = hi[d]; s_lo[warp][d] = lo[d]; }
+        }
+        __syncthreads();
+        if (tid < D) {
+            float h = s_hi[0][tid], l = s_lo[0][tid];
+            for (int w = 1; w < kWarps; ++w) { h = fmaxf(h, s_hi[w][tid]); l = fminf(l, s_lo[w][tid]); }
+            box_hi[tid] = h; box_lo[tid] = l;
+        }
+        __syncthreads();
+    }
+
+    auto product_parts = [&](int t, int& comp_in, int& ch_in, int& comp_k) {
+        comp_k = t / (G * Cin);
+        const int rem = t - comp_k * G * Cin;
+        ch_in = rem / G;
+        comp_in = rem - ch_in * G;
+    };
+
+    // ---- keys, sort ----
+    for (int t = tid; t < P; t += kThreads) {
+        uint64_t key = ~0ull;
+        if (t < T) {
+            int gi, ci, ki;
+            product_parts(t, gi, ci, ki);
+            const float* dg = data_b + (size_t(ci) * G + gi) * RF;
+            const float* kg = kernels_o + (size_t(ci) * Gk + ki) * RF;
+            uint32_t q[3] = {0u, 0u, 0u};
+#pragma unroll
+            for (int d = 0; d < D; ++d) q[d] = lbvh::quantise(__fadd_rn(__ldg(dg + 1 + d), __ldg(kg + 1 + d)), box_lo[d], box_hi[d]);
+            const uint64_t sign = __fmul_rn(__ldg(dg), __ldg(kg)) > 0.f ? 1ull : 0ull;
+            key = (sign << 62) | (uint64_t(lbvh::morton30(q[0], q[1], q[2])) << 32) | uint64_t(uint32_t(t));
+        }
+        keys[t] = key;
+    }
+    __syncthreads();
+    lbvh::bitonic_sort_shared(keys, P);
+
+    // ---- leaves, internal nodes ----
+    for (int j = tid; j < T; j += kThreads) nodesobjs[j] = int(uint32_t(keys[j]));
+    for (int i = tid; i < n_nodes; i += kThreads) level[i] = 0;
+    for (int i = tid; i < (n_internal + 31) / 32; i += kThreads) arrive_bits[i] = 0u;
+    if (tid == 0) { parent[0] = 0xFFFFu; s_max_level = 0; }
+    {
+        const lbvh::PositionTieBreakCode code{keys};
+        for (int i = tid; i < n_internal; i += kThreads) {
+            const int2 r = lbvh::determine_range(code, T, i);
+            const int gamma = lbvh::find_split(code, r.x, r.y);
+            int l = gamma, rr = gamma + 1;
+            if (min(r.x, r.y) == gamma) l += T - 1;
+            if (max(r.x, r.y) == gamma + 1) rr += T - 1;
+            left[i] = uint16_t(l);
+            right[i] = uint16_t(rr);
+            parent[l] = uint16_t(i);
+            parent[rr] = uint16_t(i);
+        }
+    }
+    __syncthreads();   // keys are dead from here on: their memory becomes mass[]
+
+    // ---- leaf masses; levels by the second-arriver climb ----
+    for (int j = tid; j < T; j += kThreads) {
+        int gi, ci, ki;
+        product_parts(nodesobjs[j], gi, ci, ki);
+        mass[n_internal + j] = __fmul_rn(__ldg(data_b + (size_t(ci) * G + gi) * RF), __ldg(kernels_o + (size_t(ci) * Gk + ki) * RF));
+    }
+    for (int leaf = tid; leaf < T; leaf += kThreads) {
+        int node = parent[n_internal + leaf];
+        for (int guard = 0; guard < kMaxLevels && node != 0xFFFF; ++guard) {
+            __threadfence_block();
+            const unsigned bit = 1u << (node & 31);
+            if ((atomicOr(&arrive_bits[node >> 5], bit) & bit) == 0u) break;
+            __threadfence_block();
+            const int lv = 1 + max(int(((volatile unsigned char*)level)[left[node]]), int(((volatile unsigned char*)level)[right[node]]));
+            ((volatile unsigned char*)level)[node] = (unsigned char)lv;
+            atomicMax(&s_max_level, lv);
+            node = parent[node];
+        }
+    }
+    __syncthreads();
+    const int max_level = s_max_level;
+    for (int lv = 1; lv <= max_level; ++lv) {
+        for (int i = tid; i < n_internal; i += kThreads)
+            if (level[i] == lv) mass[i] = __fadd_rn(mass[left[i]], mass[right[i]]);
+        __syncthreads();
+    }
+
+    // ---- greedy selection of K subtree roots (warp 0) ----
+    if (warp == 0) {
+        auto rating_of = [&](int id) -> float { return id >= n_internal ? -2.f : fabsf(mass[id]); };
+        if (lane == 0) { sel_node[0] = 0; sel_rating[0] = rating_of(0); }
+        __syncwarp();
+        int n_sel = 1;
+        while (n_sel < K) {
+            float best_rating = -1.f;
+            int best = 0x7fffffff;
+            for (int i = lane; i < n_sel; i += 32)
+                if (sel_rating[i] > best_rating) { best_rating = sel_rating[i]; best = i; }
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) {
+                const float orat = __shfl_xor_sync(0xffffffffu, best_rating, off);
+                const int oidx = __shfl_xor_sync(0xffffffffu, best, off);
+                if (orat > best_rating || (orat == best_rating && oidx < best)) { best_rating = orat; best = oidx; }
+            }
+            if (best == 0x7fffffff) break;
+            __syncwarp();
+            if (lane == 0) {
+                const int id = sel_node[best];
+                const int l = left[id], r = right[id];
+                sel_node[best] = l; sel_rating[best] = rating_of(l);
+                sel_node[n_sel] = r; sel_rating[n_sel] = rating_of(r);
+            }
+            ++n_sel;
+            __syncwarp();
+        }
+        // leaf ranges [start, end) of the selected roots: leftmost / rightmost descent
+        for (int k = lane; k < K; k += 32) {
+            int start = -1, end = -1;
+            if (k < n_sel) {
+                int s = sel_node[k];
+                while (s < n_internal) s = left[s];
+                int e = sel_node[k];
+                while (e < n_internal) e = right[e];
+                start = s; end = e + 1;
+            }
+            subtrees[2 * k] = start;
+            subtrees[2 * k + 1] = end;
+            sel_node[k] = start;
+            sel_rating[k] = __int_as_float(end);
+        }
+        if (lane == 0) s_n_selected = n_sel;
+    }
+    __syncthreads();
+
+    // ---- aggregation: one warp per output Gaussian ----
+    float* out = fitting + size_t(blockIdx.x) * K * RF;
+    float* cached = cached_pos_covs + size_t(blockIdx.x) * K * D * D;
+    for (int k = warp; k < K; k += kWarps) {
+        const int start = sel_node[k], end = __float_as_int(sel_rating[k]);
+        float* o_k = out + size_t(k) * RF;
+        float* c_k = cached + size_t(k) * D * D;
+        if (start < 0) {
+            for (int f = lane; f < RF; f += 32) {
+                float v = 0.f;
+                if (f > D && ((f - 1 - D) / D == (f - 1 - D) % D)) v = 1.f;
+                o_k[f] = v;
+            }
+            for (int e = lane; e < D * D; e += 32) c_k[e] = 0.f;
+            continue;
+        }
+        Agg<D> a;
+        a.w = 0.f;
+#pragma unroll
+        for (int i = 0; i < D; ++i) a.m[i] = 0.f;
+#pragma unroll
+        for (int e = 0; e < D * D; ++e) { a.C[e] = 0.f; a.cm[e] = 0.f; }
+        // lane l takes a contiguous slice of the range so that merging neighbours keeps the leaf order
+        const int len = end - start;
+        const int per = (len + 31) / 32;
+        const int s0 = start + lane * per, s1 = min(end, s0 + per);
+        for (int i = s0; i < s1; ++i) {
+            int gi, ci, ki;
+            product_parts(nodesobjs[i - n_internal], gi, ci, ki);
+            const float* dg = data_b + (size_t(ci) * G + gi) * RF;
+            const float* kg = kernels_o + (size_t(ci) * Gk + ki) * RF;
+            float p[D], cov[D * D];
+#pragma unroll
+            for (int d = 0; d < D; ++d) p[d] = __ldg(dg + 1 + d) + __ldg(kg + 1 + d);
+#pragma unroll
+            for (int e = 0; e < D * D; ++e) cov[e] = __ldg(dg + 1 + D + e) + __ldg(kg + 1 + D + e);
+            agg_add<D>(a, __ldg(dg) * __ldg(kg), p, cov);
+        }
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const Agg<D> other = agg_shfl_down<D>(a, off);
+            if ((lane & (2 * off - 1)) == 0) agg_merge<D>(a, other);
+        }
+        if (lane == 0) {
+            o_k[0] = a.w;
+#pragma unroll
+            for (int d = 0; d < D; ++d) o_k[1 + d] = a.m[d];
+#pragma unroll
+            for (int e = 0; e < D * D; ++e) {
+                const float pc = (a.w == 0.f) ? ((e / D == e % D) ? 1.f : 0.f) : a.C[e] / a.w;
+                c_k[e] = pc;
+                o_k[1 + D + e] = a.cm[e] + pc;
+            }
+        }
+    }
+}
+
+size_t convfit_smem_bytes(int T, int K) {
+    const int n_internal = T - 1, n_nodes = 2 * T - 1;
+    const int P = lbvh::next_pow2(T);
+    size_t bytes = size_t(P) * 8;
+    bytes += 2 * size_t((n_nodes + 7) & ~7);
+    bytes += 2 * 2 * size_t((n_internal + 7) & ~7);
+    bytes += size_t((n_nodes + 15) & ~15);
+    bytes += 4 * size_t(((n_internal + 31) / 32 + 3) & ~3);
+    bytes += 8 * size_t(K);
+    return bytes;
+}
+
+}  // namespace
+}  // namespace gmc
+
+GMC_DEFINE_TU_CHECK_READER(convolution_fitting)
+
+extern "C" int gmc_convolution_fitting_forward(const float* data, const float* kernels, int n_batch, int n_channels_in,
+                                               int n_components, int n_channels_out, int n_kernel_components,
+                                               int n_dims, int n_components_fitting, float* fitting,
+                                               float* cached_pos_covs, int32_t* nodesobjs, int32_t* fitting_subtrees,
+                                               void* stream) {
+    using namespace gmc;
+    if (n_dims != 2 && n_dims != 3) return GMC_ERR_BAD_DIMS;
+    if (n_batch <= 0 || n_channels_in <= 0 || n_components <= 0 || n_channels_out <= 0 || n_kernel_components <= 0)
+        return GMC_ERR_BAD_DIMS;
+    const long long T = (long long)n_channels_in * n_components * n_kernel_components;
+    if (T < 2 || T > kMaxProducts) return GMC_ERR_BAD_DIMS;
+    if (n_components_fitting <= 0 || n_components_fitting > 8192) return GMC_ERR_BAD_DIMS;
+    if (!data || !kernels || !fitting || !cached_pos_covs || !nodesobjs || !fitting_subtrees) return GMC_ERR_NULL_POINTER;
+    const long long blocks = (long long)n_batch * n_channels_out;
+    if (blocks > 0x7fffffffLL) return GMC_ERR_BAD_DIMS;
+    const size_t smem = convfit_smem_bytes(int(T), n_components_fitting);
+    if (smem > 220 * 1024) return GMC_ERR_BAD_DIMS;
+    const Dims n{n_batch, n_channels_in, n_components, n_channels_out, n_kernel_components, n_components_fitting};
+    cudaStream_t st = as_stream(stream);
+    if (n_dims == 2) {
+        if (smem > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(convolution_fitting_forward_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        convolution_fitting_forward_kernel<2><<<unsigned(blocks), kThreads, smem, st>>>(data, kernels, n, fitting, cached_pos_covs, nodesobjs, fitting_subtrees);
+    } else {
+        if (smem > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(convolution_fitting_forward_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        convolution_fitting_forward_kernel<3><<<unsigned(blocks), kThreads, smem, st>>>(data, kernels, n, fitting, cached_pos_covs, nodesobjs, fitting_subtrees);
+    }
+    GMC_LAUNCH_CHECK();
+    return GMC_OK;
+}

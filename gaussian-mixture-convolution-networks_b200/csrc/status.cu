@@ -13,6 +13,8 @@ int gmc_tu_check_eval_inversed(int* word);
 int gmc_tu_check_small_ops(int* word);
 int gmc_tu_check_lbvh(int* word);
 int gmc_tu_check_mhem_fit(int* word);
+int gmc_tu_check_convolution(int* word);
+int gmc_tu_check_convolution_fitting(int* word);
 
 extern "C" const char* gmc_status_string(int status) {
     switch (status) {
@@ -46,5 +48,7 @@ extern "C" int gmc_device_check_word(int* word_out) {
     if (int s = gmc_tu_check_small_ops(word_out)) return s;
     if (int s = gmc_tu_check_lbvh(word_out)) return s;
     if (int s = gmc_tu_check_mhem_fit(word_out)) return s;
+    if (int s = gmc_tu_check_convolution(word_out)) return s;
+    if (int s = gmc_tu_check_convolution_fitting(word_out)) return s;
     return GMC_OK;
 }

@@ -1,0 +1,49 @@
+"""Fused convolution + reduction to n_components_fitting Gaussians as a differentiable operator.
+
+Same import path and `apply(data, kernels, n_components_fitting)` as the reference's
+src/gmc/cpp/extensions/convolution_fitting/binding.py:22-45; forward runs gmc_convolution_fitting_forward.
+"""
+import torch
+import torch.autograd
+
+from gmc import _native
+from gmc.cpp.extensions.convolution.binding import _dims
+
+
+def forward(data: torch.Tensor, kernels: torch.Tensor, n_components_fitting: int):
+    """-> (fitting [B, Cout, K, V], cached_pos_covs [B, Cout, K, D*D], nodesobjs int32 [B, Cout, T],
+    fitting_subtrees int32 [B, Cout, 2K])."""
+    dims = _dims(data, kernels)
+    _native.require_cuda_f32(data, "data")
+    _native.require_cuda_f32(kernels, "kernels")
+    n_batch, n_in, n_comp, n_out, n_kcomp, n_dims = dims
+    T = n_in * n_comp * n_kcomp
+    K = int(n_components_fitting)
+    dev = data.device
+    fitting = torch.empty((n_batch, n_out, K, data.shape[-1]), dtype=torch.float32, device=dev)
+    cached = torch.empty((n_batch, n_out, K, n_dims * n_dims), dtype=torch.float32, device=dev)
+    nodesobjs = torch.empty((n_batch, n_out, T), dtype=torch.int32, device=dev)
+    subtrees = torch.empty((n_batch, n_out, 2 * K), dtype=torch.int32, device=dev)
+    with torch.cuda.device_of(data):
+        _native.check(_native.lib.gmc_convolution_fitting_forward(
+            _native.ptr(data), _native.ptr(kernels), *dims, K, _native.ptr(fitting), _native.ptr(cached),
+            _native.ptr(nodesobjs), _native.ptr(subtrees), _native.stream_of(data)), "convolution_fitting forward")
+    return fitting, cached, nodesobjs, subtrees
+
+
+class ConvolutionFitting(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, data: torch.Tensor, kernels: torch.Tensor, n_components_fitting: int):
+        data = data.contiguous()
+        kernels = kernels.contiguous()
+        fitting, cached_pos_cov, nodesobjs, fitting_subtrees = forward(data, kernels, n_components_fitting)
+        ctx.save_for_backward(data, kernels, fitting, cached_pos_cov, nodesobjs, fitting_subtrees)
+        ctx.n_components_fitting = n_components_fitting
+        return fitting
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        raise NotImplementedError("convolution_fitting backward is not part of this build yet")
+
+
+apply = ConvolutionFitting.apply

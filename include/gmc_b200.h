@@ -128,6 +128,40 @@ int gmc_mhem_fit_forward(const float* mixture, long long n_mixtures, int n_compo
                          float* bvh_attributes, uint64_t* scratch_keys, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Exact convolution of mixtures: data [n_batch, n_channels_in, n_components, V] (*) kernels
+ * [n_channels_out, n_channels_in, n_kernel_components, V] -> out [n_batch, n_channels_out, T, V] with
+ * T = n_channels_in * n_components * n_kernel_components; product t = comp_in + n_components * (ch_in +
+ * n_channels_in * comp_k) is (w_d w_k, mu_d + mu_k, C_d + C_k).
+ * Backward: grad [n_batch, n_channels_out, T, V] -> grad_data (like data) and grad_kernels (like kernels); either
+ * may be NULL. Outputs are fully overwritten; no atomics, results are deterministic.
+ *
+ * Replaces convolution::forward_impl / backward_impl (src/gmc/cpp/extensions/convolution/bindings.cpp:10-27,
+ * implementation_forward.h:27-103, implementation_backward.h:27-121).
+ * ---------------------------------------------------------------------------------------------- */
+int gmc_convolution_forward(const float* data, const float* kernels, float* out, int n_batch, int n_channels_in,
+                            int n_components, int n_channels_out, int n_kernel_components, int n_dims, void* stream);
+int gmc_convolution_backward(const float* grad, const float* data, const float* kernels, float* grad_data,
+                             float* grad_kernels, int n_batch, int n_channels_in, int n_components,
+                             int n_channels_out, int n_kernel_components, int n_dims, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * Fused convolution + fit: the T product Gaussians of every (batch, output channel) are reduced to
+ * n_components_fitting (K) Gaussians without being materialised (2 <= T <= 8192).
+ *   fitting          [n_batch, n_channels_out, K, V]      out; unused slots are (0, 0, identity)
+ *   cached_pos_covs  [n_batch, n_channels_out, K, D*D]    out; scatter of the product centres per output (backward)
+ *   nodesobjs        [n_batch, n_channels_out, T] int32   out; product index of every leaf in sorted-key order
+ *   fitting_subtrees [n_batch, n_channels_out, 2K] int32  out; [start, end) leaf-node ids (leaves are numbered from
+ *                    T-1) of every output, -1 for unused slots
+ *
+ * Replaces convolution_fitting_forward (src/gmc/cpp/extensions/convolution_fitting/bindings.cpp:11-21,
+ * Tree.cu:21-408, implementation_forward.h:19-137).
+ * ---------------------------------------------------------------------------------------------- */
+int gmc_convolution_fitting_forward(const float* data, const float* kernels, int n_batch, int n_channels_in,
+                                    int n_components, int n_channels_out, int n_kernel_components, int n_dims,
+                                    int n_components_fitting, float* fitting, float* cached_pos_covs,
+                                    int32_t* nodesobjs, int32_t* fitting_subtrees, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * gmc_mhem_fit_forward for callers that have no scratch memory to give. (No counterpart in the reference, which
  * allocates its temporaries itself.)
  *

@@ -133,3 +133,50 @@ def density_rel_l2(fit_a: np.ndarray, fit_b: np.ndarray, target: np.ndarray, res
     da = density_grid(fit_a, lo, hi, res)
     db = density_grid(fit_b, lo, hi, res)
     return np.linalg.norm(da - db, axis=1) / np.maximum(np.linalg.norm(db, axis=1), 1e-300)
+
+
+def convolution_forward(data: np.ndarray, kernels: np.ndarray) -> np.ndarray:
+    """Exact convolution of src/gmc/cpp/extensions/convolution/implementation_forward.h:60-100:
+    out[b, o, t] = (w_d w_k, mu_d + mu_k, C_d + C_k), t = comp_in + G * (ch_in + Cin * comp_k)."""
+    B, Cin, G, RF = data.shape
+    Cout, Cin2, Gk, _ = kernels.shape
+    assert Cin == Cin2
+    d = data[:, None, None, :, :, :]            # [B, 1, 1(k), Cin, G, RF]
+    k = kernels[None, :, :, :, :].transpose(0, 1, 3, 2, 4)[:, :, :, :, None, :]   # [1, Cout, Gk, Cin, 1, RF]
+    out = d + k
+    out[..., 0] = d[..., 0] * k[..., 0]
+    return np.ascontiguousarray(out.reshape(B, Cout, Gk * Cin * G, RF))
+
+
+def convolution_backward(grad: np.ndarray, data: np.ndarray, kernels: np.ndarray):
+    """Gradient of convolution_forward (implementation_backward.h:64-118) -> (grad_data, grad_kernels)."""
+    B, Cin, G, RF = data.shape
+    Cout, _, Gk, _ = kernels.shape
+    g = grad.reshape(B, Cout, Gk, Cin, G, RF).astype(np.float64)
+    gd = g.sum(axis=(1, 2))                                   # [B, Cin, G, RF]
+    gk = g.sum(axis=(0, 4)).transpose(0, 2, 1, 3)             # [Cout, Cin, Gk, RF]
+    gd[..., 0] = (g[..., 0] * kernels.transpose(0, 2, 1, 3)[None, :, :, :, None, 0]).sum(axis=(1, 2))
+    gk[..., 0] = (g[..., 0] * data[:, None, None, :, :, 0]).sum(axis=(0, 4)).transpose(0, 2, 1)
+    return gd, gk
+
+
+def convolution_fitting_forward(data: np.ndarray, kernels: np.ndarray, K: int, with_keys: bool = False):
+    """Restated convolution_fitting forward -> (fitting [B, Cout, K, V], cached_pos_covs, nodesobjs, subtrees[, keys])."""
+    data = np.ascontiguousarray(data, dtype=np.float32)
+    kernels = np.ascontiguousarray(kernels, dtype=np.float32)
+    B, Cin, G, RF = data.shape
+    Cout, Cin2, Gk, _ = kernels.shape
+    assert Cin == Cin2
+    D = {7: 2, 13: 3}[RF]
+    T = Cin * G * Gk
+    out = np.empty((B, Cout, K, RF), dtype=np.float32)
+    cached = np.empty((B, Cout, K, D * D), dtype=np.float32)
+    nodesobjs = np.empty((B, Cout, T), dtype=np.int32)
+    subtrees = np.empty((B, Cout, 2 * K), dtype=np.int32)
+    keys = np.empty((B, Cout, T), dtype=np.uint64) if with_keys else None
+    rc = lib().oracle_convolution_fitting_forward(_p(data), _p(kernels), *[ctypes.c_int(v) for v in (B, Cin, G, Cout, Gk, D, K)],
+                                                  _p(out), _p(cached), _p(nodesobjs), _p(subtrees), _p(keys))
+    assert rc == 0
+    if with_keys:
+        return out, cached, nodesobjs, subtrees, keys
+    return out, cached, nodesobjs, subtrees

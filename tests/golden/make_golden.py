@@ -59,10 +59,60 @@ def eval_cases(gm):
     return cases
 
 
+def convolve_cases(gm):
+    """Inputs and the reference's gm.convolve (src/gmc/mixture.py:243-274) per output channel.
+    gm.convolve(data [B, Cin, G, V], kernels[o] [1, Cin, Gk, V]) -> [B, Cin, G*Gk, V] (pairs of one input channel)."""
+    cases = {}
+    g = torch.Generator().manual_seed(4321)
+    for idx, (D, B, Cin, G, Cout, Gk) in enumerate(((2, 2, 3, 6, 2, 4), (3, 2, 2, 5, 3, 3))):
+        def mixture(n0, n1, n2, pos, cov_scale, wscale):
+            w = torch.randn(n0, n1, n2, generator=g) * wscale
+            p = torch.randn(n0, n1, n2, D, generator=g) * pos
+            A = torch.rand(n0, n1, n2, D, D, generator=g) * 2 - 1
+            c = (A @ A.transpose(-1, -2) + torch.eye(D) * 0.05) * cov_scale
+            return gm.pack_mixture(w, p, c).contiguous()
+        data = mixture(B, Cin, G, 1.0, 0.05, 1.0)
+        kernels = mixture(Cout, Cin, Gk, 0.1, 0.01, 0.1)
+        per_channel = torch.stack([gm.convolve(data, kernels[o:o + 1]) for o in range(Cout)], dim=1)
+        cases[f"conv{idx}_data"] = data.numpy()
+        cases[f"conv{idx}_kernels"] = kernels.numpy()
+        cases[f"conv{idx}_out"] = per_channel.reshape(B, Cout, Cin * G * Gk, -1).numpy()   # set of products per (b, o)
+    return cases
+
+
+def relu_fit_cases(gm, fitting):
+    """Inputs and outputs of the reference's initial_approx_to_relu / fixed_point_iteration_to_relu
+    (src/gmc/fitting.py:279-312), evaluated in fp64."""
+    cases = {}
+    g = torch.Generator().manual_seed(999)
+    for idx, (D, B, L, G) in enumerate(((2, 2, 3, 12), (3, 2, 2, 9))):
+        w = torch.randn(B, L, G, generator=g)
+        p = torch.rand(B, L, G, D, generator=g) * 2 - 1
+        A = torch.rand(B, L, G, D, D, generator=g) * 2 - 1
+        c = (A @ A.transpose(-1, -2) + torch.eye(D) * 0.05) * 0.05
+        mixture = gm.pack_mixture(w, p, c).contiguous()
+        constant = torch.randn(B, L, generator=g) * 0.3
+        m64, c64 = mixture.double(), constant.double()
+        initial = fitting.initial_approx_to_relu(m64, c64)
+        fp, ret_const = fitting.fixed_point_iteration_to_relu(m64, c64, initial)
+        cases[f"relu{idx}_mixture"] = mixture.numpy()
+        cases[f"relu{idx}_constant"] = constant.numpy()
+        cases[f"relu{idx}_initial"] = initial.numpy()
+        cases[f"relu{idx}_fixed_point"] = fp.numpy()
+        cases[f"relu{idx}_ret_const"] = ret_const.numpy()
+    return cases
+
+
 def main():
     gm, fitting, mat_tools = ref_python.load()
     np.savez_compressed(os.path.join(HERE, "eval_inversed.npz"), **eval_cases(gm))
     print("wrote eval_inversed.npz")
+    np.savez_compressed(os.path.join(HERE, "convolve.npz"), **convolve_cases(gm))
+    print("wrote convolve.npz")
+    # gm.evaluate inside the fixed-point iteration runs in fp64 through the reference's dense formulation
+    gm.evaluate_inversed = lambda m, x: gm.evaluate_componentwise_inversed(m, x).sum(-1)
+    np.savez_compressed(os.path.join(HERE, "relu_fit.npz"), **relu_fit_cases(gm, fitting))
+    print("wrote relu_fit.npz")
 
 
 if __name__ == "__main__":
