@@ -1,0 +1,127 @@
+"""GPU: the Python layer above the kernels (gmc.fitting, gmc.modules, gmc.model) against golden vectors from the
+reference's Python and against the CPU oracle."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import ROOT, rel_inf
+from oracle import cpu_oracle
+from gmc import synthetic
+
+pytestmark = pytest.mark.gpu
+
+
+def test_relu_fixed_point_matches_reference_python():
+    import gmc.fitting as fitting
+    golden = dict(np.load(os.path.join(ROOT, "tests", "golden", "relu_fit.npz")))
+    for idx in (0, 1):
+        m = torch.from_numpy(golden[f"relu{idx}_mixture"]).cuda()
+        c = torch.from_numpy(golden[f"relu{idx}_constant"]).cuda()
+        initial = fitting.initial_approx_to_relu(m, c)
+        assert rel_inf(initial.cpu().numpy(), golden[f"relu{idx}_initial"]) < 1e-6
+        fp, ret_const = fitting.fixed_point_iteration_to_relu(m, c, initial)
+        assert rel_inf(fp.cpu().numpy(), golden[f"relu{idx}_fixed_point"]) < 1e-4
+        assert rel_inf(ret_const.cpu().numpy(), golden[f"relu{idx}_ret_const"]) < 1e-6
+        out, const, steps = fitting.fixed_point_only(m, c, -1)
+        assert torch.equal(out, fp) and len(steps) == 1
+
+
+def test_evaluate_covariance_form_and_integrate(golden_eval):
+    import gmc.mixture as gm
+    c = "eval04_d2"
+    m_inv = torch.from_numpy(golden_eval[c + "_mixture"])
+    x = torch.from_numpy(golden_eval[c + "_xes"]).cuda()
+    cov = torch.linalg.inv(gm.covariances(m_inv).double()).float()
+    m_cov = gm.pack_mixture(gm.weights(m_inv), gm.positions(m_inv), cov).cuda().requires_grad_(True)
+    out = gm.evaluate(m_cov, x)
+    assert rel_inf(out.detach().cpu().numpy(), golden_eval[c + "_out"]) < 1e-3     # two fp32 inversions in the chain
+    out.sum().backward()
+    assert torch.isfinite(m_cov.grad).all()
+    integ = gm.integrate(m_cov)
+    assert rel_inf(integ.detach().cpu().numpy(), m_inv[..., 0].double().sum(-1).numpy()) < 1e-5
+    g = torch.autograd.grad(integ.sum(), m_cov)[0]
+    assert torch.equal(g[..., 0], torch.ones_like(g[..., 0])) and g[..., 1:].abs().max().item() == 0
+
+
+def test_matrix_inverse_against_torch():
+    import gmc.mat_tools as mat_tools
+    for d in (2, 3):
+        m = torch.rand(1000, d, d)
+        m = (m @ m.transpose(-1, -2) + torch.eye(d) * 0.01).cuda().requires_grad_(True)
+        mine = mat_tools.inverse(m)
+        ref = torch.linalg.inv(m.detach().double())
+        assert ((mine.detach().double() - ref) ** 2).mean().item() < 1e-5     # src/gmc/test_mat_tools.py criterion
+        assert rel_inf(mine.detach().cpu().numpy(), ref.cpu().numpy()) < 1e-3
+        mine.sum().backward()
+        assert torch.isfinite(m.grad).all()
+
+
+def test_tree_hem_against_oracle_pipeline():
+    import gmc.fitting as fitting
+    m = synthetic.fit_target_2d(2, 3, 256, 31)
+    m[..., 0] = m[..., 0].abs() + 0.01
+    out = fitting.tree_hem(m.cuda(), 32, 4).cpu().numpy().reshape(-1, 32, 7)
+    # the same pipeline on the CPU: scale to mean trace D, oracle fit, scale back (src/gmc/fitting.py:342-358)
+    flat = m.numpy().reshape(-1, 256, 7).astype(np.float64)
+    scale = (flat[..., 3] + flat[..., 6]).mean(-1) / 2
+    back = np.sqrt(scale)
+    scaled = flat.copy()
+    scaled[..., 1:3] /= back[:, None, None]
+    scaled[..., 3:] /= scale[:, None, None]
+    ref = cpu_oracle.mhem_fit_forward(scaled.astype(np.float32), 32, 4).astype(np.float64)
+    ref[..., 1:3] *= back[:, None, None]
+    ref[..., 3:] *= scale[:, None, None]
+    err = cpu_oracle.density_rel_l2(out, ref, flat)
+    assert err.max() <= 1e-3, err
+
+
+def test_convolution_module_constant_path_and_exact_mode():
+    import gmc.modules as modules
+    import gmc.mixture as gm
+    torch.manual_seed(0)
+    conv = modules.Convolution(modules.ConvolutionConfig(), n_layers_in=3, n_layers_out=4, n_kernel_components=5, n_dims=2).cuda()
+    x = synthetic.fit_target_2d(2, 3, 10, 4).cuda()
+    const = torch.rand(2, 3).cuda()
+    y, y_const = conv(x, const)
+    assert y.shape == (2, 4, 3 * 10 * 5, 7)
+    k = conv.kernels().detach()
+    expected = (const.view(2, 1, 3) * k[..., 0].sum(-1).view(1, 4, 3)).sum(2)
+    assert rel_inf(y_const.detach().cpu().numpy(), expected.cpu().numpy()) < 1e-5
+    conv.n_fitting_components = 150
+    y_fit, _ = conv(x, const)
+    # K = T: same integral per channel as the exact convolution
+    assert rel_inf(gm.integrate(y_fit.detach()).cpu().numpy(), gm.integrate(y.detach()).cpu().numpy()) < 1e-4
+    y.sum().backward()
+    assert conv.weights.grad is not None and torch.isfinite(conv.weights.grad).all()
+
+
+def test_cov_scale_norm_makes_mean_trace_equal_d():
+    # property checked by the reference's src/gmc/test_modules.py:153-172
+    import gmc.modules as modules
+    import gmc.mixture as gm
+    import gmc.mat_tools as mat_tools
+    x = synthetic.fit_target_2d(3, 4, 20, 9).cuda()
+    norm = modules.CovScaleNorm(4, batch_norm=False).cuda()
+    y, c = norm((x, None))
+    traces = mat_tools.trace(gm.covariances(y)).mean(-1)
+    assert torch.allclose(traces, torch.full_like(traces, 2.0), rtol=1e-4)
+    assert c.shape == (3, 4) and c.abs().max().item() == 0
+
+
+def test_net_forward_3d_is_finite_and_repeatable():
+    import gmc.model as model
+    cfg = model.Config(n_dims=3)
+    cfg.layers = [model.Layer(8, 1, 32, 32), model.Layer(16, 1, 16, 16), model.Layer(10, 1, 8, 8)]
+    torch.manual_seed(5)
+    net = model.Net(config=cfg).cuda().eval()
+    x = synthetic.config4_input(n_batch=6).cuda()
+    with torch.no_grad():
+        torch.manual_seed(1)
+        a = net(x)
+        torch.manual_seed(1)
+        b = net(x)
+    assert a.shape == (6, 10) and torch.isfinite(a).all()
+    assert torch.allclose(a.exp().sum(1), torch.ones(6, device=a.device), atol=1e-4)
+    assert torch.allclose(a, b, atol=1e-5)
