@@ -345,6 +345,188 @@ convolution_fitting_forward_kernel(const float* __restrict__ data, const float* 
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// backward
+// ---------------------------------------------------------------------------------------------------------------
+// With the tree frozen, output k is (W, S1 / W, S3 / W + S2 / W - m m^T) with the leaf sums W = sum w, S1 = sum w p,
+// S2 = sum w p p^T, S3 = sum w C over its leaves (p = mu_d + mu_k, C = C_d + C_k, w = w_d w_k). The gradient of every
+// sum depends on the output only, so each output gets one coefficient record
+//     a1 = dL/dS1, A2 = dL/dS2 = dL/dS3, c0 = dL/dW (all paths)
+// and a product's gradient is dw = [a1.p + <A2, p p^T + C>] (w != 0) + c0, dp = w (a1 + (A2 + A2^T) p), dC = w A2
+// (the derivative the reference spells out in util/grad/welford.h:14-97). Products are visited from the side of the
+// tensor they contribute to -- by data Gaussian, then by kernel Gaussian -- so all sums stay in registers and global
+// memory sees one atomic per value and CTA.
+template <int D>
+struct SlotCoef {
+    float a1[D];
+    float A2[D * D];
+    float c0;
+};
+
+template <int D>
+__device__ __forceinline__ void product_gradient(const SlotCoef<D>& c, float w, const float* p, const float* cov,
+                                                 float& dw, float* dp, float* dC) {
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < D; ++i) q += c.a1[i] * p[i];
+#pragma unroll
+    for (int i = 0; i < D; ++i)
+#pragma unroll
+        for (int j = 0; j < D; ++j) q += c.A2[i * D + j] * (p[i] * p[j] + cov[i * D + j]);
+    dw = (w != 0.f ? q : 0.f) + c.c0;
+#pragma unroll
+    for (int i = 0; i < D; ++i) {
+        float acc = c.a1[i];
+#pragma unroll
+        for (int j = 0; j < D; ++j) acc += (c.A2[i * D + j] + c.A2[j * D + i]) * p[j];
+        dp[i] = w * acc;
+    }
+#pragma unroll
+    for (int e = 0; e < D * D; ++e) dC[e] = w * c.A2[e];
+}
+
+template <int D>
+__global__ void __launch_bounds__(kThreads)
+convolution_fitting_backward_kernel(const float* __restrict__ grad, const float* __restrict__ data,
+                                    const float* __restrict__ kernels, Dims n, const float* __restrict__ fitting,
+                                    const float* __restrict__ cached_pos_covs, const int* __restrict__ nodesobjs_all,
+                                    const int* __restrict__ subtrees_all, float* __restrict__ grad_data,
+                                    float* __restrict__ grad_kernels) {
+    constexpr int RF = 1 + D + D * D;
+    extern __shared__ __align__(16) unsigned char smem_bytes[];
+    const int Cin = n.n_channels_in, G = n.n_components, Gk = n.n_kernel_components, K = n.n_fitting;
+    const int T = Cin * G * Gk;
+    const int n_internal = T - 1;
+    SlotCoef<D>* coef = reinterpret_cast<SlotCoef<D>*>(smem_bytes);                              // K records
+    uint16_t* slot_of = reinterpret_cast<uint16_t*>(smem_bytes + ((sizeof(SlotCoef<D>) * K + 15) & ~size_t(15)));   // T
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int b = blockIdx.x / n.n_channels_out, o = blockIdx.x - b * n.n_channels_out;
+    const float* data_b = data + size_t(b) * Cin * G * RF;
+    const float* kernels_o = kernels + size_t(o) * Cin * Gk * RF;
+    const int* nodesobjs = nodesobjs_all + size_t(blockIdx.x) * T;
+    const int* subtrees = subtrees_all + size_t(blockIdx.x) * 2 * K;
+
+    for (int t = tid; t < T; t += kThreads) slot_of[t] = 0xFFFFu;
+    for (int k = tid; k < K; k += kThreads) {
+        SlotCoef<D> c;
+#pragma unroll
+        for (int i = 0; i < D; ++i) c.a1[i] = 0.f;
+#pragma unroll
+        for (int e = 0; e < D * D; ++e) c.A2[e] = 0.f;
+        c.c0 = 0.f;
+        const float* f = fitting + (size_t(blockIdx.x) * K + k) * RF;
+        const float* g = grad + (size_t(blockIdx.x) * K + k) * RF;
+        const float* pc = cached_pos_covs + (size_t(blockIdx.x) * K + k) * D * D;
+        const float W = f[0];
+        if (subtrees[2 * k] >= 0 && W != 0.f) {
+            const float inv_w = 1.f / W;
+            float m[D], gC[D * D], vmg[D];
+#pragma unroll
+            for (int i = 0; i < D; ++i) m[i] = f[1 + i];
+#pragma unroll
+            for (int e = 0; e < D * D; ++e) gC[e] = g[1 + D + e];
+            float dot_gc_s2 = 0.f, dot_gc_cm = 0.f, dot_vmg_m = 0.f;
+#pragma unroll
+            for (int i = 0; i < D; ++i) {
+                float acc = g[1 + i];
+#pragma unroll
+                for (int j = 0; j < D; ++j) acc -= (gC[i * D + j] + gC[j * D + i]) * m[j];
+                vmg[i] = acc;
+                dot_vmg_m += acc * m[i];
+            }
+#pragma unroll
+            for (int i = 0; i < D; ++i)
+#pragma unroll
+                for (int j = 0; j < D; ++j) {
+                    const int e = i * D + j;
+                    dot_gc_s2 += gC[e] * (pc[e] + m[i] * m[j]);
+                    dot_gc_cm += gC[e] * (f[1 + D + e] - pc[e]);
+                }
+#pragma unroll
+            for (int i = 0; i < D; ++i) c.a1[i] = vmg[i] * inv_w;
+#pragma unroll
+            for (int e = 0; e < D * D; ++e) c.A2[e] = gC[e] * inv_w;
+            c.c0 = g[0] - (dot_gc_s2 + dot_vmg_m + dot_gc_cm) * inv_w;
+        }
+        coef[k] = c;
+    }
+    __syncthreads();
+    for (int k = warp; k < K; k += kWarps) {
+        const int start = subtrees[2 * k], end = subtrees[2 * k + 1];
+        if (start < 0) continue;
+        for (int j = start - n_internal + lane; j < end - n_internal; j += 32) slot_of[nodesobjs[j]] = uint16_t(k);
+    }
+    __syncthreads();
+
+    auto load_product = [&](int gi, int ci, int ki, float& w, float& wd, float& wk, float* p, float* cov) {
+        const float* dg = data_b + (size_t(ci) * G + gi) * RF;
+        const float* kg = kernels_o + (size_t(ci) * Gk + ki) * RF;
+        wd = __ldg(dg); wk = __ldg(kg);
+        w = wd * wk;
+#pragma unroll
+        for (int d = 0; d < D; ++d) p[d] = __ldg(dg + 1 + d) + __ldg(kg + 1 + d);
+#pragma unroll
+        for (int e = 0; e < D * D; ++e) cov[e] = __ldg(dg + 1 + D + e) + __ldg(kg + 1 + D + e);
+    };
+
+    // ---- by data Gaussian: thread r = (ci, g) sums over the kernel components ----
+    if (grad_data != nullptr) {
+        for (int r = tid; r < Cin * G; r += kThreads) {
+            const int ci = r / G, gi = r - ci * G;
+            float acc[RF];
+#pragma unroll
+            for (int f = 0; f < RF; ++f) acc[f] = 0.f;
+            for (int ki = 0; ki < Gk; ++ki) {
+                const int slot = slot_of[gi + G * (ci + Cin * ki)];
+                if (slot == 0xFFFF) continue;
+                float w, wd, wk, p[D], cov[D * D], dw, dp[D], dC[D * D];
+                load_product(gi, ci, ki, w, wd, wk, p, cov);
+                product_gradient<D>(coef[slot], w, p, cov, dw, dp, dC);
+                acc[0] += dw * wk;
+#pragma unroll
+                for (int d = 0; d < D; ++d) acc[1 + d] += dp[d];
+#pragma unroll
+                for (int e = 0; e < D * D; ++e) acc[1 + D + e] += dC[e];
+            }
+            float* dst = grad_data + ((size_t(b) * Cin + ci) * G + gi) * RF;
+#pragma unroll
+            for (int f = 0; f < RF; ++f) atomicAdd(dst + f, acc[f]);
+        }
+    }
+    // ---- by kernel Gaussian: warp per (ci, k), lanes stride over the data components ----
+    if (grad_kernels != nullptr) {
+        for (int r = warp; r < Cin * Gk; r += kWarps) {
+            const int ci = r / Gk, ki = r - ci * Gk;
+            float acc[RF];
+#pragma unroll
+            for (int f = 0; f < RF; ++f) acc[f] = 0.f;
+            for (int gi = lane; gi < G; gi += 32) {
+                const int slot = slot_of[gi + G * (ci + Cin * ki)];
+                if (slot == 0xFFFF) continue;
+                float w, wd, wk, p[D], cov[D * D], dw, dp[D], dC[D * D];
+                load_product(gi, ci, ki, w, wd, wk, p, cov);
+                product_gradient<D>(coef[slot], w, p, cov, dw, dp, dC);
+                acc[0] += dw * wd;
+#pragma unroll
+                for (int d = 0; d < D; ++d) acc[1 + d] += dp[d];
+#pragma unroll
+                for (int e = 0; e < D * D; ++e) acc[1 + D + e] += dC[e];
+            }
+#pragma unroll
+            for (int f = 0; f < RF; ++f) {
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) acc[f] += __shfl_xor_sync(0xffffffffu, acc[f], off);
+            }
+            if (lane == 0) {
+                float* dst = grad_kernels + ((size_t(o) * Cin + ci) * Gk + ki) * RF;
+#pragma unroll
+                for (int f = 0; f < RF; ++f) atomicAdd(dst + f, acc[f]);
+            }
+        }
+    }
+}
+
 size_t convfit_smem_bytes(int T, int K) {
     const int n_internal = T - 1, n_nodes = 2 * T - 1;
     const int P = lbvh::next_pow2(T);
@@ -387,6 +569,42 @@ extern "C" int gmc_convolution_fitting_forward(const float* data, const float* k
     } else {
         if (smem > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(convolution_fitting_forward_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
         convolution_fitting_forward_kernel<3><<<unsigned(blocks), kThreads, smem, st>>>(data, kernels, n, fitting, cached_pos_covs, nodesobjs, fitting_subtrees);
+    }
+    GMC_LAUNCH_CHECK();
+    return GMC_OK;
+}
+
+extern "C" int gmc_convolution_fitting_backward(const float* grad, const float* data, const float* kernels, int n_batch,
+                                                int n_channels_in, int n_components, int n_channels_out,
+                                                int n_kernel_components, int n_dims, int n_components_fitting,
+                                                const float* fitting, const float* cached_pos_covs,
+                                                const int32_t* nodesobjs, const int32_t* fitting_subtrees,
+                                                float* grad_data, float* grad_kernels, void* stream) {
+    using namespace gmc;
+    if (n_dims != 2 && n_dims != 3) return GMC_ERR_BAD_DIMS;
+    if (n_batch <= 0 || n_channels_in <= 0 || n_components <= 0 || n_channels_out <= 0 || n_kernel_components <= 0)
+        return GMC_ERR_BAD_DIMS;
+    const long long T = (long long)n_channels_in * n_components * n_kernel_components;
+    if (T < 2 || T > 65534) return GMC_ERR_BAD_DIMS;
+    if (n_components_fitting <= 0 || n_components_fitting > 8192) return GMC_ERR_BAD_DIMS;
+    if (!grad || !data || !kernels || !fitting || !cached_pos_covs || !nodesobjs || !fitting_subtrees) return GMC_ERR_NULL_POINTER;
+    const long long blocks = (long long)n_batch * n_channels_out;
+    if (blocks > 0x7fffffffLL) return GMC_ERR_BAD_DIMS;
+    cudaStream_t st = as_stream(stream);
+    const size_t rf = size_t(1 + n_dims + n_dims * n_dims);
+    if (grad_data) GMC_CUDA_TRY(cudaMemsetAsync(grad_data, 0, sizeof(float) * rf * n_batch * n_channels_in * n_components, st));
+    if (grad_kernels) GMC_CUDA_TRY(cudaMemsetAsync(grad_kernels, 0, sizeof(float) * rf * n_channels_out * n_channels_in * n_kernel_components, st));
+    if (!grad_data && !grad_kernels) return GMC_OK;
+    const Dims n{n_batch, n_channels_in, n_components, n_channels_out, n_kernel_components, n_components_fitting};
+    const size_t coef_bytes = (n_dims == 2 ? sizeof(SlotCoef<2>) : sizeof(SlotCoef<3>)) * size_t(n_components_fitting);
+    const size_t smem = ((coef_bytes + 15) & ~size_t(15)) + 2 * size_t(T);
+    if (smem > 220 * 1024) return GMC_ERR_BAD_DIMS;
+    if (n_dims == 2) {
+        if (smem > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(convolution_fitting_backward_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        convolution_fitting_backward_kernel<2><<<unsigned(blocks), kThreads, smem, st>>>(grad, data, kernels, n, fitting, cached_pos_covs, nodesobjs, fitting_subtrees, grad_data, grad_kernels);
+    } else {
+        if (smem > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(convolution_fitting_backward_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        convolution_fitting_backward_kernel<3><<<unsigned(blocks), kThreads, smem, st>>>(grad, data, kernels, n, fitting, cached_pos_covs, nodesobjs, fitting_subtrees, grad_data, grad_kernels);
     }
     GMC_LAUNCH_CHECK();
     return GMC_OK;

@@ -31,6 +31,22 @@ def forward(data: torch.Tensor, kernels: torch.Tensor, n_components_fitting: int
     return fitting, cached, nodesobjs, subtrees
 
 
+def backward(grad: torch.Tensor, data: torch.Tensor, kernels: torch.Tensor, n_components_fitting: int,
+             fitting: torch.Tensor, cached_pos_covs: torch.Tensor, nodesobjs: torch.Tensor, fitting_subtrees: torch.Tensor,
+             needs_data: bool = True, needs_kernels: bool = True):
+    """-> (grad_data, grad_kernels); a gradient that is not needed comes back as None."""
+    dims = _dims(data, kernels)
+    _native.require_cuda_f32(grad, "grad")
+    grad_data = torch.empty_like(data) if needs_data else None
+    grad_kernels = torch.empty_like(kernels) if needs_kernels else None
+    with torch.cuda.device_of(data):
+        _native.check(_native.lib.gmc_convolution_fitting_backward(
+            _native.ptr(grad), _native.ptr(data), _native.ptr(kernels), *dims, int(n_components_fitting),
+            _native.ptr(fitting), _native.ptr(cached_pos_covs), _native.ptr(nodesobjs), _native.ptr(fitting_subtrees),
+            _native.ptr(grad_data), _native.ptr(grad_kernels), _native.stream_of(data)), "convolution_fitting backward")
+    return grad_data, grad_kernels
+
+
 class ConvolutionFitting(torch.autograd.Function):
     @staticmethod
     def forward(ctx, data: torch.Tensor, kernels: torch.Tensor, n_components_fitting: int):
@@ -43,7 +59,11 @@ class ConvolutionFitting(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_output):
-        raise NotImplementedError("convolution_fitting backward is not part of this build yet")
+        data, kernels, fitting, cached_pos_cov, nodesobjs, fitting_subtrees = ctx.saved_tensors
+        grad_data, grad_kernels = backward(grad_output.contiguous(), data, kernels, ctx.n_components_fitting, fitting,
+                                           cached_pos_cov, nodesobjs, fitting_subtrees,
+                                           ctx.needs_input_grad[0], ctx.needs_input_grad[1])
+        return grad_data, grad_kernels, None
 
 
 apply = ConvolutionFitting.apply

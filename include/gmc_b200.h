@@ -161,6 +161,19 @@ int gmc_convolution_fitting_forward(const float* data, const float* kernels, int
                                     int n_components_fitting, float* fitting, float* cached_pos_covs,
                                     int32_t* nodesobjs, int32_t* fitting_subtrees, void* stream);
 
+/* Gradient of gmc_convolution_fitting_forward with the tree frozen. grad is [n_batch, n_channels_out, K, V]; fitting,
+ * cached_pos_covs, nodesobjs and fitting_subtrees are the forward's outputs (not modified). grad_data (like data) and
+ * grad_kernels (like kernels) may each be NULL; non-NULL outputs are fully overwritten.
+ *
+ * Replaces convolution_fitting_backward (src/gmc/cpp/extensions/convolution_fitting/bindings.cpp:23-35,
+ * implementation_backward.h:22-159; util/grad/welford.h:14-97). */
+int gmc_convolution_fitting_backward(const float* grad, const float* data, const float* kernels, int n_batch,
+                                     int n_channels_in, int n_components, int n_channels_out, int n_kernel_components,
+                                     int n_dims, int n_components_fitting, const float* fitting,
+                                     const float* cached_pos_covs, const int32_t* nodesobjs,
+                                     const int32_t* fitting_subtrees, float* grad_data, float* grad_kernels,
+                                     void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * gmc_mhem_fit_forward for callers that have no scratch memory to give. (No counterpart in the reference, which
  * allocates its temporaries itself.)

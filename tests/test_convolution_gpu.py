@@ -74,3 +74,24 @@ def test_convolution_fitting_with_k_equal_t_is_the_exact_convolution():
             sa = a[b, o][np.lexsort(a[b, o].T[::-1])]
             se = e[b, o][np.lexsort(e[b, o].T[::-1])]
             assert np.abs(sa - se).max() < 1e-4
+
+
+@pytest.mark.parametrize("D,B,Cin,G,Cout,Gk,K", [(2, 2, 3, 16, 4, 5, 16), (2, 3, 8, 64, 3, 5, 32), (3, 2, 2, 20, 3, 5, 24),
+                                                 (2, 2, 2, 7, 2, 3, 60)])
+def test_convolution_fitting_backward_matches_autograd_oracle(D, B, Cin, G, Cout, Gk, K):
+    """Analytic CUDA backward against fp64 autograd through the restated forward with the tree frozen."""
+    import gmc.cpp.extensions.convolution_fitting.binding as cf
+    from oracle import autograd_oracles
+    data, kernels = _inputs(D, B, Cin, G, Cout, Gk, 90 + G + K)
+    d = data.cuda().requires_grad_(True)
+    k = kernels.cuda().requires_grad_(True)
+    out = cf.apply(d, k, K)
+    g = torch.randn(out.shape, generator=torch.Generator().manual_seed(3))
+    out.backward(g.cuda())
+    _, _, objs, sub = cf.forward(data.cuda(), kernels.cuda(), K)
+    gd, gk, _ = autograd_oracles.convolution_fitting_backward(g.numpy(), data.numpy(), kernels.numpy(),
+                                                               objs.cpu().numpy(), sub.cpu().numpy())
+    for name, a, r in (("grad_data", d.grad.cpu().numpy(), gd), ("grad_kernels", k.grad.cpu().numpy(), gk)):
+        assert np.isfinite(a).all()
+        for field, sl in (("weight", slice(0, 1)), ("position", slice(1, 1 + D)), ("covariance", slice(1 + D, None))):
+            assert rel_inf(a[..., sl], r[..., sl]) < 1e-3, f"{name} {field}: {rel_inf(a[..., sl], r[..., sl]):.2e}"
