@@ -63,14 +63,16 @@ struct WarpScratch {
     static constexpr int RF = 1 + D + D * D;
     static constexpr int NT = 2 * R;
     static constexpr int NH = (NT * NT - NT) / 2;
-    float tgt[NT][RF];
+    float tgt[NT][RF];        // gathered child Gaussians, padded with (0, 0, I)
     float heap_d[NH];
     unsigned char heap_a[NH], heap_b[NH];
-    int idx[R];
+    int idx[R];               // initial representatives
     float r3[NT][R];
     float fw[R];
     float outp[R][D];
     float outc[R][D * D];
+    float gin[R][RF];         // backward: gradient of the node's Gaussians
+    float tgrad[NT][RF];      // backward: gradient of the gathered child Gaussians
 };
 
 // ---- the sequential part of fit_initial, run by one lane ----
@@ -105,8 +107,8 @@ __device__ void cluster_and_select(WarpScratch<D, R>& ws, int n_valid) {
         const unsigned char va = ws.heap_a[i], vb = ws.heap_b[i];
         replace_element(vd, va, vb, i, rd, ra, rb);
     }
-    // sub-graph label per Gaussian (valid Gaussians are 0 .. n_valid-1); merging relabels the higher into the lower,
-    // member order inside a sub-graph (needed for the first-max rule) is kept in `order`.
+    // sub-graphs of Gaussians (valid Gaussians are 0 .. n_valid-1); merging appends the higher sub-graph to the lower,
+    // which keeps the member order that the first-max rule below depends on
     unsigned char members[NT][NT];
     int n_members[NT];
     for (int i = 0; i < NT; ++i) { members[i][0] = (unsigned char)i; n_members[i] = i < n_valid ? 1 : 0; }
@@ -144,6 +146,116 @@ __device__ void cluster_and_select(WarpScratch<D, R>& ws, int n_valid) {
     }
 }
 
+// Reductions over the lanes of one matrix row (fixed target t, lanes t*R .. t*R+R-1) or one matrix column (fixed s,
+// lanes s, s+R, ...); every lane of the row / column ends up with the total.
+template <int R>
+__device__ __forceinline__ float row_sum(float v) {
+#pragma unroll
+    for (int off = 1; off < R; off <<= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+}
+template <int R>
+__device__ __forceinline__ float col_sum(float v) {
+#pragma unroll
+    for (int off = R; off < 2 * R * R; off <<= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    return v;
+}
+
+// Values of matrix entry (t, s) of the EM step, one entry per lane (lanes beyond the matrix repeat the last entry).
+template <int D>
+struct Entry {
+    int t, s, fi;
+    float W, Wc, V, Vc;       // target / initial integral and their clipped versions
+    float a, b;               // weights scaled to integral one: a_t = w_t / Wc, b_s = v_s / Vc
+    float inv[D * D];         // inverse covariance of initial Gaussian s
+    float diff[D];            // mu_t - mu_initial(s)
+    float val_a, val_b, ab;   // N(mu_t; initial s), exp(-1/2 tr(inv Sigma_t)), their product
+    float lik, gate, u, x, X, r1, r2, fw, fwc, r3;
+};
+
+// Needs ws.tgt (padded targets) and ws.idx. Sums that feed decisions run in a fixed order (as on the CPU checker).
+template <int D, int R>
+__device__ __forceinline__ Entry<D> em_entry(const WarpScratch<D, R>& ws, int lane) {
+    constexpr int NT = 2 * R;
+    constexpr int NE = NT * R;
+    Entry<D> e;
+    float W = 0.f;
+#pragma unroll
+    for (int i = 0; i < NT; ++i) W += ws.tgt[i][0];
+    e.W = W; e.Wc = clip(W);
+    float V = 0.f;
+#pragma unroll
+    for (int s = 0; s < R; ++s) V += ws.tgt[ws.idx[s] < NT ? ws.idx[s] : 0][0];
+    e.V = V; e.Vc = clip(V);
+    const int ent = lane < NE ? lane : NE - 1;
+    e.t = ent / R; e.s = ent - e.t * R;
+    e.fi = ws.idx[e.s] < NT ? ws.idx[e.s] : 0;
+    e.a = ws.tgt[e.t][0] / e.Wc;
+    e.b = ws.tgt[e.fi][0] / e.Vc;
+    inverse<D>(&ws.tgt[e.fi][1 + D], e.inv);
+#pragma unroll
+    for (int k = 0; k < D; ++k) e.diff[k] = ws.tgt[e.t][1 + k] - ws.tgt[e.fi][1 + k];
+    float maha = 0.f;
+#pragma unroll
+    for (int i = 0; i < D; ++i) {
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < D; ++j) acc += e.inv[i * D + j] * e.diff[j];
+        maha += e.diff[i] * acc;
+    }
+    float tr = 0.f;
+#pragma unroll
+    for (int i = 0; i < D; ++i)
+#pragma unroll
+        for (int j = 0; j < D; ++j) tr += e.inv[i * D + j] * ws.tgt[e.t][1 + D + j * D + i];
+    e.val_a = sqrtf(det<D>(e.inv)) * gauss_norm_factor<D>() * expf(-0.5f * maha);
+    e.val_b = expf(-0.5f * tr);
+    e.ab = e.val_a * e.val_b;
+    e.lik = powf(clip(e.ab), 4.f * e.a);
+    const float lg = logf(det<D>(&ws.tgt[e.t][1 + D]) / det<D>(&ws.tgt[e.fi][1 + D]));
+    const float kl = sign_of(e.b) == sign_of(e.a) ? 0.5f * (maha + tr - float(D) - lg) : 0.f;
+    e.gate = kl < kKlThreshold ? 1.f : 0.f;
+    // per target: the component with the smallest KL is always gated in (first strict minimum)
+    const int row_base = e.t * R;
+    {
+        int best = -1;
+        float smallest = INFINITY;
+#pragma unroll
+        for (int s2 = 0; s2 < R; ++s2) {
+            const float v = __shfl_sync(0xffffffffu, kl, row_base + s2);
+            if (v < smallest) { smallest = v; best = s2; }
+        }
+        if (best == e.s) e.gate = 1.f;
+    }
+    e.u = e.b * e.lik;
+    e.x = clip(e.u) * e.gate;
+    float X = 0.f;
+#pragma unroll
+    for (int s2 = 0; s2 < R; ++s2) X += __shfl_sync(0xffffffffu, e.x, row_base + s2);
+    e.X = X;
+    e.r1 = e.x / X;
+    e.r2 = e.r1 * e.a;
+    float fw = 0.f;
+#pragma unroll
+    for (int t2 = 0; t2 < NT; ++t2) fw += __shfl_sync(0xffffffffu, e.r2, t2 * R + e.s);
+    e.fw = fw; e.fwc = clip(fw);
+    e.r3 = e.r2 / e.fwc;
+    return e;
+}
+
+// Fitted positions from ws.r3 (needs a __syncwarp before and after).
+template <int D, int R>
+__device__ __forceinline__ void em_positions(WarpScratch<D, R>& ws, int lane) {
+    constexpr int NT = 2 * R;
+    for (int o = lane; o < R * D; o += 32) {
+        const int so = o / D, d = o - so * D;
+        float acc = 0.f;
+#pragma unroll
+        for (int t2 = 0; t2 < NT; ++t2) acc += ws.r3[t2][so] * ws.tgt[t2][1 + d];
+        ws.outp[so][d] = acc;
+    }
+}
+
 // ---- one hierarchical-EM step on the padded targets in ws.tgt; result goes to `out` (R * RF floats) ----
 template <int D, int R>
 __device__ void fit_em_warp(WarpScratch<D, R>& ws, int n_target, float* __restrict__ out, int* initial_packed) {
@@ -152,11 +264,6 @@ __device__ void fit_em_warp(WarpScratch<D, R>& ws, int n_target, float* __restri
     constexpr int NH = (NT * NT - NT) / 2;
     constexpr int NE = NT * R;   // matrix entries: 32 (R = 4) or 8 (R = 2)
     const int lane = threadIdx.x & 31;
-
-    float target_integral = 0.f;
-#pragma unroll
-    for (int i = 0; i < NT; ++i) target_integral += ws.tgt[i][0];
-    const float target_clipped = clip(target_integral);
 
     // pairwise centre distances in the reference's heap fill order: all pairs i < j of the n_target valid
     // Gaussians (they are compacted in front), row major; the rest of the heap array is +inf padding
@@ -184,77 +291,13 @@ __device__ void fit_em_warp(WarpScratch<D, R>& ws, int n_target, float* __restri
     if (lane == 0) cluster_and_select<D, R>(ws, n_target);
     __syncwarp();
 
-    float initial_integral = 0.f;
-#pragma unroll
-    for (int s = 0; s < R; ++s) initial_integral += ws.tgt[ws.idx[s] < NT ? ws.idx[s] : 0][0];
-    const float initial_clipped = clip(initial_integral);
-
-    // ---- lane (t, s): likelihood, KL, gate ----
-    const int e = lane < NE ? lane : NE - 1;
-    const int t = e / R, s = e - t * R;
-    const int fi = ws.idx[s] < NT ? ws.idx[s] : 0;
-    const float tw = ws.tgt[t][0] / target_clipped;        // target weight scaled to integral 1
-    const float iw = ws.tgt[fi][0] / initial_clipped;      // initial weight scaled to integral 1
-    float lik, kl;
-    {
-        float inv[D * D], diff[D];
-        inverse<D>(&ws.tgt[fi][1 + D], inv);
-#pragma unroll
-        for (int k = 0; k < D; ++k) diff[k] = ws.tgt[t][1 + k] - ws.tgt[fi][1 + k];
-        float maha = 0.f;
-#pragma unroll
-        for (int i = 0; i < D; ++i) {
-            float acc = 0.f;
-#pragma unroll
-            for (int j = 0; j < D; ++j) acc += inv[i * D + j] * diff[j];
-            maha += diff[i] * acc;
-        }
-        float tr = 0.f;
-#pragma unroll
-        for (int i = 0; i < D; ++i)
-#pragma unroll
-            for (int j = 0; j < D; ++j) tr += inv[i * D + j] * ws.tgt[t][1 + D + j * D + i];
-        const float a = sqrtf(det<D>(inv)) * gauss_norm_factor<D>() * expf(-0.5f * maha);
-        const float b = expf(-0.5f * tr);
-        lik = powf(clip(a * b), 4.f * tw);
-        const float lg = logf(det<D>(&ws.tgt[t][1 + D]) / det<D>(&ws.tgt[fi][1 + D]));
-        kl = sign_of(iw) == sign_of(tw) ? 0.5f * (maha + tr - float(D) - lg) : 0.f;
-    }
-    float gate = kl < kKlThreshold ? 1.f : 0.f;
-    // per target: the component with the smallest KL is always gated in (first strict minimum)
-    const int row_base = t * R;
-    {
-        int best = -1;
-        float smallest = INFINITY;
-#pragma unroll
-        for (int s2 = 0; s2 < R; ++s2) {
-            const float v = __shfl_sync(0xffffffffu, kl, row_base + s2);
-            if (v < smallest) { smallest = v; best = s2; }
-        }
-        if (best == s) gate = 1.f;
-    }
-    const float wl = clip(iw * lik) * gate;
-    float row_sum = 0.f;
-#pragma unroll
-    for (int s2 = 0; s2 < R; ++s2) row_sum += __shfl_sync(0xffffffffu, wl, row_base + s2);
-    const float r2 = (wl / row_sum) * tw;
-    float fw = 0.f;
-#pragma unroll
-    for (int t2 = 0; t2 < NT; ++t2) fw += __shfl_sync(0xffffffffu, r2, t2 * R + s);
+    const Entry<D> e = em_entry<D, R>(ws, lane);
     if (lane < NE) {
-        ws.r3[t][s] = r2 / clip(fw);
-        if (t == 0) ws.fw[s] = fw;
+        ws.r3[e.t][e.s] = e.r3;
+        if (e.t == 0) ws.fw[e.s] = e.fw;
     }
     __syncwarp();
-
-    // ---- moment matching ----
-    for (int o = lane; o < R * D; o += 32) {
-        const int so = o / D, d = o - so * D;
-        float acc = 0.f;
-#pragma unroll
-        for (int t2 = 0; t2 < NT; ++t2) acc += ws.r3[t2][so] * ws.tgt[t2][1 + d];
-        ws.outp[so][d] = acc;
-    }
+    em_positions<D, R>(ws, lane);
     __syncwarp();
     for (int o = lane; o < R * D * D; o += 32) {
         const int so = o / (D * D), ij = o - so * D * D, i = ij / D, j = ij - i * D;
@@ -271,7 +314,7 @@ __device__ void fit_em_warp(WarpScratch<D, R>& ws, int n_target, float* __restri
     for (int o = lane; o < R * RF; o += 32) {
         const int so = o / RF, f = o - so * RF;
         float v;
-        if (f == 0) v = ws.fw[so] * target_clipped;
+        if (f == 0) v = ws.fw[so] * e.Wc;
         else if (f <= D) v = ws.outp[so][f - 1];
         else v = ws.outc[so][f - 1 - D];
         out[o] = v;
@@ -285,13 +328,256 @@ __device__ void fit_em_warp(WarpScratch<D, R>& ws, int n_target, float* __restri
     __syncwarp();
 }
 
+// ---- reverse of fit_em_warp: ws.tgt (padded targets), ws.idx and ws.gin (gradient of the R fitted Gaussians) in,
+//      ws.tgrad (gradient of the targets) out. The KL gate and the initial indices are constants; clip() passes the
+//      gradient only above its threshold; a covariance that was replaced by the identity passes none. ----
+template <int D, int R>
+__device__ void grad_em_warp(WarpScratch<D, R>& ws) {
+    constexpr int NT = 2 * R;
+    constexpr int NE = NT * R;
+    const int lane = threadIdx.x & 31;
+
+    const Entry<D> e = em_entry<D, R>(ws, lane);
+    if (lane < NE) {
+        ws.r3[e.t][e.s] = e.r3;
+        if (e.t == 0) ws.fw[e.s] = e.fw;
+    }
+    __syncwarp();
+    em_positions<D, R>(ws, lane);
+    __syncwarp();
+
+    const float* tg = ws.tgt[e.t];
+    const float gw = ws.gin[e.s][0];
+    float gP[D], gC[D * D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) gP[i] = ws.gin[e.s][1 + i];
+#pragma unroll
+    for (int ij = 0; ij < D * D; ++ij) gC[ij] = e.fw < kEpsLarge ? 0.f : ws.gin[e.s][1 + D + ij];
+
+    // ---- moment matching ----
+    float d[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) d[i] = tg[1 + i] - ws.outp[e.s][i];
+    float g_r3 = 0.f;
+#pragma unroll
+    for (int i = 0; i < D; ++i)
+#pragma unroll
+        for (int j = 0; j < D; ++j) g_r3 += gC[i * D + j] * (d[i] * d[j] + tg[1 + D + i * D + j]);
+    float t_mu[D], t_cov[D * D];     // this entry's share of the target gradient
+    float gPt[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) {
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < D; ++j) acc += (gC[i * D + j] + gC[j * D + i]) * d[j];
+        const float gd = e.r3 * acc;
+        gPt[i] = gP[i] - col_sum<R>(gd);
+        t_mu[i] = gd + e.r3 * gPt[i];
+    }
+#pragma unroll
+    for (int i = 0; i < D; ++i) g_r3 += gPt[i] * tg[1 + i];
+#pragma unroll
+    for (int ij = 0; ij < D * D; ++ij) t_cov[ij] = e.r3 * gC[ij];
+
+    // ---- responsibilities ----
+    float gWc = 0.f;
+#pragma unroll
+    for (int s2 = 0; s2 < R; ++s2) gWc += ws.gin[s2][0] * ws.fw[s2];
+    float gF = gw * e.Wc;
+    const float gFc = col_sum<R>(-g_r3 * e.r2 / (e.fwc * e.fwc));
+    if (e.fw > kEpsSmall) gF += gFc;
+    const float g_r2 = g_r3 / e.fwc + gF;
+    const float g_r1 = g_r2 * e.a;
+    float g_a = g_r2 * e.r1;
+    float g_x = g_r1 / e.X;
+    g_x += row_sum<R>(-g_r1 * e.x / (e.X * e.X));
+    const float g_u = e.u > kEpsSmall ? g_x * e.gate : 0.f;
+    const float g_b = col_sum<R>(g_u * e.lik);
+    const float g_L = g_u * e.b;
+
+    // ---- likelihood: L = clip(a b)^(4 a_t) ----
+    const float abc = clip(e.ab), wbar = 4.f * e.a;
+    const float g_abc = g_L * wbar * powf(abc, wbar - 1.f);
+    g_a += 4.f * (g_L * e.lik * logf(abc));
+    const float g_ab = e.ab > kEpsSmall ? g_abc : 0.f;
+    const float c1 = e.val_a * (g_ab * e.val_b);         // val_a * dL/dval_a
+    const float gh = (g_ab * e.val_a) * e.val_b;         // dL/dh, val_b = exp(h), h = -1/2 tr(inv Sigma_t)
+    float i_mu[D], gS[D * D];                            // gradient of the initial centre / of inv
+#pragma unroll
+    for (int i = 0; i < D; ++i) {
+        float st = 0.f;
+#pragma unroll
+        for (int j = 0; j < D; ++j) st += e.inv[i * D + j] * e.diff[j];
+        t_mu[i] -= c1 * st;
+        i_mu[i] = c1 * st;
+    }
+    const float* ic = &ws.tgt[e.fi][1 + D];
+#pragma unroll
+    for (int i = 0; i < D; ++i)
+#pragma unroll
+        for (int j = 0; j < D; ++j) {
+            t_cov[i * D + j] += -0.5f * gh * e.inv[j * D + i];
+            gS[i * D + j] = c1 * (0.5f * ic[j * D + i] - 0.5f * e.diff[i] * e.diff[j]) - 0.5f * gh * tg[1 + D + j * D + i];
+        }
+    float i_cov[D * D];                                  // d/d Sigma_initial = -inv^T gS inv^T
+#pragma unroll
+    for (int i = 0; i < D; ++i)
+#pragma unroll
+        for (int j = 0; j < D; ++j) {
+            float acc = 0.f;
+#pragma unroll
+            for (int k = 0; k < D; ++k)
+#pragma unroll
+                for (int l = 0; l < D; ++l) acc += e.inv[k * D + i] * gS[k * D + l] * e.inv[j * D + l];
+            i_cov[i * D + j] = -acc;
+        }
+
+    // ---- fold over rows (targets) and columns (initial Gaussians) ----
+    g_a = row_sum<R>(g_a);
+#pragma unroll
+    for (int i = 0; i < D; ++i) { t_mu[i] = row_sum<R>(t_mu[i]); i_mu[i] = col_sum<R>(i_mu[i]); }
+#pragma unroll
+    for (int ij = 0; ij < D * D; ++ij) { t_cov[ij] = row_sum<R>(t_cov[ij]); i_cov[ij] = col_sum<R>(i_cov[ij]); }
+    // integrals: a_t = w_t / Wc, b_s = v_s / Vc
+    gWc += col_sum<R>(-g_a * tg[0] / (e.Wc * e.Wc));
+    const float gW = e.W > kEpsSmall ? gWc : 0.f;
+    const float gVc = row_sum<R>(-g_b * ws.tgt[e.fi][0] / (e.Vc * e.Vc));
+    const float g_v = g_b / e.Vc + (e.V > kEpsSmall ? gVc : 0.f);
+    if (lane < NE && e.s == 0) {
+        ws.tgrad[e.t][0] = g_a / e.Wc + gW;
+#pragma unroll
+        for (int i = 0; i < D; ++i) ws.tgrad[e.t][1 + i] = t_mu[i];
+#pragma unroll
+        for (int ij = 0; ij < D * D; ++ij) ws.tgrad[e.t][1 + D + ij] = t_cov[ij];
+    }
+    __syncwarp();
+    if (lane < NE && e.t == 0) {      // the initial Gaussians are targets e.fi (distinct per s)
+        ws.tgrad[e.fi][0] += g_v;
+#pragma unroll
+        for (int i = 0; i < D; ++i) ws.tgrad[e.fi][1 + i] += i_mu[i];
+#pragma unroll
+        for (int ij = 0; ij < D * D; ++ij) ws.tgrad[e.fi][1 + D + ij] += i_cov[ij];
+    }
+    __syncwarp();
+}
+
 template <int D, int R>
 struct FitSmem {
     WarpScratch<D, R> warp[kWarps];
-    int level_start_dummy;
 };
 
-// Shared layout: [FitSmem][level bytes: 2G-1 rounded up][selection: K ints + K floats + K ints]
+// Levels above the leaves (leaves 0, internal node = 1 + max of its children) by the second-arriver climb.
+// `arrive` and `level` live in shared memory; returns after a CTA-wide barrier with *max_level set.
+__device__ __forceinline__ void compute_levels(const uint16_t* __restrict__ nodes, int G, unsigned char* level, int* arrive,
+                                               int* max_level) {
+    const int n_internal = G - 1, n_nodes = 2 * G - 1;
+    for (int i = threadIdx.x; i < n_internal; i += kThreads) arrive[i] = 0;
+    for (int i = threadIdx.x; i < n_nodes; i += kThreads) level[i] = 0;
+    if (threadIdx.x == 0) *max_level = 0;
+    __syncthreads();
+    for (int leaf = threadIdx.x; leaf < G; leaf += kThreads) {
+        int parent = nodes[size_t(n_internal + leaf) * 4];
+        for (int guard = 0; guard < kMaxLevels && parent != 0xFFFF; ++guard) {
+            __threadfence_block();
+            if (atomicAdd(&arrive[parent], 1) == 0) break;
+            __threadfence_block();
+            const int l = nodes[size_t(parent) * 4 + 1], r = nodes[size_t(parent) * 4 + 2];
+            const int lv = 1 + max(int(((volatile unsigned char*)level)[l]), int(((volatile unsigned char*)level)[r]));
+            ((volatile unsigned char*)level)[parent] = (unsigned char)lv;
+            atomicMax(max_level, lv);
+            parent = nodes[size_t(parent) * 4];
+        }
+    }
+    __syncthreads();
+}
+
+// Gathers the Gaussians of the two children of `id` into ws.tgt (left first, |w| < 1e-7 dropped, padded with (0,0,I)).
+// Lane j < R stands for the left child's j-th Gaussian, lane R + j for the right child's. Returns the number gathered;
+// `in_range` / `valid` / `pos` describe this lane's Gaussian.
+template <int D, int R>
+__device__ __forceinline__ int gather_children(WarpScratch<D, R>& ws, const float* __restrict__ mix, const uint16_t* __restrict__ nodes,
+                                               const float* attrs, int n_internal, int id, int lane, int& child,
+                                               int& child_slot, bool& in_range, bool& valid, int& pos) {
+    constexpr int RF = 1 + D + D * D;
+    constexpr int AF = Attr<D, R>::kFloats;
+    const int l = nodes[size_t(id) * 4 + 1], r = nodes[size_t(id) * 4 + 2];
+    auto count_of = [&](int n) -> int { return n >= n_internal ? 1 : __float_as_int(attrs[size_t(n) * AF + R * RF + 1]); };
+    const int cl = count_of(l), cr = count_of(r);
+    child = lane < R ? l : r;
+    child_slot = lane < R ? lane : lane - R;
+    in_range = lane < 2 * R && child_slot < (lane < R ? cl : cr);
+    const float* src = nullptr;
+    if (in_range) src = child >= n_internal ? mix + size_t(nodes[size_t(child) * 4 + 3]) * RF
+                                            : attrs + size_t(child) * AF + size_t(child_slot) * RF;
+    valid = in_range && fabsf(src[0]) >= kEpsLarge;
+    const unsigned vmask = __ballot_sync(0xffffffffu, valid);
+    const int n_target = __popc(vmask);
+    pos = __popc(vmask & ((1u << lane) - 1u));
+    if (valid) {
+#pragma unroll
+        for (int f = 0; f < RF; ++f) ws.tgt[pos][f] = src[f];
+    }
+    if (lane >= n_target && lane < 2 * R) {
+        ws.tgt[lane][0] = 0.f;
+#pragma unroll
+        for (int f = 0; f < D; ++f) ws.tgt[lane][1 + f] = 0.f;
+#pragma unroll
+        for (int f = 0; f < D * D; ++f) ws.tgt[lane][1 + D + f] = (f / D == f % D) ? 1.f : 0.f;
+    }
+    __syncwarp();
+    return n_target;
+}
+
+// Greedy selection from the root (one warp): list of selected nodes in sel_node, their first output slot in
+// sel_offset; returns the list length, *written = number of Gaussians they hold.
+template <int D, int R>
+__device__ __forceinline__ int select_nodes(const float* __restrict__ mix, const uint16_t* __restrict__ nodes, const float* attrs,
+                                            int n_internal, int K, int sel_cap, int* sel_node, float* sel_rating,
+                                            int* sel_offset, int lane, int* written) {
+    constexpr int RF = 1 + D + D * D;
+    constexpr int AF = Attr<D, R>::kFloats;
+    auto count_of = [&](int n) -> int { return n >= n_internal ? 1 : __float_as_int(attrs[size_t(n) * AF + R * RF + 1]); };
+    auto integral_of = [&](int n) -> float {
+        return n >= n_internal ? mix[size_t(nodes[size_t(n) * 4 + 3]) * RF] : attrs[size_t(n) * AF + R * RF];
+    };
+    auto rating_of = [&](int n) -> float { return count_of(n) < R ? -2.f : fabsf(integral_of(n)); };
+    if (lane == 0) { sel_node[0] = 0; sel_rating[0] = rating_of(0); }
+    __syncwarp();
+    int n_list = 1;
+    int n_selected = count_of(0);
+    while (n_selected < K - R && n_list < sel_cap) {
+        float best_rating = -1.f;
+        int best = 0x7fffffff;
+        for (int i = lane; i < n_list; i += 32)
+            if (sel_rating[i] > best_rating) { best_rating = sel_rating[i]; best = i; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float orat = __shfl_xor_sync(0xffffffffu, best_rating, o);
+            const int oidx = __shfl_xor_sync(0xffffffffu, best, o);
+            if (orat > best_rating || (orat == best_rating && oidx < best)) { best_rating = orat; best = oidx; }
+        }
+        if (best == 0x7fffffff) break;   // no full node left
+        const int id = sel_node[best];
+        const int l = nodes[size_t(id) * 4 + 1], r = nodes[size_t(id) * 4 + 2];
+        __syncwarp();
+        if (lane == 0) {
+            sel_node[best] = l; sel_rating[best] = rating_of(l);
+            sel_node[n_list] = r; sel_rating[n_list] = rating_of(r);
+        }
+        n_selected = n_selected - R + count_of(l) + count_of(r);
+        ++n_list;
+        __syncwarp();
+    }
+    if (lane == 0) {
+        int w = 0;
+        for (int i = 0; i < n_list; ++i) { sel_offset[i] = w; w += count_of(sel_node[i]); }
+        *written = w;
+    }
+    __syncwarp();
+    return n_list;
+}
+
+// Shared layout: [FitSmem][level bytes: 2G-1 rounded up][arrive: G-1 ints][selection: 3 x sel_cap words][has_grad bytes]
 template <int D, int R>
 __global__ void __launch_bounds__(kThreads)
 mhem_fit_forward_kernel(const float* __restrict__ mixture, const uint16_t* __restrict__ nodes_all, float* __restrict__ attrs_all,
@@ -316,26 +602,7 @@ mhem_fit_forward_kernel(const float* __restrict__ mixture, const uint16_t* __res
     float* attrs = attrs_all + size_t(blockIdx.x) * n_internal * AF;
     float* out = out_all + size_t(blockIdx.x) * K * RF;
 
-    // ---- levels: leaves are 0, an internal node is 1 + max(children); second arriver computes ----
-    for (int i = tid; i < n_internal; i += kThreads) arrive[i] = 0;
-    for (int i = tid; i < n_nodes; i += kThreads) level[i] = 0;
-    if (tid == 0) s_max_level = 0;
-    __syncthreads();
-    for (int leaf = tid; leaf < G; leaf += kThreads) {
-        int id = n_internal + leaf;
-        int parent = nodes[size_t(id) * 4];
-        for (int guard = 0; guard < kMaxLevels && parent != 0xFFFF; ++guard) {
-            __threadfence_block();
-            if (atomicAdd(&arrive[parent], 1) == 0) break;
-            __threadfence_block();
-            const int l = nodes[size_t(parent) * 4 + 1], r = nodes[size_t(parent) * 4 + 2];
-            const int lv = 1 + max(int(((volatile unsigned char*)level)[l]), int(((volatile unsigned char*)level)[r]));
-            ((volatile unsigned char*)level)[parent] = (unsigned char)lv;
-            atomicMax(&s_max_level, lv);
-            parent = nodes[size_t(parent) * 4];
-        }
-    }
-    __syncthreads();
+    compute_levels(nodes, G, level, arrive, &s_max_level);
     const int max_level = s_max_level;
 
     auto child_count = [&](int id) -> int { return id >= n_internal ? 1 : __float_as_int(attrs[size_t(id) * AF + R * RF + 1]); };
@@ -351,34 +618,12 @@ mhem_fit_forward_kernel(const float* __restrict__ mixture, const uint16_t* __res
             const unsigned todo = __ballot_sync(0xffffffffu, cand < n_internal && level[cand] == lv);
             for (unsigned bits = todo; bits; bits &= bits - 1) {
                 const int id = base + __ffs(bits) - 1;
-                const int l = nodes[size_t(id) * 4 + 1], r = nodes[size_t(id) * 4 + 2];
-                // gather: lane j < R reads the left child's j-th Gaussian, lane R + j the right child's
-                const int cl = child_count(l), cr = child_count(r);
-                const int which = lane < R ? l : r;
-                const int j = lane < R ? lane : lane - R;
-                const bool in_range = lane < 2 * R && j < (lane < R ? cl : cr);
-                const float* src = nullptr;
-                if (in_range) src = which >= n_internal ? mix + size_t(nodes[size_t(which) * 4 + 3]) * RF
-                                                        : attrs + size_t(which) * AF + size_t(j) * RF;
-                const bool valid = in_range && fabsf(src[0]) >= kEpsLarge;
-                const unsigned vmask = __ballot_sync(0xffffffffu, valid);
-                const int n_target = __popc(vmask);
-                if (valid) {
-                    const int pos = __popc(vmask & ((1u << lane) - 1u));
-#pragma unroll
-                    for (int f = 0; f < RF; ++f) ws.tgt[pos][f] = src[f];
-                }
-                if (lane >= n_target && lane < 2 * R) {
-                    ws.tgt[lane][0] = 0.f;
-#pragma unroll
-                    for (int f = 0; f < D; ++f) ws.tgt[lane][1 + f] = 0.f;
-#pragma unroll
-                    for (int f = 0; f < D * D; ++f) ws.tgt[lane][1 + D + f] = (f / D == f % D) ? 1.f : 0.f;
-                }
-                __syncwarp();
+                int child, child_slot, pos;
+                bool in_range, valid;
+                const int n_target = gather_children<D, R>(ws, mix, nodes, attrs, n_internal, id, lane, child, child_slot, in_range, valid, pos);
                 float* rec = attrs + size_t(id) * AF;
                 if (lane == 0) {
-                    rec[R * RF] = child_integral(l) + child_integral(r);
+                    rec[R * RF] = child_integral(nodes[size_t(id) * 4 + 1]) + child_integral(nodes[size_t(id) * 4 + 2]);
                     rec[R * RF + 1] = __int_as_float(n_target > R ? R : n_target);
                     rec[R * RF + 3] = 0.f;
                 }
@@ -398,42 +643,10 @@ mhem_fit_forward_kernel(const float* __restrict__ mixture, const uint16_t* __res
         __syncthreads();
     }
 
-    // ---- greedy selection from the root (warp 0) ----
+    // ---- greedy selection from the root (warp 0), then copy-out ----
     if (warp == 0) {
-        auto rating_of = [&](int id) -> float { return child_count(id) < R ? -2.f : fabsf(child_integral(id)); };
-        if (lane == 0) { sel_node[0] = 0; sel_rating[0] = rating_of(0); }
-        __syncwarp();
-        int n_list = 1;
-        int n_selected = child_count(0);
-        while (n_selected < K - R && n_list < sel_cap) {
-            float best_rating = -1.f;
-            int best = 0x7fffffff;
-            for (int i = lane; i < n_list; i += 32)
-                if (sel_rating[i] > best_rating) { best_rating = sel_rating[i]; best = i; }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float orat = __shfl_xor_sync(0xffffffffu, best_rating, o);
-                const int oidx = __shfl_xor_sync(0xffffffffu, best, o);
-                if (orat > best_rating || (orat == best_rating && oidx < best)) { best_rating = orat; best = oidx; }
-            }
-            if (best == 0x7fffffff) break;   // no full node left
-            const int id = sel_node[best];
-            const int l = nodes[size_t(id) * 4 + 1], r = nodes[size_t(id) * 4 + 2];
-            __syncwarp();
-            if (lane == 0) {
-                sel_node[best] = l; sel_rating[best] = rating_of(l);
-                sel_node[n_list] = r; sel_rating[n_list] = rating_of(r);
-            }
-            n_selected = n_selected - R + child_count(l) + child_count(r);
-            ++n_list;
-            __syncwarp();
-        }
-        if (lane == 0) {
-            int w = 0;
-            for (int i = 0; i < n_list; ++i) { sel_offset[i] = w; w += child_count(sel_node[i]); }
-            s_n_selected_nodes = n_list;
-            s_written = w;
-        }
+        const int n_list = select_nodes<D, R>(mix, nodes, attrs, n_internal, K, sel_cap, sel_node, sel_rating, sel_offset, lane, &s_written);
+        if (lane == 0) s_n_selected_nodes = n_list;
     }
     __syncthreads();
     const int n_list = s_n_selected_nodes;
@@ -455,10 +668,118 @@ mhem_fit_forward_kernel(const float* __restrict__ mixture, const uint16_t* __res
     }
 }
 
+// Backward: the selection is replayed to put the incoming gradient on the selected nodes, then levels are processed
+// from the top; a node that holds a gradient passes it to the Gaussians of its children (through grad_em_warp if the
+// node was fitted, unchanged otherwise). node_grad [n_internal, R * RF] is scratch; grad_target starts zeroed.
+template <int D, int R>
+__global__ void __launch_bounds__(kThreads)
+mhem_fit_backward_kernel(const float* __restrict__ grad_all, const float* __restrict__ mixture,
+                         const uint16_t* __restrict__ nodes_all, const float* __restrict__ attrs_all,
+                         float* __restrict__ node_grad_all, float* __restrict__ grad_target_all, int n_components,
+                         int n_fitting) {
+    constexpr int RF = 1 + D + D * D;
+    constexpr int AF = Attr<D, R>::kFloats;
+    constexpr int NT = 2 * R;
+    extern __shared__ __align__(16) unsigned char smem_bytes[];
+    FitSmem<D, R>& sm = *reinterpret_cast<FitSmem<D, R>*>(smem_bytes);
+    const int G = n_components, K = n_fitting;
+    const int n_internal = G - 1, n_nodes = 2 * G - 1;
+    unsigned char* level = smem_bytes + sizeof(FitSmem<D, R>);
+    int* arrive = reinterpret_cast<int*>(level + ((n_nodes + 15) & ~15));
+    const int sel_cap = K > 1024 ? K : 1024;
+    int* sel_node = arrive + n_internal;
+    float* sel_rating = reinterpret_cast<float*>(sel_node + sel_cap);
+    int* sel_offset = reinterpret_cast<int*>(sel_rating + sel_cap);
+    unsigned char* has_grad = reinterpret_cast<unsigned char*>(sel_offset + sel_cap);
+    __shared__ int s_max_level, s_n_selected_nodes, s_written;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* mix = mixture + size_t(blockIdx.x) * G * RF;
+    const uint16_t* nodes = nodes_all + size_t(blockIdx.x) * n_nodes * 4;
+    const float* attrs = attrs_all + size_t(blockIdx.x) * n_internal * AF;
+    const float* grad = grad_all + size_t(blockIdx.x) * K * RF;
+    float* node_grad = node_grad_all + size_t(blockIdx.x) * n_internal * R * RF;
+    float* grad_target = grad_target_all + size_t(blockIdx.x) * G * RF;
+
+    for (int i = tid; i < n_internal; i += kThreads) has_grad[i] = 0;
+    compute_levels(nodes, G, level, arrive, &s_max_level);
+    const int max_level = s_max_level;
+    auto count_of = [&](int n) -> int { return n >= n_internal ? 1 : __float_as_int(attrs[size_t(n) * AF + R * RF + 1]); };
+
+    if (warp == 0) {
+        const int n_list = select_nodes<D, R>(mix, nodes, attrs, n_internal, K, sel_cap, sel_node, sel_rating, sel_offset, lane, &s_written);
+        if (lane == 0) s_n_selected_nodes = n_list;
+    }
+    __syncthreads();
+    const int n_list = s_n_selected_nodes;
+    for (int i = warp; i < n_list; i += kWarps) {
+        const int id = sel_node[i];
+        const int cnt = count_of(id);
+        if (id >= n_internal) {      // a selected leaf hands its gradient straight to its Gaussian
+            const int obj = nodes[size_t(id) * 4 + 3];
+            if (sel_offset[i] < K && fabsf(mix[size_t(obj) * RF]) >= kEpsLarge)
+                for (int f = lane; f < RF; f += 32) grad_target[size_t(obj) * RF + f] = grad[size_t(sel_offset[i]) * RF + f];
+        } else {
+            for (int o = lane; o < R * RF; o += 32) {
+                const int slot = sel_offset[i] + o / RF;
+                node_grad[size_t(id) * R * RF + o] = (o < cnt * RF && slot < K) ? grad[size_t(sel_offset[i]) * RF + o] : 0.f;
+            }
+            if (lane == 0) has_grad[id] = 1;
+        }
+    }
+    __threadfence_block();
+    __syncthreads();
+
+    WarpScratch<D, R>& ws = sm.warp[warp];
+    for (int lv = max_level; lv >= 1; --lv) {
+        for (int base = warp * 32; base < n_internal; base += kWarps * 32) {
+            const int cand = base + lane;
+            const unsigned todo = __ballot_sync(0xffffffffu, cand < n_internal && level[cand] == lv && has_grad[cand]);
+            for (unsigned bits = todo; bits; bits &= bits - 1) {
+                const int id = base + __ffs(bits) - 1;
+                int child, child_slot, pos;
+                bool in_range, valid;
+                const int n_target = gather_children<D, R>(ws, mix, nodes, attrs, n_internal, id, lane, child, child_slot, in_range, valid, pos);
+                if (n_target > R) {
+                    for (int o = lane; o < R * RF; o += 32) ws.gin[o / RF][o % RF] = node_grad[size_t(id) * R * RF + o];
+                    if (lane < R) ws.idx[lane] = (__float_as_int(attrs[size_t(id) * AF + R * RF + 2]) >> (8 * lane)) & 0xFF;
+                    __syncwarp();
+                    grad_em_warp<D, R>(ws);
+                } else {
+                    for (int o = lane; o < NT * RF; o += 32) {
+                        const int so = o / RF;
+                        ws.tgrad[so][o % RF] = so < n_target ? node_grad[size_t(id) * R * RF + o] : 0.f;
+                    }
+                    __syncwarp();
+                }
+                // hand the gradients to the children's Gaussians (dropped ones get zero)
+                if (in_range) {
+                    if (child >= n_internal) {
+                        if (valid) {
+                            float* dst = grad_target + size_t(nodes[size_t(child) * 4 + 3]) * RF;
+#pragma unroll
+                            for (int f = 0; f < RF; ++f) dst[f] = ws.tgrad[pos][f];
+                        }
+                    } else {
+                        float* dst = node_grad + size_t(child) * R * RF + size_t(child_slot) * RF;
+#pragma unroll
+                        for (int f = 0; f < RF; ++f) dst[f] = valid ? ws.tgrad[pos][f] : 0.f;
+                        has_grad[child] = 1;
+                    }
+                }
+                __syncwarp();
+            }
+        }
+        __threadfence_block();
+        __syncthreads();
+    }
+}
+
 template <int D, int R>
 size_t fit_smem_bytes(int G, int K) {
     const int n_nodes = 2 * G - 1;
-    return sizeof(FitSmem<D, R>) + size_t((n_nodes + 15) & ~15) + sizeof(int) * size_t(G - 1) + size_t(K > 1024 ? K : 1024) * 12;
+    return sizeof(FitSmem<D, R>) + size_t((n_nodes + 15) & ~15) + sizeof(int) * size_t(G - 1) +
+           size_t(K > 1024 ? K : 1024) * 12 + size_t((G + 15) & ~15);
 }
 
 template <int D, int R>
@@ -469,6 +790,18 @@ int launch_fit(const float* mixture, long long n_mixtures, int G, int K, const u
     if (smem > 200 * 1024) return GMC_ERR_BAD_DIMS;
     if (smem > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
     kernel<<<unsigned(n_mixtures), kThreads, smem, stream>>>(mixture, nodes, attrs, out, G, K);
+    GMC_LAUNCH_CHECK();
+    return GMC_OK;
+}
+
+template <int D, int R>
+int launch_fit_backward(const float* grad, const float* mixture, long long n_mixtures, int G, int K, const uint16_t* nodes,
+                        const float* attrs, float* node_grad, float* grad_target, cudaStream_t stream) {
+    auto kernel = mhem_fit_backward_kernel<D, R>;
+    const size_t smem = fit_smem_bytes<D, R>(G, K);
+    if (smem > 200 * 1024) return GMC_ERR_BAD_DIMS;
+    if (smem > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    kernel<<<unsigned(n_mixtures), kThreads, smem, stream>>>(grad, mixture, nodes, attrs, node_grad, grad_target, G, K);
     GMC_LAUNCH_CHECK();
     return GMC_OK;
 }
@@ -500,6 +833,27 @@ extern "C" int gmc_mhem_fit_forward(const float* mixture, long long n_mixtures, 
     if (n_dims == 2) return reduction_n == 2 ? GMC_FIT(2, 2) : GMC_FIT(2, 4);
     return reduction_n == 2 ? GMC_FIT(3, 2) : GMC_FIT(3, 4);
 #undef GMC_FIT
+}
+
+extern "C" int gmc_mhem_fit_backward(const float* grad, const float* mixture, long long n_mixtures, int n_components,
+                                     int n_dims, int n_components_fitting, int reduction_n, const int16_t* bvh_nodes,
+                                     const float* bvh_attributes, float* scratch_node_grad, float* grad_mixture,
+                                     void* stream) {
+    using namespace gmc;
+    if (n_dims != 2 && n_dims != 3) return GMC_ERR_BAD_DIMS;
+    if (reduction_n != 2 && reduction_n != 4) return GMC_ERR_UNSUPPORTED;
+    if (n_components_fitting <= 0 || n_components_fitting % reduction_n != 0 || n_components_fitting > 4096) return GMC_ERR_BAD_DIMS;
+    if (n_mixtures < 0 || n_components < 2) return GMC_ERR_BAD_DIMS;
+    if (n_mixtures == 0) return GMC_OK;
+    if (!grad || !mixture || !bvh_nodes || !bvh_attributes || !scratch_node_grad || !grad_mixture) return GMC_ERR_NULL_POINTER;
+    cudaStream_t st = as_stream(stream);
+    const size_t rf = size_t(1 + n_dims + n_dims * n_dims);
+    GMC_CUDA_TRY(cudaMemsetAsync(grad_mixture, 0, sizeof(float) * rf * size_t(n_mixtures) * n_components, st));
+    const uint16_t* nodes = reinterpret_cast<const uint16_t*>(bvh_nodes);
+#define GMC_FITB(D_, R_) launch_fit_backward<D_, R_>(grad, mixture, n_mixtures, n_components, n_components_fitting, nodes, bvh_attributes, scratch_node_grad, grad_mixture, st)
+    if (n_dims == 2) return reduction_n == 2 ? GMC_FITB(2, 2) : GMC_FITB(2, 4);
+    return reduction_n == 2 ? GMC_FITB(3, 2) : GMC_FITB(3, 4);
+#undef GMC_FITB
 }
 
 // ---------------------------------------------------------------------------------------------------------------

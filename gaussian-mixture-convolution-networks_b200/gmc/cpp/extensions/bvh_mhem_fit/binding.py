@@ -42,6 +42,26 @@ def forward(mixture: torch.Tensor, n_components_fitting: int, reduction_n: int):
     return fitting, nodes, attribs
 
 
+def backward(grad: torch.Tensor, fitting_mixture: torch.Tensor, target_mixture: torch.Tensor, bvh_nodes: torch.Tensor,
+             bvh_attribs: torch.Tensor, n_components_fitting: int, reduction_n: int) -> torch.Tensor:
+    """Gradient w.r.t. the target mixture. The saved forward tensors are left untouched."""
+    n_batch, n_layers, n_components, n_dims = _dims(target_mixture)
+    _native.require_cuda_f32(grad, "grad")
+    _native.require_cuda_f32(target_mixture, "target_mixture")
+    if tuple(grad.shape) != (n_batch, n_layers, n_components_fitting, target_mixture.shape[-1]):
+        raise RuntimeError("grad has the wrong shape")
+    n_mix = n_batch * n_layers
+    grad_target = torch.empty_like(target_mixture)
+    scratch = torch.empty((n_mix, (n_components - 1) * reduction_n * target_mixture.shape[-1]), dtype=torch.float32,
+                          device=target_mixture.device)
+    with torch.cuda.device_of(target_mixture):
+        _native.check(_native.lib.gmc_mhem_fit_backward(
+            _native.ptr(grad), _native.ptr(target_mixture), n_mix, n_components, n_dims, n_components_fitting,
+            reduction_n, _native.ptr(bvh_nodes), _native.ptr(bvh_attribs), _native.ptr(scratch),
+            _native.ptr(grad_target), _native.stream_of(target_mixture)), "bvh_mhem_fit backward")
+    return grad_target
+
+
 class BvhMhemFit(torch.autograd.Function):
     @staticmethod
     def forward(ctx, target_mixture: torch.Tensor, n_components_fitting: int, reduction_n: int):
@@ -55,7 +75,14 @@ class BvhMhemFit(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_output):
-        raise NotImplementedError("bvh_mhem_fit backward is not part of this build yet")
+        fitting_mixture, target_mixture, bvh_nodes, bvh_attribs = ctx.saved_tensors
+        grad_target = backward(grad_output.contiguous(), fitting_mixture, target_mixture, bvh_nodes, bvh_attribs,
+                               ctx.n_components_fitting, ctx.reduction_n)
+        if torch.any(torch.isnan(grad_target)):
+            raise RuntimeError("bvh_mhem_fit backward produced NaNs "
+                               f"(target has NaNs: {torch.any(torch.isnan(target_mixture)).item()}, "
+                               f"grad_output has NaNs: {torch.any(torch.isnan(grad_output)).item()})")
+        return grad_target, None, None
 
 
 apply = BvhMhemFit.apply

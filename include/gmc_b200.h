@@ -127,6 +127,18 @@ int gmc_mhem_fit_forward(const float* mixture, long long n_mixtures, int n_compo
                          int n_components_fitting, int reduction_n, float* fitting, int16_t* bvh_nodes,
                          float* bvh_attributes, uint64_t* scratch_keys, void* stream);
 
+/* Gradient of gmc_mhem_fit_forward with the tree, the node selection, the initial representatives and the KL gate
+ * held fixed. grad is [n_mixtures, K, V]; mixture, bvh_nodes and bvh_attributes are the forward's input / outputs (not
+ * modified); scratch_node_grad is [n_mixtures, (n_components-1) * reduction_n * V] floats of scratch;
+ * grad_mixture [n_mixtures, n_components, V] is fully overwritten.
+ *
+ * Replaces bvh_mhem_fit_backward (src/gmc/cpp/extensions/bvh_mhem_fit/bindings.cpp:24-40,
+ * implementation_backward.h:41-594). Unlike the reference, the saved attributes are not overwritten, so the same
+ * forward result can be differentiated more than once. */
+int gmc_mhem_fit_backward(const float* grad, const float* mixture, long long n_mixtures, int n_components, int n_dims,
+                          int n_components_fitting, int reduction_n, const int16_t* bvh_nodes,
+                          const float* bvh_attributes, float* scratch_node_grad, float* grad_mixture, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Exact convolution of mixtures: data [n_batch, n_channels_in, n_components, V] (*) kernels
  * [n_channels_out, n_channels_in, n_kernel_components, V] -> out [n_batch, n_channels_out, T, V] with

@@ -73,3 +73,130 @@ def convolution_fitting_backward(grad: np.ndarray, data: np.ndarray, kernels: np
     out = convolution_fitting_given_tree(d, k, nodesobjs, subtrees)
     (out * torch.from_numpy(np.asarray(grad, dtype=np.float64))).sum().backward()
     return d.grad.numpy(), k.grad.numpy(), out.detach().numpy()
+
+
+# ---------------------------------------------------------------------------------------------
+# BVH-MHEM fit
+# ---------------------------------------------------------------------------------------------
+_EPS_SMALL = 0.0000000000001
+_EPS_LARGE = 0.0000001
+_KL_THRESHOLD = 0.5
+
+
+def _clip(v: torch.Tensor) -> torch.Tensor:
+    """max(v, small) with the reference's gradient rule: the gradient passes only where v > small (util/epsilon.h:13-14)."""
+    return torch.where(v > _EPS_SMALL, v, torch.full_like(v, _EPS_SMALL))
+
+
+def _fit_em(target: torch.Tensor, initial_idx, R: int) -> torch.Tensor:
+    """One hierarchical-EM step (implementation_forward.h:188-323) on `target` [n, V] (R < n <= 2R) with the initial
+    representatives given; returns [R, V]. The KL gate is evaluated without gradient (it is a 0/1 matrix)."""
+    n, RF = target.shape
+    D = {7: 2, 13: 3}[RF]
+    NT = 2 * R
+    dt = target.dtype
+    pad = torch.zeros(NT - n, RF, dtype=dt)
+    pad[:, 1 + D:] = torch.eye(D, dtype=dt).reshape(-1)
+    tgt = torch.cat((target, pad), 0)
+    w, mu, cov = tgt[:, 0], tgt[:, 1:1 + D], tgt[:, 1 + D:].view(NT, D, D)
+    Wc = _clip(w.sum())
+    a = w / Wc
+    idx = torch.as_tensor([int(i) for i in initial_idx], dtype=torch.int64)
+    v = w[idx]
+    b = v / _clip(v.sum())
+    mu_i, cov_i = mu[idx], cov[idx]
+    inv_i = torch.linalg.inv(cov_i)                                            # [R, D, D]
+    diff = mu[:, None, :] - mu_i[None, :, :]                                   # [NT, R, D]
+    maha = torch.einsum("tsi,sij,tsj->ts", diff, inv_i, diff)
+    tr = torch.einsum("sij,tji->ts", inv_i, cov)
+    factor = (2 * math.pi) ** (-0.5 * D)
+    val_a = torch.sqrt(torch.linalg.det(inv_i))[None, :] * factor * torch.exp(-0.5 * maha)
+    val_b = torch.exp(-0.5 * tr)
+    lik = torch.pow(_clip(val_a * val_b), 4.0 * a[:, None])
+    with torch.no_grad():
+        lg = torch.log(torch.linalg.det(cov)[:, None] / torch.linalg.det(cov_i)[None, :])
+        kl = 0.5 * (maha + tr - D - lg)
+        same_sign = (a[:, None] >= 0) == (b[None, :] >= 0)
+        kl = torch.where(same_sign, kl, torch.zeros_like(kl))
+        gate = (kl < _KL_THRESHOLD).to(dt)
+        gate[torch.arange(NT), kl.argmin(dim=1)] = 1.0
+    x = _clip(b[None, :] * lik) * gate
+    r1 = x / x.sum(1, keepdim=True)
+    r2 = r1 * a[:, None]
+    fw = r2.sum(0)
+    r3 = r2 / _clip(fw)[None, :]
+    pos = torch.einsum("ts,ti->si", r3, mu)
+    d = mu[:, None, :] - pos[None, :, :]
+    q = d[:, :, :, None] * d[:, :, None, :] + cov[:, None, :, :]
+    c = torch.einsum("ts,tsij->sij", r3, q)
+    degenerate = (fw < _EPS_LARGE)[:, None, None]
+    c = torch.where(degenerate, torch.eye(D, dtype=dt).expand(R, D, D), c)
+    return torch.cat(((fw * Wc)[:, None], pos, c.reshape(R, D * D)), 1)
+
+
+def mhem_fit_given_decisions(mixture: torch.Tensor, nodes: np.ndarray, counts: np.ndarray, integrals: np.ndarray,
+                             initial: np.ndarray, K: int, R: int) -> torch.Tensor:
+    """Forward of the BVH-MHEM fit for ONE mixture [G, V] with the tree, the per-node Gaussian counts / integrals (for
+    the selection) and the initial indices taken from the forward oracle; differentiable in `mixture`."""
+    G, RF = mixture.shape
+    D = {7: 2, 13: 3}[RF]
+    n_internal = G - 1
+    nodes = nodes.astype(np.int64)
+    attr = {}
+
+    def gaussians_of(node):
+        if node >= n_internal:
+            return mixture[nodes[node, 3]][None, :]
+        return attr[node]
+
+    # post-order over internal nodes
+    order, stack = [], [0]
+    while stack:
+        node = stack.pop()
+        if node >= n_internal:
+            continue
+        order.append(node)
+        stack.extend((int(nodes[node, 1]), int(nodes[node, 2])))
+    for node in reversed(order):
+        child = torch.cat((gaussians_of(int(nodes[node, 1])), gaussians_of(int(nodes[node, 2]))), 0)
+        keep = (child[:, 0].detach().abs() >= _EPS_LARGE).nonzero()[:, 0]
+        child = child[keep]
+        assert min(R, child.shape[0]) == counts[node], "count mismatch with the forward oracle"
+        attr[node] = _fit_em(child, initial[node], R) if child.shape[0] > R else child
+
+    def rating(node):
+        return -2.0 if counts[node] < R else abs(float(integrals[node]))
+
+    selected, ratings = [0], [rating(0)]
+    n_selected = int(counts[0])
+    while n_selected < K - R:
+        best, best_rating = -1, -1.0
+        for i, r in enumerate(ratings):
+            if r > best_rating:
+                best, best_rating = i, r
+        if best < 0:
+            break
+        node = selected[best]
+        l, r = int(nodes[node, 1]), int(nodes[node, 2])
+        selected[best], ratings[best] = l, rating(l)
+        selected.append(r)
+        ratings.append(rating(r))
+        n_selected = n_selected - R + int(counts[l]) + int(counts[r])
+    rows = [gaussians_of(node) for node in selected]
+    out = torch.cat(rows, 0)
+    pad = torch.zeros(K - out.shape[0], RF, dtype=mixture.dtype)
+    pad[:, 1 + D:] = torch.eye(D, dtype=mixture.dtype).reshape(-1)
+    return torch.cat((out, pad), 0)
+
+
+def mhem_fit_backward(grad: np.ndarray, mixtures: np.ndarray, dump: dict, K: int, R: int):
+    """fp64 gradient of sum(fit(mixture) * grad) for mixtures [n, G, V]; also returns the fp64 forward."""
+    n = mixtures.shape[0]
+    grads, outs = [], []
+    for i in range(n):
+        m = torch.from_numpy(np.asarray(mixtures[i], dtype=np.float64)).requires_grad_(True)
+        out = mhem_fit_given_decisions(m, dump["nodes"][i], dump["counts"][i], dump["integrals"][i], dump["initial"][i], K, R)
+        (out * torch.from_numpy(np.asarray(grad[i], dtype=np.float64))).sum().backward()
+        grads.append(m.grad.numpy())
+        outs.append(out.detach().numpy())
+    return np.stack(grads), np.stack(outs)
