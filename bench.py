@@ -43,6 +43,9 @@ def _args():
     ap.add_argument("--batch", type=int, default=B_PER_GPU,
                     help="batch per GPU (default: the configuration's 32; smaller values are for profiler captures)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiler captures)")
+    ap.add_argument("--config", type=int, default=1, choices=[1, 2, 3, 4],
+                    help="1 (default, the headline): 3D evaluation fwd+bwd; 2: 2D ReLU fit with BVH-MHEM reduction; "
+                         "3: 2D convolution fitting layer; 4: 3D GMCN forward")
     return ap.parse_args()
 
 
@@ -288,6 +291,197 @@ def run_ours(args, rank, world, local_rank):
     print(json.dumps(line), flush=True)
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# secondary configurations (2: ReLU fit + BVH-MHEM, 3: convolution fitting, 4: GMCN-3D forward)
+# ---------------------------------------------------------------------------------------------------------------
+def _gmcn3d(torch, model, fitting_method=None):
+    """Network of configuration 4: conv 1->8 fit 64, 8->16 fit 32, 16->32 fit 16, 32->64 fit 8 (5-component kernels),
+    integrate, linear layer to 10 logits; random initialisation, evaluation mode."""
+    cfg = model.Config(n_dims=3)
+    cfg.layers = [model.Layer(8, 1, 64, 64), model.Layer(16, 1, 32, 32), model.Layer(32, 1, 16, 16), model.Layer(64, 1, 8, 8)]
+    if fitting_method is not None:
+        cfg.relu_config.fitting_method = fitting_method
+    torch.manual_seed(4)
+    net = model.Net(config=cfg).eval()
+    head = torch.nn.Linear(64, 10)
+    return net, head
+
+
+def _secondary_setup(args, rank, dev):
+    """-> (metric, unit, units per step and rank, step(), host_inputs, workload text, algorithmic bytes, cpu_baseline())"""
+    import torch
+    from gmc import synthetic
+    import gmc.fitting as fitting
+    if args.config == 2:
+        n_batch = args.batch if args.batch != B_PER_GPU else 32
+        m_h, c_h = synthetic.config2(n_batch=n_batch, seed=1002 + rank)
+        m, c = m_h.to(dev), c_h.to(dev)
+        cfg = fitting.Config(n_reduction=4)
+        units = n_batch * 32 * 1024
+
+        def step(inputs=None):
+            mm, cc = (m, c) if inputs is None else inputs
+            with torch.no_grad():
+                return fitting.fixed_point_and_tree_hem(mm, cc, 64, cfg)[0]
+
+        def cpu():
+            from oracle import cpu_oracle
+            sample, _ = synthetic.config2(n_batch=2)
+            flat = sample.numpy().reshape(-1, 1024, 7).copy()
+            flat[..., 0] = abs(flat[..., 0]) + 0.01
+            t0 = time.perf_counter()
+            cpu_oracle.mhem_fit_forward(flat, 64, 4)
+            dt = time.perf_counter() - t0
+            return {"value": flat.shape[0] * 1024 / dt, "unit": "gaussians/s", "cores": cpu_oracle.num_threads(), "kind": "port",
+                    "sample": f"LBVH + BVH-MHEM fit of {flat.shape[0]} mixtures x 1024 Gaussians ({dt:.2f} s); the "
+                              "fixed-point evaluations are not included in the CPU figure"}
+        # LBVH 56 B/Gaussian + MHEM per mixture 28672 + 2*128*(2G-1) + 1792 B (node attributes written and read once)
+        alg_bytes = units * 56 + n_batch * 32 * (28672 + 2 * 128 * 2047 + 1792)
+        return ("gaussians_per_s_relu_fit_bvh_mhem_2d", "gaussians/s", units, step, (m_h, c_h),
+                f"config2: fixed_point_and_tree_hem, B={n_batch}/GPU L=32 G=1024 -> K=64, R=4", alg_bytes, cpu)
+    if args.config == 3:
+        import gmc.cpp.extensions.convolution_fitting.binding as cf
+        n_batch = args.batch if args.batch != B_PER_GPU else 64
+        d_h, k_h, K = synthetic.config3(n_batch=n_batch, seed=1003 + rank)
+        d, k = d_h.to(dev), k_h.to(dev)
+        units = n_batch * 16 * 5120
+
+        def step(inputs=None):
+            dd, kk = (d, k) if inputs is None else inputs
+            return cf.forward(dd, kk, K)[0]
+
+        def cpu():
+            from oracle import cpu_oracle
+            sd, sk, _ = synthetic.config3(n_batch=8)
+            t0 = time.perf_counter()
+            cpu_oracle.convolution_fitting_forward(sd.numpy(), sk.numpy(), K)
+            dt = time.perf_counter() - t0
+            return {"value": 8 * 16 * 5120 / dt, "unit": "product-gaussians/s", "cores": cpu_oracle.num_threads(),
+                    "kind": "port", "sample": f"batch slice B=8 of the same layer (128 trees x 5120 products, {dt:.2f} s)"}
+        alg_bytes = (d_h.numel() + k_h.numel()) * 4 + n_batch * 16 * (5120 * 4 + 2 * K * 4 + K * 7 * 4 + K * 4 * 4)
+        return ("product_gaussians_per_s_convolution_fitting_2d", "product-gaussians/s", units, step, (d_h, k_h),
+                f"config3: convolution_fitting forward, B={n_batch}/GPU Cin=8 G=128 Cout=16 Gk=5 -> K=128 (T=5120)",
+                alg_bytes, cpu)
+    import gmc.model as model
+    n_batch = args.batch if args.batch != B_PER_GPU else 256
+    x_h = synthetic.config4_input(n_batch=n_batch, seed=1004 + rank)
+    x = x_h.to(dev)
+    net, head = _gmcn3d(torch, model)
+    net, head = net.to(dev), head.to(dev)
+
+    def step(inputs=None):
+        xx = x if inputs is None else inputs[0]
+        with torch.no_grad():
+            return head(net.features(xx))
+
+    def cpu():
+        from oracle import cpu_oracle
+        # dominant stage on the CPU: the four convolution-fitting layers on a batch slice (random data of the layer shapes)
+        g = torch.Generator().manual_seed(1)
+        total, dt = 0, 0.0
+        for (cin, gcomp, cout, kfit) in ((1, 64, 8, 64), (8, 64, 16, 32), (16, 32, 32, 16), (32, 16, 64, 8)):
+            cov, _ = synthetic.covariances_and_inverses((4, cin, gcomp), 3, 0.03, 0.15, g)
+            data = synthetic.pack(torch.rand(4, cin, gcomp, generator=g), torch.rand(4, cin, gcomp, 3, generator=g) * 2 - 1, cov)
+            kcov, _ = synthetic.covariances_and_inverses((cout, cin, 5), 3, 0.1, 0.4, g)
+            kern = synthetic.pack(torch.randn(cout, cin, 5, generator=g) + 0.1, torch.randn(cout, cin, 5, 3, generator=g), kcov)
+            t0 = time.perf_counter()
+            cpu_oracle.convolution_fitting_forward(data.numpy(), kern.numpy(), kfit)
+            dt += time.perf_counter() - t0
+        return {"value": 4 / dt, "unit": "samples/s", "cores": cpu_oracle.num_threads(), "kind": "port",
+                "sample": f"the four convolution-fitting layers only (the dominant stage) on 4 samples ({dt:.2f} s); "
+                          "ReLU fixed-point evaluations and normalisations are not included"}
+    keys = n_batch * (8 * 320 + (16 + 32 + 64) * 2560)
+    return ("samples_per_s_gmcn3d_forward", "samples/s", n_batch, step, (x_h,),
+            f"config4: GMCN-3D forward, B={n_batch}/GPU, 64 input Gaussians, conv-fit layers 1->8->16->32->64 "
+            f"(K=64/32/16/8, ReLU fit fixed_point_only), integrate, linear to 10 logits",
+            keys * 4 + n_batch * 64 * 13 * 4, cpu)
+
+
+def run_secondary(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    from gmc import sharding
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    metric, unit, units, step, host_inputs, workload, alg_bytes, cpu = _secondary_setup(args, rank, dev)
+    host_inputs = tuple(t.pin_memory() for t in host_inputs)
+    gather = sharding.OutputGatherer(world, dev) if world > 1 else None
+
+    def full_step():
+        out = step()
+        if gather is not None:
+            gather.start(out)
+            gather.finish()
+        return out
+
+    for _ in range(max(args.warmup, 3)):
+        full_step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    e0.record()
+    for _ in range(args.steps):
+        full_step()
+    e1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1) / args.steps
+
+    e2e_steps = max(3, min(args.steps, 20))
+    out_h = None
+
+    def e2e_step():
+        nonlocal out_h
+        dev_in = tuple(t.to(dev, non_blocking=True) for t in host_inputs)
+        out = step(dev_in)
+        if out_h is None:
+            out_h = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+        out_h.copy_(out, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+    t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = t.tolist()
+    if rank != 0:
+        return
+    peaks, peaks_kind = _measured_peaks()
+    hbm = float(peaks["hbm_gbs"])
+    achieved = alg_bytes / (ms * 1e-3) / 1e9
+    line = {"metric": metric, "value": world * units / (ms * 1e-3), "unit": unit, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": workload, "l2": "working set of a step is smaller than L2 for some stages; not flushed",
+                       "sharding": f"batch over {world} rank(s)" + (", all-gather of outputs" if world > 1 else "")},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
+                         "traffic": None, "algorithmic_bytes_per_step": alg_bytes,
+                         "note": f"whole step against {peaks_kind} copy bandwidth; the stages are latency bound at these "
+                                 "sizes, see profiles/"},
+            "e2e": {"value": world * units / (e2e_ms * 1e-3), "unit": unit,
+                    "h2d_bytes_per_step": sum(t.numel() * 4 for t in host_inputs),
+                    "d2h_bytes_per_step": out_h.numel() * 4, "ms_per_step": e2e_ms, "steps": e2e_steps},
+            "gpu_launches": None, "clocks": clocks}
+    if not args.no_cpu_baseline and world == 1:
+        line["cpu_baseline"] = cpu()
+    print(json.dumps(line), flush=True)
+
+
 def main():
     args = _args()
     rank = int(os.environ.get("RANK", "0"))
@@ -303,7 +497,10 @@ def main():
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
-        run_ours(args, rank, world, local_rank)
+        if args.config == 1:
+            run_ours(args, rank, world, local_rank)
+        else:
+            run_secondary(args, rank, world, local_rank)
     finally:
         if world > 1:
             import torch.distributed as dist

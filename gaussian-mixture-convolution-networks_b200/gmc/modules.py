@@ -181,7 +181,6 @@ class CovScaleNorm(torch.nn.modules.Module):
         else:
             avg_trace = traces.mean(dim=2)
         factor = torch.sqrt(gm.n_dimensions(x_gm) / avg_trace).view(n_batch, gm.n_layers(x_gm), 1)
-        assert not torch.any(torch.isnan(factor)) and not torch.any(torch.isinf(factor))
         y_gm = gm.spatial_scale(x_gm, factor)
         if x_constant is None:
             x_constant = torch.zeros(n_batch, gm.n_layers(x_gm), device=x_gm.device)
@@ -226,5 +225,4 @@ class BatchNorm(torch.nn.modules.Module):
         if self.learnable_scaling is not None:
             factor = factor * self.learnable_scaling
         factor = factor.view(-1, n_channels, 1)
-        assert not torch.any(torch.isnan(factor)) and not torch.any(torch.isinf(factor))
         return gm.pack_mixture(gm.weights(x_gm) * factor, gm.positions(x_gm), gm.covariances(x_gm)), x_constant - mean
