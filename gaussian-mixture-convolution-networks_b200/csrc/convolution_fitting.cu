@@ -5,8 +5,10 @@
 // shared memory:
 //   keys        (w_d w_k > 0) << 62 | 30-bit Morton code of mu_d + mu_k in the tree's bounding box << 32 | product index
 //   sort        ascending (bitonic, in shared memory)
-//   tree        Karras nodes over (key high word + sorted position); leaves = sorted products
-//   mass        per node, children summed in tree order (levels above the leaves processed in order)
+//   tree+mass   the binary radix tree over (key high word + sorted position) -- the same hierarchy as the reference's
+//               Karras construction -- is built bottom-up: every leaf climbs, the second child to arrive at a node
+//               completes it (range, children, mass = mass(left) + mass(right)) and climbs on, so construction and
+//               the mass pass are one sweep without binary searches
 //   selection   K - 1 greedy splits of the selected internal node with the largest |mass|
 //   aggregation per selected subtree the weighted mean / scatter of the product centres and the weighted mean of
 //               the product covariances; one warp per output Gaussian, lanes hold partial aggregates that are
@@ -18,7 +20,10 @@
 namespace gmc {
 namespace {
 
-constexpr int kThreads = 256;
+#ifndef GMC_CONVFIT_THREADS
+#define GMC_CONVFIT_THREADS 512
+#endif
+constexpr int kThreads = GMC_CONVFIT_THREADS;
 constexpr int kWarps = kThreads / 32;
 constexpr int kMaxProducts = 8192;
 constexpr int kMaxLevels = 72;
@@ -98,20 +103,21 @@ convolution_fitting_forward_kernel(const float* __restrict__ data, const float* 
     extern __shared__ __align__(16) unsigned char smem_bytes[];
     const int Cin = n.n_channels_in, G = n.n_components, Gk = n.n_kernel_components, K = n.n_fitting;
     const int T = Cin * G * Gk;
-    const int n_internal = T - 1, n_nodes = 2 * T - 1;
+    const int n_internal = T - 1;
     const int P = lbvh::next_pow2(T);
     // shared layout
-    uint64_t* keys = reinterpret_cast<uint64_t*>(smem_bytes);                 // P keys; later reused as mass[n_nodes]
+    uint64_t* keys = reinterpret_cast<uint64_t*>(smem_bytes);                 // P keys; later reused as mass[2T - 1]
     float* mass = reinterpret_cast<float*>(smem_bytes);
-    uint16_t* parent = reinterpret_cast<uint16_t*>(smem_bytes + size_t(P) * 8);   // n_nodes
-    uint16_t* left = parent + ((n_nodes + 7) & ~7);                               // n_internal
-    uint16_t* right = left + ((n_internal + 7) & ~7);                             // n_internal
-    unsigned char* level = reinterpret_cast<unsigned char*>(right + ((n_internal + 7) & ~7));   // n_nodes
-    unsigned* arrive_bits = reinterpret_cast<unsigned*>(level + ((n_nodes + 15) & ~15));        // ceil(n_internal / 32)
-    int* sel_node = reinterpret_cast<int*>(arrive_bits + ((n_internal + 31) / 32 + 3 & ~3));     // K
-    float* sel_rating = reinterpret_cast<float*>(sel_node + K);                                  // K
+    uint16_t* left = reinterpret_cast<uint16_t*>(smem_bytes + size_t(P) * 8);     // n_internal each:
+    uint16_t* right = left + ((n_internal + 7) & ~7);
+    uint16_t* first = right + ((n_internal + 7) & ~7);                            // leaf range [first, last] of a node
+    uint16_t* last = first + ((n_internal + 7) & ~7);
+    unsigned char* cpl = reinterpret_cast<unsigned char*>(last + ((n_internal + 7) & ~7));   // common prefix of leaf i, i+1
+    unsigned* arrive_bits = reinterpret_cast<unsigned*>(cpl + ((n_internal + 15) & ~15));    // ceil(n_internal / 32)
+    int* sel_node = reinterpret_cast<int*>(arrive_bits + ((n_internal + 31) / 32 + 3 & ~3));  // K
+    unsigned* sel_rating = reinterpret_cast<unsigned*>(sel_node + K);                          // K
     __shared__ float s_hi[kWarps][D], s_lo[kWarps][D], box_hi[D], box_lo[D];
-    __shared__ int s_max_level, s_n_selected;
+    __shared__ int s_root, s_n_selected;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int b = blockIdx.x / n.n_channels_out, o = blockIdx.x - b * n.n_channels_out;
@@ -193,73 +199,58 @@ convolution_fitting_forward_kernel(const float* __restrict__ data, const float* 
     __syncthreads();
     lbvh::bitonic_sort_shared(keys, P);
 
-    // ---- leaves, internal nodes ----
+    // ---- leaves; common prefix lengths of neighbouring codes ----
     for (int j = tid; j < T; j += kThreads) nodesobjs[j] = int(uint32_t(keys[j]));
-    for (int i = tid; i < n_nodes; i += kThreads) level[i] = 0;
     for (int i = tid; i < (n_internal + 31) / 32; i += kThreads) arrive_bits[i] = 0u;
-    if (tid == 0) { parent[0] = 0xFFFFu; s_max_level = 0; }
     {
         const lbvh::PositionTieBreakCode code{keys};
-        for (int i = tid; i < n_internal; i += kThreads) {
-            const int2 r = lbvh::determine_range(code, T, i);
-            const int gamma = lbvh::find_split(code, r.x, r.y);
-            int l = gamma, rr = gamma + 1;
-            if (min(r.x, r.y) == gamma) l += T - 1;
-            if (max(r.x, r.y) == gamma + 1) rr += T - 1;
-            left[i] = uint16_t(l);
-            right[i] = uint16_t(rr);
-            parent[l] = uint16_t(i);
-            parent[rr] = uint16_t(i);
-        }
+        for (int i = tid; i < n_internal; i += kThreads) cpl[i] = (unsigned char)lbvh::common_upper_bits(code(i), code(i + 1));
     }
     __syncthreads();   // keys are dead from here on: their memory becomes mass[]
 
-    // ---- leaf masses; levels by the second-arriver climb ----
-    for (int j = tid; j < T; j += kThreads) {
-        int gi, ci, ki;
-        product_parts(nodesobjs[j], gi, ci, ki);
-        mass[n_internal + j] = __fmul_rn(__ldg(data_b + (size_t(ci) * G + gi) * RF), __ldg(kernels_o + (size_t(ci) * Gk + ki) * RF));
-    }
+    // ---- bottom-up construction with the mass pass folded in ----
+    // Internal node p is the split between leaves p and p + 1. A node with leaf range [l, r] hangs below node r (as its
+    // left child) if the codes differ less across r | r+1 than across l-1 | l, else below node l - 1 (as right child).
     for (int leaf = tid; leaf < T; leaf += kThreads) {
-        int node = parent[n_internal + leaf];
-        for (int guard = 0; guard < kMaxLevels && node != 0xFFFF; ++guard) {
+        int gi, ci, ki;
+        product_parts(nodesobjs[leaf], gi, ci, ki);
+        const float w = __fmul_rn(__ldg(data_b + (size_t(ci) * G + gi) * RF), __ldg(kernels_o + (size_t(ci) * Gk + ki) * RF));
+        int node = n_internal + leaf, l = leaf, r = leaf;
+        ((volatile float*)mass)[node] = w;
+        for (int guard = 0; guard < kMaxLevels; ++guard) {
+            if (l == 0 && r == T - 1) { s_root = node; break; }
+            const bool up_right = (l == 0) || (r != T - 1 && cpl[r] > cpl[l - 1]);
+            const int p = up_right ? r : l - 1;
+            if (up_right) { ((volatile uint16_t*)left)[p] = uint16_t(node); ((volatile uint16_t*)first)[p] = uint16_t(l); }
+            else { ((volatile uint16_t*)right)[p] = uint16_t(node); ((volatile uint16_t*)last)[p] = uint16_t(r); }
             __threadfence_block();
-            const unsigned bit = 1u << (node & 31);
-            if ((atomicOr(&arrive_bits[node >> 5], bit) & bit) == 0u) break;
+            const unsigned bit = 1u << (p & 31);
+            if ((atomicOr(&arrive_bits[p >> 5], bit) & bit) == 0u) break;   // the sibling will complete this node
             __threadfence_block();
-            const int lv = 1 + max(int(((volatile unsigned char*)level)[left[node]]), int(((volatile unsigned char*)level)[right[node]]));
-            ((volatile unsigned char*)level)[node] = (unsigned char)lv;
-            atomicMax(&s_max_level, lv);
-            node = parent[node];
+            if (up_right) r = ((volatile uint16_t*)last)[p];
+            else l = ((volatile uint16_t*)first)[p];
+            ((volatile float*)mass)[p] = __fadd_rn(((volatile float*)mass)[((volatile uint16_t*)left)[p]],
+                                                   ((volatile float*)mass)[((volatile uint16_t*)right)[p]]);
+            node = p;
         }
     }
     __syncthreads();
-    const int max_level = s_max_level;
-    for (int lv = 1; lv <= max_level; ++lv) {
-        for (int i = tid; i < n_internal; i += kThreads)
-            if (level[i] == lv) mass[i] = __fadd_rn(mass[left[i]], mass[right[i]]);
-        __syncthreads();
-    }
 
     // ---- greedy selection of K subtree roots (warp 0) ----
+    // rating as an order-preserving integer: internal node -> bits(|mass|) + 1, leaf -> 0 (never selected)
     if (warp == 0) {
-        auto rating_of = [&](int id) -> float { return id >= n_internal ? -2.f : fabsf(mass[id]); };
-        if (lane == 0) { sel_node[0] = 0; sel_rating[0] = rating_of(0); }
+        auto rating_of = [&](int id) -> unsigned { return id >= n_internal ? 0u : __float_as_uint(fabsf(mass[id])) + 1u; };
+        if (lane == 0) { sel_node[0] = s_root; sel_rating[0] = rating_of(s_root); }
         __syncwarp();
         int n_sel = 1;
         while (n_sel < K) {
-            float best_rating = -1.f;
+            unsigned best_rating = 0u;
             int best = 0x7fffffff;
             for (int i = lane; i < n_sel; i += 32)
                 if (sel_rating[i] > best_rating) { best_rating = sel_rating[i]; best = i; }
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) {
-                const float orat = __shfl_xor_sync(0xffffffffu, best_rating, off);
-                const int oidx = __shfl_xor_sync(0xffffffffu, best, off);
-                if (orat > best_rating || (orat == best_rating && oidx < best)) { best_rating = orat; best = oidx; }
-            }
-            if (best == 0x7fffffff) break;
-            __syncwarp();
+            const unsigned top = __reduce_max_sync(0xffffffffu, best_rating);
+            if (top == 0u) break;                                        // only leaves left
+            best = __reduce_min_sync(0xffffffffu, best_rating == top ? best : 0x7fffffff);   // first of the maxima
             if (lane == 0) {
                 const int id = sel_node[best];
                 const int l = left[id], r = right[id];
@@ -269,20 +260,21 @@ convolution_fitting_forward_kernel(const float* __restrict__ data, const float* 
             ++n_sel;
             __syncwarp();
         }
-        // leaf ranges [start, end) of the selected roots: leftmost / rightmost descent
+        // leaf ranges [start, end) of the selected roots
         for (int k = lane; k < K; k += 32) {
             int start = -1, end = -1;
             if (k < n_sel) {
-                int s = sel_node[k];
-                while (s < n_internal) s = left[s];
-                int e = sel_node[k];
-                while (e < n_internal) e = right[e];
-                start = s; end = e + 1;
+                const int id = sel_node[k];
+                start = id >= n_internal ? id : n_internal + first[id];
+                end = id >= n_internal ? id + 1 : n_internal + last[id] + 1;
             }
             subtrees[2 * k] = start;
             subtrees[2 * k + 1] = end;
-            sel_node[k] = start;
-            sel_rating[k] = __int_as_float(end);
+        }
+        __syncwarp();
+        for (int k = lane; k < K; k += 32) {
+            sel_node[k] = subtrees[2 * k];
+            sel_rating[k] = unsigned(subtrees[2 * k + 1]);
         }
         if (lane == 0) s_n_selected = n_sel;
     }
@@ -292,7 +284,7 @@ convolution_fitting_forward_kernel(const float* __restrict__ data, const float* 
     float* out = fitting + size_t(blockIdx.x) * K * RF;
     float* cached = cached_pos_covs + size_t(blockIdx.x) * K * D * D;
     for (int k = warp; k < K; k += kWarps) {
-        const int start = sel_node[k], end = __float_as_int(sel_rating[k]);
+        const int start = sel_node[k], end = int(sel_rating[k]);
         float* o_k = out + size_t(k) * RF;
         float* c_k = cached + size_t(k) * D * D;
         if (start < 0) {
@@ -528,12 +520,11 @@ convolution_fitting_backward_kernel(const float* __restrict__ grad, const float*
 }
 
 size_t convfit_smem_bytes(int T, int K) {
-    const int n_internal = T - 1, n_nodes = 2 * T - 1;
+    const int n_internal = T - 1;
     const int P = lbvh::next_pow2(T);
     size_t bytes = size_t(P) * 8;
-    bytes += 2 * size_t((n_nodes + 7) & ~7);
-    bytes += 2 * 2 * size_t((n_internal + 7) & ~7);
-    bytes += size_t((n_nodes + 15) & ~15);
+    bytes += 4 * 2 * size_t((n_internal + 7) & ~7);
+    bytes += size_t((n_internal + 15) & ~15);
     bytes += 4 * size_t(((n_internal + 31) / 32 + 3) & ~3);
     bytes += 8 * size_t(K);
     return bytes;
