@@ -104,18 +104,20 @@ convolution_fitting_forward_kernel(const float* __restrict__ data, const float* 
     const int Cin = n.n_channels_in, G = n.n_components, Gk = n.n_kernel_components, K = n.n_fitting;
     const int T = Cin * G * Gk;
     const int n_internal = T - 1;
-    const int P = lbvh::next_pow2(T);
-    // shared layout
-    uint64_t* keys = reinterpret_cast<uint64_t*>(smem_bytes);                 // P keys; later reused as mass[2T - 1]
+    // shared layout: [keys A: T x 8][keys B: T x 8][cpl][arrive bits][selection][radix histograms]
+    // after the sort buffer A is reused as mass[2T - 1] and buffer B as the node arrays (4 x (T - 1) x 2 bytes)
+    uint64_t* keys_a = reinterpret_cast<uint64_t*>(smem_bytes);
+    uint64_t* keys_b = keys_a + T;
     float* mass = reinterpret_cast<float*>(smem_bytes);
-    uint16_t* left = reinterpret_cast<uint16_t*>(smem_bytes + size_t(P) * 8);     // n_internal each:
-    uint16_t* right = left + ((n_internal + 7) & ~7);
-    uint16_t* first = right + ((n_internal + 7) & ~7);                            // leaf range [first, last] of a node
-    uint16_t* last = first + ((n_internal + 7) & ~7);
-    unsigned char* cpl = reinterpret_cast<unsigned char*>(last + ((n_internal + 7) & ~7));   // common prefix of leaf i, i+1
+    uint16_t* left = reinterpret_cast<uint16_t*>(keys_b);                         // n_internal each:
+    uint16_t* right = left + n_internal;
+    uint16_t* first = right + n_internal;                                         // leaf range [first, last] of a node
+    uint16_t* last = first + n_internal;
+    unsigned char* cpl = reinterpret_cast<unsigned char*>(keys_b + T);            // common prefix of leaf i, i+1
     unsigned* arrive_bits = reinterpret_cast<unsigned*>(cpl + ((n_internal + 15) & ~15));    // ceil(n_internal / 32)
     int* sel_node = reinterpret_cast<int*>(arrive_bits + ((n_internal + 31) / 32 + 3 & ~3));  // K
     unsigned* sel_rating = reinterpret_cast<unsigned*>(sel_node + K);                          // K
+    unsigned* radix_hist = sel_rating + K;                                                     // (kWarps + 1) * 256
     __shared__ float s_hi[kWarps][D], s_lo[kWarps][D], box_hi[D], box_lo[D];
     __shared__ int s_root, s_n_selected;
 
@@ -180,24 +182,20 @@ convolution_fitting_forward_kernel(const float* __restrict__ data, const float* 
         comp_in = rem - ch_in * G;
     };
 
-    // ---- keys, sort ----
-    for (int t = tid; t < P; t += kThreads) {
-        uint64_t key = ~0ull;
-        if (t < T) {
-            int gi, ci, ki;
-            product_parts(t, gi, ci, ki);
-            const float* dg = data_b + (size_t(ci) * G + gi) * RF;
-            const float* kg = kernels_o + (size_t(ci) * Gk + ki) * RF;
-            uint32_t q[3] = {0u, 0u, 0u};
+    // ---- keys, sort (stable on bits 32..63 = sign | Morton code; equal codes keep ascending product index) ----
+    for (int t = tid; t < T; t += kThreads) {
+        int gi, ci, ki;
+        product_parts(t, gi, ci, ki);
+        const float* dg = data_b + (size_t(ci) * G + gi) * RF;
+        const float* kg = kernels_o + (size_t(ci) * Gk + ki) * RF;
+        uint32_t q[3] = {0u, 0u, 0u};
 #pragma unroll
-            for (int d = 0; d < D; ++d) q[d] = lbvh::quantise(__fadd_rn(__ldg(dg + 1 + d), __ldg(kg + 1 + d)), box_lo[d], box_hi[d]);
-            const uint64_t sign = __fmul_rn(__ldg(dg), __ldg(kg)) > 0.f ? 1ull : 0ull;
-            key = (sign << 62) | (uint64_t(lbvh::morton30(q[0], q[1], q[2])) << 32) | uint64_t(uint32_t(t));
-        }
-        keys[t] = key;
+        for (int d = 0; d < D; ++d) q[d] = lbvh::quantise(__fadd_rn(__ldg(dg + 1 + d), __ldg(kg + 1 + d)), box_lo[d], box_hi[d]);
+        const uint64_t sign = __fmul_rn(__ldg(dg), __ldg(kg)) > 0.f ? 1ull : 0ull;
+        keys_a[t] = (sign << 62) | (uint64_t(lbvh::morton30(q[0], q[1], q[2])) << 32) | uint64_t(uint32_t(t));
     }
     __syncthreads();
-    lbvh::bitonic_sort_shared(keys, P);
+    const uint64_t* keys = lbvh::radix_sort_shared(keys_a, keys_b, T, 32, 4, radix_hist);   // 4 passes: back in A
 
     // ---- leaves; common prefix lengths of neighbouring codes ----
     for (int j = tid; j < T; j += kThreads) nodesobjs[j] = int(uint32_t(keys[j]));
@@ -206,7 +204,7 @@ convolution_fitting_forward_kernel(const float* __restrict__ data, const float* 
         const lbvh::PositionTieBreakCode code{keys};
         for (int i = tid; i < n_internal; i += kThreads) cpl[i] = (unsigned char)lbvh::common_upper_bits(code(i), code(i + 1));
     }
-    __syncthreads();   // keys are dead from here on: their memory becomes mass[]
+    __syncthreads();   // keys are dead from here on: buffer A becomes mass[], buffer B the node arrays
 
     // ---- bottom-up construction with the mass pass folded in ----
     // Internal node p is the split between leaves p and p + 1. A node with leaf range [l, r] hangs below node r (as its
@@ -521,12 +519,11 @@ convolution_fitting_backward_kernel(const float* __restrict__ grad, const float*
 
 size_t convfit_smem_bytes(int T, int K) {
     const int n_internal = T - 1;
-    const int P = lbvh::next_pow2(T);
-    size_t bytes = size_t(P) * 8;
-    bytes += 4 * 2 * size_t((n_internal + 7) & ~7);
+    size_t bytes = 2 * size_t(T) * 8;
     bytes += size_t((n_internal + 15) & ~15);
     bytes += 4 * size_t(((n_internal + 31) / 32 + 3) & ~3);
     bytes += 8 * size_t(K);
+    bytes += 4 * size_t(kWarps + 1) * 256;
     return bytes;
 }
 

@@ -55,6 +55,85 @@ __device__ __forceinline__ void bitonic_sort_shared(uint64_t* keys, int n_pow2) 
     }
 }
 
+// Stable LSD radix sort of n 64-bit keys on the bit range [first_bit, first_bit + 8 * n_passes), CTA-wide, in shared
+// memory. `a` holds the input and `b` is a second buffer of n keys; the sorted keys end up in `a` if n_passes is even
+// and in `b` otherwise (the function returns the pointer). `hist` needs (number of warps) * 256 + 256 unsigned.
+// Every warp owns a contiguous slice of the keys; per pass it counts its digits, the CTA scans the (digit, warp)
+// counts, and the warp scatters its slice in order -- ranks inside one 32-key step come from __match_any_sync, so
+// equal digits keep their input order.
+__device__ __forceinline__ uint64_t* radix_sort_shared(uint64_t* a, uint64_t* b, int n, int first_bit, int n_passes,
+                                                       unsigned* hist) {
+    const int n_warps = blockDim.x >> 5;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int chunk = (((n + n_warps - 1) / n_warps) + 31) & ~31;
+    const int begin = min(n, warp * chunk), end = min(n, begin + chunk);
+    unsigned* my_hist = hist + warp * 256;
+    unsigned* totals = hist + n_warps * 256;
+    const unsigned lt_mask = (1u << lane) - 1u;
+    for (int pass = 0; pass < n_passes; ++pass) {
+        const int shift = first_bit + 8 * pass;
+        for (int i = lane; i < 256; i += 32) my_hist[i] = 0u;
+        __syncwarp();
+        for (int i0 = begin; i0 < end; i0 += 32) {
+            const int i = i0 + lane;
+            const bool active = i < end;
+            const unsigned act = __ballot_sync(0xffffffffu, active);
+            if (active) {
+                const unsigned digit = unsigned(a[i] >> shift) & 0xFFu;
+                const unsigned peers = __match_any_sync(act, digit);
+                if ((peers & lt_mask) == 0u) my_hist[digit] += __popc(peers);
+            }
+            __syncwarp();
+        }
+        __syncthreads();
+        // exclusive scan over (digit major, warp minor)
+        if (threadIdx.x < 256) {
+            unsigned run = 0u;
+            for (int w = 0; w < n_warps; ++w) {
+                const unsigned c = hist[w * 256 + threadIdx.x];
+                hist[w * 256 + threadIdx.x] = run;
+                run += c;
+            }
+            totals[threadIdx.x] = run;
+        }
+        __syncthreads();
+        if (warp == 0) {
+            unsigned v[8], sum = 0u;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { v[k] = totals[lane * 8 + k]; sum += v[k]; }
+            unsigned incl = sum;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const unsigned o = __shfl_up_sync(0xffffffffu, incl, off);
+                if (lane >= off) incl += o;
+            }
+            unsigned run = incl - sum;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { totals[lane * 8 + k] = run; run += v[k]; }
+        }
+        __syncthreads();
+        for (int i0 = begin; i0 < end; i0 += 32) {
+            const int i = i0 + lane;
+            const bool active = i < end;
+            const unsigned act = __ballot_sync(0xffffffffu, active);
+            unsigned digit = 0u, peers = 0u;
+            uint64_t key = 0ull;
+            if (active) {
+                key = a[i];
+                digit = unsigned(key >> shift) & 0xFFu;
+                peers = __match_any_sync(act, digit);
+                b[totals[digit] + my_hist[digit] + __popc(peers & lt_mask)] = key;
+            }
+            __syncwarp();
+            if (active && (peers & lt_mask) == 0u) my_hist[digit] += __popc(peers);
+            __syncwarp();
+        }
+        __syncthreads();
+        uint64_t* t = a; a = b; b = t;
+    }
+    return a;
+}
+
 __device__ __forceinline__ int common_upper_bits(uint64_t a, uint64_t b) { return __clzll(int64_t(a ^ b)); }
 
 // Code functor: plain key (BVH fit) or (key & high 32 bits) + sorted position (convolution fit).
