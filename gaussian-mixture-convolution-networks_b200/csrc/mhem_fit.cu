@@ -23,7 +23,10 @@ int lbvh_build_launch(const float* mixture, long long n_mixtures, int n_componen
 
 namespace {
 
-constexpr int kThreads = 128;
+#ifndef GMC_FIT_THREADS
+#define GMC_FIT_THREADS 256
+#endif
+constexpr int kThreads = GMC_FIT_THREADS;
 constexpr int kWarps = kThreads / 32;
 constexpr int kMaxLevels = 72;
 constexpr float kEpsSmall = 0.0000000000001f;
@@ -107,37 +110,37 @@ __device__ void cluster_and_select(WarpScratch<D, R>& ws, int n_valid) {
         const unsigned char va = ws.heap_a[i], vb = ws.heap_b[i];
         replace_element(vd, va, vb, i, rd, ra, rb);
     }
-    // sub-graphs of Gaussians (valid Gaussians are 0 .. n_valid-1); merging appends the higher sub-graph to the lower,
-    // which keeps the member order that the first-max rule below depends on
-    unsigned char members[NT][NT];
-    int n_members[NT];
-    for (int i = 0; i < NT; ++i) { members[i][0] = (unsigned char)i; n_members[i] = i < n_valid ? 1 : 0; }
+    // Sub-graphs of Gaussians (valid Gaussians are 0 .. n_valid-1, sub-graph i starts as {i}). Merging appends the
+    // higher sub-graph's member list to the lower one's, which keeps the member order that the first-max rule below
+    // depends on. All state is packed into 64-bit words (8 bits per Gaussian), so it lives in registers:
+    //   labels: sub-graph of Gaussian g;  nexts: successor of g in its member list (0xFF = end);  tails: last member.
+    auto get = [](uint64_t v, int i) -> int { return int((v >> (8 * i)) & 0xFFull); };
+    auto set = [](uint64_t& v, int i, int x) { v = (v & ~(0xFFull << (8 * i))) | (uint64_t(x) << (8 * i)); };
+    uint64_t labels = 0ull, tails = 0ull, nexts = ~0ull;
+#pragma unroll
+    for (int i = 0; i < NT; ++i) { labels |= uint64_t(i) << (8 * i); tails |= uint64_t(i) << (8 * i); }
     int n_subgraphs = n_valid;
-    auto subgraph_of = [&](unsigned char id) {
-        for (int i = 0; i < n_valid; ++i)
-            for (int j = 0; j < n_members[i]; ++j)
-                if (members[i][j] == id) return i;
-        return -1;
-    };
     while (n_subgraphs > R) {
         replace_element(INFINITY, 255, 255, 0, rd, ra, rb);
         if (!(rd < INFINITY)) break;
-        const int sa = subgraph_of(ra), sb = subgraph_of(rb);
-        if (sa != sb && sa >= 0 && sb >= 0) {
+        const int sa = get(labels, ra), sb = get(labels, rb);
+        if (sa != sb) {
             const int lo = min(sa, sb), hi = max(sa, sb);
-            for (int j = 0; j < n_members[hi]; ++j) members[lo][n_members[lo]++] = members[hi][j];
-            n_members[hi] = 0;
+#pragma unroll
+            for (int g = 0; g < NT; ++g)
+                if (get(labels, g) == hi) set(labels, g, lo);
+            set(nexts, get(tails, lo), hi);       // the head of sub-graph hi is Gaussian hi
+            set(tails, lo, get(tails, hi));
             --n_subgraphs;
         }
     }
     int sg = -1;
     for (int i = 0; i < R; ++i) {
-        do { ++sg; } while (sg < n_valid && n_members[sg] == 0);
+        do { ++sg; } while (sg < n_valid && get(labels, sg) != sg);   // a sub-graph is alive while its head labels itself
         int selected = 255;
         float max_abs = 0.f;
         if (sg < n_valid) {
-            for (int j = 0; j < n_members[sg]; ++j) {
-                const int gid = members[sg][j];
+            for (int gid = sg; gid != 0xFF; gid = get(nexts, gid)) {
                 const float aw = fabsf(ws.tgt[gid][0]);
                 if (aw > max_abs) { max_abs = aw; selected = gid; }
             }
