@@ -1,8 +1,9 @@
 // Fused convolution + reduction to K Gaussians per (batch, output channel), forward.
 //
 // The T = Cin * G * Gk product Gaussians (w_d w_k, mu_d + mu_k, C_d + C_k) of an output channel are never
-// materialised. One CTA per (batch, output channel) tree keeps everything but the inputs and the saved outputs in
-// shared memory:
+// materialised. Two kernels: the tree kernel (one CTA per (batch, output channel) tree, everything but the inputs
+// and the saved outputs in shared memory) does keys .. selection; the aggregation kernel (one warp per output
+// Gaussian) does the last step:
 //   keys        (w_d w_k > 0) << 62 | 30-bit Morton code of mu_d + mu_k in the tree's bounding box << 32 | product index
 //   sort        ascending (bitonic, in shared memory)
 //   tree+mass   the binary radix tree over (key high word + sorted position) -- the same hierarchy as the reference's
@@ -96,9 +97,8 @@ __device__ __forceinline__ Agg<D> agg_shfl_down(const Agg<D>& a, int offset) {
 
 template <int D>
 __global__ void __launch_bounds__(kThreads)
-convolution_fitting_forward_kernel(const float* __restrict__ data, const float* __restrict__ kernels, Dims n,
-                                   float* __restrict__ fitting, float* __restrict__ cached_pos_covs,
-                                   int* __restrict__ nodesobjs_all, int* __restrict__ subtrees_all) {
+convolution_fitting_tree_kernel(const float* __restrict__ data, const float* __restrict__ kernels, Dims n,
+                                int* __restrict__ nodesobjs_all, int* __restrict__ subtrees_all) {
     constexpr int RF = 1 + D + D * D;
     extern __shared__ __align__(16) unsigned char smem_bytes[];
     const int Cin = n.n_channels_in, G = n.n_components, Gk = n.n_kernel_components, K = n.n_fitting;
@@ -119,7 +119,7 @@ convolution_fitting_forward_kernel(const float* __restrict__ data, const float* 
     unsigned* sel_rating = reinterpret_cast<unsigned*>(sel_node + K);                          // K
     unsigned* radix_hist = sel_rating + K;                                                     // (kWarps + 1) * 256
     __shared__ float s_hi[kWarps][D], s_lo[kWarps][D], box_hi[D], box_lo[D];
-    __shared__ int s_root, s_n_selected;
+    __shared__ int s_root;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int b = blockIdx.x / n.n_channels_out, o = blockIdx.x - b * n.n_channels_out;
@@ -269,68 +269,82 @@ convolution_fitting_forward_kernel(const float* __restrict__ data, const float* 
             subtrees[2 * k] = start;
             subtrees[2 * k + 1] = end;
         }
-        __syncwarp();
-        for (int k = lane; k < K; k += 32) {
-            sel_node[k] = subtrees[2 * k];
-            sel_rating[k] = unsigned(subtrees[2 * k + 1]);
-        }
-        if (lane == 0) s_n_selected = n_sel;
     }
-    __syncthreads();
+}
 
-    // ---- aggregation: one warp per output Gaussian ----
-    float* out = fitting + size_t(blockIdx.x) * K * RF;
-    float* cached = cached_pos_covs + size_t(blockIdx.x) * K * D * D;
-    for (int k = warp; k < K; k += kWarps) {
-        const int start = sel_node[k], end = int(sel_rating[k]);
-        float* o_k = out + size_t(k) * RF;
-        float* c_k = cached + size_t(k) * D * D;
-        if (start < 0) {
-            for (int f = lane; f < RF; f += 32) {
-                float v = 0.f;
-                if (f > D && ((f - 1 - D) / D == (f - 1 - D) % D)) v = 1.f;
-                o_k[f] = v;
-            }
-            for (int e = lane; e < D * D; e += 32) c_k[e] = 0.f;
-            continue;
+// Aggregation kernel: one warp per output Gaussian (batch, output channel, k), reading the leaf order and the
+// subtree ranges that the tree kernel wrote. Lanes take contiguous slices of the leaf range and keep partial weighted
+// mean / scatter aggregates that are merged pairwise in leaf order.
+template <int D>
+__global__ void __launch_bounds__(256)
+convolution_fitting_aggregate_kernel(const float* __restrict__ data, const float* __restrict__ kernels, Dims n,
+                                     const int* __restrict__ nodesobjs_all, const int* __restrict__ subtrees_all,
+                                     float* __restrict__ fitting, float* __restrict__ cached_pos_covs,
+                                     long long n_outputs) {
+    constexpr int RF = 1 + D + D * D;
+    const int Cin = n.n_channels_in, G = n.n_components, Gk = n.n_kernel_components, K = n.n_fitting;
+    const int T = Cin * G * Gk;
+    const int n_internal = T - 1;
+    const int lane = threadIdx.x & 31;
+    const long long out_id = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (out_id >= n_outputs) return;
+    const long long tree = out_id / K;
+    const int k = int(out_id - tree * K);
+    const int b = int(tree / n.n_channels_out), o = int(tree - (long long)b * n.n_channels_out);
+    const float* data_b = data + size_t(b) * Cin * G * RF;
+    const float* kernels_o = kernels + size_t(o) * Cin * Gk * RF;
+    const int* nodesobjs = nodesobjs_all + size_t(tree) * T;
+    const int start = subtrees_all[size_t(tree) * 2 * K + 2 * k], end = subtrees_all[size_t(tree) * 2 * K + 2 * k + 1];
+    float* o_k = fitting + size_t(out_id) * RF;
+    float* c_k = cached_pos_covs + size_t(out_id) * D * D;
+    if (start < 0) {
+        for (int f = lane; f < RF; f += 32) {
+            float v = 0.f;
+            if (f > D && ((f - 1 - D) / D == (f - 1 - D) % D)) v = 1.f;
+            o_k[f] = v;
         }
-        Agg<D> a;
-        a.w = 0.f;
+        for (int e = lane; e < D * D; e += 32) c_k[e] = 0.f;
+        return;
+    }
+    Agg<D> a;
+    a.w = 0.f;
 #pragma unroll
-        for (int i = 0; i < D; ++i) a.m[i] = 0.f;
+    for (int i = 0; i < D; ++i) a.m[i] = 0.f;
 #pragma unroll
-        for (int e = 0; e < D * D; ++e) { a.C[e] = 0.f; a.cm[e] = 0.f; }
-        // lane l takes a contiguous slice of the range so that merging neighbours keeps the leaf order
-        const int len = end - start;
-        const int per = (len + 31) / 32;
-        const int s0 = start + lane * per, s1 = min(end, s0 + per);
-        for (int i = s0; i < s1; ++i) {
-            int gi, ci, ki;
-            product_parts(nodesobjs[i - n_internal], gi, ci, ki);
-            const float* dg = data_b + (size_t(ci) * G + gi) * RF;
-            const float* kg = kernels_o + (size_t(ci) * Gk + ki) * RF;
-            float p[D], cov[D * D];
+    for (int e = 0; e < D * D; ++e) { a.C[e] = 0.f; a.cm[e] = 0.f; }
+    // lane l takes a contiguous slice of the range so that merging neighbours keeps the leaf order
+    const int len = end - start;
+    const int per = (len + 31) / 32;
+    const int s0 = start + lane * per, s1 = min(end, s0 + per);
+    for (int i = s0; i < s1; ++i) {
+        const int t = nodesobjs[i - n_internal];
+        const int ki = t / (G * Cin);
+        const int rem = t - ki * G * Cin;
+        const int ci = rem / G;
+        const int gi = rem - ci * G;
+        const float* dg = data_b + (size_t(ci) * G + gi) * RF;
+        const float* kg = kernels_o + (size_t(ci) * Gk + ki) * RF;
+        float p[D], cov[D * D];
 #pragma unroll
-            for (int d = 0; d < D; ++d) p[d] = __ldg(dg + 1 + d) + __ldg(kg + 1 + d);
+        for (int d = 0; d < D; ++d) p[d] = __ldg(dg + 1 + d) + __ldg(kg + 1 + d);
 #pragma unroll
-            for (int e = 0; e < D * D; ++e) cov[e] = __ldg(dg + 1 + D + e) + __ldg(kg + 1 + D + e);
-            agg_add<D>(a, __ldg(dg) * __ldg(kg), p, cov);
-        }
+        for (int e = 0; e < D * D; ++e) cov[e] = __ldg(dg + 1 + D + e) + __ldg(kg + 1 + D + e);
+        agg_add<D>(a, __ldg(dg) * __ldg(kg), p, cov);
+    }
 #pragma unroll
-        for (int off = 1; off < 32; off <<= 1) {
-            const Agg<D> other = agg_shfl_down<D>(a, off);
-            if ((lane & (2 * off - 1)) == 0) agg_merge<D>(a, other);
-        }
-        if (lane == 0) {
-            o_k[0] = a.w;
+    for (int off = 1; off < 32; off <<= 1) {
+        const Agg<D> other = agg_shfl_down<D>(a, off);
+        if ((lane & (2 * off - 1)) == 0) agg_merge<D>(a, other);
+    }
+    if (lane == 0) {
+        o_k[0] = a.w;
 #pragma unroll
-            for (int d = 0; d < D; ++d) o_k[1 + d] = a.m[d];
+        for (int d = 0; d < D; ++d) o_k[1 + d] = a.m[d];
 #pragma unroll
-            for (int e = 0; e < D * D; ++e) {
-                const float pc = (a.w == 0.f) ? ((e / D == e % D) ? 1.f : 0.f) : a.C[e] / a.w;
-                c_k[e] = pc;
-                o_k[1 + D + e] = a.cm[e] + pc;
-            }
+        for (int e = 0; e < D * D; ++e) {
+            const float pc = (a.w == 0.f) ? ((e / D == e % D) ? 1.f : 0.f) : a.C[e] / a.w;
+            c_k[e] = pc;
+            o_k[1 + D + e] = a.cm[e] + pc;
         }
     }
 }
@@ -551,12 +565,19 @@ extern "C" int gmc_convolution_fitting_forward(const float* data, const float* k
     if (smem > 220 * 1024) return GMC_ERR_BAD_DIMS;
     const Dims n{n_batch, n_channels_in, n_components, n_channels_out, n_kernel_components, n_components_fitting};
     cudaStream_t st = as_stream(stream);
+    const long long n_outputs = blocks * n_components_fitting;
+    const long long agg_blocks = (n_outputs + 7) / 8;
+    if (agg_blocks > 0x7fffffffLL) return GMC_ERR_BAD_DIMS;
     if (n_dims == 2) {
-        if (smem > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(convolution_fitting_forward_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-        convolution_fitting_forward_kernel<2><<<unsigned(blocks), kThreads, smem, st>>>(data, kernels, n, fitting, cached_pos_covs, nodesobjs, fitting_subtrees);
+        if (smem > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(convolution_fitting_tree_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        convolution_fitting_tree_kernel<2><<<unsigned(blocks), kThreads, smem, st>>>(data, kernels, n, nodesobjs, fitting_subtrees);
+        GMC_LAUNCH_CHECK();
+        convolution_fitting_aggregate_kernel<2><<<unsigned(agg_blocks), 256, 0, st>>>(data, kernels, n, nodesobjs, fitting_subtrees, fitting, cached_pos_covs, n_outputs);
     } else {
-        if (smem > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(convolution_fitting_forward_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-        convolution_fitting_forward_kernel<3><<<unsigned(blocks), kThreads, smem, st>>>(data, kernels, n, fitting, cached_pos_covs, nodesobjs, fitting_subtrees);
+        if (smem > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(convolution_fitting_tree_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        convolution_fitting_tree_kernel<3><<<unsigned(blocks), kThreads, smem, st>>>(data, kernels, n, nodesobjs, fitting_subtrees);
+        GMC_LAUNCH_CHECK();
+        convolution_fitting_aggregate_kernel<3><<<unsigned(agg_blocks), 256, 0, st>>>(data, kernels, n, nodesobjs, fitting_subtrees, fitting, cached_pos_covs, n_outputs);
     }
     GMC_LAUNCH_CHECK();
     return GMC_OK;
