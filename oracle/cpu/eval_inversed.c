@@ -151,6 +151,15 @@
 DEFINE_EVAL(float, f32, expf, sqrtf)
 DEFINE_EVAL(double, f64, exp, sqrt)
 
+/* torch.distributed.run exports OMP_NUM_THREADS=1 to its workers; the timed CPU baseline asks for all cores instead. */
+void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+#else
+    (void)n;
+#endif
+}
+
 int oracle_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();
