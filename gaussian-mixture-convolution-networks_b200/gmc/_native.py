@@ -58,6 +58,7 @@ _declare("gmc_convolution_fitting_forward", [_c_float_p] * 2 + [_c_int] * 7 + [_
 _declare("gmc_convolution_fitting_backward", [_c_float_p] * 3 + [_c_int] * 7 + [_c_void_p] * 7)
 _declare("gmc_mhem_fit_backward", [_c_float_p, _c_float_p, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_int, _c_void_p,
                                    _c_void_p, _c_void_p, _c_void_p, _c_void_p])
+_declare("gmc_symeig", [_c_float_p] * 3 + [ctypes.c_longlong, _c_int, _c_void_p])
 _declare("gmc_integrate", [_c_float_p] * 2 + [ctypes.c_longlong, _c_int, _c_int, _c_void_p])
 
 

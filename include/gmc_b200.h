@@ -86,6 +86,14 @@ int gmc_eval_inversed_backward(const float* grad_out, const float* mixture, cons
  * ---------------------------------------------------------------------------------------------- */
 int gmc_matrix_inverse(const float* matrices, float* inverses, long long n_matrices, int n_dims, void* stream);
 
+/* Eigen-decomposition of n_matrices symmetric row-major DxD matrices: eigenvalues [n, D] ascending, eigenvectors
+ * [n, D, D] with the vectors in the columns. Closed form; accuracy about 1e-3 relative in fp32 for nearly degenerate
+ * spectra (the reference states the same for its implementation).
+ * Replaces pieces_bindings.symeig (src/gmc/cpp/extensions/pieces/symeig.cu, math/symeig_detail.h:17-138).
+ * ---------------------------------------------------------------------------------------------- */
+int gmc_symeig(const float* matrices, float* eigenvalues, float* eigenvectors, long long n_matrices, int n_dims,
+               void* stream);
+
 /* Integral of each mixture = sum of its weights (weights are integrals, not amplitudes).
  * mixture is [n_mixtures, n_components, 1+D+D*D], integrals is [n_mixtures].
  * Replaces gm.integrate (src/gmc/mixture.py:87-91), which the reference computes with a torch reduction.

@@ -125,3 +125,35 @@ def test_net_forward_3d_is_finite_and_repeatable():
     assert a.shape == (6, 10) and torch.isfinite(a).all()
     assert torch.allclose(a.exp().sum(1), torch.ones(6, device=a.device), atol=1e-4)
     assert torch.allclose(a, b, atol=1e-5)
+
+
+@pytest.mark.parametrize("d", [2, 3])
+def test_symeig_criteria_of_the_reference_test(d):
+    # src/gmc/cpp/extensions/math/test_symeig.py: unit length, orthogonality, A v = lambda v, all within 1.5e-3 (fp32)
+    import gmc.mat_tools as mat_tools
+    precision = 1.5e-3
+    t = torch.rand(10, 5, 100, d, d, generator=torch.Generator().manual_seed(d))
+    t = (t @ t.transpose(-1, -2) + torch.eye(d) * 0.000001).cuda().requires_grad_(True)
+    values, vectors = mat_tools.symeig(t)
+    ref_values = torch.linalg.eigvalsh(t.detach().double())
+    assert (values.detach().double() - ref_values).abs().max().item() < precision
+    assert ((vectors.norm(dim=-2) - 1) ** 2).max().item() < precision
+    for i in range(d):
+        for j in range(i + 1, d):
+            assert (vectors[..., i] * vectors[..., j]).sum(-1).abs().max().item() < precision
+    errors = (t @ vectors) - vectors * values.unsqueeze(-2)
+    assert errors.abs().max().item() < precision
+    # backward: gradient of sum(eigenvalues) = trace -> identity
+    values.sum().backward()
+    eye = torch.eye(d, device=t.device).expand_as(t.grad)
+    assert (t.grad - eye).abs().max().item() < 1e-3
+
+
+def test_splitter_keeps_the_integral_and_reaches_the_target_count():
+    import gmc.fitting as fitting
+    import gmc.mixture as gm
+    m = synthetic.fit_target_2d(2, 3, 12, 77, s_lo=0.02, s_hi=0.2).cuda()
+    out = fitting.splitter(m, [16, 20])
+    assert out.shape == (2, 3, 20, 7)
+    assert rel_inf(gm.integrate(out).cpu().numpy(), gm.integrate(m).cpu().numpy()) < 1e-5
+    assert torch.all(gm.covariances(out).det() > 0)
