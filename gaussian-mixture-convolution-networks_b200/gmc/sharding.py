@@ -68,3 +68,20 @@ class OutputGatherer:
             self._work.wait()
             self._work = None
         return self.buffer
+
+
+def all_reduce_gradients(module: torch.nn.Module, group=None, average: bool = True) -> None:
+    """Data-parallel training step glue: sums (or averages) the parameter gradients of `module` over all ranks, in
+    one flattened collective. Kernel mixtures are small, so one bucket is enough."""
+    params = [p for p in module.parameters() if p.grad is not None]
+    if not params:
+        return
+    flat = torch.cat([p.grad.reshape(-1) for p in params])
+    dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
+    if average:
+        flat /= dist.get_world_size(group)
+    offset = 0
+    for p in params:
+        n = p.grad.numel()
+        p.grad.copy_(flat[offset:offset + n].view_as(p.grad))
+        offset += n

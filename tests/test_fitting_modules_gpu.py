@@ -157,3 +157,49 @@ def test_splitter_keeps_the_integral_and_reaches_the_target_count():
     assert out.shape == (2, 3, 20, 7)
     assert rel_inf(gm.integrate(out).cpu().numpy(), gm.integrate(m).cpu().numpy()) < 1e-5
     assert torch.all(gm.covariances(out).det() > 0)
+
+
+def test_render_grid_matches_direct_evaluation():
+    import gmc.render as render
+    import gmc.mixture as gm
+    m = synthetic.fit_target_2d(2, 3, 9, 3).cuda()
+    const = torch.rand(2, 3).cuda()
+    img = render.render(m, const, x_low=-1, y_low=-1, x_high=1, y_high=1, width=8, height=6)
+    assert img.shape == (2, 3, 8, 6)
+    x = torch.tensor([[[[-1.0, -1.0], [1.0, 1.0]]]]).cuda()
+    direct = gm.evaluate(m, x) + const.unsqueeze(-1)
+    assert torch.allclose(img[:, :, 0, 0], direct[:, :, 0], rtol=1e-4, atol=1e-5)
+    assert torch.allclose(img[:, :, -1, -1], direct[:, :, 1], rtol=1e-4, atol=1e-5)
+    assert (render.render_with_relu(m, const, width=4, height=4) >= 0).all()
+
+
+@pytest.mark.parametrize("method", ["fixed_point_only", "fixed_point_and_tree_hem"])
+def test_net_training_step_runs_every_backward_kernel(method):
+    """Forward + backward + optimiser step through Net on the GPU: convolution-fitting backward, evaluation backward
+    (ReLU fixed point), matrix-inverse backward and, with the tree reduction, the BVH-MHEM backward."""
+    import gmc.model as model
+    import gmc.fitting as fitting
+    cfg = model.Config(n_dims=2)
+    cfg.layers = [model.Layer(4, 1, 24, 12), model.Layer(10, 1, 16, 8)]
+    cfg.relu_config.fitting_method = getattr(fitting, method)
+    torch.manual_seed(11)
+    net = model.Net(config=cfg).cuda().train()
+    x = synthetic.fit_target_2d(6, 1, 20, 5)
+    x[..., 0] = x[..., 0].abs() + 0.1
+    x = x.cuda()
+    target = torch.randint(0, 10, (6,), generator=torch.Generator().manual_seed(1)).cuda()
+    opt = torch.optim.Adam(net.parameters(), lr=1e-3)
+    losses = []
+    for _ in range(3):
+        opt.zero_grad()
+        torch.manual_seed(2)           # BatchNorm samples random positions
+        loss = torch.nn.functional.nll_loss(net(x), target)
+        loss.backward()
+        grads = [p.grad for p in net.parameters() if p.grad is not None]
+        assert grads and all(torch.isfinite(g).all() for g in grads)
+        assert any(g.abs().max().item() > 0 for g in grads)
+        opt.step()
+        losses.append(loss.item())
+    assert all(l == l for l in losses)
+    for g in net.gmcs:
+        assert g.weights.grad is not None and g.positions.grad is not None and g.covariance_factors.grad is not None

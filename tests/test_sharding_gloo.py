@@ -39,6 +39,17 @@ def _worker(rank, world, port, mode, result_dir):
             g.start(shard + 1.0)
             assert torch.equal(g.finish(), full + 1.0)
             torch.save(torch.tensor(1), os.path.join(result_dir, f"ok{rank}"))
+        elif mode == "grads":
+            torch.manual_seed(0)
+            lin = torch.nn.Linear(3, 2)
+            x = torch.full((4, 3), float(rank + 1))
+            lin(x).sum().backward()
+            local = [p.grad.clone() for p in lin.parameters()]
+            sharding.all_reduce_gradients(lin, average=True)
+            # ranks fed x = 1 and x = 2: the weight gradient averages to 1.5 * 4, the bias gradient stays 4
+            assert torch.allclose(lin.weight.grad, torch.full((2, 3), 6.0))
+            assert torch.allclose(lin.bias.grad, local[1])
+            torch.save(torch.tensor(1), os.path.join(result_dir, f"ok{rank}"))
         elif mode == "ragged":
             bad = shard if rank == 0 else shard[:1]
             try:
@@ -89,6 +100,10 @@ def test_shard_range_covers_batch():
 
 def test_all_gather_two_ranks(tmp_path):
     _run("gather", tmp_path, (0, 1))
+
+
+def test_gradient_all_reduce_two_ranks(tmp_path):
+    _run("grads", tmp_path, (0, 1))
 
 
 def test_unequal_shards_raise_on_every_rank(tmp_path):
