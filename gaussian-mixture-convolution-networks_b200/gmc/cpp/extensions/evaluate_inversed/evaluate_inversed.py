@@ -36,7 +36,61 @@ def _check_shapes(mixture: torch.Tensor, xes: torch.Tensor):
     return n_batch, n_layers, n_components, n_dims, xes.shape[0], xes.shape[1], xes.shape[2]
 
 
+def _require_host_f32(t: torch.Tensor, name: str) -> None:
+    if t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous():
+        raise _native.GmcError(f"{name} must be a contiguous float32 CPU tensor")
+
+
+def host_forward_backward(mixture: torch.Tensor, xes: torch.Tensor, grad_output: torch.Tensor = None,
+                          requires_grad_mixture: bool = True, requires_grad_xes: bool = True, n_slices: int = 0,
+                          out: torch.Tensor = None, grad_mixture: torch.Tensor = None, grad_xes: torch.Tensor = None,
+                          device=None, want_forward: bool = True):
+    """Evaluation (and, with grad_output, its gradients) of CPU tensors on the GPU through
+    gmc_eval_inversed_host: batch slices are copied in, computed and copied out in a three-stream pipeline.
+    Page-locked tensors (`pin_memory()`) let the copies overlap the kernels; result tensors may be passed in
+    to reuse page-locked storage. Returns (out, grad_mixture, grad_xes); entries not asked for are None."""
+    ns = _check_shapes(mixture, xes)
+    _require_host_f32(mixture, "mixture")
+    _require_host_f32(xes, "xes")
+    n_batch, n_layers, n_components, _, _, _, n_xes = ns
+    do_backward = grad_output is not None
+    if do_backward:
+        _require_host_f32(grad_output, "grad_output")
+        if tuple(grad_output.shape) != (n_batch, n_layers, n_xes):
+            raise RuntimeError("grad_output has the wrong shape")
+
+    def result(t, shape, name, wanted):
+        if not wanted:
+            return None
+        if t is None:
+            return torch.empty(shape, dtype=torch.float32)
+        _require_host_f32(t, name)
+        if tuple(t.shape) != tuple(shape):
+            raise RuntimeError(f"{name} has the wrong shape")
+        return t
+
+    out = result(out, (n_batch, n_layers, n_xes), "out", want_forward)
+    grad_mixture = result(grad_mixture, mixture.shape, "grad_mixture", do_backward and requires_grad_mixture)
+    grad_xes = result(grad_xes, xes.shape, "grad_xes", do_backward and requires_grad_xes)
+    if n_xes == 0 or n_components == 0 or n_batch == 0 or n_layers == 0:
+        for t in (out, grad_mixture, grad_xes):
+            if t is not None:
+                t.zero_()
+        return out, grad_mixture, grad_xes
+    if not torch.cuda.is_available():
+        raise _native.GmcError("no CUDA device: this library has no CPU implementation")
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        _native.check(_native.lib.gmc_eval_inversed_host(
+            _native.ptr(mixture), _native.ptr(xes), _native.ptr(grad_output), _native.ptr(out),
+            _native.ptr(grad_mixture), _native.ptr(grad_xes), *ns, int(n_slices)), "evaluate_inversed (host buffers)")
+    return out, grad_mixture, grad_xes
+
+
 def parallel_forward(mixture: torch.Tensor, xes: torch.Tensor):
+    if not mixture.is_cuda and not xes.is_cuda:
+        # CPU tensors (the reference runs its host implementation for them, evaluate_inversed.cpp:19): GPU through staging
+        return (host_forward_backward(mixture.contiguous(), xes.contiguous())[0],)
     ns = _check_shapes(mixture, xes)
     _native.require_cuda_f32(mixture, "mixture")
     _native.require_cuda_f32(xes, "xes")
@@ -52,6 +106,11 @@ def parallel_forward(mixture: torch.Tensor, xes: torch.Tensor):
 
 
 def parallel_backward(grad_output, mixture, xes, forward_out, requires_grad_mixture: bool, requires_grad_xes: bool):
+    if not mixture.is_cuda and not xes.is_cuda and not grad_output.is_cuda:
+        _, gm_, gx_ = host_forward_backward(mixture.contiguous(), xes.contiguous(), grad_output.contiguous(),
+                                            requires_grad_mixture, requires_grad_xes, want_forward=False)
+        # gradients that are not required come back as zeros, as below
+        return (gm_ if gm_ is not None else torch.zeros_like(mixture)), (gx_ if gx_ is not None else torch.zeros_like(xes))
     ns = _check_shapes(mixture, xes)
     _native.require_cuda_f32(mixture, "mixture")
     _native.require_cuda_f32(xes, "xes")

@@ -76,6 +76,23 @@ int gmc_eval_inversed_backward(const float* grad_out, const float* mixture, cons
                                int n_batch, int n_layers, int n_components, int n_dims,
                                int n_batch_xes, int n_layers_xes, int n_xes, void* stream);
 
+/* The evaluation above (and, when grad_out is not NULL, its gradients) for tensors that live in HOST memory:
+ * every pointer is a host pointer, the work is done on the current CUDA device. The batch is cut into n_slices
+ * slices (0 = default) that move through a copy-in / kernels / copy-out pipeline on three internal streams, so with
+ * page-locked buffers the copies of both directions overlap the kernels. The call returns when the host outputs are
+ * complete. out may be NULL when only gradients are wanted; grad_mixture / grad_xes may each be NULL. When xes is
+ * shared by the whole batch (n_batch_xes == 1 < n_batch) the batch is processed as one slice.
+ * The device workspace and the streams are created on first use and kept per device; gmc_host_pipeline_release()
+ * frees those of the current device.
+ *
+ * Serves the callers that hand CPU tensors to evaluate_inversed::parallel_forward / parallel_backward, which the
+ * reference sends to its host implementation (evaluate_inversed.cpp:19 and :34); here they run on the GPU.
+ * ---------------------------------------------------------------------------------------------- */
+int gmc_eval_inversed_host(const float* mixture, const float* xes, const float* grad_out, float* out,
+                           float* grad_mixture, float* grad_xes, int n_batch, int n_layers, int n_components,
+                           int n_dims, int n_batch_xes, int n_layers_xes, int n_xes, int n_slices);
+int gmc_host_pipeline_release(void);
+
 /* ------------------------------------------------------------------------------------------------
  * Batched inverse of n_matrices contiguous row-major DxD matrices (D in {2,3}); `inverses` holds the
  * mathematical inverse in the same layout. In-place (inverses == matrices) is allowed.

@@ -149,3 +149,44 @@ def test_config1_full_size_identities():
     ref = cpu_oracle.eval_forward(ms, xs)
     assert rel_inf(out[b, l, :2048].detach().cpu().numpy(), ref[0, 0]) < TOL
     assert torch.isfinite(mt.grad).all() and torch.isfinite(xt.grad).all()
+
+
+@pytest.mark.parametrize("D", [2, 3])
+@pytest.mark.parametrize("B,bx,n_slices,pinned", [(5, True, 2, True), (5, True, 0, False), (4, False, 3, True),
+                                                   (1, True, 4, True), (9, True, 4, True)])
+def test_host_buffer_pipeline_equals_the_device_path(D, B, bx, n_slices, pinned):
+    """gmc_eval_inversed_host (batch slices through copy-in / kernels / copy-out streams) returns the values of the
+    device entry points for whole, ragged and single slices, shared xes, page-locked and pageable buffers. The forward
+    is bit-identical; the gradients differ only by the order of the atomic sums."""
+    import gmc.cpp.extensions.evaluate_inversed.evaluate_inversed as ev
+    rng = np.random.default_rng(100 * D + B)
+    mixture, xes, grad_out = _random_case(rng, B, 3, 70, 900, D, bx, True)
+    out_d, gm_d, gx_d = _gpu_eval(mixture, xes, grad_out)
+    host = [torch.from_numpy(a) for a in (mixture, xes, grad_out)]
+    if pinned:
+        host = [t.pin_memory() for t in host]
+    for _ in range(2):     # second call reuses the cached workspace
+        out_h, gm_h, gx_h = ev.host_forward_backward(*host, n_slices=n_slices)
+    assert not out_h.is_cuda and not gm_h.is_cuda and not gx_h.is_cuda
+    assert np.array_equal(out_h.numpy(), out_d)
+    assert rel_inf(gm_h.numpy(), gm_d) < 1e-5 and rel_inf(gx_h.numpy(), gx_d) < 1e-5
+    # forward only / one gradient only
+    o2, g2, x2 = ev.host_forward_backward(host[0], host[1])
+    assert g2 is None and x2 is None and np.array_equal(o2.numpy(), out_d)
+    o3, g3, x3 = ev.host_forward_backward(*host, requires_grad_xes=False, want_forward=False, n_slices=n_slices)
+    assert o3 is None and x3 is None and rel_inf(g3.numpy(), gm_d) < 1e-5
+    assert ev._native.lib.gmc_host_pipeline_release() == 0
+
+
+def test_cpu_tensors_go_through_the_operator():
+    """CPU tensors given to the differentiable operator are evaluated on the GPU (the reference runs its host code)."""
+    import gmc.cpp.extensions.evaluate_inversed.evaluate_inversed as ev
+    rng = np.random.default_rng(5)
+    mixture, xes, grad_out = _random_case(rng, 2, 2, 40, 300, 3, True, False)
+    out_d, gm_d, gx_d = _gpu_eval(mixture, xes, grad_out)
+    m = torch.from_numpy(mixture).requires_grad_(True)
+    x = torch.from_numpy(xes).requires_grad_(True)
+    out = ev.apply(m, x)
+    out.backward(torch.from_numpy(grad_out))
+    assert not out.is_cuda and np.array_equal(out.detach().numpy(), out_d)
+    assert rel_inf(m.grad.numpy(), gm_d) < 1e-5 and rel_inf(x.grad.numpy(), gx_d) < 1e-5
