@@ -5,11 +5,13 @@
 // and the saved outputs in shared memory) does keys .. selection; the aggregation kernel (one warp per output
 // Gaussian) does the last step:
 //   keys        (w_d w_k > 0) << 62 | 30-bit Morton code of mu_d + mu_k in the tree's bounding box << 32 | product index
-//   sort        ascending (bitonic, in shared memory)
+//   sort        ascending, stable 8-bit LSD radix sort in shared memory
 //   tree+mass   the binary radix tree over (key high word + sorted position) -- the same hierarchy as the reference's
-//               Karras construction -- is built bottom-up: every leaf climbs, the second child to arrive at a node
-//               completes it (range, children, mass = mass(left) + mass(right)) and climbs on, so construction and
-//               the mass pass are one sweep without binary searches
+//               Karras construction -- is built bottom-up: every leaf climbs; a child swaps a 64-bit message (its id,
+//               its end of the leaf range, its mass) into the parent's slot with one atomic exchange, the second
+//               child to arrive gets the sibling's message back, completes the node (range, children,
+//               mass = mass(left) + mass(right)) and queues it; the queue of one round is the dense work list of the
+//               next, so construction and the mass pass are one sweep without binary searches and without idle lanes
 //   selection   K - 1 greedy splits of the selected internal node with the largest |mass|
 //   aggregation per selected subtree the weighted mean / scatter of the product centres and the weighted mean of
 //               the product covariances; one warp per output Gaussian, lanes hold partial aggregates that are
@@ -28,6 +30,9 @@ constexpr int kThreads = GMC_CONVFIT_THREADS;
 constexpr int kWarps = kThreads / 32;
 constexpr int kMaxProducts = 8192;
 constexpr int kMaxLevels = 72;
+#ifndef GMC_CONVFIT_MINB
+#define GMC_CONVFIT_MINB 4
+#endif
 
 struct Dims {
     int n_batch, n_channels_in, n_components, n_channels_out, n_kernel_components, n_fitting;
@@ -96,7 +101,7 @@ __device__ __forceinline__ Agg<D> agg_shfl_down(const Agg<D>& a, int offset) {
 }
 
 template <int D>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, GMC_CONVFIT_MINB)
 convolution_fitting_tree_kernel(const float* __restrict__ data, const float* __restrict__ kernels, Dims n,
                                 int* __restrict__ nodesobjs_all, int* __restrict__ subtrees_all) {
     constexpr int RF = 1 + D + D * D;
@@ -104,20 +109,18 @@ convolution_fitting_tree_kernel(const float* __restrict__ data, const float* __r
     const int Cin = n.n_channels_in, G = n.n_components, Gk = n.n_kernel_components, K = n.n_fitting;
     const int T = Cin * G * Gk;
     const int n_internal = T - 1;
-    // shared layout: [keys A: T x 8][keys B: T x 8][cpl][arrive bits][selection][radix histograms]
-    // after the sort buffer A is reused as mass[2T - 1] and buffer B as the node arrays (4 x (T - 1) x 2 bytes)
+    // shared layout: [keys A: T x 8][keys B: T x 8][radix scratch | cpl, selection]
+    // after the sort the buffer without the sorted keys holds one 64-bit slot per internal node (hand-over message of
+    // the first child, then {mass(left), mass(right)}); once the keys are dead their buffer holds the node arrays
     uint64_t* keys_a = reinterpret_cast<uint64_t*>(smem_bytes);
     uint64_t* keys_b = keys_a + T;
-    float* mass = reinterpret_cast<float*>(smem_bytes);
-    uint16_t* left = reinterpret_cast<uint16_t*>(keys_b);                         // n_internal each:
-    uint16_t* right = left + n_internal;
-    uint16_t* first = right + n_internal;                                         // leaf range [first, last] of a node
-    uint16_t* last = first + n_internal;
+    void* radix_scratch = keys_b + T;
     unsigned char* cpl = reinterpret_cast<unsigned char*>(keys_b + T);            // common prefix of leaf i, i+1
-    unsigned* arrive_bits = reinterpret_cast<unsigned*>(cpl + ((n_internal + 15) & ~15));    // ceil(n_internal / 32)
-    int* sel_node = reinterpret_cast<int*>(arrive_bits + ((n_internal + 31) / 32 + 3 & ~3));  // K
-    unsigned* sel_rating = reinterpret_cast<unsigned*>(sel_node + K);                          // K
-    unsigned* radix_hist = sel_rating + K;                                                     // (kWarps + 1) * 256
+    int* sel_node = reinterpret_cast<int*>(cpl + ((n_internal + 15) & ~15));      // K
+    unsigned* sel_rating = reinterpret_cast<unsigned*>(sel_node + K);             // K
+    uint16_t* queues = reinterpret_cast<uint16_t*>(sel_rating + K);               // 2 x queue_stride: completed nodes
+    const int queue_stride = (T / 2 + 8) & ~7;                                    // of a round (ping-pong)
+    __shared__ int queue_count[kMaxLevels + 1];
     __shared__ float s_hi[kWarps][D], s_lo[kWarps][D], box_hi[D], box_lo[D];
     __shared__ int s_root;
 
@@ -195,50 +198,102 @@ convolution_fitting_tree_kernel(const float* __restrict__ data, const float* __r
         keys_a[t] = (sign << 62) | (uint64_t(lbvh::morton30(q[0], q[1], q[2])) << 32) | uint64_t(uint32_t(t));
     }
     __syncthreads();
-    const uint64_t* keys = lbvh::radix_sort_shared(keys_a, keys_b, T, 32, 4, radix_hist);   // 4 passes: back in A
+    const uint64_t* keys = lbvh::radix_sort_shared(keys_a, keys_b, T, 32, 4, radix_scratch);   // 4 passes: back in A
 
-    // ---- leaves; common prefix lengths of neighbouring codes ----
+    // ---- leaves; common prefix lengths of neighbouring codes; empty slots ----
+    uint64_t* slots = keys == keys_a ? keys_b : keys_a;
+    uint32_t* children = reinterpret_cast<uint32_t*>(const_cast<uint64_t*>(keys));   // left | right << 16
+    uint32_t* ranges = children + n_internal;                                        // first | last << 16 (leaf range)
     for (int j = tid; j < T; j += kThreads) nodesobjs[j] = int(uint32_t(keys[j]));
-    for (int i = tid; i < (n_internal + 31) / 32; i += kThreads) arrive_bits[i] = 0u;
+    for (int i = tid; i < n_internal; i += kThreads) slots[i] = 0ull;
+    for (int i = tid; i <= kMaxLevels; i += kThreads) queue_count[i] = 0;
     {
         const lbvh::PositionTieBreakCode code{keys};
         for (int i = tid; i < n_internal; i += kThreads) cpl[i] = (unsigned char)lbvh::common_upper_bits(code(i), code(i + 1));
     }
-    __syncthreads();   // keys are dead from here on: buffer A becomes mass[], buffer B the node arrays
+    __syncthreads();   // keys are dead from here on: their buffer becomes the node arrays
 
     // ---- bottom-up construction with the mass pass folded in ----
     // Internal node p is the split between leaves p and p + 1. A node with leaf range [l, r] hangs below node r (as its
     // left child) if the codes differ less across r | r+1 than across l-1 | l, else below node l - 1 (as right child).
-    for (int leaf = tid; leaf < T; leaf += kThreads) {
-        int gi, ci, ki;
-        product_parts(nodesobjs[leaf], gi, ci, ki);
-        const float w = __fmul_rn(__ldg(data_b + (size_t(ci) * G + gi) * RF), __ldg(kernels_o + (size_t(ci) * Gk + ki) * RF));
-        int node = n_internal + leaf, l = leaf, r = leaf;
-        ((volatile float*)mass)[node] = w;
-        for (int guard = 0; guard < kMaxLevels; ++guard) {
-            if (l == 0 && r == T - 1) { s_root = node; break; }
+    // message: bit 63 valid | node id << 45 | own end of the leaf range << 32 | mass bits
+    // Round 0 sends every leaf to its parent; round k sends the nodes completed in round k - 1 (read back from the
+    // node arrays). Nobody waits: the first child to arrive just leaves its message.
+    const unsigned lt_mask = (1u << lane) - 1u;
+    auto arrive = [&](bool active, uint32_t node, int l, int r, float m, uint16_t* queue_out, int* count_out) {
+        bool completed = false;
+        int p = 0;
+        if (active) {
             const bool up_right = (l == 0) || (r != T - 1 && cpl[r] > cpl[l - 1]);
-            const int p = up_right ? r : l - 1;
-            if (up_right) { ((volatile uint16_t*)left)[p] = uint16_t(node); ((volatile uint16_t*)first)[p] = uint16_t(l); }
-            else { ((volatile uint16_t*)right)[p] = uint16_t(node); ((volatile uint16_t*)last)[p] = uint16_t(r); }
-            __threadfence_block();
-            const unsigned bit = 1u << (p & 31);
-            if ((atomicOr(&arrive_bits[p >> 5], bit) & bit) == 0u) break;   // the sibling will complete this node
-            __threadfence_block();
-            if (up_right) r = ((volatile uint16_t*)last)[p];
-            else l = ((volatile uint16_t*)first)[p];
-            ((volatile float*)mass)[p] = __fadd_rn(((volatile float*)mass)[((volatile uint16_t*)left)[p]],
-                                                   ((volatile float*)mass)[((volatile uint16_t*)right)[p]]);
-            node = p;
+            p = up_right ? r : l - 1;
+            const uint32_t hi = 0x80000000u | (node << 13) | uint32_t(up_right ? l : r);
+            const unsigned long long old = atomicExch(reinterpret_cast<unsigned long long*>(slots + p),
+                                                      (uint64_t(hi) << 32) | __float_as_uint(m));
+            if (old != 0ull) {                       // second child: complete node p
+                const uint32_t sib_hi = uint32_t(old >> 32);
+                const uint32_t sib_node = (sib_hi >> 13) & 0x3fffu, sib_end = sib_hi & 0x1fffu;
+                const float sib_mass = __uint_as_float(uint32_t(old));
+                if (up_right) {                      // this child is the left one
+                    children[p] = node | (sib_node << 16);
+                    r = int(sib_end);
+                    *reinterpret_cast<float2*>(slots + p) = make_float2(m, sib_mass);
+                } else {
+                    children[p] = sib_node | (node << 16);
+                    l = int(sib_end);
+                    *reinterpret_cast<float2*>(slots + p) = make_float2(sib_mass, m);
+                }
+                ranges[p] = uint32_t(l) | (uint32_t(r) << 16);
+                if (l == 0 && r == T - 1) s_root = p;
+                else completed = true;
+            }
         }
+        const unsigned done = __ballot_sync(0xffffffffu, completed);
+        if (done != 0u) {
+            int at = 0;
+            if (lane == 0) at = atomicAdd(count_out, __popc(done));
+            at = __shfl_sync(0xffffffffu, at, 0);
+            if (completed) queue_out[at + __popc(done & lt_mask)] = uint16_t(p);
+        }
+    };
+    for (int leaf0 = 0; leaf0 < T; leaf0 += kThreads) {
+        const int leaf = leaf0 + tid;
+        float m = 0.f;
+        if (leaf < T) {
+            int gi, ci, ki;
+            product_parts(nodesobjs[leaf], gi, ci, ki);
+            m = __fmul_rn(__ldg(data_b + (size_t(ci) * G + gi) * RF), __ldg(kernels_o + (size_t(ci) * Gk + ki) * RF));
+        }
+        arrive(leaf < T, uint32_t(n_internal + leaf), leaf, leaf, m, queues, &queue_count[1]);
     }
     __syncthreads();
+    for (int round = 1; round < kMaxLevels; ++round) {
+        const int n_in = queue_count[round];
+        if (n_in == 0) break;
+        const uint16_t* queue_in = queues + ((round - 1) & 1) * queue_stride;
+        for (int i0 = 0; i0 < n_in; i0 += kThreads) {
+            const int i = i0 + tid;
+            uint32_t node = 0u, lr = 0u;
+            float m = 0.f;
+            if (i < n_in) {
+                node = queue_in[i];
+                lr = ranges[node];
+                const float2 masses = *reinterpret_cast<const float2*>(slots + node);
+                m = __fadd_rn(masses.x, masses.y);
+            }
+            arrive(i < n_in, node, int(lr & 0xffffu), int(lr >> 16), m, queues + (round & 1) * queue_stride,
+                   &queue_count[round + 1]);
+        }
+        __syncthreads();
+    }
 
     // ---- greedy selection of K subtree roots (warp 0) ----
     // rating as an order-preserving integer: internal node -> bits(|mass|) + 1, leaf -> 0 (never selected)
     if (warp == 0) {
-        auto rating_of = [&](int id) -> unsigned { return id >= n_internal ? 0u : __float_as_uint(fabsf(mass[id])) + 1u; };
-        if (lane == 0) { sel_node[0] = s_root; sel_rating[0] = rating_of(s_root); }
+        auto rating_of = [&](int id, float mass) -> unsigned {
+            return id >= n_internal ? 0u : __float_as_uint(fabsf(mass)) + 1u;
+        };
+        // the root is expanded first whatever its mass: any non-zero rating does
+        if (lane == 0) { sel_node[0] = s_root; sel_rating[0] = s_root >= n_internal ? 0u : 1u; }
         __syncwarp();
         int n_sel = 1;
         while (n_sel < K) {
@@ -251,9 +306,10 @@ convolution_fitting_tree_kernel(const float* __restrict__ data, const float* __r
             best = __reduce_min_sync(0xffffffffu, best_rating == top ? best : 0x7fffffff);   // first of the maxima
             if (lane == 0) {
                 const int id = sel_node[best];
-                const int l = left[id], r = right[id];
-                sel_node[best] = l; sel_rating[best] = rating_of(l);
-                sel_node[n_sel] = r; sel_rating[n_sel] = rating_of(r);
+                const int l = int(children[id] & 0xffffu), r = int(children[id] >> 16);
+                const float2 masses = *reinterpret_cast<const float2*>(slots + id);
+                sel_node[best] = l; sel_rating[best] = rating_of(l, masses.x);
+                sel_node[n_sel] = r; sel_rating[n_sel] = rating_of(r, masses.y);
             }
             ++n_sel;
             __syncwarp();
@@ -263,8 +319,8 @@ convolution_fitting_tree_kernel(const float* __restrict__ data, const float* __r
             int start = -1, end = -1;
             if (k < n_sel) {
                 const int id = sel_node[k];
-                start = id >= n_internal ? id : n_internal + first[id];
-                end = id >= n_internal ? id + 1 : n_internal + last[id] + 1;
+                start = id >= n_internal ? id : n_internal + int(ranges[id] & 0xffffu);
+                end = id >= n_internal ? id + 1 : n_internal + int(ranges[id] >> 16) + 1;
             }
             subtrees[2 * k] = start;
             subtrees[2 * k + 1] = end;
@@ -534,10 +590,10 @@ convolution_fitting_backward_kernel(const float* __restrict__ grad, const float*
 size_t convfit_smem_bytes(int T, int K) {
     const int n_internal = T - 1;
     size_t bytes = 2 * size_t(T) * 8;
-    bytes += size_t((n_internal + 15) & ~15);
-    bytes += 4 * size_t(((n_internal + 31) / 32 + 3) & ~3);
-    bytes += 8 * size_t(K);
-    bytes += 4 * size_t(kWarps + 1) * 256;
+    const size_t after_sort = size_t((n_internal + 15) & ~15) + 8 * size_t(K)    // cpl, selection,
+                              + 2 * 2 * size_t((T / 2 + 8) & ~7);                 // two node queues
+    const size_t radix = 2 * size_t(kWarps + 1) * 256 + 32;                      // dead once the keys are sorted
+    bytes += after_sort > radix ? after_sort : radix;
     return bytes;
 }
 

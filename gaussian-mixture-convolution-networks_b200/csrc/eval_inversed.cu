@@ -29,6 +29,9 @@ namespace {
 #ifndef GMC_FWD_P
 #define GMC_FWD_P 8
 #endif
+#ifndef GMC_FWD_MINB
+#define GMC_FWD_MINB 1
+#endif
 #ifndef GMC_BWD_PPI
 #define GMC_BWD_PPI 2
 #endif
@@ -104,7 +107,7 @@ struct FwdSmem {
 };
 
 template <int D, int P>
-__global__ void __launch_bounds__(kFwdThreads)
+__global__ void __launch_bounds__(kFwdThreads, GMC_FWD_MINB)
 eval_forward_kernel(const float* __restrict__ mixture, const float* __restrict__ xes, float* __restrict__ out,
                     int n_layers, int n_components, int n_batch_xes, int n_layers_xes, int n_xes,
                     int tiles_per_mixture) {

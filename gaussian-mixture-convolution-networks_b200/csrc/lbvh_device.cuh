@@ -57,22 +57,29 @@ __device__ __forceinline__ void bitonic_sort_shared(uint64_t* keys, int n_pow2) 
 
 // Stable LSD radix sort of n 64-bit keys on the bit range [first_bit, first_bit + 8 * n_passes), CTA-wide, in shared
 // memory. `a` holds the input and `b` is a second buffer of n keys; the sorted keys end up in `a` if n_passes is even
-// and in `b` otherwise (the function returns the pointer). `hist` needs (number of warps) * 256 + 256 unsigned.
-// Every warp owns a contiguous slice of the keys; per pass it counts its digits, the CTA scans the (digit, warp)
-// counts, and the warp scatters its slice in order -- ranks inside one 32-key step come from __match_any_sync, so
-// equal digits keep their input order.
+// and in `b` otherwise (the function returns the pointer). `scratch` needs 2 * ((number of warps) * 256 + 256) + 32 bytes, 4-byte aligned; n must stay below 65536.
+// Bits 16..31 of every key must be zero and outside the sorted bit range: they carry the rank between the two loops of
+// a pass (n / number of warps, rounded up to 32, must stay below 65536) and are zero again on return.
+//
+// Every warp owns a contiguous slice of the keys. Counting loop: per 32-key step __match_any_sync groups equal digits,
+// the first lane of a group bumps the warp's digit counter and hands the old value to its group, and every key stores
+// its rank among the warp's keys of that digit. The CTA then turns the (digit, warp) counts into offsets, and the
+// scatter loop is one independent read-modify-write per key, so equal digits keep their input order.
 __device__ __forceinline__ uint64_t* radix_sort_shared(uint64_t* a, uint64_t* b, int n, int first_bit, int n_passes,
-                                                       unsigned* hist) {
+                                                       void* scratch) {
     const int n_warps = blockDim.x >> 5;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int chunk = (((n + n_warps - 1) / n_warps) + 31) & ~31;
     const int begin = min(n, warp * chunk), end = min(n, begin + chunk);
-    unsigned* my_hist = hist + warp * 256;
-    unsigned* totals = hist + n_warps * 256;
+    uint16_t* hist = reinterpret_cast<uint16_t*>(scratch);      // [warp][digit]: counts, then offsets below 65536
+    uint16_t* my_hist = hist + warp * 256;
+    uint16_t* totals = hist + n_warps * 256;
+    unsigned* warp_sums = reinterpret_cast<unsigned*>(totals + 256);
     const unsigned lt_mask = (1u << lane) - 1u;
     for (int pass = 0; pass < n_passes; ++pass) {
         const int shift = first_bit + 8 * pass;
-        for (int i = lane; i < 256; i += 32) my_hist[i] = 0u;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) reinterpret_cast<unsigned*>(my_hist)[lane + 32 * k] = 0u;
         __syncwarp();
         for (int i0 = begin; i0 < end; i0 += 32) {
             const int i = i0 + lane;
@@ -81,52 +88,48 @@ __device__ __forceinline__ uint64_t* radix_sort_shared(uint64_t* a, uint64_t* b,
             if (active) {
                 const unsigned digit = unsigned(a[i] >> shift) & 0xFFu;
                 const unsigned peers = __match_any_sync(act, digit);
-                if ((peers & lt_mask) == 0u) my_hist[digit] += __popc(peers);
+                const int leader = __ffs(peers) - 1;
+                unsigned before = 0u;
+                if (lane == leader) {
+                    before = my_hist[digit];
+                    my_hist[digit] = uint16_t(before + __popc(peers));
+                }
+                before = __shfl_sync(act, before, leader);
+                reinterpret_cast<uint16_t*>(a + i)[1] = uint16_t(before + __popc(peers & lt_mask));
             }
             __syncwarp();
         }
         __syncthreads();
-        // exclusive scan over (digit major, warp minor)
+        // (digit, warp) counts -> exclusive offsets: over the warps of a digit, then over the digits
         if (threadIdx.x < 256) {
             unsigned run = 0u;
             for (int w = 0; w < n_warps; ++w) {
                 const unsigned c = hist[w * 256 + threadIdx.x];
-                hist[w * 256 + threadIdx.x] = run;
+                hist[w * 256 + threadIdx.x] = uint16_t(run);
                 run += c;
             }
-            totals[threadIdx.x] = run;
-        }
-        __syncthreads();
-        if (warp == 0) {
-            unsigned v[8], sum = 0u;
-#pragma unroll
-            for (int k = 0; k < 8; ++k) { v[k] = totals[lane * 8 + k]; sum += v[k]; }
-            unsigned incl = sum;
+            unsigned incl = run;
 #pragma unroll
             for (int off = 1; off < 32; off <<= 1) {
                 const unsigned o = __shfl_up_sync(0xffffffffu, incl, off);
                 if (lane >= off) incl += o;
             }
-            unsigned run = incl - sum;
-#pragma unroll
-            for (int k = 0; k < 8; ++k) { totals[lane * 8 + k] = run; run += v[k]; }
+            totals[threadIdx.x] = uint16_t(incl - run);        // exclusive inside this group of 32 digits
+            if (lane == 31) warp_sums[warp] = incl;
         }
         __syncthreads();
+        unsigned group_base = 0u;                    // lane k < 8: number of keys with a digit below 32 * k
+#pragma unroll
+        for (int k = 0; k < 7; ++k) group_base += k < lane ? warp_sums[k] : 0u;
         for (int i0 = begin; i0 < end; i0 += 32) {
             const int i = i0 + lane;
             const bool active = i < end;
-            const unsigned act = __ballot_sync(0xffffffffu, active);
-            unsigned digit = 0u, peers = 0u;
-            uint64_t key = 0ull;
-            if (active) {
-                key = a[i];
-                digit = unsigned(key >> shift) & 0xFFu;
-                peers = __match_any_sync(act, digit);
-                b[totals[digit] + my_hist[digit] + __popc(peers & lt_mask)] = key;
-            }
-            __syncwarp();
-            if (active && (peers & lt_mask) == 0u) my_hist[digit] += __popc(peers);
-            __syncwarp();
+            const uint64_t key = active ? a[i] : 0ull;
+            const unsigned digit = unsigned(key >> shift) & 0xFFu;
+            const unsigned base = __shfl_sync(0xffffffffu, group_base, int(digit >> 5));
+            if (active)
+                b[base + unsigned(totals[digit]) + unsigned(my_hist[digit]) + (unsigned(key >> 16) & 0xFFFFu)] =
+                    key & ~0xFFFF0000ull;
         }
         __syncthreads();
         uint64_t* t = a; a = b; b = t;
