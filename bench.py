@@ -42,6 +42,7 @@ def _args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=B_PER_GPU,
                     help="batch per GPU (default: the configuration's 32; smaller values are for profiler captures)")
+    ap.add_argument("--no-cuda-graph", action="store_true", help="config 4: launch the forward kernel by kernel")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiler captures)")
     ap.add_argument("--config", type=int, default=1, choices=[1, 2, 3, 4],
                     help="1 (default, the headline): 3D evaluation fwd+bwd; 2: 2D ReLU fit with BVH-MHEM reduction; "
@@ -366,10 +367,18 @@ def _secondary_setup(args, rank, dev):
     net, head = _gmcn3d(torch, model)
     net, head = net.to(dev), head.to(dev)
 
-    def step(inputs=None):
-        xx = x if inputs is None else inputs[0]
+    def eager(xx):
         with torch.no_grad():
             return head(net.features(xx))
+
+    graphed = None
+    if not args.no_cuda_graph:
+        from gmc.cuda_graph import GraphedForward
+        graphed = GraphedForward(eager, x)          # the whole forward pass as one graph launch
+
+    def step(inputs=None):
+        xx = x if inputs is None else inputs[0]
+        return graphed(xx) if graphed is not None else eager(xx)
 
     def cpu():
         from oracle import cpu_oracle
@@ -391,7 +400,8 @@ def _secondary_setup(args, rank, dev):
     keys = n_batch * (8 * 320 + (16 + 32 + 64) * 2560)
     return ("samples_per_s_gmcn3d_forward", "samples/s", n_batch, step, (x_h,),
             f"config4: GMCN-3D forward, B={n_batch}/GPU, 64 input Gaussians, conv-fit layers 1->8->16->32->64 "
-            f"(K=64/32/16/8, ReLU fit fixed_point_only), integrate, linear to 10 logits",
+            f"(K=64/32/16/8, ReLU fit fixed_point_only), integrate, linear to 10 logits; "
+            + ("one CUDA graph per forward" if graphed is not None else "kernel-by-kernel launches"),
             keys * 4 + n_batch * 64 * 13 * 4, cpu)
 
 

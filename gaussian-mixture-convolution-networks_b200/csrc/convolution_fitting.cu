@@ -38,67 +38,19 @@ struct Dims {
     int n_batch, n_channels_in, n_components, n_channels_out, n_kernel_components, n_fitting;
 };
 
-template <int D>
-struct Agg {            // weighted mean / scatter of positions, weighted mean of covariances
-    float w;            // sum of weights
-    float m[D];         // mean position
-    float C[D * D];     // sum w (p - m)(p - m)^T
-    float cm[D * D];    // weighted mean covariance
+// Quotient and remainder of small non-negative integers (below 2^23) by a fixed divisor without the integer
+// division sequence: the float estimate is off by at most one.
+struct FastDivisor {
+    int d;
+    float inv;
+    __device__ __forceinline__ explicit FastDivisor(int divisor) : d(divisor), inv(1.0f / float(divisor)) {}
+    __device__ __forceinline__ void split(int x, int& q, int& r) const {
+        q = __float2int_rz(__fmul_rn(float(x), inv));
+        r = x - q * d;
+        if (r < 0) { r += d; --q; }
+        else if (r >= d) { r -= d; ++q; }
+    }
 };
-
-template <int D>
-__device__ __forceinline__ void agg_add(Agg<D>& a, float w, const float* p, const float* cov) {
-    a.w += w;
-    if (w == 0.f) return;
-    const float f = w / a.w;
-    float d1[D], d2[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) { d1[i] = p[i] - a.m[i]; a.m[i] += f * d1[i]; d2[i] = p[i] - a.m[i]; }
-#pragma unroll
-    for (int i = 0; i < D; ++i)
-#pragma unroll
-        for (int j = 0; j < D; ++j) a.C[i * D + j] += w * (d1[j] * d2[i]);
-#pragma unroll
-    for (int e = 0; e < D * D; ++e) a.cm[e] += f * (cov[e] - a.cm[e]);
-}
-
-// merges b into a (b comes later in leaf order)
-template <int D>
-__device__ __forceinline__ void agg_merge(Agg<D>& a, const Agg<D>& b) {
-    const float w = a.w + b.w;
-    if (b.w == 0.f && a.w != 0.f) return;   // nothing to add (keeps a's moments untouched)
-    if (w == 0.f) {                         // both empty, or weights that cancel exactly: no defined mean
-        if (a.w == 0.f && b.w == 0.f) return;
-    }
-    const float f = (w != 0.f) ? b.w / w : 0.f;
-    float delta[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) delta[i] = b.m[i] - a.m[i];
-    const float cross = a.w * f;
-#pragma unroll
-    for (int i = 0; i < D; ++i)
-#pragma unroll
-        for (int j = 0; j < D; ++j) a.C[i * D + j] += b.C[i * D + j] + cross * delta[i] * delta[j];
-#pragma unroll
-    for (int i = 0; i < D; ++i) a.m[i] += f * delta[i];
-#pragma unroll
-    for (int e = 0; e < D * D; ++e) a.cm[e] += f * (b.cm[e] - a.cm[e]);
-    a.w = w;
-}
-
-template <int D>
-__device__ __forceinline__ Agg<D> agg_shfl_down(const Agg<D>& a, int offset) {
-    Agg<D> r;
-    r.w = __shfl_down_sync(0xffffffffu, a.w, offset);
-#pragma unroll
-    for (int i = 0; i < D; ++i) r.m[i] = __shfl_down_sync(0xffffffffu, a.m[i], offset);
-#pragma unroll
-    for (int e = 0; e < D * D; ++e) {
-        r.C[e] = __shfl_down_sync(0xffffffffu, a.C[e], offset);
-        r.cm[e] = __shfl_down_sync(0xffffffffu, a.cm[e], offset);
-    }
-    return r;
-}
 
 template <int D>
 __global__ void __launch_bounds__(kThreads, GMC_CONVFIT_MINB)
@@ -131,6 +83,26 @@ convolution_fitting_tree_kernel(const float* __restrict__ data, const float* __r
     int* nodesobjs = nodesobjs_all + size_t(blockIdx.x) * T;
     int* subtrees = subtrees_all + size_t(blockIdx.x) * 2 * K;
 
+    // ---- (weight, centre) of the tree's input Gaussians: data records [Cin * G], then kernel records [Cin * Gk], one
+    //      float4 each, in key buffer B (free until the sort) when they fit; else every use gathers from global ----
+    const int n_data = Cin * G;
+    const bool staged = size_t(n_data + Cin * Gk) * sizeof(float4) <= size_t(T) * sizeof(uint64_t);
+    const float4* records = reinterpret_cast<const float4*>(keys_b);
+    if (staged) {
+        float4* dst = reinterpret_cast<float4*>(keys_b);
+        for (int i = tid; i < n_data + Cin * Gk; i += kThreads) {
+            const float* r = i < n_data ? data_b + size_t(i) * RF : kernels_o + size_t(i - n_data) * RF;
+            dst[i] = make_float4(__ldg(r), __ldg(r + 1), __ldg(r + 2), D == 3 ? __ldg(r + 3) : 0.f);
+        }
+        __syncthreads();
+    }
+    auto record = [&](bool kernel_side, int idx) -> float4 {
+        if (staged) return records[kernel_side ? n_data + idx : idx];
+        const float* r = kernel_side ? kernels_o + size_t(idx) * RF : data_b + size_t(idx) * RF;
+        return make_float4(__ldg(r), __ldg(r + 1), __ldg(r + 2), D == 3 ? __ldg(r + 3) : 0.f);
+    };
+    auto coordinate = [](const float4& v, int d) -> float { return d == 0 ? v.y : (d == 1 ? v.z : v.w); };
+
     // ---- bounding box: max over channels of (data max + kernel max), min likewise ----
     {
         float hi[D], lo[D];
@@ -140,18 +112,16 @@ convolution_fitting_tree_kernel(const float* __restrict__ data, const float* __r
             float dh[D], dl[D], kh[D], kl[D];
 #pragma unroll
             for (int d = 0; d < D; ++d) { dh[d] = kh[d] = -INFINITY; dl[d] = kl[d] = INFINITY; }
-            for (int g = lane; g < G; g += 32)
+            for (int g = lane; g < G; g += 32) {
+                const float4 v = record(false, ci * G + g);
 #pragma unroll
-                for (int d = 0; d < D; ++d) {
-                    const float v = __ldg(data_b + (size_t(ci) * G + g) * RF + 1 + d);
-                    dh[d] = fmaxf(dh[d], v); dl[d] = fminf(dl[d], v);
-                }
-            for (int g = lane; g < Gk; g += 32)
+                for (int d = 0; d < D; ++d) { dh[d] = fmaxf(dh[d], coordinate(v, d)); dl[d] = fminf(dl[d], coordinate(v, d)); }
+            }
+            for (int g = lane; g < Gk; g += 32) {
+                const float4 v = record(true, ci * Gk + g);
 #pragma unroll
-                for (int d = 0; d < D; ++d) {
-                    const float v = __ldg(kernels_o + (size_t(ci) * Gk + g) * RF + 1 + d);
-                    kh[d] = fmaxf(kh[d], v); kl[d] = fminf(kl[d], v);
-                }
+                for (int d = 0; d < D; ++d) { kh[d] = fmaxf(kh[d], coordinate(v, d)); kl[d] = fminf(kl[d], coordinate(v, d)); }
+            }
 #pragma unroll
             for (int d = 0; d < D; ++d) {
 #pragma unroll
@@ -178,23 +148,22 @@ convolution_fitting_tree_kernel(const float* __restrict__ data, const float* __r
         __syncthreads();
     }
 
+    const FastDivisor by_gc(G * Cin), by_g(G);
     auto product_parts = [&](int t, int& comp_in, int& ch_in, int& comp_k) {
-        comp_k = t / (G * Cin);
-        const int rem = t - comp_k * G * Cin;
-        ch_in = rem / G;
-        comp_in = rem - ch_in * G;
+        int rem;
+        by_gc.split(t, comp_k, rem);
+        by_g.split(rem, ch_in, comp_in);
     };
 
     // ---- keys, sort (stable on bits 32..63 = sign | Morton code; equal codes keep ascending product index) ----
     for (int t = tid; t < T; t += kThreads) {
         int gi, ci, ki;
         product_parts(t, gi, ci, ki);
-        const float* dg = data_b + (size_t(ci) * G + gi) * RF;
-        const float* kg = kernels_o + (size_t(ci) * Gk + ki) * RF;
+        const float4 dg = record(false, ci * G + gi), kg = record(true, ci * Gk + ki);
         uint32_t q[3] = {0u, 0u, 0u};
 #pragma unroll
-        for (int d = 0; d < D; ++d) q[d] = lbvh::quantise(__fadd_rn(__ldg(dg + 1 + d), __ldg(kg + 1 + d)), box_lo[d], box_hi[d]);
-        const uint64_t sign = __fmul_rn(__ldg(dg), __ldg(kg)) > 0.f ? 1ull : 0ull;
+        for (int d = 0; d < D; ++d) q[d] = lbvh::quantise(__fadd_rn(coordinate(dg, d), coordinate(kg, d)), box_lo[d], box_hi[d]);
+        const uint64_t sign = __fmul_rn(dg.x, kg.x) > 0.f ? 1ull : 0ull;
         keys_a[t] = (sign << 62) | (uint64_t(lbvh::morton30(q[0], q[1], q[2])) << 32) | uint64_t(uint32_t(t));
     }
     __syncthreads();
@@ -328,31 +297,20 @@ convolution_fitting_tree_kernel(const float* __restrict__ data, const float* __r
     }
 }
 
-// Aggregation kernel: one warp per output Gaussian (batch, output channel, k), reading the leaf order and the
-// subtree ranges that the tree kernel wrote. Lanes take contiguous slices of the leaf range and keep partial weighted
-// mean / scatter aggregates that are merged pairwise in leaf order.
-template <int D>
-__global__ void __launch_bounds__(256)
-convolution_fitting_aggregate_kernel(const float* __restrict__ data, const float* __restrict__ kernels, Dims n,
-                                     const int* __restrict__ nodesobjs_all, const int* __restrict__ subtrees_all,
-                                     float* __restrict__ fitting, float* __restrict__ cached_pos_covs,
-                                     long long n_outputs) {
+template <bool STAGED>
+__device__ __forceinline__ float load_record(const float* p) {
+    if constexpr (STAGED) return *p;
+    else return __ldg(p);
+}
+
+// One warp, one output Gaussian: sums over the leaves [start, end) of its subtree (see the kernel below).
+template <int D, bool STAGED>
+__device__ __forceinline__ void aggregate_output(const float* data_b, const float* kernels_o, const int* nodesobjs,
+                                                 const int* subtree, float* o_k, float* c_k, const FastDivisor& by_gc,
+                                                 const FastDivisor& by_g, int G, int Gk, int lane) {
     constexpr int RF = 1 + D + D * D;
-    const int Cin = n.n_channels_in, G = n.n_components, Gk = n.n_kernel_components, K = n.n_fitting;
-    const int T = Cin * G * Gk;
-    const int n_internal = T - 1;
-    const int lane = threadIdx.x & 31;
-    const long long out_id = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (out_id >= n_outputs) return;
-    const long long tree = out_id / K;
-    const int k = int(out_id - tree * K);
-    const int b = int(tree / n.n_channels_out), o = int(tree - (long long)b * n.n_channels_out);
-    const float* data_b = data + size_t(b) * Cin * G * RF;
-    const float* kernels_o = kernels + size_t(o) * Cin * Gk * RF;
-    const int* nodesobjs = nodesobjs_all + size_t(tree) * T;
-    const int start = subtrees_all[size_t(tree) * 2 * K + 2 * k], end = subtrees_all[size_t(tree) * 2 * K + 2 * k + 1];
-    float* o_k = fitting + size_t(out_id) * RF;
-    float* c_k = cached_pos_covs + size_t(out_id) * D * D;
+    constexpr int NS = D * (D + 1) / 2;
+    const int start = subtree[0], end = subtree[1];
     if (start < 0) {
         for (int f = lane; f < RF; f += 32) {
             float v = 0.f;
@@ -362,47 +320,144 @@ convolution_fitting_aggregate_kernel(const float* __restrict__ data, const float
         for (int e = lane; e < D * D; e += 32) c_k[e] = 0.f;
         return;
     }
-    Agg<D> a;
-    a.w = 0.f;
+    auto records = [&](int t, const float*& dg, const float*& kg) {
+        int ki, rem, ci, gi;
+        by_gc.split(t, ki, rem);
+        by_g.split(rem, ci, gi);
+        dg = data_b + (size_t(ci) * G + gi) * RF;
+        kg = kernels_o + (size_t(ci) * Gk + ki) * RF;
+    };
+    float p0[D];
+    {
+        const float *dg, *kg;
+        records(__ldg(nodesobjs + start), dg, kg);
 #pragma unroll
-    for (int i = 0; i < D; ++i) a.m[i] = 0.f;
+        for (int d = 0; d < D; ++d) p0[d] = load_record<STAGED>(dg + 1 + d) + load_record<STAGED>(kg + 1 + d);
+    }
+    float W = 0.f, S1[D], S2[NS], S3[D * D];
 #pragma unroll
-    for (int e = 0; e < D * D; ++e) { a.C[e] = 0.f; a.cm[e] = 0.f; }
-    // lane l takes a contiguous slice of the range so that merging neighbours keeps the leaf order
-    const int len = end - start;
-    const int per = (len + 31) / 32;
-    const int s0 = start + lane * per, s1 = min(end, s0 + per);
-    for (int i = s0; i < s1; ++i) {
-        const int t = nodesobjs[i - n_internal];
-        const int ki = t / (G * Cin);
-        const int rem = t - ki * G * Cin;
-        const int ci = rem / G;
-        const int gi = rem - ci * G;
-        const float* dg = data_b + (size_t(ci) * G + gi) * RF;
-        const float* kg = kernels_o + (size_t(ci) * Gk + ki) * RF;
-        float p[D], cov[D * D];
+    for (int d = 0; d < D; ++d) S1[d] = 0.f;
 #pragma unroll
-        for (int d = 0; d < D; ++d) p[d] = __ldg(dg + 1 + d) + __ldg(kg + 1 + d);
+    for (int e = 0; e < NS; ++e) S2[e] = 0.f;
 #pragma unroll
-        for (int e = 0; e < D * D; ++e) cov[e] = __ldg(dg + 1 + D + e) + __ldg(kg + 1 + D + e);
-        agg_add<D>(a, __ldg(dg) * __ldg(kg), p, cov);
+    for (int e = 0; e < D * D; ++e) S3[e] = 0.f;
+    for (int i = start + lane; i < end; i += 32) {
+        const float *dg, *kg;
+        records(__ldg(nodesobjs + i), dg, kg);
+        const float w = load_record<STAGED>(dg) * load_record<STAGED>(kg);
+        float q[D], wq[D];
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+            q[d] = (load_record<STAGED>(dg + 1 + d) + load_record<STAGED>(kg + 1 + d)) - p0[d];
+            wq[d] = w * q[d];
+            S1[d] += wq[d];
+        }
+        W += w;
+        int e2 = 0;
+#pragma unroll
+        for (int a = 0; a < D; ++a)
+#pragma unroll
+            for (int c = a; c < D; ++c) { S2[e2] = fmaf(wq[a], q[c], S2[e2]); ++e2; }
+#pragma unroll
+        for (int e = 0; e < D * D; ++e) S3[e] = fmaf(w, load_record<STAGED>(dg + 1 + D + e) + load_record<STAGED>(kg + 1 + D + e), S3[e]);
     }
 #pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-        const Agg<D> other = agg_shfl_down<D>(a, off);
-        if ((lane & (2 * off - 1)) == 0) agg_merge<D>(a, other);
+    for (int off = 16; off > 0; off >>= 1) {
+        W += __shfl_xor_sync(0xffffffffu, W, off);
+#pragma unroll
+        for (int d = 0; d < D; ++d) S1[d] += __shfl_xor_sync(0xffffffffu, S1[d], off);
+#pragma unroll
+        for (int e = 0; e < NS; ++e) S2[e] += __shfl_xor_sync(0xffffffffu, S2[e], off);
+#pragma unroll
+        for (int e = 0; e < D * D; ++e) S3[e] += __shfl_xor_sync(0xffffffffu, S3[e], off);
     }
     if (lane == 0) {
-        o_k[0] = a.w;
+        o_k[0] = W;
+        if (W == 0.f) {
 #pragma unroll
-        for (int d = 0; d < D; ++d) o_k[1 + d] = a.m[d];
+            for (int d = 0; d < D; ++d) o_k[1 + d] = 0.f;
+#pragma unroll
+            for (int e = 0; e < D * D; ++e) {
+                const float pc = (e / D == e % D) ? 1.f : 0.f;
+                c_k[e] = pc;
+                o_k[1 + D + e] = pc;
+            }
+            return;
+        }
+        const float inv = 1.f / W;
+        float mq[D];
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+            mq[d] = S1[d] * inv;
+            o_k[1 + d] = p0[d] + mq[d];
+        }
+        int e2 = 0;
+        float pc[D * D];
+#pragma unroll
+        for (int a = 0; a < D; ++a)
+#pragma unroll
+            for (int c = a; c < D; ++c) {
+                const float v = S2[e2++] * inv - mq[a] * mq[c];
+                pc[a * D + c] = v;
+                pc[c * D + a] = v;
+            }
 #pragma unroll
         for (int e = 0; e < D * D; ++e) {
-            const float pc = (a.w == 0.f) ? ((e / D == e % D) ? 1.f : 0.f) : a.C[e] / a.w;
-            c_k[e] = pc;
-            o_k[1 + D + e] = a.cm[e] + pc;
+            c_k[e] = pc[e];
+            o_k[1 + D + e] = S3[e] * inv + pc[e];
         }
     }
+}
+
+
+// Aggregation kernel: one warp per output Gaussian (batch, output channel, k), reading the leaf order and the
+// subtree ranges that the tree kernel wrote. With q = p - p0 (p0 = centre of the first leaf of the range, so the sums
+// stay in cluster-local coordinates) the lanes accumulate
+//     W = sum w, S1 = sum w q, S2 = sum w q q^T, S3 = sum w C
+// over a strided share of the leaves and a butterfly adds the 32 partial sums. Output: weight W, position
+// p0 + S1 / W, covariance S3 / W + [S2 / W - (S1 / W)(S1 / W)^T]; the bracket (the scatter of the centres) is saved in
+// cached_pos_covs for the backward pass. W == 0 gives (0, 0, identity) like the sequential weighted update of the
+// reference (implementation_forward.h:60-124), which never leaves its initial state in that case.
+//
+// A CTA (8 warps) serves up to kAggOutputsPerCta outputs of ONE tree. When the tree's input records (Cin * (G + Gk)
+// Gaussians) fit, they are staged in shared memory first (STAGED): the leaves of a subtree name arbitrary records,
+// and gathering 26 floats per leaf from global memory is bound by L1 wavefronts.
+constexpr int kAggOutputsPerCta = 32;
+constexpr size_t kAggMaxStagedBytes = 96 * 1024;
+
+template <int D, bool STAGED>
+__global__ void __launch_bounds__(256)
+convolution_fitting_aggregate_kernel(const float* __restrict__ data, const float* __restrict__ kernels, Dims n,
+                                     const int* __restrict__ nodesobjs_all, const int* __restrict__ subtrees_all,
+                                     float* __restrict__ fitting, float* __restrict__ cached_pos_covs,
+                                     int groups_per_tree) {
+    constexpr int RF = 1 + D + D * D;
+    extern __shared__ __align__(16) unsigned char smem_bytes[];
+    const int Cin = n.n_channels_in, G = n.n_components, Gk = n.n_kernel_components, K = n.n_fitting;
+    const int T = Cin * G * Gk;
+    const int n_internal = T - 1;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const long long tree = blockIdx.x / groups_per_tree;
+    const int group = blockIdx.x - int(tree) * groups_per_tree;
+    const int b = int(tree / n.n_channels_out), o = int(tree - (long long)b * n.n_channels_out);
+    const float* data_b = data + size_t(b) * Cin * G * RF;
+    const float* kernels_o = kernels + size_t(o) * Cin * Gk * RF;
+    if constexpr (STAGED) {
+        float* staged = reinterpret_cast<float*>(smem_bytes);
+        const int n_data = Cin * G * RF, n_kernel = Cin * Gk * RF;
+        for (int i = threadIdx.x; i < n_data; i += 256) staged[i] = __ldg(data_b + i);
+        for (int i = threadIdx.x; i < n_kernel; i += 256) staged[n_data + i] = __ldg(kernels_o + i);
+        __syncthreads();
+        data_b = staged;
+        kernels_o = staged + n_data;
+    }
+    const int* nodesobjs = nodesobjs_all + size_t(tree) * T - n_internal;     // indexed by node id of the leaf
+    const FastDivisor by_gc(G * Cin), by_g(G);
+    const int k_end = min(K, (group + 1) * kAggOutputsPerCta);
+    for (int k = group * kAggOutputsPerCta + warp; k < k_end; k += 8)
+        aggregate_output<D, STAGED>(data_b, kernels_o, nodesobjs, subtrees_all + (size_t(tree) * K + k) * 2,
+                                    fitting + (size_t(tree) * K + k) * RF, cached_pos_covs + (size_t(tree) * K + k) * D * D,
+                                    by_gc, by_g, G, Gk, lane);
 }
 
 // ---------------------------------------------------------------------------------------------------------------
@@ -597,6 +652,29 @@ size_t convfit_smem_bytes(int T, int K) {
     return bytes;
 }
 
+template <int D>
+int launch_convfit_forward(const float* data, const float* kernels, const Dims& n, int32_t* nodesobjs,
+                           int32_t* fitting_subtrees, float* fitting, float* cached_pos_covs, long long blocks,
+                           size_t smem, long long agg_blocks, int groups_per_tree, bool staged, size_t staged_bytes,
+                           cudaStream_t st) {
+    if (smem > 48 * 1024)
+        GMC_CUDA_TRY(cudaFuncSetAttribute(convolution_fitting_tree_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    convolution_fitting_tree_kernel<D><<<unsigned(blocks), kThreads, smem, st>>>(data, kernels, n, nodesobjs, fitting_subtrees);
+    GMC_LAUNCH_CHECK();
+    if (staged) {
+        if (staged_bytes > 48 * 1024)
+            GMC_CUDA_TRY(cudaFuncSetAttribute(convolution_fitting_aggregate_kernel<D, true>,
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, int(staged_bytes)));
+        convolution_fitting_aggregate_kernel<D, true><<<unsigned(agg_blocks), 256, staged_bytes, st>>>(
+            data, kernels, n, nodesobjs, fitting_subtrees, fitting, cached_pos_covs, groups_per_tree);
+    } else {
+        convolution_fitting_aggregate_kernel<D, false><<<unsigned(agg_blocks), 256, 0, st>>>(
+            data, kernels, n, nodesobjs, fitting_subtrees, fitting, cached_pos_covs, groups_per_tree);
+    }
+    GMC_LAUNCH_CHECK();
+    return GMC_OK;
+}
+
 }  // namespace
 }  // namespace gmc
 
@@ -621,21 +699,21 @@ extern "C" int gmc_convolution_fitting_forward(const float* data, const float* k
     if (smem > 220 * 1024) return GMC_ERR_BAD_DIMS;
     const Dims n{n_batch, n_channels_in, n_components, n_channels_out, n_kernel_components, n_components_fitting};
     cudaStream_t st = as_stream(stream);
-    const long long n_outputs = blocks * n_components_fitting;
-    const long long agg_blocks = (n_outputs + 7) / 8;
+    const int groups_per_tree = (n_components_fitting + kAggOutputsPerCta - 1) / kAggOutputsPerCta;
+    const long long agg_blocks = blocks * groups_per_tree;
     if (agg_blocks > 0x7fffffffLL) return GMC_ERR_BAD_DIMS;
+    const size_t staged_bytes = sizeof(float) * size_t(n_channels_in) * (n_components + n_kernel_components) *
+                                size_t(1 + n_dims + n_dims * n_dims);
+    const bool staged = staged_bytes <= kAggMaxStagedBytes;
     if (n_dims == 2) {
-        if (smem > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(convolution_fitting_tree_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-        convolution_fitting_tree_kernel<2><<<unsigned(blocks), kThreads, smem, st>>>(data, kernels, n, nodesobjs, fitting_subtrees);
-        GMC_LAUNCH_CHECK();
-        convolution_fitting_aggregate_kernel<2><<<unsigned(agg_blocks), 256, 0, st>>>(data, kernels, n, nodesobjs, fitting_subtrees, fitting, cached_pos_covs, n_outputs);
+        if (int s = launch_convfit_forward<2>(data, kernels, n, nodesobjs, fitting_subtrees, fitting, cached_pos_covs,
+                                              blocks, smem, agg_blocks, groups_per_tree, staged, staged_bytes, st))
+            return s;
     } else {
-        if (smem > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(convolution_fitting_tree_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-        convolution_fitting_tree_kernel<3><<<unsigned(blocks), kThreads, smem, st>>>(data, kernels, n, nodesobjs, fitting_subtrees);
-        GMC_LAUNCH_CHECK();
-        convolution_fitting_aggregate_kernel<3><<<unsigned(agg_blocks), 256, 0, st>>>(data, kernels, n, nodesobjs, fitting_subtrees, fitting, cached_pos_covs, n_outputs);
+        if (int s = launch_convfit_forward<3>(data, kernels, n, nodesobjs, fitting_subtrees, fitting, cached_pos_covs,
+                                              blocks, smem, agg_blocks, groups_per_tree, staged, staged_bytes, st))
+            return s;
     }
-    GMC_LAUNCH_CHECK();
     return GMC_OK;
 }
 

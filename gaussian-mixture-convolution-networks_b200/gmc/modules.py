@@ -82,7 +82,7 @@ class Convolution(torch.nn.modules.Module):
         weights = self.weights * self.weight_sd + self.weight_mean
         A = self.covariance_factors
         cov = A @ A.transpose(-1, -2)
-        eps = self.covariance_epsilon * max(1.0, torch.max(cov.detach().abs()).item())
+        eps = self.covariance_epsilon * torch.clamp(cov.detach().abs().max(), min=1.0)    # stays on the device
         cov = cov + torch.eye(self.n_dims, dtype=torch.float32, device=A.device) * eps
         return gm.pack_mixture(weights, self.positions * self.position_range, cov * self.covariance_range)
 

@@ -14,12 +14,13 @@ pytestmark = pytest.mark.gpu
 def _inputs(D, B, Cin, G, Cout, Gk, seed):
     if D == 2:
         data, kernels, _ = synthetic.config3(n_batch=B, seed=seed)
-        return data[:, :Cin, :G].contiguous(), kernels[:Cout, :Cin, :Gk].contiguous()
+        if Cin <= data.shape[1] and G <= data.shape[2] and Cout <= kernels.shape[0] and Gk <= kernels.shape[2]:
+            return data[:, :Cin, :G].contiguous(), kernels[:Cout, :Cin, :Gk].contiguous()
     g = torch.Generator().manual_seed(seed)
-    cov_d, _ = synthetic.covariances_and_inverses((B, Cin, G), 3, 0.03, 0.15, g)
-    data = synthetic.pack(torch.randn(B, Cin, G, generator=g), torch.rand(B, Cin, G, 3, generator=g) * 2 - 1, cov_d)
-    cov_k, _ = synthetic.covariances_and_inverses((Cout, Cin, Gk), 3, 0.02, 0.1, g)
-    kernels = synthetic.pack(torch.randn(Cout, Cin, Gk, generator=g) * 0.1, torch.randn(Cout, Cin, Gk, 3, generator=g) * 0.1, cov_k)
+    cov_d, _ = synthetic.covariances_and_inverses((B, Cin, G), D, 0.03, 0.15, g)
+    data = synthetic.pack(torch.randn(B, Cin, G, generator=g), torch.rand(B, Cin, G, D, generator=g) * 2 - 1, cov_d)
+    cov_k, _ = synthetic.covariances_and_inverses((Cout, Cin, Gk), D, 0.02, 0.1, g)
+    kernels = synthetic.pack(torch.randn(Cout, Cin, Gk, generator=g) * 0.1, torch.randn(Cout, Cin, Gk, D, generator=g) * 0.1, cov_k)
     return data, kernels
 
 
@@ -40,7 +41,10 @@ def test_exact_convolution_forward_and_backward(D, B, Cin, G, Cout, Gk):
 
 
 @pytest.mark.parametrize("D,B,Cin,G,Cout,Gk,K", [(2, 2, 3, 16, 4, 5, 16), (2, 4, 8, 128, 3, 5, 128), (3, 2, 1, 64, 8, 5, 64),
-                                                 (3, 2, 8, 64, 2, 5, 32), (2, 2, 2, 7, 2, 3, 42), (2, 1, 1, 2, 1, 1, 4)])
+                                                 (3, 2, 8, 64, 2, 5, 32), (2, 2, 2, 7, 2, 3, 42), (2, 1, 1, 2, 1, 1, 4),
+                                                 (3, 2, 2, 3, 2, 2, 6),          # inputs too many to stage beside the keys
+                                                 (2, 1, 4, 1000, 1, 2, 16),      # inputs too large to stage for the sums
+                                                 (3, 1, 32, 16, 3, 5, 8), (3, 2, 8, 64, 2, 5, 70)])
 def test_convolution_fitting_forward_matches_oracle(D, B, Cin, G, Cout, Gk, K):
     import gmc.cpp.extensions.convolution_fitting.binding as cf
     data, kernels = _inputs(D, B, Cin, G, Cout, Gk, 70 + G + K)

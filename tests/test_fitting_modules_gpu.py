@@ -203,3 +203,36 @@ def test_net_training_step_runs_every_backward_kernel(method):
     assert all(l == l for l in losses)
     for g in net.gmcs:
         assert g.weights.grad is not None and g.positions.grad is not None and g.covariance_factors.grad is not None
+
+
+def test_graphed_forward_equals_eager_forward(monkeypatch):
+    """The GMCN forward captured as a CUDA graph returns the eager result, also for a second input. The normalisation
+    layers sample random positions, so the sampler is replaced by a fixed sequence for the comparison."""
+    import math
+    import gmc.model as model
+    from gmc.cuda_graph import GraphedForward
+
+    def fixed_rand(*shape, device=None, **kwargs):
+        if len(shape) == 1 and isinstance(shape[0], (tuple, list, torch.Size)):
+            shape = tuple(shape[0])
+        n = math.prod(shape)
+        return ((torch.arange(n, device=device, dtype=torch.float32) * 0.6180339887) % 1.0).view(*shape)
+
+    cfg = model.Config(n_dims=3)
+    cfg.layers = [model.Layer(4, 1, 16, 16), model.Layer(10, 1, 8, 8)]
+    torch.manual_seed(5)
+    net = model.Net(config=cfg).cuda().eval()
+    xs = [synthetic.config4_input(n_batch=3, seed=s).cuda() for s in (1, 2)]
+    monkeypatch.setattr(torch, "rand", fixed_rand)
+
+    def fn(x):
+        return net.features(x)
+
+    graph = GraphedForward(fn, xs[0])
+    for x in xs:
+        with torch.no_grad():
+            ref = fn(x)
+        out = graph(x).clone()
+        assert torch.allclose(out, ref, rtol=1e-5, atol=1e-6)
+    with pytest.raises(ValueError):
+        graph(xs[0][:2])
