@@ -1,0 +1,200 @@
+// ReLU approximation of a mixture by one fixed-point step, fused into one kernel (inference path).
+//
+// For a mixture (w_j, mu_j, C_j) with constant c the reference (src/gmc/fitting.py:279-312 with n_iter = 1) computes
+//   initial weights  w'_j = w_j                 if w_j + c > 0
+//                          -max(c, 0)           otherwise
+//   start            x0_j = |w'_j| + 0.1
+//   target           b_i  = max(sum_j w_j  E_ij + c, 0) - max(c, 0)
+//   step             x_i  = x0_i (b_i + 0.05) / (sum_j x0_j E_ij + 0.05)
+// with E_ij = (2 pi)^(-D/2) sqrt(det S_j) exp(-1/2 (mu_i - mu_j)^T S_j (mu_i - mu_j)), S_j = C_j^-1: both mixtures are
+// evaluated at the component centres and share centres and covariances, so one exponential per (i, j) serves both
+// sums, and the inverse covariances never leave the chip. Output: (x, mu, C) and the constant max(c, 0).
+//
+// Layout of the work: thread = one centre i of one mixture; the Gaussians of a mixture are staged in shared memory in
+// "ready" form (negated centre, A = -1/2 log2(e) sym(S), norm, w, x0) in chunks of kChunk. A CTA of 128 threads serves
+// 128 / G whole mixtures when G <= 128 and one mixture otherwise.
+#include "common.cuh"
+
+namespace gmc {
+namespace {
+
+constexpr int kThreads = 128;
+constexpr int kChunk = 1024;
+constexpr float kExpScale = -0.5f * kLog2e;
+
+template <int D>
+struct Ready {
+    static constexpr int kFloats = D + D * (D + 1) / 2 + 3;    // -mu | A | norm, w, x0: 8 (2D) or 12 (3D) floats
+};
+
+// Floats between the staged mixtures of one CTA: a multiple of 4 (float4 reads) whose quarter is odd, so that the
+// records read by the mixtures of one warp fall into different banks.
+__host__ __device__ inline int stage_stride_floats(int floats) {
+    int quads = (floats + 3) / 4;
+    if ((quads & 1) == 0) ++quads;
+    return quads * 4;
+}
+
+template <int D>
+__device__ __forceinline__ void make_ready(const float* r, float constant, float relu_constant, float* out) {
+    constexpr int NS = D * (D + 1) / 2;
+    const float w = r[0];
+#pragma unroll
+    for (int d = 0; d < D; ++d) out[d] = -r[1 + d];
+    const float* C = r + 1 + D;
+    float det;
+    if constexpr (D == 2) {
+        det = C[0] * C[3] - C[1] * C[2];
+        const float inv = 1.f / det;
+        out[D + 0] = kExpScale * C[3] * inv;
+        out[D + 1] = kExpScale * -0.5f * (C[1] + C[2]) * inv;
+        out[D + 2] = kExpScale * C[0] * inv;
+    } else {
+        const float a = C[0], b = C[1], c = C[2], d = C[3], e = C[4], f = C[5], g = C[6], h = C[7], k = C[8];
+        const float A = e * k - f * h, B = -(d * k - f * g), Cc = d * h - e * g;
+        det = a * A + b * B + c * Cc;
+        const float inv = 1.f / det;
+        const float s01 = -(b * k - c * h) * inv, s02 = (b * f - c * e) * inv, s10 = B * inv, s12 = -(a * f - c * d) * inv;
+        const float s20 = Cc * inv, s21 = -(a * h - b * g) * inv;
+        out[D + 0] = kExpScale * A * inv;
+        out[D + 1] = kExpScale * 0.5f * (s01 + s10);
+        out[D + 2] = kExpScale * 0.5f * (s02 + s20);
+        out[D + 3] = kExpScale * (a * k - c * g) * inv;
+        out[D + 4] = kExpScale * 0.5f * (s12 + s21);
+        out[D + 5] = kExpScale * (a * e - b * d) * inv;
+    }
+    out[D + NS + 0] = gauss_norm_factor<D>() * rsqrtf(det);         // sqrt(det S) = 1 / sqrt(det C)
+    out[D + NS + 1] = w;
+    const float initial = (w + constant > 0.f) ? w : -relu_constant;
+    out[D + NS + 2] = fabsf(initial) + 0.1f;
+}
+
+template <int D>
+__global__ void __launch_bounds__(kThreads)
+relu_fixed_point_kernel(const float* __restrict__ mixtures, const float* __restrict__ constants,
+                        float* __restrict__ out_mixtures, float* __restrict__ out_constants,
+                        float* __restrict__ out_initial, long long n_mixtures, int G, int mixtures_per_cta) {
+    constexpr int RF = 1 + D + D * D;
+    constexpr int NS = D * (D + 1) / 2;
+    constexpr int RD = Ready<D>::kFloats;
+    extern __shared__ __align__(16) float ready[];     // [mixtures_per_cta][min(G, kChunk)][RD]
+    const int tid = threadIdx.x;
+    const long long first = (long long)blockIdx.x * mixtures_per_cta;
+    const int local = mixtures_per_cta > 1 ? tid / G : 0;            // which of the CTA's mixtures
+    const long long mix = first + local;
+    const bool mixture_ok = local < mixtures_per_cta && mix < n_mixtures;
+    const float constant = mixture_ok ? __ldg(constants + mix) : 0.f;
+    const float relu_constant = fmaxf(constant, 0.f);
+    const float* src = mixtures + mix * (long long)G * RF;
+    const int stage_stride = stage_stride_floats(min(G, kChunk) * RD);
+    const bool single_chunk = G <= kChunk;
+
+    // rows of this thread: i = row0, row0 + kThreads, ... (one row when G <= kThreads)
+    const int row0 = mixtures_per_cta > 1 ? tid - local * G : tid;
+    for (int base = 0; base < G; base += (mixtures_per_cta > 1 ? G : kThreads)) {
+        const int i = base + row0;
+        const bool row_ok = mixture_ok && i < G;
+        float p[D], sum_w = 0.f, sum_x = 0.f;
+#pragma unroll
+        for (int d = 0; d < D; ++d) p[d] = row_ok ? __ldg(src + (size_t)i * RF + 1 + d) : 0.f;
+        for (int j0 = 0; j0 < G; j0 += kChunk) {
+            const int jc = min(kChunk, G - j0);
+            __syncthreads();                                          // previous chunk fully consumed
+            if (single_chunk && base > 0) {
+                // the only chunk is already staged
+            } else if (mixtures_per_cta > 1) {
+                if (mixture_ok && row0 < jc) {                        // thread (mixture, j) stages Gaussian j
+                    float r[RF];
+#pragma unroll
+                    for (int f = 0; f < RF; ++f) r[f] = __ldg(src + (size_t)(j0 + row0) * RF + f);
+                    make_ready<D>(r, constant, relu_constant, ready + local * stage_stride + row0 * RD);
+                }
+            } else {
+                for (int j = tid; j < jc; j += kThreads) {
+                    float r[RF];
+#pragma unroll
+                    for (int f = 0; f < RF; ++f) r[f] = __ldg(src + (size_t)(j0 + j) * RF + f);
+                    make_ready<D>(r, constant, relu_constant, ready + j * RD);
+                }
+            }
+            __syncthreads();
+            if (row_ok) {
+                const float4* g4 = reinterpret_cast<const float4*>(ready + local * stage_stride);
+#pragma unroll 4
+                for (int j = 0; j < jc; ++j) {
+                    float g[RD];
+#pragma unroll
+                    for (int v = 0; v < RD / 4; ++v) {
+                        const float4 t = g4[j * (RD / 4) + v];
+                        g[4 * v] = t.x; g[4 * v + 1] = t.y; g[4 * v + 2] = t.z; g[4 * v + 3] = t.w;
+                    }
+                    float q;
+                    if constexpr (D == 2) {
+                        const float t0 = p[0] + g[0], t1 = p[1] + g[1];
+                        q = t0 * (g[2] * t0 + 2.f * g[3] * t1) + t1 * (g[4] * t1);
+                    } else {
+                        const float t0 = p[0] + g[0], t1 = p[1] + g[1], t2 = p[2] + g[2];
+                        q = t0 * (g[3] * t0 + 2.f * (g[4] * t1 + g[5] * t2)) + t1 * (g[6] * t1 + 2.f * g[7] * t2) +
+                            t2 * (g[8] * t2);
+                    }
+                    const float e = g[D + NS] * ex2_approx(q);
+                    sum_w = fmaf(g[D + NS + 1], e, sum_w);
+                    sum_x = fmaf(g[D + NS + 2], e, sum_x);
+                }
+            }
+        }
+        if (row_ok) {
+            const float w = __ldg(src + (size_t)i * RF);
+            const float initial = (w + constant > 0.f) ? w : -relu_constant;
+            const float x0 = fabsf(initial) + 0.1f;
+            const float b = fmaxf(sum_w + constant, 0.f) - relu_constant;
+            const float x = x0 * (b + 0.05f) / (sum_x + 0.05f);
+            float* dst = out_mixtures + (mix * (long long)G + i) * RF;
+            dst[0] = x;
+#pragma unroll
+            for (int f = 1; f < RF; ++f) dst[f] = __ldg(src + (size_t)i * RF + f);
+            if (out_initial) {
+                float* ini = out_initial + (mix * (long long)G + i) * RF;
+                ini[0] = initial;
+#pragma unroll
+                for (int f = 1; f < RF; ++f) ini[f] = __ldg(src + (size_t)i * RF + f);
+            }
+            if (i == 0) out_constants[mix] = relu_constant;
+        }
+    }
+}
+
+}  // namespace
+}  // namespace gmc
+
+GMC_DEFINE_TU_CHECK_READER(relu_fixed_point)
+
+extern "C" int gmc_relu_fixed_point(const float* mixtures, const float* constants, float* out_mixtures,
+                                    float* out_constants, float* out_initial, long long n_mixtures, int n_components,
+                                    int n_dims, void* stream) {
+    using namespace gmc;
+    if (n_dims != 2 && n_dims != 3) return GMC_ERR_BAD_DIMS;
+    if (n_mixtures < 0 || n_components <= 0) return GMC_ERR_BAD_DIMS;
+    if (n_mixtures == 0) return GMC_OK;
+    if (!mixtures || !constants || !out_mixtures || !out_constants) return GMC_ERR_NULL_POINTER;
+    const int per_cta = n_components <= kThreads ? kThreads / n_components : 1;
+    const long long blocks = (n_mixtures + per_cta - 1) / per_cta;
+    if (blocks > 0x7fffffffLL) return GMC_ERR_BAD_DIMS;
+    const int staged = n_components < kChunk ? n_components : kChunk;
+    const int rd = n_dims == 2 ? Ready<2>::kFloats : Ready<3>::kFloats;
+    const size_t smem = sizeof(float) * size_t(per_cta) * stage_stride_floats(staged * rd);
+    cudaStream_t st = as_stream(stream);
+    if (n_dims == 2) {
+        if (smem > 48 * 1024)
+            GMC_CUDA_TRY(cudaFuncSetAttribute(relu_fixed_point_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        relu_fixed_point_kernel<2><<<unsigned(blocks), kThreads, smem, st>>>(mixtures, constants, out_mixtures, out_constants,
+                                                                           out_initial, n_mixtures, n_components, per_cta);
+    } else {
+        if (smem > 48 * 1024)
+            GMC_CUDA_TRY(cudaFuncSetAttribute(relu_fixed_point_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        relu_fixed_point_kernel<3><<<unsigned(blocks), kThreads, smem, st>>>(mixtures, constants, out_mixtures, out_constants,
+                                                                           out_initial, n_mixtures, n_components, per_cta);
+    }
+    GMC_LAUNCH_CHECK();
+    return GMC_OK;
+}

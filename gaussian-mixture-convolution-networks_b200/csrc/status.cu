@@ -15,6 +15,7 @@ int gmc_tu_check_lbvh(int* word);
 int gmc_tu_check_mhem_fit(int* word);
 int gmc_tu_check_convolution(int* word);
 int gmc_tu_check_convolution_fitting(int* word);
+int gmc_tu_check_relu_fixed_point(int* word);
 
 extern "C" const char* gmc_status_string(int status) {
     switch (status) {
@@ -50,5 +51,6 @@ extern "C" int gmc_device_check_word(int* word_out) {
     if (int s = gmc_tu_check_mhem_fit(word_out)) return s;
     if (int s = gmc_tu_check_convolution(word_out)) return s;
     if (int s = gmc_tu_check_convolution_fitting(word_out)) return s;
+    if (int s = gmc_tu_check_relu_fixed_point(word_out)) return s;
     return GMC_OK;
 }

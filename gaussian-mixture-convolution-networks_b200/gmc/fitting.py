@@ -91,7 +91,36 @@ class _Log:
             self.writer.add_scalar(name.format(self.layer), fun(self.points), self.epoch)
 
 
+FUSED_FIXED_POINT_MAX_COMPONENTS = 128
+
+
+def fused_relu_fixed_point(mixture: Tensor, constant: Tensor) -> typing.Tuple[Tensor, Tensor, Tensor]:
+    """(initial, fixed point, constant) of `initial_approx_to_relu` + `fixed_point_iteration_to_relu(n_iter=1)` in one
+    kernel (gmc_relu_fixed_point); no gradient is recorded."""
+    from gmc import _native
+    m = mixture.detach().contiguous()
+    c = constant.detach().contiguous()
+    _native.require_cuda_f32(m, "mixture")
+    _native.require_cuda_f32(c, "constant")
+    fp = torch.empty_like(m)
+    initial = torch.empty_like(m)
+    ret_const = torch.empty_like(c)
+    if m.numel() > 0:
+        with torch.cuda.device_of(m):
+            _native.check(_native.lib.gmc_relu_fixed_point(
+                _native.ptr(m), _native.ptr(c), _native.ptr(fp), _native.ptr(ret_const), _native.ptr(initial),
+                gm.n_batch(m) * gm.n_layers(m), gm.n_components(m), gm.n_dimensions(m), _native.stream_of(m)),
+                "relu fixed point")
+    return initial, fp, ret_const
+
+
 def _fixed_point_stage(mixture, constant, log, target=None):
+    needs_grad = torch.is_grad_enabled() and (mixture.requires_grad or constant.requires_grad)
+    if (target is None and not needs_grad and mixture.is_cuda and mixture.dtype == torch.float32
+            and 0 < gm.n_components(mixture) <= FUSED_FIXED_POINT_MAX_COMPONENTS):
+        initial, fp, ret_const = fused_relu_fixed_point(mixture, constant)
+        log.scalar("51.1 fitting {} fixed point iteration mse =", lambda p: mse(mixture, constant, fp, ret_const, p))
+        return initial, fp, ret_const
     start = mixture if target is None else target
     initial = initial_approx_to_relu(start, constant)
     fp, ret_const = fixed_point_iteration_to_relu(mixture, constant, initial)

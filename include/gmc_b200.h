@@ -94,6 +94,19 @@ int gmc_eval_inversed_host(const float* mixture, const float* xes, const float* 
 int gmc_host_pipeline_release(void);
 
 /* ------------------------------------------------------------------------------------------------
+ * ReLU approximation of mixtures (covariance form, [n_mixtures, n_components, 1+D+D*D]) with per-mixture constants by
+ * one fixed-point step, fused (inference path, no gradient):
+ *   out_mixtures  = fixed_point_iteration_to_relu(mixture, constant, initial_approx_to_relu(mixture, constant))
+ *   out_constants = max(constant, 0)
+ *   out_initial   = initial_approx_to_relu(mixture, constant)          (may be NULL)
+ * Replaces the chain of the reference's src/gmc/fitting.py:279-312 (initial_approx_to_relu,
+ * fixed_point_iteration_to_relu with n_iter = 1: two mixture evaluations at the component centres, two covariance
+ * inversions and the element-wise updates around them).
+ * ---------------------------------------------------------------------------------------------- */
+int gmc_relu_fixed_point(const float* mixtures, const float* constants, float* out_mixtures, float* out_constants,
+                         float* out_initial, long long n_mixtures, int n_components, int n_dims, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Batched inverse of n_matrices contiguous row-major DxD matrices (D in {2,3}); `inverses` holds the
  * mathematical inverse in the same layout. In-place (inverses == matrices) is allowed.
  *

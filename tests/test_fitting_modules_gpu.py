@@ -24,8 +24,13 @@ def test_relu_fixed_point_matches_reference_python():
         fp, ret_const = fitting.fixed_point_iteration_to_relu(m, c, initial)
         assert rel_inf(fp.cpu().numpy(), golden[f"relu{idx}_fixed_point"]) < 1e-4
         assert rel_inf(ret_const.cpu().numpy(), golden[f"relu{idx}_ret_const"]) < 1e-6
+        # the strategy takes the fused kernel when no gradient is needed: pinned to the same golden vectors
         out, const, steps = fitting.fixed_point_only(m, c, -1)
-        assert torch.equal(out, fp) and len(steps) == 1
+        assert len(steps) == 1 and rel_inf(steps[0].cpu().numpy(), golden[f"relu{idx}_initial"]) < 1e-6
+        assert rel_inf(out.cpu().numpy(), golden[f"relu{idx}_fixed_point"]) < 1e-4
+        assert rel_inf(const.cpu().numpy(), golden[f"relu{idx}_ret_const"]) < 1e-6
+        out_g = fitting.fixed_point_only(m.clone().requires_grad_(True), c, -1)[0]
+        assert torch.equal(out_g.detach(), fp)
 
 
 def test_evaluate_covariance_form_and_integrate(golden_eval):
@@ -236,3 +241,27 @@ def test_graphed_forward_equals_eager_forward(monkeypatch):
         assert torch.allclose(out, ref, rtol=1e-5, atol=1e-6)
     with pytest.raises(ValueError):
         graph(xs[0][:2])
+
+
+@pytest.mark.parametrize("D,B,L,G", [(2, 3, 4, 16), (3, 2, 5, 8), (3, 2, 3, 64), (2, 2, 2, 48), (3, 1, 2, 300), (2, 1, 1, 1100),
+                                     (3, 1, 1, 1)])
+def test_fused_relu_fixed_point_equals_the_composite_path(D, B, L, G):
+    """gmc_relu_fixed_point against initial_approx_to_relu + fixed_point_iteration_to_relu built from the evaluation
+    kernel: several mixtures per CTA, one mixture per CTA, more components than one shared-memory chunk."""
+    import gmc.fitting as fitting
+    import gmc.mixture as gm
+    m = (synthetic.fit_target_2d(B, L, G, 7 + G) if D == 2 else
+         synthetic.config4_input(n_batch=B * L * max(1, (G + 63) // 64), seed=G).reshape(B, L, -1, 13)[:, :, :G].contiguous()).cuda()
+    m[..., 0] = torch.randn(m.shape[:-1], generator=torch.Generator().manual_seed(G)).cuda()     # both signs
+    c = torch.randn(B, L, generator=torch.Generator().manual_seed(1)).cuda() * 0.3
+    initial_ref = fitting.initial_approx_to_relu(m, c)
+    fp_ref, const_ref = fitting.fixed_point_iteration_to_relu(m, c, initial_ref)
+    initial, fp, const = fitting.fused_relu_fixed_point(m, c)
+    assert torch.equal(initial, initial_ref) and torch.equal(const, const_ref)
+    assert torch.equal(fp[..., 1:], fp_ref[..., 1:])
+    assert torch.allclose(gm.weights(fp), gm.weights(fp_ref), rtol=1e-4, atol=1e-6)
+    # the strategy uses the fused kernel without autograd and the composite path with it
+    with torch.no_grad():
+        a = fitting.fixed_point_only(m, c, G)[0]
+    b = fitting.fixed_point_only(m.clone().requires_grad_(True), c, G)[0]
+    assert torch.allclose(a, b.detach(), rtol=1e-4, atol=1e-6)
