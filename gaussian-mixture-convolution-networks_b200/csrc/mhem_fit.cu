@@ -69,6 +69,7 @@ struct WarpScratch {
     float tgt[NT][RF];        // gathered child Gaussians, padded with (0, 0, I)
     float heap_d[NH];
     unsigned char heap_a[NH], heap_b[NH];
+    unsigned char order[32];  // pair (lane) with the k-th smallest distance
     int idx[R];               // initial representatives
     float r3[NT][R];
     float fw[R];
@@ -76,6 +77,52 @@ struct WarpScratch {
     float outc[R][D * D];
     float gin[R][RF];         // backward: gradient of the node's Gaussians
     float tgrad[NT][RF];      // backward: gradient of the gathered child Gaussians
+};
+
+// Sub-graphs of the single-linkage clustering (valid Gaussians are 0 .. n_valid-1, sub-graph i starts as {i}). Merging
+// appends the higher sub-graph's member list to the lower one's, which keeps the member order that the first-max rule
+// of select() depends on. All state is packed into 64-bit words (8 bits per Gaussian), so it lives in registers:
+//   labels: sub-graph of Gaussian g;  nexts: successor of g in its member list (0xFF = end);  tails: last member.
+template <int NT>
+struct SubGraphs {
+    uint64_t labels = 0ull, tails = 0ull, nexts = ~0ull;
+    __device__ __forceinline__ SubGraphs() {
+#pragma unroll
+        for (int i = 0; i < NT; ++i) { labels |= uint64_t(i) << (8 * i); tails |= uint64_t(i) << (8 * i); }
+    }
+    static __device__ __forceinline__ int get(uint64_t v, int i) { return int((v >> (8 * i)) & 0xFFull); }
+    static __device__ __forceinline__ void set(uint64_t& v, int i, int x) {
+        v = (v & ~(0xFFull << (8 * i))) | (uint64_t(x) << (8 * i));
+    }
+    // joins the sub-graphs of Gaussians a and b; false if they already were one
+    __device__ __forceinline__ bool merge(int a, int b) {
+        const int sa = get(labels, a), sb = get(labels, b);
+        if (sa == sb) return false;
+        const int lo = min(sa, sb), hi = max(sa, sb);
+#pragma unroll
+        for (int g = 0; g < NT; ++g)
+            if (get(labels, g) == hi) set(labels, g, lo);
+        set(nexts, get(tails, lo), hi);       // the head of sub-graph hi is Gaussian hi
+        set(tails, lo, get(tails, hi));
+        return true;
+    }
+    // representative of each of the first R live sub-graphs: its member with the largest |weight| (first of equals)
+    template <int D, int R, typename Scratch>
+    __device__ __forceinline__ void select(Scratch& ws, int n_valid, bool write) const {
+        int sg = -1;
+        for (int i = 0; i < R; ++i) {
+            do { ++sg; } while (sg < n_valid && get(labels, sg) != sg);   // alive while its head labels itself
+            int selected = 255;
+            float max_abs = 0.f;
+            if (sg < n_valid) {
+                for (int gid = sg; gid != 0xFF; gid = get(nexts, gid)) {
+                    const float aw = fabsf(ws.tgt[gid][0]);
+                    if (aw > max_abs) { max_abs = aw; selected = gid; }
+                }
+            }
+            if (write) ws.idx[i] = selected;
+        }
+    }
 };
 
 // ---- the sequential part of fit_initial, run by one lane ----
@@ -110,43 +157,52 @@ __device__ void cluster_and_select(WarpScratch<D, R>& ws, int n_valid) {
         const unsigned char va = ws.heap_a[i], vb = ws.heap_b[i];
         replace_element(vd, va, vb, i, rd, ra, rb);
     }
-    // Sub-graphs of Gaussians (valid Gaussians are 0 .. n_valid-1, sub-graph i starts as {i}). Merging appends the
-    // higher sub-graph's member list to the lower one's, which keeps the member order that the first-max rule below
-    // depends on. All state is packed into 64-bit words (8 bits per Gaussian), so it lives in registers:
-    //   labels: sub-graph of Gaussian g;  nexts: successor of g in its member list (0xFF = end);  tails: last member.
-    auto get = [](uint64_t v, int i) -> int { return int((v >> (8 * i)) & 0xFFull); };
-    auto set = [](uint64_t& v, int i, int x) { v = (v & ~(0xFFull << (8 * i))) | (uint64_t(x) << (8 * i)); };
-    uint64_t labels = 0ull, tails = 0ull, nexts = ~0ull;
-#pragma unroll
-    for (int i = 0; i < NT; ++i) { labels |= uint64_t(i) << (8 * i); tails |= uint64_t(i) << (8 * i); }
+    SubGraphs<NT> graphs;
     int n_subgraphs = n_valid;
     while (n_subgraphs > R) {
         replace_element(INFINITY, 255, 255, 0, rd, ra, rb);
         if (!(rd < INFINITY)) break;
-        const int sa = get(labels, ra), sb = get(labels, rb);
-        if (sa != sb) {
-            const int lo = min(sa, sb), hi = max(sa, sb);
+        if (graphs.merge(ra, rb)) --n_subgraphs;
+    }
+    graphs.template select<D, R>(ws, n_valid, true);
+}
+
+// The same clustering when all finite distances differ (the usual case): a min-heap then pops the pairs in ascending
+// order of distance, so the pop order is the rank of a pair's distance. Lane e < NH holds pair e = (a, b) with
+// distance d (+inf = no edge); the ranks come from NH shuffles, the merges run on registers, uniformly in all lanes.
+// Returns false (and does nothing) if two finite distances are equal or one is NaN: the caller then runs the heap,
+// whose order among equal keys is part of the reference's result.
+template <int D, int R>
+__device__ __forceinline__ bool cluster_and_select_ranked(WarpScratch<D, R>& ws, int n_valid, float d, int a, int b) {
+    constexpr int NT = 2 * R;
+    constexpr int NH = (NT * NT - NT) / 2;
+    const int lane = threadIdx.x & 31;
+    const bool finite = lane < NH && d < INFINITY;
+    bool unusable = lane < NH && d != d;
+    int rank = 0;
 #pragma unroll
-            for (int g = 0; g < NT; ++g)
-                if (get(labels, g) == hi) set(labels, g, lo);
-            set(nexts, get(tails, lo), hi);       // the head of sub-graph hi is Gaussian hi
-            set(tails, lo, get(tails, hi));
-            --n_subgraphs;
+    for (int k = 0; k < NH; ++k) {
+        const float dk = __shfl_sync(0xffffffffu, d, k);
+        if (k != lane) {
+            if (dk < d || (dk == d && k < lane)) ++rank;
+            if (finite && dk == d) unusable = true;
         }
     }
-    int sg = -1;
-    for (int i = 0; i < R; ++i) {
-        do { ++sg; } while (sg < n_valid && get(labels, sg) != sg);   // a sub-graph is alive while its head labels itself
-        int selected = 255;
-        float max_abs = 0.f;
-        if (sg < n_valid) {
-            for (int gid = sg; gid != 0xFF; gid = get(nexts, gid)) {
-                const float aw = fabsf(ws.tgt[gid][0]);
-                if (aw > max_abs) { max_abs = aw; selected = gid; }
-            }
-        }
-        ws.idx[i] = selected;
+    if (__any_sync(0xffffffffu, unusable)) return false;
+    if (lane < NH) ws.order[rank] = (unsigned char)lane;
+    __syncwarp();
+    const int ab = a | (b << 8);
+    SubGraphs<NT> graphs;
+    int n_subgraphs = n_valid;
+    for (int k = 0; k < NH && n_subgraphs > R; ++k) {
+        const int e = ws.order[k];
+        const float dk = __shfl_sync(0xffffffffu, d, e);
+        const int abk = __shfl_sync(0xffffffffu, ab, e);
+        if (!(dk < INFINITY)) break;
+        if (graphs.merge(abk & 0xFF, abk >> 8)) --n_subgraphs;
     }
+    graphs.template select<D, R>(ws, n_valid, lane == 0);
+    return true;
 }
 
 // Reductions over the lanes of one matrix row (fixed target t, lanes t*R .. t*R+R-1) or one matrix column (fixed s,
@@ -283,15 +339,18 @@ __device__ void fit_em_warp(WarpScratch<D, R>& ws, int n_target, float* __restri
             for (int k = 0; k < D; ++k) { const float tt = ws.tgt[i][1 + k] - ws.tgt[j][1 + k]; d += tt * tt; }
             if (sign_of(wa) != sign_of(wb) || fabsf(wa) < kEpsLarge || fabsf(wb) < kEpsLarge) d = INFINITY;
         }
-        if (lane < NH) { ws.heap_d[lane] = INFINITY; ws.heap_a[lane] = 255; ws.heap_b[lane] = 255; }
-        __syncwarp();
-        if (real_pair) {
-            const int pos = i * n_target - (i * (i + 1)) / 2 + (j - i - 1);
-            ws.heap_d[pos] = d; ws.heap_a[pos] = (unsigned char)i; ws.heap_b[pos] = (unsigned char)j;
+        if (!cluster_and_select_ranked<D, R>(ws, n_target, d, i, j)) {
+            // equal distances: the heap decides their order
+            if (lane < NH) { ws.heap_d[lane] = INFINITY; ws.heap_a[lane] = 255; ws.heap_b[lane] = 255; }
+            __syncwarp();
+            if (real_pair) {
+                const int pos = i * n_target - (i * (i + 1)) / 2 + (j - i - 1);
+                ws.heap_d[pos] = d; ws.heap_a[pos] = (unsigned char)i; ws.heap_b[pos] = (unsigned char)j;
+            }
+            __syncwarp();
+            if (lane == 0) cluster_and_select<D, R>(ws, n_target);
         }
-        __syncwarp();
     }
-    if (lane == 0) cluster_and_select<D, R>(ws, n_target);
     __syncwarp();
 
     const Entry<D> e = em_entry<D, R>(ws, lane);

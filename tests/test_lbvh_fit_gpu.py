@@ -82,6 +82,32 @@ def test_fit_forward_matches_oracle(D, G, K, R):
     np.testing.assert_allclose(out, ref, rtol=5e-3, atol=1e-5)
 
 
+@pytest.mark.parametrize("D,R", [(2, 4), (3, 4), (2, 2)])
+def test_fit_with_equal_centre_distances_follows_the_heap_order(D, R):
+    """Centres on a regular grid (many exactly equal pair distances) and a repeated centre (distance 0): the order in
+    which the reference's heap pops equal keys decides the clustering, so the kernel must leave its ranked fast path.
+    (Ties between FITTED centres of higher levels are decided by rounding noise and are not a parity case.)"""
+    import gmc.cpp.extensions.bvh_mhem_fit.binding as fit
+    G, K = 64, 16
+    m = _mixture(D, 2, 2, G, 900 + D + R)
+    side = 8 if D == 2 else 4
+    axes = [torch.arange(side, dtype=torch.float32) * 0.25 for _ in range(D)]
+    grid = torch.stack(torch.meshgrid(*axes, indexing="ij"), -1).reshape(-1, D)
+    m[0, 0, :, 1:1 + D] = grid[:G]
+    m[0, 1, :, 1:1 + D] = grid[:G] * 0.5
+    m[1, 0, 8:10, 1:1 + D] = m[1, 0, 8:9, 1:1 + D]          # two Gaussians on one centre
+    RF = m.shape[-1]
+    fitting, nodes, attribs = fit.forward(m.cuda(), K, R)
+    flat = m.numpy().reshape(-1, G, RF)
+    ref, dump = cpu_oracle.mhem_fit_forward(flat, K, R, dump=True)
+    assert np.array_equal(nodes.cpu().numpy().view(np.uint16).reshape(-1, 2 * G - 1, 4), dump["nodes"])
+    gaussians, integrals, counts, initial = _unpack_attrs(attribs, G, R, RF)
+    assert np.array_equal(counts, dump["counts"][:, :G - 1])
+    fitted = dump["initial"][:, :G - 1, 0] != 255
+    assert np.array_equal(initial[fitted], dump["initial"][:, :G - 1][fitted])
+    np.testing.assert_allclose(fitting.cpu().numpy().reshape(-1, K, RF), ref, rtol=5e-3, atol=1e-5)
+
+
 def test_fit_large_k_returns_the_input_set():
     import gmc.cpp.extensions.bvh_mhem_fit.binding as fit
     G, R = 48, 4
