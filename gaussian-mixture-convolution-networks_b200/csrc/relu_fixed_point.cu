@@ -164,6 +164,173 @@ relu_fixed_point_kernel(const float* __restrict__ mixtures, const float* __restr
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Large mixtures (one CTA per mixture, G >= kLargeMin): the pair loop in packed fp32x2 arithmetic. Two Gaussians share
+// one instruction (their ready values are interleaved in shared memory, so one broadcast float4 load delivers two
+// packed operands), a thread owns P centres, and the normalisation is folded into the two weights, which leaves
+// 9 (2D) / 14 (3D) packed operations and two ex2 per (centre, Gaussian pair) for BOTH sums.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kLargeMin = 256;
+constexpr int kLargePoints = 4;
+
+__device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
+__device__ __forceinline__ float2 ex2_2(float2 q) { return make_float2(ex2_approx(q.x), ex2_approx(q.y)); }
+
+template <int D>
+struct ReadyLarge {
+    // per Gaussian: -mu | A (off-diagonals doubled) | norm w, norm x0 | pad = 8 (2D) or 12 (3D) floats, whole float4
+    static constexpr int kPairFloats = 2 * (D == 2 ? 8 : 12);
+};
+
+template <int D, int P>
+__global__ void __launch_bounds__(kThreads)
+relu_fixed_point_large_kernel(const float* __restrict__ mixtures, const float* __restrict__ constants,
+                              float* __restrict__ out_mixtures, float* __restrict__ out_constants,
+                              float* __restrict__ out_initial, int G) {
+    constexpr int RF = 1 + D + D * D;
+    constexpr int NS = D * (D + 1) / 2;
+    constexpr int RD = Ready<D>::kFloats;
+    constexpr int PF = ReadyLarge<D>::kPairFloats;
+    constexpr int PV = PF / 4;                        // float4 per Gaussian pair
+    extern __shared__ __align__(16) float ready[];    // [kChunk / 2][PF]
+    const int tid = threadIdx.x;
+    const long long mix = blockIdx.x;
+    const float constant = __ldg(constants + mix);
+    const float relu_constant = fmaxf(constant, 0.f);
+    const float* src = mixtures + mix * (long long)G * RF;
+    const bool single_chunk = G <= kChunk;
+
+    for (int base = 0; base < G; base += kThreads * P) {
+        float2 x[P][D], sum_w[P], sum_x[P];
+#pragma unroll
+        for (int p = 0; p < P; ++p) {
+            const int i = base + tid + p * kThreads;
+#pragma unroll
+            for (int d = 0; d < D; ++d) {
+                const float v = i < G ? __ldg(src + (size_t)i * RF + 1 + d) : 0.f;
+                x[p][d] = f2(v, v);
+            }
+            sum_w[p] = f2(0.f, 0.f);
+            sum_x[p] = f2(0.f, 0.f);
+        }
+        for (int j0 = 0; j0 < G; j0 += kChunk) {
+            const int jc = min(kChunk, G - j0);
+            const int jc_even = (jc + 1) & ~1;
+            __syncthreads();
+            if (!(single_chunk && base > 0)) {
+                for (int j = tid; j < jc_even; j += kThreads) {
+                    float rdy[RD];
+                    if (j < jc) {
+                        float r[RF];
+#pragma unroll
+                        for (int f = 0; f < RF; ++f) r[f] = __ldg(src + (size_t)(j0 + j) * RF + f);
+                        make_ready<D>(r, constant, relu_constant, rdy);
+                    } else {
+#pragma unroll
+                        for (int f = 0; f < RD; ++f) rdy[f] = 0.f;      // padding Gaussian: both weights 0
+                    }
+                    float* dst = ready + (j >> 1) * PF + (j & 1);
+#pragma unroll
+                    for (int f = 0; f < D; ++f) dst[2 * f] = rdy[f];
+                    if constexpr (D == 2) {
+                        dst[2 * 2] = rdy[2]; dst[2 * 3] = 2.f * rdy[3]; dst[2 * 4] = rdy[4];
+                    } else {
+                        dst[2 * 3] = rdy[3]; dst[2 * 4] = 2.f * rdy[4]; dst[2 * 5] = 2.f * rdy[5];
+                        dst[2 * 6] = rdy[6]; dst[2 * 7] = 2.f * rdy[7]; dst[2 * 8] = rdy[8];
+                    }
+                    dst[2 * (D + NS)] = rdy[D + NS] * rdy[D + NS + 1];          // norm * w
+                    dst[2 * (D + NS + 1)] = rdy[D + NS] * rdy[D + NS + 2];      // norm * x0
+                    dst[2 * (D + NS + 2)] = 0.f;                                // pad
+                }
+            }
+            __syncthreads();
+            const float4* rp = reinterpret_cast<const float4*>(ready);
+            const int n_pairs = jc_even >> 1;
+#pragma unroll 2
+            for (int j = 0; j < n_pairs; ++j) {
+                float4 v[PV];
+#pragma unroll
+                for (int k = 0; k < PV; ++k) v[k] = rp[j * PV + k];
+                if constexpr (D == 2) {
+                    const float2 nm0 = f2(v[0].x, v[0].y), nm1 = f2(v[0].z, v[0].w), a00 = f2(v[1].x, v[1].y),
+                                 a01 = f2(v[1].z, v[1].w), a11 = f2(v[2].x, v[2].y), cw = f2(v[2].z, v[2].w),
+                                 cx = f2(v[3].x, v[3].y);
+#pragma unroll
+                    for (int p = 0; p < P; ++p) {
+                        const float2 t0 = __fadd2_rn(x[p][0], nm0), t1 = __fadd2_rn(x[p][1], nm1);
+                        const float2 r0 = __ffma2_rn(a01, t1, __fmul2_rn(a00, t0));
+                        const float2 r1 = __fmul2_rn(a11, t1);
+                        const float2 e = ex2_2(__ffma2_rn(t1, r1, __fmul2_rn(t0, r0)));
+                        sum_w[p] = __ffma2_rn(cw, e, sum_w[p]);
+                        sum_x[p] = __ffma2_rn(cx, e, sum_x[p]);
+                    }
+                } else {
+                    const float2 nm0 = f2(v[0].x, v[0].y), nm1 = f2(v[0].z, v[0].w), nm2 = f2(v[1].x, v[1].y),
+                                 a00 = f2(v[1].z, v[1].w), a01 = f2(v[2].x, v[2].y), a02 = f2(v[2].z, v[2].w),
+                                 a11 = f2(v[3].x, v[3].y), a12 = f2(v[3].z, v[3].w), a22 = f2(v[4].x, v[4].y),
+                                 cw = f2(v[4].z, v[4].w), cx = f2(v[5].x, v[5].y);
+#pragma unroll
+                    for (int p = 0; p < P; ++p) {
+                        const float2 t0 = __fadd2_rn(x[p][0], nm0), t1 = __fadd2_rn(x[p][1], nm1),
+                                     t2 = __fadd2_rn(x[p][2], nm2);
+                        const float2 r0 = __ffma2_rn(a02, t2, __ffma2_rn(a01, t1, __fmul2_rn(a00, t0)));
+                        const float2 r1 = __ffma2_rn(a12, t2, __fmul2_rn(a11, t1));
+                        const float2 r2 = __fmul2_rn(a22, t2);
+                        const float2 e = ex2_2(__ffma2_rn(t2, r2, __ffma2_rn(t1, r1, __fmul2_rn(t0, r0))));
+                        sum_w[p] = __ffma2_rn(cw, e, sum_w[p]);
+                        sum_x[p] = __ffma2_rn(cx, e, sum_x[p]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int p = 0; p < P; ++p) {
+            const int i = base + tid + p * kThreads;
+            if (i >= G) continue;
+            const float w = __ldg(src + (size_t)i * RF);
+            const float initial = (w + constant > 0.f) ? w : -relu_constant;
+            const float x0 = fabsf(initial) + 0.1f;
+            const float b = fmaxf(sum_w[p].x + sum_w[p].y + constant, 0.f) - relu_constant;
+            float* dst = out_mixtures + (mix * (long long)G + i) * RF;
+            dst[0] = x0 * (b + 0.05f) / (sum_x[p].x + sum_x[p].y + 0.05f);
+#pragma unroll
+            for (int f = 1; f < RF; ++f) dst[f] = __ldg(src + (size_t)i * RF + f);
+            if (out_initial) {
+                float* ini = out_initial + (mix * (long long)G + i) * RF;
+                ini[0] = initial;
+#pragma unroll
+                for (int f = 1; f < RF; ++f) ini[f] = __ldg(src + (size_t)i * RF + f);
+            }
+        }
+        if (base == 0 && tid == 0) out_constants[mix] = relu_constant;
+    }
+}
+
+template <int D>
+int launch_relu_fixed_point(const float* mixtures, const float* constants, float* out_mixtures, float* out_constants,
+                            float* out_initial, long long n_mixtures, int G, cudaStream_t st) {
+    if (G >= kLargeMin) {
+        if (n_mixtures > 0x7fffffffLL) return GMC_ERR_BAD_DIMS;
+        const int staged_pairs = (min(G, kChunk) + 1) / 2;
+        const size_t smem = sizeof(float) * size_t(staged_pairs) * ReadyLarge<D>::kPairFloats;
+        auto kernel = relu_fixed_point_large_kernel<D, kLargePoints>;
+        if (smem > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        kernel<<<unsigned(n_mixtures), kThreads, smem, st>>>(mixtures, constants, out_mixtures, out_constants, out_initial, G);
+        GMC_LAUNCH_CHECK();
+        return GMC_OK;
+    }
+    const int per_cta = G <= kThreads ? kThreads / G : 1;
+    const long long blocks = (n_mixtures + per_cta - 1) / per_cta;
+    if (blocks > 0x7fffffffLL) return GMC_ERR_BAD_DIMS;
+    const size_t smem = sizeof(float) * size_t(per_cta) * stage_stride_floats(min(G, kChunk) * Ready<D>::kFloats);
+    auto kernel = relu_fixed_point_kernel<D>;
+    if (smem > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    kernel<<<unsigned(blocks), kThreads, smem, st>>>(mixtures, constants, out_mixtures, out_constants, out_initial,
+                                                    n_mixtures, G, per_cta);
+    GMC_LAUNCH_CHECK();
+    return GMC_OK;
+}
+
 }  // namespace
 }  // namespace gmc
 
@@ -177,24 +344,10 @@ extern "C" int gmc_relu_fixed_point(const float* mixtures, const float* constant
     if (n_mixtures < 0 || n_components <= 0) return GMC_ERR_BAD_DIMS;
     if (n_mixtures == 0) return GMC_OK;
     if (!mixtures || !constants || !out_mixtures || !out_constants) return GMC_ERR_NULL_POINTER;
-    const int per_cta = n_components <= kThreads ? kThreads / n_components : 1;
-    const long long blocks = (n_mixtures + per_cta - 1) / per_cta;
-    if (blocks > 0x7fffffffLL) return GMC_ERR_BAD_DIMS;
-    const int staged = n_components < kChunk ? n_components : kChunk;
-    const int rd = n_dims == 2 ? Ready<2>::kFloats : Ready<3>::kFloats;
-    const size_t smem = sizeof(float) * size_t(per_cta) * stage_stride_floats(staged * rd);
     cudaStream_t st = as_stream(stream);
-    if (n_dims == 2) {
-        if (smem > 48 * 1024)
-            GMC_CUDA_TRY(cudaFuncSetAttribute(relu_fixed_point_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-        relu_fixed_point_kernel<2><<<unsigned(blocks), kThreads, smem, st>>>(mixtures, constants, out_mixtures, out_constants,
-                                                                           out_initial, n_mixtures, n_components, per_cta);
-    } else {
-        if (smem > 48 * 1024)
-            GMC_CUDA_TRY(cudaFuncSetAttribute(relu_fixed_point_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-        relu_fixed_point_kernel<3><<<unsigned(blocks), kThreads, smem, st>>>(mixtures, constants, out_mixtures, out_constants,
-                                                                           out_initial, n_mixtures, n_components, per_cta);
-    }
-    GMC_LAUNCH_CHECK();
-    return GMC_OK;
+    return n_dims == 2 ? launch_relu_fixed_point<2>(mixtures, constants, out_mixtures, out_constants, out_initial,
+                                                    n_mixtures, n_components, st)
+                       : launch_relu_fixed_point<3>(mixtures, constants, out_mixtures, out_constants, out_initial,
+                                                    n_mixtures, n_components, st);
 }
+

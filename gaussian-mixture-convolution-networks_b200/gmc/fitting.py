@@ -91,7 +91,7 @@ class _Log:
             self.writer.add_scalar(name.format(self.layer), fun(self.points), self.epoch)
 
 
-FUSED_FIXED_POINT_MAX_COMPONENTS = 128
+FUSED_FIXED_POINT_MAX_COMPONENTS = 4096
 
 
 def fused_relu_fixed_point(mixture: Tensor, constant: Tensor) -> typing.Tuple[Tensor, Tensor, Tensor]:
