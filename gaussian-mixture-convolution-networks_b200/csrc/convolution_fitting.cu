@@ -14,8 +14,8 @@
 //               next, so construction and the mass pass are one sweep without binary searches and without idle lanes
 //   selection   K - 1 greedy splits of the selected internal node with the largest |mass|
 //   aggregation per selected subtree the weighted mean / scatter of the product centres and the weighted mean of
-//               the product covariances; one warp per output Gaussian, lanes hold partial aggregates that are
-//               merged pairwise (the reference walks the leaves sequentially in one thread)
+//               the product covariances; one warp per output Gaussian, lanes sum a strided share of the leaves in
+//               cluster-local coordinates (the reference walks the leaves sequentially in one thread)
 // Same decisions as the reference's convolution_fitting/Tree.cu:63-408 and implementation_forward.h:19-124.
 #include "common.cuh"
 #include "lbvh_device.cuh"
@@ -37,6 +37,16 @@ constexpr int kMaxLevels = 72;
 struct Dims {
     int n_batch, n_channels_in, n_components, n_channels_out, n_kernel_components, n_fitting;
 };
+
+// Warp-wide maximum / minimum of floats (no NaN) with one integer reduction instruction each: the bit pattern with
+// the magnitude bits of negative numbers flipped orders like the float.
+__device__ __forceinline__ int ordered_bits(float v) {
+    const int i = __float_as_int(v);
+    return i ^ ((i >> 31) & 0x7fffffff);
+}
+__device__ __forceinline__ float from_ordered_bits(int i) { return __int_as_float(i ^ ((i >> 31) & 0x7fffffff)); }
+__device__ __forceinline__ float warp_max(float v) { return from_ordered_bits(__reduce_max_sync(0xffffffffu, ordered_bits(v))); }
+__device__ __forceinline__ float warp_min(float v) { return from_ordered_bits(__reduce_min_sync(0xffffffffu, ordered_bits(v))); }
 
 // Quotient and remainder of small non-negative integers (below 2^23) by a fixed divisor without the integer
 // division sequence: the float estimate is off by at most one.
@@ -124,15 +134,8 @@ convolution_fitting_tree_kernel(const float* __restrict__ data, const float* __r
             }
 #pragma unroll
             for (int d = 0; d < D; ++d) {
-#pragma unroll
-                for (int off = 16; off > 0; off >>= 1) {
-                    dh[d] = fmaxf(dh[d], __shfl_xor_sync(0xffffffffu, dh[d], off));
-                    dl[d] = fminf(dl[d], __shfl_xor_sync(0xffffffffu, dl[d], off));
-                    kh[d] = fmaxf(kh[d], __shfl_xor_sync(0xffffffffu, kh[d], off));
-                    kl[d] = fminf(kl[d], __shfl_xor_sync(0xffffffffu, kl[d], off));
-                }
-                hi[d] = fmaxf(hi[d], __fadd_rn(dh[d], kh[d]));
-                lo[d] = fminf(lo[d], __fadd_rn(dl[d], kl[d]));
+                hi[d] = fmaxf(hi[d], __fadd_rn(warp_max(dh[d]), warp_max(kh[d])));
+                lo[d] = fminf(lo[d], __fadd_rn(warp_min(dl[d]), warp_min(kl[d])));
             }
         }
         if (lane == 0) {
@@ -240,6 +243,7 @@ convolution_fitting_tree_kernel(const float* __restrict__ data, const float* __r
         if (n_in == 0) break;
         const uint16_t* queue_in = queues + ((round - 1) & 1) * queue_stride;
         for (int i0 = 0; i0 < n_in; i0 += kThreads) {
+            if (i0 + warp * 32 >= n_in) break;               // nothing queued for this warp (warp-uniform)
             const int i = i0 + tid;
             uint32_t node = 0u, lr = 0u;
             float m = 0.f;
