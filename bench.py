@@ -38,7 +38,7 @@ def _args():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--cpu-batch", type=int, default=4, help="batch slice timed on the host cores")
+    ap.add_argument("--cpu-batch", type=int, default=16, help="batch slice timed on the host cores")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=B_PER_GPU,
                     help="batch per GPU (default: the configuration's 32; smaller values are for profiler captures)")
@@ -113,6 +113,18 @@ class ClockSampler:
         s = sorted(self.samples)
         reasons = sorted(r for r in self.reasons if r not in ("None", "GpuIdle", "ApplicationsClocksSetting"))
         return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": reasons, "samples": len(s)}
+
+
+def _repeat_for(fn, min_seconds=10.0, max_reps=1000):
+    """Runs fn() until min_seconds of wall time have passed -> (repetitions, seconds)."""
+    fn()                                  # page in / thread pool warm-up, not timed
+    reps, t0 = 0, time.perf_counter()
+    while True:
+        fn()
+        reps += 1
+        dt = time.perf_counter() - t0
+        if dt >= min_seconds or reps >= max_reps:
+            return reps, dt
 
 
 def _cpu_baseline(cpu_batch):
@@ -326,12 +338,11 @@ def _secondary_setup(args, rank, dev):
             sample, _ = synthetic.config2(n_batch=32)
             flat = sample.numpy().reshape(-1, 1024, 7).copy()
             flat[..., 0] = abs(flat[..., 0]) + 0.01
-            t0 = time.perf_counter()
-            cpu_oracle.mhem_fit_forward(flat, 64, 4)
-            dt = time.perf_counter() - t0
-            return {"value": flat.shape[0] * 1024 / dt, "unit": "gaussians/s", "cores": cpu_oracle.num_threads(), "kind": "port",
-                    "sample": f"LBVH + BVH-MHEM fit of {flat.shape[0]} mixtures x 1024 Gaussians ({dt:.2f} s); the "
-                              "fixed-point evaluations are not included in the CPU figure"}
+            reps, dt = _repeat_for(lambda: cpu_oracle.mhem_fit_forward(flat, 64, 4))
+            return {"value": reps * flat.shape[0] * 1024 / dt, "unit": "gaussians/s", "cores": cpu_oracle.num_threads(),
+                    "kind": "port",
+                    "sample": f"LBVH + BVH-MHEM fit of {flat.shape[0]} mixtures x 1024 Gaussians, {reps} passes "
+                              f"({dt:.2f} s); the fixed-point evaluations are not included in the CPU figure"}
         # LBVH 56 B/Gaussian + MHEM per mixture 28672 + 2*128*(2G-1) + 1792 B (node attributes written and read once)
         alg_bytes = units * 56 + n_batch * 32 * (28672 + 2 * 128 * 2047 + 1792)
         return ("gaussians_per_s_relu_fit_bvh_mhem_2d", "gaussians/s", units, step, (m_h, c_h),
@@ -351,11 +362,11 @@ def _secondary_setup(args, rank, dev):
             from oracle import cpu_oracle
             cpu_oracle.use_all_cores()
             sd, sk, _ = synthetic.config3(n_batch=64)
-            t0 = time.perf_counter()
-            cpu_oracle.convolution_fitting_forward(sd.numpy(), sk.numpy(), K)
-            dt = time.perf_counter() - t0
-            return {"value": 64 * 16 * 5120 / dt, "unit": "product-gaussians/s", "cores": cpu_oracle.num_threads(),
-                    "kind": "port", "sample": f"the whole layer once (1024 trees x 5120 products, {dt:.2f} s)"}
+            sdn, skn = sd.numpy(), sk.numpy()
+            reps, dt = _repeat_for(lambda: cpu_oracle.convolution_fitting_forward(sdn, skn, K))
+            return {"value": reps * 64 * 16 * 5120 / dt, "unit": "product-gaussians/s", "cores": cpu_oracle.num_threads(),
+                    "kind": "port",
+                    "sample": f"the whole layer (1024 trees x 5120 products), {reps} passes ({dt:.2f} s)"}
         alg_bytes = (d_h.numel() + k_h.numel()) * 4 + n_batch * 16 * (5120 * 4 + 2 * K * 4 + K * 7 * 4 + K * 4 * 4)
         return ("product_gaussians_per_s_convolution_fitting_2d", "product-gaussians/s", units, step, (d_h, k_h),
                 f"config3: convolution_fitting forward, B={n_batch}/GPU Cin=8 G=128 Cout=16 Gk=5 -> K=128 (T=5120)",
@@ -385,18 +396,22 @@ def _secondary_setup(args, rank, dev):
         cpu_oracle.use_all_cores()
         # dominant stage on the CPU: the four convolution-fitting layers on a batch slice (random data of the layer shapes)
         g = torch.Generator().manual_seed(1)
-        total, dt = 0, 0.0
+        layers = []
         for (cin, gcomp, cout, kfit) in ((1, 64, 8, 64), (8, 64, 16, 32), (16, 32, 32, 16), (32, 16, 64, 8)):
             cov, _ = synthetic.covariances_and_inverses((32, cin, gcomp), 3, 0.03, 0.15, g)
             data = synthetic.pack(torch.rand(32, cin, gcomp, generator=g), torch.rand(32, cin, gcomp, 3, generator=g) * 2 - 1, cov)
             kcov, _ = synthetic.covariances_and_inverses((cout, cin, 5), 3, 0.1, 0.4, g)
             kern = synthetic.pack(torch.randn(cout, cin, 5, generator=g) + 0.1, torch.randn(cout, cin, 5, 3, generator=g), kcov)
-            t0 = time.perf_counter()
-            cpu_oracle.convolution_fitting_forward(data.numpy(), kern.numpy(), kfit)
-            dt += time.perf_counter() - t0
-        return {"value": 32 / dt, "unit": "samples/s", "cores": cpu_oracle.num_threads(), "kind": "port",
-                "sample": f"the four convolution-fitting layers only (the dominant stage) on 32 samples ({dt:.2f} s); "
-                          "ReLU fixed-point evaluations and normalisations are not included"}
+            layers.append((data.numpy(), kern.numpy(), kfit))
+
+        def four_layers():
+            for data, kern, kfit in layers:
+                cpu_oracle.convolution_fitting_forward(data, kern, kfit)
+
+        reps, dt = _repeat_for(four_layers)
+        return {"value": reps * 32 / dt, "unit": "samples/s", "cores": cpu_oracle.num_threads(), "kind": "port",
+                "sample": f"the four convolution-fitting layers only (the dominant stage) on 32 samples, {reps} passes "
+                          f"({dt:.2f} s); ReLU fixed-point evaluations and normalisations are not included"}
     keys = n_batch * (8 * 320 + (16 + 32 + 64) * 2560)
     return ("samples_per_s_gmcn3d_forward", "samples/s", n_batch, step, (x_h,),
             f"config4: GMCN-3D forward, B={n_batch}/GPU, 64 input Gaussians, conv-fit layers 1->8->16->32->64 "
@@ -502,6 +517,8 @@ def main():
         import torch
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"      # keeps NCCL's version banner out of stdout (one JSON line only)
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:

@@ -301,10 +301,41 @@ convolution_fitting_tree_kernel(const float* __restrict__ data, const float* __r
     }
 }
 
-template <bool STAGED>
-__device__ __forceinline__ float load_record(const float* p) {
-    if constexpr (STAGED) return *p;
-    else return __ldg(p);
+// Staged input record. 3D: the 13 floats of a Gaussian are read as 4 float4; records are 20 floats apart, an odd
+// number of float4, so that arbitrary records spread evenly over the 8 groups of 4 banks (a stride of 16 floats would
+// put all records on two of them). 2D: the 7 floats are read one by one at their natural (odd) stride, which measured
+// faster than 2 float4 at a stride of 12.
+template <int D>
+struct StagedRecord {
+    static constexpr int kFloats = D == 2 ? 7 : 16;
+    static constexpr int kStride = D == 2 ? 7 : 20;
+};
+
+// All floats of input Gaussian `index`: from the padded shared-memory copy (float4 reads: a quarter of the
+// shared-memory wavefronts of scalar reads at arbitrary records) or from global memory.
+template <int D, bool STAGED>
+__device__ __forceinline__ void load_gaussian(const float* base, int index, float* out) {
+    constexpr int RF = 1 + D + D * D;
+    if constexpr (STAGED && D == 2) {
+        const float* src = base + size_t(index) * RF;
+#pragma unroll
+        for (int f = 0; f < RF; ++f) out[f] = src[f];
+    } else if constexpr (STAGED) {
+        constexpr int RP = StagedRecord<D>::kFloats;
+        const float4* src = reinterpret_cast<const float4*>(base + size_t(index) * StagedRecord<D>::kStride);
+        float padded[RP];
+#pragma unroll
+        for (int v = 0; v < RP / 4; ++v) {
+            const float4 t = src[v];
+            padded[4 * v] = t.x; padded[4 * v + 1] = t.y; padded[4 * v + 2] = t.z; padded[4 * v + 3] = t.w;
+        }
+#pragma unroll
+        for (int f = 0; f < RF; ++f) out[f] = padded[f];
+    } else {
+        const float* src = base + size_t(index) * RF;
+#pragma unroll
+        for (int f = 0; f < RF; ++f) out[f] = __ldg(src + f);
+    }
 }
 
 // One warp, one output Gaussian: sums over the leaves [start, end) of its subtree (see the kernel below).
@@ -324,19 +355,19 @@ __device__ __forceinline__ void aggregate_output(const float* data_b, const floa
         for (int e = lane; e < D * D; e += 32) c_k[e] = 0.f;
         return;
     }
-    auto records = [&](int t, const float*& dg, const float*& kg) {
+    auto records = [&](int t, float* dg, float* kg) {
         int ki, rem, ci, gi;
         by_gc.split(t, ki, rem);
         by_g.split(rem, ci, gi);
-        dg = data_b + (size_t(ci) * G + gi) * RF;
-        kg = kernels_o + (size_t(ci) * Gk + ki) * RF;
+        load_gaussian<D, STAGED>(data_b, ci * G + gi, dg);
+        load_gaussian<D, STAGED>(kernels_o, ci * Gk + ki, kg);
     };
     float p0[D];
     {
-        const float *dg, *kg;
+        float dg[RF], kg[RF];
         records(__ldg(nodesobjs + start), dg, kg);
 #pragma unroll
-        for (int d = 0; d < D; ++d) p0[d] = load_record<STAGED>(dg + 1 + d) + load_record<STAGED>(kg + 1 + d);
+        for (int d = 0; d < D; ++d) p0[d] = dg[1 + d] + kg[1 + d];
     }
     float W = 0.f, S1[D], S2[NS], S3[D * D];
 #pragma unroll
@@ -346,13 +377,13 @@ __device__ __forceinline__ void aggregate_output(const float* data_b, const floa
 #pragma unroll
     for (int e = 0; e < D * D; ++e) S3[e] = 0.f;
     for (int i = start + lane; i < end; i += 32) {
-        const float *dg, *kg;
+        float dg[RF], kg[RF];
         records(__ldg(nodesobjs + i), dg, kg);
-        const float w = load_record<STAGED>(dg) * load_record<STAGED>(kg);
+        const float w = dg[0] * kg[0];
         float q[D], wq[D];
 #pragma unroll
         for (int d = 0; d < D; ++d) {
-            q[d] = (load_record<STAGED>(dg + 1 + d) + load_record<STAGED>(kg + 1 + d)) - p0[d];
+            q[d] = (dg[1 + d] + kg[1 + d]) - p0[d];
             wq[d] = w * q[d];
             S1[d] += wq[d];
         }
@@ -363,7 +394,7 @@ __device__ __forceinline__ void aggregate_output(const float* data_b, const floa
 #pragma unroll
             for (int c = a; c < D; ++c) { S2[e2] = fmaf(wq[a], q[c], S2[e2]); ++e2; }
 #pragma unroll
-        for (int e = 0; e < D * D; ++e) S3[e] = fmaf(w, load_record<STAGED>(dg + 1 + D + e) + load_record<STAGED>(kg + 1 + D + e), S3[e]);
+        for (int e = 0; e < D * D; ++e) S3[e] = fmaf(w, dg[1 + D + e] + kg[1 + D + e], S3[e]);
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
@@ -447,13 +478,17 @@ convolution_fitting_aggregate_kernel(const float* __restrict__ data, const float
     const float* data_b = data + size_t(b) * Cin * G * RF;
     const float* kernels_o = kernels + size_t(o) * Cin * Gk * RF;
     if constexpr (STAGED) {
+        constexpr int RP = StagedRecord<D>::kStride;
         float* staged = reinterpret_cast<float*>(smem_bytes);
         const int n_data = Cin * G * RF, n_kernel = Cin * Gk * RF;
-        for (int i = threadIdx.x; i < n_data; i += 256) staged[i] = __ldg(data_b + i);
-        for (int i = threadIdx.x; i < n_kernel; i += 256) staged[n_data + i] = __ldg(kernels_o + i);
+        for (int i = threadIdx.x; i < n_data + n_kernel; i += 256) {
+            const float v = i < n_data ? __ldg(data_b + i) : __ldg(kernels_o + (i - n_data));
+            const int record = i / RF;                       // kernel records follow the data records
+            staged[record * RP + (i - record * RF)] = v;
+        }
         __syncthreads();
         data_b = staged;
-        kernels_o = staged + n_data;
+        kernels_o = staged + size_t(Cin) * G * RP;
     }
     const int* nodesobjs = nodesobjs_all + size_t(tree) * T - n_internal;     // indexed by node id of the leaf
     const FastDivisor by_gc(G * Cin), by_g(G);
@@ -707,7 +742,7 @@ extern "C" int gmc_convolution_fitting_forward(const float* data, const float* k
     const long long agg_blocks = blocks * groups_per_tree;
     if (agg_blocks > 0x7fffffffLL) return GMC_ERR_BAD_DIMS;
     const size_t staged_bytes = sizeof(float) * size_t(n_channels_in) * (n_components + n_kernel_components) *
-                                size_t(1 + n_dims + n_dims * n_dims);
+                                size_t(n_dims == 2 ? StagedRecord<2>::kStride : StagedRecord<3>::kStride);
     const bool staged = staged_bytes <= kAggMaxStagedBytes;
     if (n_dims == 2) {
         if (int s = launch_convfit_forward<2>(data, kernels, n, nodesobjs, fitting_subtrees, fitting, cached_pos_covs,
