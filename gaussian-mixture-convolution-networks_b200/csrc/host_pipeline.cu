@@ -95,11 +95,39 @@ extern "C" int gmc_eval_inversed_host(const float* mixture, const float* xes, co
 
     // xes shared by the whole batch: its gradient sums over the batch inside one launch, so the batch stays whole
     const bool shared_xes = n_batch_xes == 1 && n_batch > 1;
-    if (n_slices <= 0) n_slices = 8;
-    if (n_slices > n_batch) n_slices = n_batch;
-    if (shared_xes) n_slices = 1;
-    const int per = (n_batch + n_slices - 1) / n_slices;          // batch entries per slice
-    n_slices = (n_batch + per - 1) / per;
+    // Slice plan. n_slices > 0: equal slices. n_slices == 0: slices of about n_batch / 8 with short slices at both
+    // ends (1, 2, ... entries), because the copy-in of the first slice and the copy-out of the last one are the only
+    // copies that nothing overlaps.
+    constexpr int kMaxSlices = 256;
+    int starts[kMaxSlices + 1];
+    int per;                                                       // largest slice
+    if (shared_xes || n_slices == 1) {
+        starts[0] = 0; starts[1] = n_batch; n_slices = 1; per = n_batch;
+    } else if (n_slices > 0) {
+        if (n_slices > n_batch) n_slices = n_batch;
+        if (n_slices > kMaxSlices) n_slices = kMaxSlices;
+        per = (n_batch + n_slices - 1) / n_slices;
+        n_slices = (n_batch + per - 1) / per;
+        for (int i = 0; i <= n_slices; ++i) starts[i] = i * per < n_batch ? i * per : n_batch;
+    } else {
+        per = n_batch >= 8 ? n_batch / 8 : 1;
+        int sizes[kMaxSlices];
+        int n = 0, head = 0, tail = n_batch;
+        // ramp up from the front and mirror it at the back while at least two full slices remain in the middle
+        int ramp[8], n_ramp = 0;
+        for (int r = 1; r < per && n_ramp < 8 && tail - head - 2 * r >= 2 * per; r *= 2) {
+            ramp[n_ramp++] = r; head += r; tail -= r;
+        }
+        for (int i = 0; i < n_ramp; ++i) sizes[n++] = ramp[i];
+        for (int b0 = head; b0 < tail && n < kMaxSlices - 8; b0 += per) sizes[n++] = (b0 + per <= tail) ? per : tail - b0;
+        for (int i = n_ramp - 1; i >= 0; --i) sizes[n++] = ramp[i];
+        n_slices = n;
+        starts[0] = 0;
+        for (int i = 0; i < n; ++i) starts[i + 1] = starts[i] + sizes[i];
+        if (starts[n_slices] != n_batch) {                         // plan did not fit the table: one slice per entry group
+            n_slices = 1; starts[1] = n_batch; per = n_batch;
+        }
+    }
 
     const size_t rf = size_t(1 + n_dims + n_dims * n_dims);
     const size_t m_row = size_t(n_layers) * n_components * rf;     // floats per batch entry
@@ -122,8 +150,8 @@ extern "C" int gmc_eval_inversed_host(const float* mixture, const float* xes, co
     int status = GMC_OK;
     for (int i = 0; i < n_slices && status == GMC_OK; ++i) {
         const int k = i % kSlots;
-        const int b0 = i * per;
-        const int nb = (b0 + per <= n_batch) ? per : n_batch - b0;
+        const int b0 = starts[i];
+        const int nb = starts[i + 1] - b0;
         const int nbx = n_batch_xes == 1 ? 1 : nb;
         const int bx0 = n_batch_xes == 1 ? 0 : b0;
         float* d = p.slot[k];

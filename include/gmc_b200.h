@@ -93,6 +93,11 @@ int gmc_eval_inversed_host(const float* mixture, const float* xes, const float* 
                            int n_dims, int n_batch_xes, int n_layers_xes, int n_xes, int n_slices);
 int gmc_host_pipeline_release(void);
 
+/* Measurement aid: launches independent scalar FFMA chains (32 warps per SM, nothing but FFMA) on the stream and
+ * returns the number of floating-point operations of the launch in *flop_out; timed with CUDA events it gives the
+ * FP32 peak of the device at its current clocks. sink: one device float (never written). No reference counterpart. */
+int gmc_fp32_fma_probe(float* sink, int iterations, double* flop_out, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * ReLU approximation of mixtures (covariance form, [n_mixtures, n_components, 1+D+D*D]) with per-mixture constants by
  * one fixed-point step, fused (inference path, no gradient):
