@@ -2,7 +2,8 @@
 //
 // The batch is cut into slices. Three streams run a software pipeline over two device slots:
 //   copy-in  : host -> device of slice i+1 (mixture, xes, grad_out)
-//   compute  : forward + backward kernels of slice i
+//   compute  : forward + backward kernels of slice i (one stream per slot, so that the first CTAs of a slice fill the
+//              SMs that the last wave of the previous slice leaves idle)
 //   copy-out : device -> host of slice i-1 (out, grad_mixture, grad_xes)
 // PCIe is full duplex, so with page-locked host buffers both copy directions hide behind the kernels and the
 // call costs about one slice of copy-in, the kernels, and one slice of copy-out.
@@ -21,7 +22,7 @@ constexpr int kMaxDevices = 64;
 
 struct DevicePipe {
     bool ready = false;
-    cudaStream_t s_in = nullptr, s_comp = nullptr, s_out = nullptr;
+    cudaStream_t s_in = nullptr, s_comp[kSlots] = {}, s_out = nullptr;
     cudaEvent_t in_done[kSlots] = {}, comp_done[kSlots] = {}, out_done[kSlots] = {};
     float* slot[kSlots] = {};
     size_t slot_floats = 0;
@@ -33,7 +34,7 @@ DevicePipe g_pipes[kMaxDevices];
 int pipe_prepare(DevicePipe& p, size_t need_floats) {
     if (!p.ready) {
         GMC_CUDA_TRY(cudaStreamCreateWithFlags(&p.s_in, cudaStreamNonBlocking));
-        GMC_CUDA_TRY(cudaStreamCreateWithFlags(&p.s_comp, cudaStreamNonBlocking));
+        for (int k = 0; k < kSlots; ++k) GMC_CUDA_TRY(cudaStreamCreateWithFlags(&p.s_comp[k], cudaStreamNonBlocking));
         GMC_CUDA_TRY(cudaStreamCreateWithFlags(&p.s_out, cudaStreamNonBlocking));
         for (int k = 0; k < kSlots; ++k) {
             GMC_CUDA_TRY(cudaEventCreateWithFlags(&p.in_done[k], cudaEventDisableTiming));
@@ -64,7 +65,7 @@ int pipe_release(DevicePipe& p) {
         GMC_CUDA_TRY(cudaEventDestroy(p.out_done[k]));
     }
     GMC_CUDA_TRY(cudaStreamDestroy(p.s_in));
-    GMC_CUDA_TRY(cudaStreamDestroy(p.s_comp));
+    for (int k = 0; k < kSlots; ++k) GMC_CUDA_TRY(cudaStreamDestroy(p.s_comp[k]));
     GMC_CUDA_TRY(cudaStreamDestroy(p.s_out));
     p = DevicePipe();
     return GMC_OK;
@@ -168,17 +169,17 @@ extern "C" int gmc_eval_inversed_host(const float* mixture, const float* xes, co
         GMC_CUDA_TRY(cudaEventRecord(p.in_done[k], p.s_in));
 
         // compute: the slot's outputs are free once slice i-2 has been copied out
-        GMC_CUDA_TRY(cudaStreamWaitEvent(p.s_comp, p.in_done[k], 0));
-        if (i >= kSlots) GMC_CUDA_TRY(cudaStreamWaitEvent(p.s_comp, p.out_done[k], 0));
+        GMC_CUDA_TRY(cudaStreamWaitEvent(p.s_comp[k], p.in_done[k], 0));
+        if (i >= kSlots) GMC_CUDA_TRY(cudaStreamWaitEvent(p.s_comp[k], p.out_done[k], 0));
         if (out)
             status = gmc_eval_inversed_forward(d + off_m, d + off_x, d + off_o, nb, n_layers, n_components, n_dims, nbx,
-                                               n_layers_xes, n_xes, p.s_comp);
+                                               n_layers_xes, n_xes, p.s_comp[k]);
         if (status == GMC_OK && backward)
             status = gmc_eval_inversed_backward(d + off_g, d + off_m, d + off_x, grad_mixture ? d + off_gm : nullptr,
                                                 grad_xes ? d + off_gx : nullptr, nb, n_layers, n_components, n_dims,
-                                                nbx, n_layers_xes, n_xes, p.s_comp);
+                                                nbx, n_layers_xes, n_xes, p.s_comp[k]);
         if (status != GMC_OK) break;
-        GMC_CUDA_TRY(cudaEventRecord(p.comp_done[k], p.s_comp));
+        GMC_CUDA_TRY(cudaEventRecord(p.comp_done[k], p.s_comp[k]));
 
         // copy-out
         GMC_CUDA_TRY(cudaStreamWaitEvent(p.s_out, p.comp_done[k], 0));
@@ -195,7 +196,8 @@ extern "C" int gmc_eval_inversed_host(const float* mixture, const float* xes, co
     }
     // the host buffers are valid when the call returns; drain all three streams even after an error
     cudaError_t e1 = cudaStreamSynchronize(p.s_in);
-    cudaError_t e2 = cudaStreamSynchronize(p.s_comp);
+    cudaError_t e2 = cudaStreamSynchronize(p.s_comp[0]);
+    if (e2 == cudaSuccess) e2 = cudaStreamSynchronize(p.s_comp[1]);
     cudaError_t e3 = cudaStreamSynchronize(p.s_out);
     if (status != GMC_OK) return status;
     GMC_CUDA_TRY(e1);
