@@ -103,6 +103,38 @@ def relu_fit_cases(gm, fitting):
     return cases
 
 
+def strategy_cases(gm, fitting):
+    """Outputs of the reference's other ReLU-fit strategies (src/gmc/fitting.py:19-54 solver, :117-153
+    fixed_point_and_max, :204-240 fixed_point_and_mhem with representative_select_for_relu / mhem_fit_a_to_b,
+    :243-276 splitter), evaluated in fp64 on seeded inputs."""
+    cases = {}
+    g = torch.Generator().manual_seed(2024)
+    for idx, (D, B, L, G, K) in enumerate(((2, 2, 2, 20, 8), (3, 2, 2, 12, 4))):
+        w = torch.randn(B, L, G, generator=g)
+        p = torch.rand(B, L, G, D, generator=g) * 2 - 1
+        A = torch.rand(B, L, G, D, D, generator=g) * 2 - 1
+        c = (A @ A.transpose(-1, -2) + torch.eye(D) * 0.05) * 0.05
+        mixture = gm.pack_mixture(w, p, c).contiguous()
+        constant = torch.randn(B, L, generator=g) * 0.3
+        m64, c64 = mixture.double(), constant.double()
+        cases[f"s{idx}_mixture"] = mixture.numpy()
+        cases[f"s{idx}_constant"] = constant.numpy()
+        cases[f"s{idx}_k"] = np.array(K)
+        out, const, _ = fitting.fixed_point_and_max(m64, c64, K)
+        cases[f"s{idx}_max"], cases[f"s{idx}_max_const"] = out.numpy(), const.numpy()
+        out, const, steps = fitting.fixed_point_and_mhem(m64, c64, K)
+        cases[f"s{idx}_mhem"], cases[f"s{idx}_mhem_selected"] = out.numpy(), steps[2].numpy()
+        # the dense EM raises likelihoods to powers of about 20 |w|: the reference's own fp32 run differs from its
+        # fp64 run by up to 6e-3, so the fp32 result is stored as well
+        cases[f"s{idx}_mhem_f32"] = fitting.fixed_point_and_mhem(mixture, constant, K)[0].numpy()
+        # the reference's solver adds the constant without a trailing axis (fitting.py:40): it only accepts [B, L, 1]
+        out, const, _ = fitting.solver(m64, c64.unsqueeze(-1), K)
+        cases[f"s{idx}_solver"] = out.numpy()
+        positive = gm.pack_mixture(gm.weights(m64).abs() + 0.1, gm.positions(m64), gm.covariances(m64))
+        cases[f"s{idx}_split"] = fitting.splitter(positive, [G + 3, G + 5]).numpy()
+    return cases
+
+
 def main():
     gm, fitting, mat_tools = ref_python.load()
     np.savez_compressed(os.path.join(HERE, "eval_inversed.npz"), **eval_cases(gm))
@@ -113,6 +145,8 @@ def main():
     gm.evaluate_inversed = lambda m, x: gm.evaluate_componentwise_inversed(m, x).sum(-1)
     np.savez_compressed(os.path.join(HERE, "relu_fit.npz"), **relu_fit_cases(gm, fitting))
     print("wrote relu_fit.npz")
+    np.savez_compressed(os.path.join(HERE, "strategies.npz"), **strategy_cases(gm, fitting))
+    print("wrote strategies.npz")
 
 
 if __name__ == "__main__":

@@ -265,3 +265,48 @@ def test_fused_relu_fixed_point_equals_the_composite_path(D, B, L, G):
         a = fitting.fixed_point_only(m, c, G)[0]
     b = fitting.fixed_point_only(m.clone().requires_grad_(True), c, G)[0]
     assert torch.allclose(a, b.detach(), rtol=1e-4, atol=1e-6)
+
+
+def _sorted_rows(a):
+    """Rows of every [.., n, V] mixture sorted lexicographically (strategies may order equal sets differently)."""
+    flat = a.reshape(-1, a.shape[-2], a.shape[-1])
+    return np.stack([m[np.lexsort(m.T[::-1])] for m in flat])
+
+
+def test_other_relu_fit_strategies_match_reference_python():
+    """fixed_point_and_max, fixed_point_and_mhem (dense EM), solver (pseudo inverse) and splitter against outputs of
+    the reference's own Python (tests/golden/strategies.npz; fp64 there, fp32 kernels here)."""
+    import gmc.fitting as fitting
+    import gmc.mixture as gm
+    golden = dict(np.load(os.path.join(ROOT, "tests", "golden", "strategies.npz")))
+    for idx in (0, 1):
+        m = torch.from_numpy(golden[f"s{idx}_mixture"]).cuda()
+        c = torch.from_numpy(golden[f"s{idx}_constant"]).cuda()
+        K = int(golden[f"s{idx}_k"])
+        G = m.shape[2]
+        out, const, steps = fitting.fixed_point_and_max(m, c, K)
+        assert rel_inf(out.cpu().numpy(), golden[f"s{idx}_max"]) < 1e-4
+        assert rel_inf(const.cpu().numpy(), golden[f"s{idx}_max_const"]) < 1e-6 and len(steps) == 2
+        out, const, steps = fitting.fixed_point_and_mhem(m, c, K)
+        assert len(steps) == 3 and rel_inf(steps[2].cpu().numpy(), golden[f"s{idx}_mhem_selected"]) < 1e-4
+        assert rel_inf(out.cpu().numpy(), golden[f"s{idx}_mhem_f32"]) < 1e-4      # the reference's own fp32 run
+        assert rel_inf(out.cpu().numpy(), golden[f"s{idx}_mhem"]) < 1e-2          # fp64: powers of about 20 |w| amplify rounding
+        out, const, steps = fitting.solver(m, c, K)
+        # the pseudo inverse of a badly conditioned G x G system in fp32: compare what the weights are solved for,
+        # the values of the fitted mixture at the centres
+        ref = torch.from_numpy(golden[f"s{idx}_solver"]).cuda().float()
+        centres = gm.positions(m)
+        assert rel_inf(gm.evaluate(out, centres).cpu().numpy(), gm.evaluate(ref, centres).cpu().numpy()) < 2e-2
+        positive = gm.pack_mixture(gm.weights(m).abs() + 0.1, gm.positions(m), gm.covariances(m))
+        split = fitting.splitter(positive, [G + 3, G + 5])
+        ref_split = golden[f"s{idx}_split"]
+        assert split.shape == ref_split.shape
+        # The displacement of the two halves is built from a ROW of the eigenvector matrix (reference fitting.py:265),
+        # i.e. it mixes components of eigenvectors whose signs are the eigen-solver's choice: the centres of the halves
+        # are not pinned. Pinned: the set of (weight, covariance) rows and the weighted mean of the centres.
+        D = gm.n_dimensions(m)
+        mine, ref = split.cpu().numpy(), ref_split
+        keep = [0] + list(range(1 + D, mine.shape[-1]))
+        assert np.abs(_sorted_rows(mine[..., keep]) - _sorted_rows(ref[..., keep])).max() < 1e-3
+        centre = lambda a: (a[..., :1] * a[..., 1:1 + D]).sum(-2)
+        assert np.abs(centre(mine) - centre(ref)).max() < 1e-3
