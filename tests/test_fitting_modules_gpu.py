@@ -1,5 +1,6 @@
 """GPU: the Python layer above the kernels (gmc.fitting, gmc.modules, gmc.model) against golden vectors from the
 reference's Python and against the CPU oracle."""
+import math
 import os
 
 import numpy as np
@@ -310,3 +311,60 @@ def test_other_relu_fit_strategies_match_reference_python():
         assert np.abs(_sorted_rows(mine[..., keep]) - _sorted_rows(ref[..., keep])).max() < 1e-3
         centre = lambda a: (a[..., :1] * a[..., 1:1 + D]).sum(-2)
         assert np.abs(centre(mine) - centre(ref)).max() < 1e-3
+
+
+def test_dropout_batchnorm_and_the_two_optimiser_step():
+    """Dropout drops whole channels only in training; BatchNorm (per-sample mode) makes the sampled standard deviation
+    one; the training step of the reference's runners (loss optimiser + weight-decay optimiser,
+    src/modelnet_classification/main.py:111-124) runs through Net."""
+    import gmc.mixture as gm
+    import gmc.model as model
+    import gmc.modules as modules
+    m = synthetic.fit_target_2d(8, 16, 10, 21).cuda()
+    m[..., 0] = m[..., 0].abs() + 0.1
+    const = torch.zeros(8, 16).cuda()
+    drop = modules.Dropout(0.5).cuda()
+    drop.eval()
+    assert torch.equal(drop((m, const))[0], m)
+    drop.train()
+    torch.manual_seed(0)
+    out, _ = drop((m, const))
+    dropped = gm.weights(out).abs().sum(-1) == 0
+    assert 0 < dropped.sum().item() < dropped.numel()
+    assert torch.equal(gm.positions(out)[dropped], torch.zeros_like(gm.positions(out)[dropped]))
+    assert torch.allclose(gm.weights(out)[~dropped], 2.0 * gm.weights(m)[~dropped])
+    eye = torch.eye(2).cuda().expand_as(gm.covariances(out)[dropped])
+    assert torch.equal(gm.covariances(out)[dropped], eye)
+
+    norm = modules.BatchNorm(16, batch_norm=False).cuda()
+    torch.manual_seed(1)
+    y, y_const = norm((m, const))
+    lo = gm.positions(y).reshape(8, -1, 2).min(1)[0].view(8, 1, 1, 2)
+    hi = gm.positions(y).reshape(8, -1, 2).max(1)[0].view(8, 1, 1, 2)
+    torch.manual_seed(1)                               # the layer's own 1000 sample points
+    pts = (torch.rand(8, 16, 1000, 2, device="cuda") * 1.3 - 0.15) * (hi - lo) + lo
+    values = (gm.evaluate(y, pts) + y_const.unsqueeze(-1)).detach()
+    assert (values.std(dim=2) - 1).abs().max().item() < 1e-3
+    # the constant is shifted by the mean of the UNSCALED samples, as in the reference (modules.py:425)
+    unscaled_mean = (gm.evaluate(m, pts) + const.unsqueeze(-1)).mean(dim=2)
+    assert torch.allclose(y_const, const - unscaled_mean, atol=1e-5)
+
+    cfg = model.Config(n_dims=2)
+    cfg.layers = [model.Layer(4, 1, 16, 8), model.Layer(10, 1, 8, 4)]
+    torch.manual_seed(3)
+    net = model.Net(config=cfg).cuda().train()
+    kernel_optimiser = torch.optim.Adam(net.parameters(), lr=1e-3)
+    weight_decay_optimiser = torch.optim.SGD(net.parameters(), lr=1e-2)
+    x = synthetic.fit_target_2d(4, 1, 12, 5)
+    x[..., 0] = x[..., 0].abs() + 0.1
+    target = torch.tensor([1, 3, 5, 7]).cuda()
+    before = net.weight_decay_loss().item()
+    for _ in range(2):
+        loss = torch.nn.functional.nll_loss(net(x.cuda()), target)
+        kernel_optimiser.zero_grad()
+        loss.backward()
+        kernel_optimiser.step()
+        weight_decay_optimiser.zero_grad()
+        net.weight_decay_loss().backward()
+        weight_decay_optimiser.step()
+    assert math.isfinite(loss.item()) and net.weight_decay_loss().item() < before + 1e-3
