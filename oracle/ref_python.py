@@ -1,6 +1,7 @@
 """TEST INFRASTRUCTURE. Imports the reference's own Python (gmc.mixture, gmc.fitting, ...) on CPU.
 
-Only usable where the reference checkout is present (REFERENCE_SRC, default /root/reference/src): the golden
+Only usable where the reference checkout is present (environment variable GMC_REFERENCE_SRC, default: the directory
+`reference/src` next to this repository): the golden
 fixture generator under tests/golden/ uses it; nothing that runs on the GPU machine does. The reference's
 Python builds its CUDA extensions at import time; those wrapper modules are replaced by stand-ins that
 route to the reference's pure-PyTorch twins (gm.old_evaluate_inversed, torch.linalg.inv, torch.linalg.eigh)
@@ -12,7 +13,8 @@ import types
 
 import torch
 
-REFERENCE_SRC = os.environ.get("GMC_REFERENCE_SRC", "/root/reference/src")
+_REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REFERENCE_SRC = os.environ.get("GMC_REFERENCE_SRC", os.path.join(os.path.dirname(_REPO), "reference", "src"))
 
 
 def available() -> bool:
