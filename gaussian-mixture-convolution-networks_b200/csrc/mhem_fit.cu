@@ -99,9 +99,13 @@ struct SubGraphs {
         const int sa = get(labels, a), sb = get(labels, b);
         if (sa == sb) return false;
         const int lo = min(sa, sb), hi = max(sa, sb);
-#pragma unroll
-        for (int g = 0; g < NT; ++g)
-            if (get(labels, g) == hi) set(labels, g, lo);
+        // every label byte equal to hi becomes lo (byte-wise compare on the two halves of the packed word)
+        const unsigned hi4 = unsigned(hi) * 0x01010101u, lo4 = unsigned(lo) * 0x01010101u;
+        unsigned l0 = unsigned(labels), l1 = unsigned(labels >> 32);
+        const unsigned m0 = __vcmpeq4(l0, hi4), m1 = __vcmpeq4(l1, hi4);      // 0xFF in the matching bytes
+        l0 = (l0 & ~m0) | (lo4 & m0);
+        l1 = (l1 & ~m1) | (lo4 & m1);
+        labels = uint64_t(l0) | (uint64_t(l1) << 32);
         set(nexts, get(tails, lo), hi);       // the head of sub-graph hi is Gaussian hi
         set(tails, lo, get(tails, hi));
         return true;
