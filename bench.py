@@ -40,8 +40,10 @@ def _args():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--cpu-batch", type=int, default=16, help="batch slice timed on the host cores")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--batch", type=int, default=B_PER_GPU,
+    ap.add_argument("--batch", type=int, default=None,
                     help="batch per GPU (default: the configuration's 32; smaller values are for profiler captures)")
+    ap.add_argument("--relu-fit", choices=["fixed_point_only", "fixed_point_and_tree_hem"], default="fixed_point_only",
+                    help="config 4: ReLU fitting strategy of the layers (the second one runs LBVH + BVH-MHEM in 3D)")
     ap.add_argument("--no-cuda-graph", action="store_true", help="config 4: launch the forward kernel by kernel")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiler captures)")
     ap.add_argument("--config", type=int, default=1, choices=[1, 2, 3, 4],
@@ -201,7 +203,7 @@ def run_ours(args, rank, world, local_rank):
     dev = torch.device("cuda", local_rank)
 
     # every rank owns its own batch shard (different seed per rank)
-    B_PER_GPU = args.batch
+    B_PER_GPU = args.batch if args.batch is not None else globals()["B_PER_GPU"]
     m_h, x_h, g_h = synthetic.config1(n_batch=B_PER_GPU, seed=1001 + rank)
     m_h, x_h, g_h = m_h.pin_memory(), x_h.pin_memory(), g_h.pin_memory()
     m, x, g = m_h.to(dev), x_h.to(dev), g_h.to(dev)
@@ -345,7 +347,7 @@ def _secondary_setup(args, rank, dev):
     from gmc import synthetic
     import gmc.fitting as fitting
     if args.config == 2:
-        n_batch = args.batch if args.batch != B_PER_GPU else 32
+        n_batch = args.batch if args.batch is not None else 32
         m_h, c_h = synthetic.config2(n_batch=n_batch, seed=1002 + rank)
         m, c = m_h.to(dev), c_h.to(dev)
         cfg = fitting.Config(n_reduction=4)
@@ -373,7 +375,7 @@ def _secondary_setup(args, rank, dev):
                 f"config2: fixed_point_and_tree_hem, B={n_batch}/GPU L=32 G=1024 -> K=64, R=4", alg_bytes, cpu)
     if args.config == 3:
         import gmc.cpp.extensions.convolution_fitting.binding as cf
-        n_batch = args.batch if args.batch != B_PER_GPU else 64
+        n_batch = args.batch if args.batch is not None else 64
         d_h, k_h, K = synthetic.config3(n_batch=n_batch, seed=1003 + rank)
         d, k = d_h.to(dev), k_h.to(dev)
         units = n_batch * 16 * 5120
@@ -396,10 +398,10 @@ def _secondary_setup(args, rank, dev):
                 f"config3: convolution_fitting forward, B={n_batch}/GPU Cin=8 G=128 Cout=16 Gk=5 -> K=128 (T=5120)",
                 alg_bytes, cpu)
     import gmc.model as model
-    n_batch = args.batch if args.batch != B_PER_GPU else 256
+    n_batch = args.batch if args.batch is not None else 256
     x_h = synthetic.config4_input(n_batch=n_batch, seed=1004 + rank)
     x = x_h.to(dev)
-    net, head = _gmcn3d(torch, model)
+    net, head = _gmcn3d(torch, model, getattr(fitting, args.relu_fit))
     net, head = net.to(dev), head.to(dev)
 
     def eager(xx):
@@ -409,7 +411,12 @@ def _secondary_setup(args, rank, dev):
     graphed = None
     if not args.no_cuda_graph:
         from gmc.cuda_graph import GraphedForward
-        graphed = GraphedForward(eager, x)          # the whole forward pass as one graph launch
+        try:
+            graphed = GraphedForward(eager, x)      # the whole forward pass as one graph launch
+        except RuntimeError as err:                 # a strategy that synchronises with the host cannot be captured
+            print(f"CUDA graph capture failed ({str(err).splitlines()[0]}); launching kernel by kernel", file=sys.stderr)
+            torch.cuda.synchronize()
+            graphed = None
 
     def step(inputs=None):
         xx = x if inputs is None else inputs[0]
@@ -439,7 +446,7 @@ def _secondary_setup(args, rank, dev):
     keys = n_batch * (8 * 320 + (16 + 32 + 64) * 2560)
     return ("samples_per_s_gmcn3d_forward", "samples/s", n_batch, step, (x_h,),
             f"config4: GMCN-3D forward, B={n_batch}/GPU, 64 input Gaussians, conv-fit layers 1->8->16->32->64 "
-            f"(K=64/32/16/8, ReLU fit fixed_point_only), integrate, linear to 10 logits; "
+            f"(K=64/32/16/8, ReLU fit {args.relu_fit}), integrate, linear to 10 logits; "
             + ("one CUDA graph per forward" if graphed is not None else "kernel-by-kernel launches"),
             keys * 4 + n_batch * 64 * 13 * 4, cpu)
 

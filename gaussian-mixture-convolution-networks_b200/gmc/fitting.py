@@ -227,13 +227,14 @@ def solver(mixture: Tensor, constant: Tensor, n_components: int, config: Config 
 # ---------------------------------------------------------------------------------------------
 # reductions (reference fitting.py:243-276, 342-530)
 # ---------------------------------------------------------------------------------------------
-def tree_hem(m: Tensor, n_components: int, n_reduction: int) -> Tensor:
+def tree_hem(m: Tensor, n_components: int, n_reduction: int, check_inputs: bool = False) -> Tensor:
     """BVH-MHEM reduction; the mixture is scaled per (batch, layer) to a mean covariance trace of D first."""
     scale = mat_tools.trace(gm.covariances(m)).mean(-1, keepdim=True) / gm.n_dimensions(m)
-    assert (scale > 0).all().item()
     back = torch.sqrt(scale)
     forth = 1 / back
-    assert not torch.any(torch.isnan(forth)) and not torch.any(torch.isinf(forth))
+    if check_inputs:       # host synchronisation: off by default so that a forward pass can be captured in a CUDA graph
+        assert (scale > 0).all().item()
+        assert not torch.any(torch.isnan(forth)) and not torch.any(torch.isinf(forth))
     m = gm.spatial_scale(m, forth)
     m = cppBvhMhemFit.apply(m, n_components, n_reduction)
     return gm.spatial_scale(m, back)

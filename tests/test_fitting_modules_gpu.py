@@ -244,7 +244,7 @@ def test_graphed_forward_equals_eager_forward(monkeypatch):
         graph(xs[0][:2])
 
 
-@pytest.mark.parametrize("D,B,L,G", [(2, 3, 4, 16), (3, 2, 5, 8), (3, 2, 3, 64), (2, 2, 2, 48), (3, 1, 2, 300), (2, 1, 1, 1100),
+@pytest.mark.parametrize("D,B,L,G", [(2, 3, 4, 16), (3, 2, 5, 8), (3, 2, 3, 64), (2, 2, 2, 48), (3, 1, 2, 300), (2, 1, 1, 1100), (2, 2, 1, 200), (3, 1, 1, 129),
                                      (3, 1, 1, 1)])
 def test_fused_relu_fixed_point_equals_the_composite_path(D, B, L, G):
     """gmc_relu_fixed_point against initial_approx_to_relu + fixed_point_iteration_to_relu built from the evaluation
