@@ -422,6 +422,8 @@ def _secondary_setup(args, rank, dev):
         xx = x if inputs is None else inputs[0]
         return graphed(xx) if graphed is not None else eager(xx)
 
+    step.uncaptured = lambda: eager(x)      # the same launches outside the graph, for the launch count
+
     def cpu():
         from oracle import cpu_oracle
         cpu_oracle.use_all_cores()
@@ -462,6 +464,11 @@ def run_secondary(args, rank, world, local_rank):
     metric, unit, units, step, host_inputs, workload, alg_bytes, cpu = _secondary_setup(args, rank, dev)
     host_inputs = tuple(t.pin_memory() for t in host_inputs)
     gather = sharding.OutputGatherer(world, dev) if world > 1 else None
+    # kernels of this library per step (the library counts its launches; a graph replay repeats the captured ones)
+    from gmc import _native
+    launches_before = _native.lib.gmc_kernel_launch_count()
+    getattr(step, "uncaptured", step)()
+    launches_per_step = _native.lib.gmc_kernel_launch_count() - launches_before
 
     def full_step():
         out = step()
@@ -530,7 +537,7 @@ def run_secondary(args, rank, world, local_rank):
             "e2e": {"value": world * units / (e2e_ms * 1e-3), "unit": unit,
                     "h2d_bytes_per_step": sum(t.numel() * 4 for t in host_inputs),
                     "d2h_bytes_per_step": out_h.numel() * 4, "ms_per_step": e2e_ms, "steps": e2e_steps},
-            "gpu_launches": None, "clocks": clocks}
+            "gpu_launches": launches_per_step * args.steps, "clocks": clocks}
     if not args.no_cpu_baseline and world == 1:
         line["cpu_baseline"] = cpu()
     print(json.dumps(line), flush=True)

@@ -21,7 +21,14 @@ void set_last_cuda_error(cudaError_t e);
         }                                                   \
     } while (0)
 
-#define GMC_LAUNCH_CHECK() GMC_CUDA_TRY(cudaGetLastError())
+// Counts kernel launches of the library (read by gmc_kernel_launch_count; benchmark bookkeeping).
+void note_kernel_launch();
+
+#define GMC_LAUNCH_CHECK()                  \
+    do {                                    \
+        ::gmc::note_kernel_launch();        \
+        GMC_CUDA_TRY(cudaGetLastError());   \
+    } while (0)
 
 // One word per translation unit (the library is built without relocatable device code). Kernels OR
 // a code into it when a bounded wait gives up or a self check fails; gmc_device_check_word() reads

@@ -1,12 +1,18 @@
 // Status strings, the per-thread CUDA error message and the device check word reader.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace gmc {
 namespace {
 thread_local cudaError_t t_last_error = cudaSuccess;
+std::atomic<long long> g_kernel_launches{0};
 }
 void set_last_cuda_error(cudaError_t e) { t_last_error = e; }
+void note_kernel_launch() { g_kernel_launches.fetch_add(1, std::memory_order_relaxed); }
 }  // namespace gmc
+
+extern "C" long long gmc_kernel_launch_count(void) { return gmc::g_kernel_launches.load(std::memory_order_relaxed); }
 
 // one reader per translation unit that owns kernels
 int gmc_tu_check_eval_inversed(int* word);

@@ -29,6 +29,8 @@ lib.gmc_last_cuda_error.restype = ctypes.c_char_p
 lib.gmc_last_cuda_error.argtypes = []
 lib.gmc_version.restype = ctypes.c_char_p
 lib.gmc_version.argtypes = []
+lib.gmc_kernel_launch_count.restype = ctypes.c_longlong
+lib.gmc_kernel_launch_count.argtypes = []
 lib.gmc_device_check_word.restype = _c_int
 lib.gmc_device_check_word.argtypes = [ctypes.POINTER(_c_int)]
 

@@ -47,6 +47,8 @@ const char* gmc_version(void);
 /* Reads and clears the device-side check word of the current device (synchronises the device).
  * 0 = no kernel reported a problem since the last call. */
 int gmc_device_check_word(int* word_out);
+/* Number of kernels this library has launched in the process so far (all threads, all devices). */
+long long gmc_kernel_launch_count(void);
 
 /* ------------------------------------------------------------------------------------------------
  * Mixture evaluation with the matrix slot holding the INVERSE covariance S:
