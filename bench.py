@@ -168,7 +168,7 @@ def run_reference(args, rank):
             "config": {"workload": f"config1 slice: 3D evaluate_inversed fwd+bwd, B={args.cpu_batch} L={L} G={G} N={N}"},
             "cpu_baseline": base,
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line), flush=True)
+    _emit(line)
 
 
 def _measure_fp32_peak(torch, dev):
@@ -322,7 +322,7 @@ def run_ours(args, rank, world, local_rank):
     }
     if not args.no_cpu_baseline and world == 1:
         line["cpu_baseline"], _ = _cpu_baseline(args.cpu_batch)
-    print(json.dumps(line), flush=True)
+    _emit(line)
 
 
 # ---------------------------------------------------------------------------------------------------------------
@@ -540,10 +540,29 @@ def run_secondary(args, rank, world, local_rank):
             "gpu_launches": launches_per_step * args.steps, "clocks": clocks}
     if not args.no_cpu_baseline and world == 1:
         line["cpu_baseline"] = cpu()
-    print(json.dumps(line), flush=True)
+    _emit(line)
+
+
+_RESULT_FD = None
+
+
+def _emit(line):
+    """Writes the one JSON line to the process's real stdout (see main)."""
+    text = json.dumps(line) + "\n"
+    if _RESULT_FD is None:
+        sys.stdout.write(text)
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, text.encode())
 
 
 def main():
+    # Libraries (NCCL's version banner, for one) write to file descriptor 1. The JSON line must be the only thing on
+    # stdout, so everything else that goes to descriptor 1 is sent to stderr and the line is written to the saved one.
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     args = _args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -555,7 +574,6 @@ def main():
         import torch
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # NCCL's banner and logs go to stderr: stdout is one JSON line
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
