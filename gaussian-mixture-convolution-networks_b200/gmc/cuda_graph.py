@@ -12,7 +12,9 @@ class GraphedForward:
     """graph = GraphedForward(fn, example_input); out = graph(x) for x of the example's shape, dtype and device.
 
     `fn` must be free of host synchronisation (no .item(), no data-dependent Python control flow) and is run under
-    torch.no_grad(). The returned tensor is the graph's static output buffer: it is overwritten by the next call."""
+    torch.no_grad(). The returned tensor is the graph's static output buffer: it is overwritten by the next call.
+    Whatever `fn` derives from parameters on the Python side and caches (the kernel mixtures of the convolution
+    layers) is frozen into the graph: capture again after changing parameters."""
 
     def __init__(self, fn, example_input: torch.Tensor, warmup: int = 3):
         if not example_input.is_cuda:

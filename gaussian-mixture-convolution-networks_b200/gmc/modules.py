@@ -79,6 +79,21 @@ class Convolution(torch.nn.modules.Module):
         self.covariance_factors.requires_grad = self.learn_covariances and flag
 
     def kernels(self) -> Tensor:
+        if not (self.training or torch.is_grad_enabled()):
+            # inference: the kernel mixture only changes when a parameter does
+            def stamp(v):     # parameters by storage and version, plain numbers by value
+                return (v.data_ptr(), v._version) if isinstance(v, torch.Tensor) else v
+            key = tuple(stamp(v) for v in (self.weights, self.positions, self.covariance_factors, self.position_range,
+                                           self.covariance_range, self.weight_sd, self.weight_mean,
+                                           self.covariance_epsilon))
+            cached = getattr(self, "_kernels_cache", None)
+            if cached is None or cached[0] != key:
+                cached = (key, self._build_kernels().detach())
+                self._kernels_cache = cached
+            return cached[1]
+        return self._build_kernels()
+
+    def _build_kernels(self) -> Tensor:
         weights = self.weights * self.weight_sd + self.weight_mean
         A = self.covariance_factors
         cov = A @ A.transpose(-1, -2)

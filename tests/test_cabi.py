@@ -45,6 +45,27 @@ def test_argument_checks_return_status_without_gpu():
     assert b(null, one, one, one, one, 1, 1, 1, 2, 1, 1, 1, null) == 3
 
 
+def test_argument_checks_of_the_added_entry_points():
+    from gmc import _native
+    null = ctypes.c_void_p(0)
+    one = ctypes.c_void_p(16)
+    r = _native.lib.gmc_relu_fixed_point
+    assert r(one, one, one, one, null, 1, 4, 5, null) == 1        # D = 5
+    assert r(one, one, one, one, null, 1, 0, 2, null) == 1        # no components
+    assert r(null, one, one, one, null, 1, 4, 2, null) == 3       # NULL mixtures
+    assert r(one, one, one, one, null, 0, 4, 2, null) == 0        # nothing to do
+    h = _native.lib.gmc_eval_inversed_host
+    assert h(one, one, null, one, null, null, 1, 1, 1, 4, 1, 1, 1, 0) == 1          # D = 4
+    assert h(one, one, null, one, null, null, 2, 1, 1, 2, 3, 1, 1, 0) == 2          # batch broadcast mismatch
+    assert h(null, one, null, one, null, null, 1, 1, 1, 2, 1, 1, 1, 0) == 3         # NULL mixture
+    assert h(one, one, null, null, null, null, 1, 1, 1, 2, 1, 1, 1, 0) == 3         # neither output nor gradient asked
+    assert h(one, one, null, one, one, null, 1, 1, 1, 2, 1, 1, 1, 0) == 3           # gradient without grad_out
+    p = _native.lib.gmc_fp32_fma_probe
+    flop = ctypes.c_double(0)
+    assert p(null, 10, ctypes.byref(flop), null) == 3 and p(one, 0, ctypes.byref(flop), null) == 1
+    assert _native.lib.gmc_kernel_launch_count() >= 0
+
+
 def test_cpu_tensors_are_rejected_loudly():
     import gmc.cpp.extensions.evaluate_inversed.evaluate_inversed as ev
     with pytest.raises(RuntimeError, match="no CPU implementation"):

@@ -368,3 +368,19 @@ def test_dropout_batchnorm_and_the_two_optimiser_step():
         net.weight_decay_loss().backward()
         weight_decay_optimiser.step()
     assert math.isfinite(loss.item()) and net.weight_decay_loss().item() < before + 1e-3
+
+
+def test_convolution_kernel_cache_follows_the_parameters():
+    """In inference the kernel mixture is built once and rebuilt when a parameter changes; training never caches."""
+    import gmc.modules as modules
+    conv = modules.Convolution(modules.ConvolutionConfig(), 2, 3, n_kernel_components=4, n_dims=2).cuda().eval()
+    with torch.no_grad():
+        a = conv.kernels()
+        assert conv.kernels() is a
+        conv.weights.add_(1.0)
+        b = conv.kernels()
+        assert b is not a and not torch.equal(a, b)
+    assert conv.kernels().requires_grad            # autograd on: built fresh, differentiable
+    conv.train()
+    with torch.no_grad():
+        assert conv.kernels() is not conv.kernels()
