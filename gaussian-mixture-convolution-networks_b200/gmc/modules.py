@@ -218,6 +218,11 @@ class BatchNorm(torch.nn.modules.Module):
         n_batch, n_channels, d = gm.n_batch(x_gm), gm.n_layers(x_gm), gm.n_dimensions(x_gm)
         if x_constant is None:
             x_constant = torch.zeros(n_batch, n_channels, device=x_gm.device)
+        if self.batch_norm and not self.training:
+            # evaluation with batch statistics: only the running averages are used, so nothing is sampled
+            # (the reference samples and evaluates here as well and then discards the result, modules.py:396-410)
+            sd, mean = self.averaged_channel_sd.detach(), self.averaged_channel_mean.detach()
+            return self._scaled(x_gm, x_constant, sd, mean, n_channels)
         n_samples = 10000 // n_batch if self.batch_norm else 1000
         centres = gm.positions(x_gm).reshape(n_batch, -1, d).detach()
         lo = centres.min(dim=1)[0].view(n_batch, 1, 1, d)
@@ -236,6 +241,9 @@ class BatchNorm(torch.nn.modules.Module):
             sd, mean = self.averaged_channel_sd.detach(), self.averaged_channel_mean.detach()
         else:
             sd, mean = torch.std_mean(values, dim=2)
+        return self._scaled(x_gm, x_constant, sd, mean, n_channels)
+
+    def _scaled(self, x_gm, x_constant, sd, mean, n_channels):
         factor = 1 / sd.clamp_min(0.001)
         if self.learnable_scaling is not None:
             factor = factor * self.learnable_scaling
