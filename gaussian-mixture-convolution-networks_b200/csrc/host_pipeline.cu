@@ -1,6 +1,6 @@
 // Mixture evaluation (forward, optionally with its backward) on HOST buffers.
 //
-// The batch is cut into slices. Three streams run a software pipeline over two device slots:
+// The batch is cut into slices. Streams run a software pipeline over kSlots device slots:
 //   copy-in  : host -> device of slice i+1 (mixture, xes, grad_out)
 //   compute  : forward + backward kernels of slice i (one stream per slot, so that the first CTAs of a slice fill the
 //              SMs that the last wave of the previous slice leaves idle)
@@ -17,7 +17,7 @@
 namespace gmc {
 namespace {
 
-constexpr int kSlots = 2;
+constexpr int kSlots = 4;
 constexpr int kMaxDevices = 64;
 
 struct DevicePipe {
@@ -196,8 +196,11 @@ extern "C" int gmc_eval_inversed_host(const float* mixture, const float* xes, co
     }
     // the host buffers are valid when the call returns; drain all three streams even after an error
     cudaError_t e1 = cudaStreamSynchronize(p.s_in);
-    cudaError_t e2 = cudaStreamSynchronize(p.s_comp[0]);
-    if (e2 == cudaSuccess) e2 = cudaStreamSynchronize(p.s_comp[1]);
+    cudaError_t e2 = cudaSuccess;
+    for (int k = 0; k < kSlots; ++k) {
+        const cudaError_t e = cudaStreamSynchronize(p.s_comp[k]);
+        if (e2 == cudaSuccess) e2 = e;
+    }
     cudaError_t e3 = cudaStreamSynchronize(p.s_out);
     if (status != GMC_OK) return status;
     GMC_CUDA_TRY(e1);
