@@ -676,14 +676,34 @@ mhem_fit_forward_kernel(const float* __restrict__ mixture, const uint16_t* __res
         return id >= n_internal ? mix[size_t(nodes[size_t(id) * 4 + 3]) * RF] : attrs[size_t(id) * AF + R * RF];
     };
 
+    // ---- node ids grouped by level (counting sort; arrive[] is dead and holds the list), so that the warps of the
+    //      CTA share the nodes of a level evenly whatever their ids are ----
+    __shared__ int level_start[258], level_cursor[258];
+    uint16_t* order = reinterpret_cast<uint16_t*>(arrive);
+    for (int i = tid; i < 258; i += kThreads) level_start[i] = 0;
+    __syncthreads();
+    for (int i = tid; i < n_internal; i += kThreads) atomicAdd(&level_start[level[i]], 1);
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0;
+        for (int lv = 0; lv <= max_level + 1; ++lv) {
+            const int c = level_start[lv];
+            level_start[lv] = run;
+            level_cursor[lv] = run;
+            run += c;
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < n_internal; i += kThreads) order[atomicAdd(&level_cursor[level[i]], 1)] = uint16_t(i);
+    __syncthreads();
+
     // ---- bottom-up, level by level, one warp per node ----
     WarpScratch<D, R>& ws = sm.warp[warp];
     for (int lv = 1; lv <= max_level; ++lv) {
-        for (int base = warp * 32; base < n_internal; base += kWarps * 32) {
-            const int cand = base + lane;
-            const unsigned todo = __ballot_sync(0xffffffffu, cand < n_internal && level[cand] == lv);
-            for (unsigned bits = todo; bits; bits &= bits - 1) {
-                const int id = base + __ffs(bits) - 1;
+        {
+            const int level_end = level_start[lv + 1];
+            for (int at = level_start[lv] + warp; at < level_end; at += kWarps) {
+                const int id = order[at];
                 int child, child_slot, pos;
                 bool in_range, valid;
                 const int n_target = gather_children<D, R>(ws, mix, nodes, attrs, n_internal, id, lane, child, child_slot, in_range, valid, pos);
