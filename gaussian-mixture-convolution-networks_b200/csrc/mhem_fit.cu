@@ -557,6 +557,30 @@ __device__ __forceinline__ void compute_levels(const uint16_t* __restrict__ node
     __syncthreads();
 }
 
+// Node ids grouped by level (counting sort): nodes of level lv are order[level_start[lv] .. level_start[lv + 1]), in no
+// particular order inside a level. With it the warps of a CTA share the nodes of a level evenly whatever their ids are.
+// level_start and level_cursor hold 258 ints each; ends with a CTA-wide barrier.
+__device__ __forceinline__ void group_by_level(const unsigned char* level, int n_internal, int max_level, uint16_t* order,
+                                               int* level_start, int* level_cursor) {
+    const int tid = threadIdx.x;
+    for (int i = tid; i < 258; i += kThreads) level_start[i] = 0;
+    __syncthreads();
+    for (int i = tid; i < n_internal; i += kThreads) atomicAdd(&level_start[level[i]], 1);
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0;
+        for (int lv = 0; lv <= max_level + 1; ++lv) {
+            const int c = level_start[lv];
+            level_start[lv] = run;
+            level_cursor[lv] = run;
+            run += c;
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < n_internal; i += kThreads) order[atomicAdd(&level_cursor[level[i]], 1)] = uint16_t(i);
+    __syncthreads();
+}
+
 // Gathers the Gaussians of the two children of `id` into ws.tgt (left first, |w| < 1e-7 dropped, padded with (0,0,I)).
 // Lane j < R stands for the left child's j-th Gaussian, lane R + j for the right child's. Returns the number gathered;
 // `in_range` / `valid` / `pos` describe this lane's Gaussian.
@@ -676,26 +700,10 @@ mhem_fit_forward_kernel(const float* __restrict__ mixture, const uint16_t* __res
         return id >= n_internal ? mix[size_t(nodes[size_t(id) * 4 + 3]) * RF] : attrs[size_t(id) * AF + R * RF];
     };
 
-    // ---- node ids grouped by level (counting sort; arrive[] is dead and holds the list), so that the warps of the
-    //      CTA share the nodes of a level evenly whatever their ids are ----
+    // ---- node ids grouped by level (arrive[] is dead after compute_levels and holds the list) ----
     __shared__ int level_start[258], level_cursor[258];
     uint16_t* order = reinterpret_cast<uint16_t*>(arrive);
-    for (int i = tid; i < 258; i += kThreads) level_start[i] = 0;
-    __syncthreads();
-    for (int i = tid; i < n_internal; i += kThreads) atomicAdd(&level_start[level[i]], 1);
-    __syncthreads();
-    if (tid == 0) {
-        int run = 0;
-        for (int lv = 0; lv <= max_level + 1; ++lv) {
-            const int c = level_start[lv];
-            level_start[lv] = run;
-            level_cursor[lv] = run;
-            run += c;
-        }
-    }
-    __syncthreads();
-    for (int i = tid; i < n_internal; i += kThreads) order[atomicAdd(&level_cursor[level[i]], 1)] = uint16_t(i);
-    __syncthreads();
+    group_by_level(level, n_internal, max_level, order, level_start, level_cursor);
 
     // ---- bottom-up, level by level, one warp per node ----
     WarpScratch<D, R>& ws = sm.warp[warp];
@@ -816,13 +824,17 @@ mhem_fit_backward_kernel(const float* __restrict__ grad_all, const float* __rest
     __threadfence_block();
     __syncthreads();
 
+    __shared__ int level_start[258], level_cursor[258];
+    uint16_t* order = reinterpret_cast<uint16_t*>(arrive);     // arrive[] is dead after compute_levels
+    group_by_level(level, n_internal, max_level, order, level_start, level_cursor);
+
     WarpScratch<D, R>& ws = sm.warp[warp];
     for (int lv = max_level; lv >= 1; --lv) {
-        for (int base = warp * 32; base < n_internal; base += kWarps * 32) {
-            const int cand = base + lane;
-            const unsigned todo = __ballot_sync(0xffffffffu, cand < n_internal && level[cand] == lv && has_grad[cand]);
-            for (unsigned bits = todo; bits; bits &= bits - 1) {
-                const int id = base + __ffs(bits) - 1;
+        {
+            const int level_end = level_start[lv + 1];
+            for (int at = level_start[lv] + warp; at < level_end; at += kWarps) {
+                const int id = order[at];
+                if (!has_grad[id]) continue;
                 int child, child_slot, pos;
                 bool in_range, valid;
                 const int n_target = gather_children<D, R>(ws, mix, nodes, attrs, n_internal, id, lane, child, child_slot, in_range, valid, pos);
