@@ -39,6 +39,51 @@ __global__ void __launch_bounds__(kThreads) matrix_inverse_kernel(const float* _
     for (int i = threadIdx.x; i < here * E; i += kThreads) dst[i] = tile[i];
 }
 
+// Gradient of the inverse: out = -inv * grad * inv per matrix (the reference's formula, transposes dropped), one matrix
+// per thread, through shared memory like the forward.
+template <int D>
+__global__ void __launch_bounds__(kThreads) matrix_inverse_backward_kernel(const float* __restrict__ inverses,
+                                                                           const float* __restrict__ grad,
+                                                                           float* __restrict__ out, long long n) {
+    constexpr int E = D * D;
+    __shared__ float tile_inv[kThreads * E];
+    __shared__ float tile_grad[kThreads * E];
+    const long long first = (long long)blockIdx.x * kThreads;
+    const int here = int(min((long long)kThreads, n - first));
+    for (int i = threadIdx.x; i < here * E; i += kThreads) {
+        tile_inv[i] = __ldg(inverses + first * E + i);
+        tile_grad[i] = __ldg(grad + first * E + i);
+    }
+    __syncthreads();
+    if (threadIdx.x < here) {
+        const float* a = tile_inv + threadIdx.x * E;
+        float* g = tile_grad + threadIdx.x * E;
+        float ag[E], r[E];
+#pragma unroll
+        for (int i = 0; i < D; ++i)
+#pragma unroll
+            for (int j = 0; j < D; ++j) {
+                float acc = 0.f;
+#pragma unroll
+                for (int k = 0; k < D; ++k) acc += a[i * D + k] * g[k * D + j];
+                ag[i * D + j] = acc;
+            }
+#pragma unroll
+        for (int i = 0; i < D; ++i)
+#pragma unroll
+            for (int j = 0; j < D; ++j) {
+                float acc = 0.f;
+#pragma unroll
+                for (int k = 0; k < D; ++k) acc += ag[i * D + k] * a[k * D + j];
+                r[i * D + j] = -acc;
+            }
+#pragma unroll
+        for (int e = 0; e < E; ++e) g[e] = r[e];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < here * E; i += kThreads) out[first * E + i] = tile_grad[i];
+}
+
 // One warp per mixture: sum of the weight column.
 __global__ void __launch_bounds__(kThreads) integrate_kernel(const float* __restrict__ mixture, float* __restrict__ out,
                                                              long long n_mixtures, int n_components, int record) {
@@ -170,6 +215,23 @@ extern "C" int gmc_matrix_inverse(const float* matrices, float* inverses, long l
     if (blocks > 0x7fffffffLL) return GMC_ERR_BAD_DIMS;
     if (n_dims == 2) matrix_inverse_kernel<2><<<unsigned(blocks), kThreads, 0, as_stream(stream)>>>(matrices, inverses, n_matrices);
     else matrix_inverse_kernel<3><<<unsigned(blocks), kThreads, 0, as_stream(stream)>>>(matrices, inverses, n_matrices);
+    GMC_LAUNCH_CHECK();
+    return GMC_OK;
+}
+
+extern "C" int gmc_matrix_inverse_backward(const float* inverses, const float* grad, float* grad_matrices,
+                                           long long n_matrices, int n_dims, void* stream) {
+    using namespace gmc;
+    if (n_dims != 2 && n_dims != 3) return GMC_ERR_BAD_DIMS;
+    if (n_matrices < 0) return GMC_ERR_BAD_DIMS;
+    if (n_matrices == 0) return GMC_OK;
+    if (!inverses || !grad || !grad_matrices) return GMC_ERR_NULL_POINTER;
+    const long long blocks = (n_matrices + kThreads - 1) / kThreads;
+    if (blocks > 0x7fffffffLL) return GMC_ERR_BAD_DIMS;
+    if (n_dims == 2)
+        matrix_inverse_backward_kernel<2><<<unsigned(blocks), kThreads, 0, as_stream(stream)>>>(inverses, grad, grad_matrices, n_matrices);
+    else
+        matrix_inverse_backward_kernel<3><<<unsigned(blocks), kThreads, 0, as_stream(stream)>>>(inverses, grad, grad_matrices, n_matrices);
     GMC_LAUNCH_CHECK();
     return GMC_OK;
 }

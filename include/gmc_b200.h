@@ -122,6 +122,11 @@ int gmc_relu_fixed_point(const float* mixtures, const float* constants, float* o
  * (src/gmc/cpp/extensions/pieces/matrix_inverse.cu:23-73).
  * ---------------------------------------------------------------------------------------------- */
 int gmc_matrix_inverse(const float* matrices, float* inverses, long long n_matrices, int n_dims, void* stream);
+/* Gradient of the inverse for an incoming gradient of the same shape: grad_matrices = -inverse * grad * inverse per
+ * matrix, with the inverses that gmc_matrix_inverse returned.
+ * Replaces MatrixInverse.backward (src/gmc/cpp/extensions/math/matrix_inverse.py:31-33). */
+int gmc_matrix_inverse_backward(const float* inverses, const float* grad, float* grad_matrices,
+                                long long n_matrices, int n_dims, void* stream);
 
 /* Eigen-decomposition of n_matrices symmetric row-major DxD matrices: eigenvalues [n, D] ascending, eigenvectors
  * [n, D, D] with the vectors in the columns. Closed form; accuracy about 1e-3 relative in fp32 for nearly degenerate

@@ -60,8 +60,12 @@ def test_matrix_inverse_against_torch():
         ref = torch.linalg.inv(m.detach().double())
         assert ((mine.detach().double() - ref) ** 2).mean().item() < 1e-5     # src/gmc/test_mat_tools.py criterion
         assert rel_inf(mine.detach().cpu().numpy(), ref.cpu().numpy()) < 1e-3
-        mine.sum().backward()
-        assert torch.isfinite(m.grad).all()
+        g = torch.randn(mine.shape, generator=torch.Generator().manual_seed(d)).cuda()
+        g = g + g.transpose(-1, -2)            # symmetric incoming gradient: the case the operator is written for
+        mine.backward(g)
+        m64 = m.detach().double().requires_grad_(True)
+        torch.linalg.inv(m64).backward(g.double())
+        assert rel_inf(m.grad.cpu().numpy(), m64.grad.cpu().numpy()) < 1e-3
 
 
 def test_tree_hem_against_oracle_pipeline():
