@@ -194,7 +194,7 @@ extern "C" int gmc_eval_inversed_host(const float* mixture, const float* xes, co
                                          cudaMemcpyDeviceToHost, p.s_out));
         GMC_CUDA_TRY(cudaEventRecord(p.out_done[k], p.s_out));
     }
-    // the host buffers are valid when the call returns; drain all three streams even after an error
+    // the host buffers are valid when the call returns; drain every stream even after an error
     cudaError_t e1 = cudaStreamSynchronize(p.s_in);
     cudaError_t e2 = cudaSuccess;
     for (int k = 0; k < kSlots; ++k) {

@@ -46,7 +46,7 @@ def host_forward_backward(mixture: torch.Tensor, xes: torch.Tensor, grad_output:
                           out: torch.Tensor = None, grad_mixture: torch.Tensor = None, grad_xes: torch.Tensor = None,
                           device=None, want_forward: bool = True):
     """Evaluation (and, with grad_output, its gradients) of CPU tensors on the GPU through
-    gmc_eval_inversed_host: batch slices are copied in, computed and copied out in a three-stream pipeline.
+    gmc_eval_inversed_host: batch slices are copied in, computed and copied out in a pipeline of copy and kernel streams.
     Page-locked tensors (`pin_memory()`) let the copies overlap the kernels; result tensors may be passed in
     to reuse page-locked storage. Returns (out, grad_mixture, grad_xes); entries not asked for are None."""
     ns = _check_shapes(mixture, xes)
