@@ -79,9 +79,9 @@ int gmc_eval_inversed_backward(const float* grad_out, const float* mixture, cons
                                int n_batch_xes, int n_layers_xes, int n_xes, void* stream);
 
 /* The evaluation above (and, when grad_out is not NULL, its gradients) for tensors that live in HOST memory:
- * every pointer is a host pointer, the work is done on the current CUDA device. The batch is cut into n_slices
- * slices (0 = default) that move through a copy-in / kernels / copy-out pipeline on internal streams (0 = default plan: short slices at both ends), so with
- * page-locked buffers the copies of both directions overlap the kernels. The call returns when the host outputs are
+ * every pointer is a host pointer, the work is done on the current CUDA device. The batch is cut into n_slices equal
+ * slices (0 = default plan: about eight slices with short ones at both ends) that move through a copy-in / kernels /
+ * copy-out pipeline on internal streams, so with page-locked buffers the copies of both directions overlap the kernels. The call returns when the host outputs are
  * complete. out may be NULL when only gradients are wanted; grad_mixture / grad_xes may each be NULL. When xes is
  * shared by the whole batch (n_batch_xes == 1 < n_batch) the batch is processed as one slice.
  * The device workspace and the streams are created on first use and kept per device; gmc_host_pipeline_release()
