@@ -376,9 +376,12 @@ __device__ __forceinline__ void aggregate_output(const float* data_b, const floa
     for (int e = 0; e < NS; ++e) S2[e] = 0.f;
 #pragma unroll
     for (int e = 0; e < D * D; ++e) S3[e] = 0.f;
+    int t_next = start + lane < end ? __ldg(nodesobjs + start + lane) : 0;
     for (int i = start + lane; i < end; i += 32) {
         float dg[RF], kg[RF];
-        records(__ldg(nodesobjs + i), dg, kg);
+        const int t = t_next;
+        if (i + 32 < end) t_next = __ldg(nodesobjs + i + 32);     // the next leaf's index is on its way while this one is summed
+        records(t, dg, kg);
         const float w = dg[0] * kg[0];
         float q[D], wq[D];
 #pragma unroll
@@ -481,10 +484,20 @@ convolution_fitting_aggregate_kernel(const float* __restrict__ data, const float
         constexpr int RP = StagedRecord<D>::kStride;
         float* staged = reinterpret_cast<float*>(smem_bytes);
         const int n_data = Cin * G * RF, n_kernel = Cin * Gk * RF;
-        for (int i = threadIdx.x; i < n_data + n_kernel; i += 256) {
-            const float v = i < n_data ? __ldg(data_b + i) : __ldg(kernels_o + (i - n_data));
-            const int record = i / RF;                       // kernel records follow the data records
-            staged[record * RP + (i - record * RF)] = v;
+        // eight loads in flight per thread: the copy is bound by the latency of the global loads
+        for (int i0 = threadIdx.x; i0 < n_data + n_kernel; i0 += 256 * 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = i0 + u * 256;
+                v[u] = i < n_data ? __ldg(data_b + i) : (i < n_data + n_kernel ? __ldg(kernels_o + (i - n_data)) : 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = i0 + u * 256;
+                const int record = i / RF;                   // kernel records follow the data records
+                if (i < n_data + n_kernel) staged[record * RP + (i - record * RF)] = v[u];
+            }
         }
         __syncthreads();
         data_b = staged;
