@@ -131,7 +131,7 @@ def _repeat_for(fn, min_seconds=10.0, max_reps=1000):
 
 def _cpu_baseline(cpu_batch):
     """Reference CPU algorithm (oracle restatement, fp32, OpenMP over query points) on a batch slice."""
-    from gmc import synthetic
+    import synthetic_inputs as synthetic
     from oracle import cpu_oracle
     cpu_oracle.use_all_cores()
     m, x, g = synthetic.config1(n_batch=cpu_batch)
@@ -194,7 +194,8 @@ def run_ours(args, rank, world, local_rank):
     import torch
     import torch.distributed as dist
     import gmc.mixture as gm
-    from gmc import synthetic, sharding
+    from gmc import sharding
+    import synthetic_inputs as synthetic
     import gmc.cpp.extensions.evaluate_inversed.evaluate_inversed as ev
 
     if not torch.cuda.is_available():
@@ -344,7 +345,7 @@ def _gmcn3d(torch, model, fitting_method=None):
 def _secondary_setup(args, rank, dev):
     """-> (metric, unit, units per step and rank, step(), host_inputs, workload text, algorithmic bytes, cpu_baseline())"""
     import torch
-    from gmc import synthetic
+    import synthetic_inputs as synthetic
     import gmc.fitting as fitting
     if args.config == 2:
         n_batch = args.batch if args.batch is not None else 32

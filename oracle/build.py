@@ -1,8 +1,6 @@
 """TEST INFRASTRUCTURE. Builds the CPU oracle (oracle/cpu/*.c, *.cpp) into oracle/_build/liboracle.so with gcc/g++.
 
-The reference's own native sources are not compiled: they include glm, gcem and yamc headers that are
-neither vendored in the reference tree (its cpp/glm, cpp/gcem, cpp/yamc folders are empty clone targets)
-nor installed here, so there is no oracle/_ref.
+The reference's own native sources are built separately by oracle/build_ref.py into oracle/_ref/.
 """
 import os
 import subprocess

@@ -1,6 +1,7 @@
 """Generates the golden fixtures of this folder by running the REFERENCE's own Python on CPU.
 
 Run where the reference checkout exists:   python tests/golden/make_golden.py
+reference_native.npz additionally holds outputs of the reference's NATIVE code (CPU path) built by oracle/build_ref.py.
 Inputs are seeded fp32 tensors; outputs come from the reference's gm.old_evaluate_inversed
 (src/gmc/mixture.py:102-141, the ground truth of the reference's own src/gmc/test_cpp_eval.py) evaluated in
 fp64 on the same values, with gradients from torch autograd through it.
@@ -135,7 +136,108 @@ def strategy_cases(gm, fitting):
     return cases
 
 
+def support_collections(reference_root):
+    """The inline 2D mixtures and incoming-gradient sets of the reference's native unit tests
+    (src/gmc/cpp/extensions/unittests/support.h:228-1020), read from the header as text:
+    {function name: [arrays of shape [n, 7]]}."""
+    import re
+    path = os.path.join(reference_root, "src", "gmc", "cpp", "extensions", "unittests", "support.h")
+    text = open(path).read()
+    heads = [(m.start(), m.group(1)) for m in re.finditer(r"std::vector<torch::Tensor>\s+(\w+)\s*\(\)", text)]
+    out = {}
+    for i, (pos, name) in enumerate(heads):
+        body = text[pos:heads[i + 1][0] if i + 1 < len(heads) else len(text)]
+        tensors = []
+        for m in re.finditer(r"torch::tensor\(\{(.*?)\}\)\s*\.view\(\{([\d, ]+)\}\)", body, re.S):
+            shape = [int(v) for v in m.group(2).split(",")]
+            values = [float(v.rstrip("f")) for v in re.findall(r"-?\d*\.?\d+(?:e-?\d+)?f?", m.group(1))]
+            tensors.append(np.asarray(values, dtype=np.float32).reshape(shape[-2], shape[-1]))
+        if tensors:
+            out[name] = tensors
+    return out
+
+
+def reference_native_cases(reference_root):
+    """Outputs of the REFERENCE's own native CPU code (oracle/_ref/libgmc_ref.so, built from the reference sources by
+    oracle/build_ref.py) on (a) the inline mixtures / gradient sets of its unit tests and (b) small seeded cases:
+    LBVH keys and nodes, BVH-MHEM fit forward + backward, convolution_fitting forward + backward."""
+    from oracle import ref_native
+    cases = {}
+    coll = support_collections(reference_root)
+    grads_by_k = {2: coll["_collectionOf2d2GsGrads"], 4: coll["_collectionOf2d4GsGrads"],
+                  8: coll["_collectionOf2d8GsGrads"], 32: coll["_collectionOf2d32GsGradsWellBehaving"]}
+    plan = []   # (collection, K, R)
+    for name, tensors in sorted(coll.items()):
+        if "Mixtures" not in name:
+            continue
+        G = tensors[0].shape[0]
+        plan.append((name, {4: 2, 8: 4, 16: 8, 128: 32}[G], {4: 2, 8: 4, 16: 4, 128: 4}[G]))
+        if G == 8:
+            plan.append((name, 4, 2))
+    idx = 0
+    for name, K, R in plan:
+        for mi, mixture in enumerate(coll[name]):
+            G = mixture.shape[0]
+            m = mixture.reshape(1, 1, G, 7)
+            grad = grads_by_k[K][mi % len(grads_by_k[K])].reshape(1, 1, K, 7)
+            fit, dump = ref_native.mhem_fit_forward(m, K, R, dump=True)
+            if not (np.isfinite(fit).all()):
+                continue
+            key = f"mhem{idx:03d}"
+            cases[key + "_source"] = np.array(f"{name}[{mi}] K={K} R={R}")
+            cases[key + "_mixture"] = m
+            cases[key + "_kr"] = np.array([K, R])
+            cases[key + "_grad"] = grad
+            cases[key + "_fitting"] = fit
+            cases[key + "_nodes"] = dump["nodes"]
+            cases[key + "_counts"] = dump["counts"]
+            cases[key + "_grad_target"] = ref_native.mhem_fit_backward(grad, m, K, R)
+            keys, nodes = ref_native.lbvh_build(m)
+            cases[key + "_keys"] = keys
+            idx += 1
+    # seeded cases: 3D fit, convolution fitting in 2D and 3D
+    g = torch.Generator().manual_seed(31337)
+
+    def mixture(n0, n1, n2, D, pos, cov_scale, wlo, whi):
+        w = torch.rand(n0, n1, n2, generator=g) * (whi - wlo) + wlo
+        p = torch.randn(n0, n1, n2, D, generator=g) * pos
+        A = torch.rand(n0, n1, n2, D, D, generator=g) * 2 - 1
+        c = (A @ A.transpose(-1, -2) + torch.eye(D) * 0.05) * cov_scale
+        return torch.cat((w.unsqueeze(-1), p, c.reshape(n0, n1, n2, D * D)), -1).contiguous().numpy()
+
+    for D, G, K, R in ((3, 40, 8, 4), (3, 24, 8, 2), (2, 96, 16, 4)):
+        m = mixture(1, 2, G, D, 1.0, 0.02, 0.1, 1.0)
+        grad = torch.randn(1, 2, K, m.shape[-1], generator=g).numpy()
+        fit, dump = ref_native.mhem_fit_forward(m, K, R, dump=True)
+        key = f"mhem{idx:03d}"
+        cases[key + "_source"] = np.array(f"seeded D={D} G={G} K={K} R={R}")
+        cases[key + "_mixture"], cases[key + "_kr"], cases[key + "_grad"] = m, np.array([K, R]), grad
+        cases[key + "_fitting"], cases[key + "_nodes"], cases[key + "_counts"] = fit, dump["nodes"], dump["counts"]
+        cases[key + "_grad_target"] = ref_native.mhem_fit_backward(grad, m, K, R)
+        cases[key + "_keys"] = ref_native.lbvh_build(m)[0]
+        idx += 1
+    cases["n_mhem"] = np.array(idx)
+    for ci, (D, B, Cin, G, Cout, Gk, K) in enumerate(((2, 2, 3, 16, 2, 5, 8), (3, 1, 4, 12, 3, 5, 6), (2, 1, 2, 9, 2, 3, 54))):
+        data = mixture(B, Cin, G, D, 1.0, 0.02, -1.0, 1.0)
+        kernels = mixture(Cout, Cin, Gk, D, 0.1, 0.005, -0.3, 0.3)
+        grad = torch.randn(B, Cout, K, data.shape[-1], generator=g).numpy()
+        out, cached, objs, sub, tree = ref_native.convolution_fitting_forward(data, kernels, K, tree=True)
+        gd, gk = ref_native.convolution_fitting_backward(grad, data, kernels, K)
+        key = f"cf{ci}"
+        cases[key + "_data"], cases[key + "_kernels"], cases[key + "_k"], cases[key + "_grad"] = data, kernels, np.array(K), grad
+        cases[key + "_fitting"], cases[key + "_cached"], cases[key + "_nodesobjs"], cases[key + "_subtrees"] = out, cached, objs, sub
+        cases[key + "_keys"], cases[key + "_nodes"], cases[key + "_mass"] = tree["keys"], tree["nodes"], tree["mass"]
+        cases[key + "_grad_data"], cases[key + "_grad_kernels"] = gd, gk
+    cases["n_cf"] = np.array(3)
+    return cases
+
+
 def main():
+    reference_root = os.environ.get("GMC_REFERENCE_ROOT", "/root/reference")
+    from oracle import build_ref
+    build_ref.build()
+    np.savez_compressed(os.path.join(HERE, "reference_native.npz"), **reference_native_cases(reference_root))
+    print("wrote reference_native.npz")
     gm, fitting, mat_tools = ref_python.load()
     np.savez_compressed(os.path.join(HERE, "eval_inversed.npz"), **eval_cases(gm))
     print("wrote eval_inversed.npz")

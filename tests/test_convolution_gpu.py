@@ -6,7 +6,7 @@ import torch
 
 from conftest import rel_inf
 from oracle import cpu_oracle
-from gmc import synthetic
+import synthetic_inputs as synthetic
 
 pytestmark = pytest.mark.gpu
 

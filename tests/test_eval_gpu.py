@@ -95,7 +95,7 @@ def test_large_n_uses_the_four_points_per_thread_forward():
 
 
 def test_config0():
-    from gmc import synthetic
+    import synthetic_inputs as synthetic
     m, x, g = synthetic.config0()
     _check(m.numpy(), x.numpy(), g.numpy(), what="config0")
 
@@ -128,7 +128,7 @@ def test_config1_full_size_identities():
     """Full benchmark size (2^32 pairs). The output is linear in the weights, so
     sum_n grad_out[n] out[n] == sum_g w_g dL/dw_g for every (batch, layer); a CPU oracle slice pins values."""
     import gmc.cpp.extensions.evaluate_inversed.evaluate_inversed as ev
-    from gmc import synthetic
+    import synthetic_inputs as synthetic
     m, x, g = synthetic.config1()
     mt = m.cuda().requires_grad_(True)
     xt = x.cuda().requires_grad_(True)

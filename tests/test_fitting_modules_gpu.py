@@ -9,7 +9,7 @@ import torch
 
 from conftest import ROOT, rel_inf
 from oracle import cpu_oracle
-from gmc import synthetic
+import synthetic_inputs as synthetic
 
 pytestmark = pytest.mark.gpu
 

@@ -5,7 +5,7 @@ import pytest
 import torch
 
 from oracle import cpu_oracle
-from gmc import synthetic
+import synthetic_inputs as synthetic
 
 pytestmark = pytest.mark.gpu
 

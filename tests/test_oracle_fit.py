@@ -3,7 +3,7 @@ golden outputs for these stages, so the restatement is checked through invariant
 import numpy as np
 
 from oracle import cpu_oracle
-from gmc import synthetic
+import synthetic_inputs as synthetic
 
 
 def _positive_mixture(B, L, G, seed, D=2):

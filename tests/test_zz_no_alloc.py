@@ -9,7 +9,7 @@ import numpy as np
 import pytest
 import torch
 
-from gmc import synthetic
+import synthetic_inputs as synthetic
 
 pytestmark = pytest.mark.gpu
 
