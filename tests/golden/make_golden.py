@@ -232,7 +232,108 @@ def reference_native_cases(reference_root):
     return cases
 
 
+def gmcn3d_network_case():
+    """The REFERENCE's own network (src/gmc/model.py Net with src/gmc/modules.py layers) run on CPU with every
+    extension routed to the reference's native CPU code: the layer stack of benchmark configuration 4 (conv 1->8 fit
+    64, 8->16 fit 32, 16->32 fit 16, 32->64 fit 8; 5-component kernels; default ReLU fit and normalisation settings;
+    evaluation mode; parameters from the constructors under torch.manual_seed(4)) on a batch of 2 seeded inputs.
+    Stored: the mixture after every layer's normalisation, the integrated features, and per-parameter checksums
+    (the constructors of this package draw the same values under the same seed; the test asserts that first)."""
+    sys.path.insert(0, ROOT)
+    import synthetic_inputs as synthetic
+    gm, modules, model = ref_python.load_network()
+    cfg = model.Config(n_dims=3)
+    cfg.n_classes = 64            # the reference's forward ends in view(n_batch, n_classes); the tail is not stored
+    cfg.layers = [model.Layer(8, 1, 64, 64), model.Layer(16, 1, 32, 32), model.Layer(32, 1, 16, 16), model.Layer(64, 1, 8, 8)]
+    torch.manual_seed(4)
+    net = model.Net(config=cfg).eval()
+    x = synthetic.config4_input(2, 1004)
+    acts, feats, convs = [], [], []
+    for i in range(4):
+        net.norms[i].register_forward_hook(lambda mod, inp, out: acts.append(out[0].detach().clone()))
+        net.gmcs[i].register_forward_hook(lambda mod, inp, out: convs.append(out[0].detach().clone()))
+    net.normX.register_forward_hook(lambda mod, inp, out: feats.append(inp[0].detach().clone()))
+    with torch.no_grad():
+        net(x)
+    cases = {"input": x.numpy(), "features": feats[0].numpy()}
+    for i in range(4):
+        cases[f"layer{i}"] = acts[i].numpy()
+        cases[f"conv{i}"] = convs[i].numpy()
+    names = sorted(net.state_dict().keys())
+    cases["param_names"] = np.array(names)
+    cases["param_checksums"] = np.array([[float(v.double().sum()), float(v.double().abs().sum())]
+                                         for v in (net.state_dict()[n] for n in names)])
+    return cases
+
+
+def relu_tree_hem_case():
+    """The reference's fixed_point_and_tree_hem (src/gmc/fitting.py:162-201, tree_hem :342-358) with the reference's
+    native BVH-MHEM fit and native evaluation, at the shape of benchmark configuration 2 (2D, 1024 -> 64, R = 4) on
+    two mixtures, and in 3D (64 -> 16, R = 4 and R = 2)."""
+    import gmc.fitting as fitting
+    import synthetic_inputs as synthetic
+    cases = {}
+    target, constant = synthetic.config2(n_batch=1, n_layers=2, seed=1002)
+    out, ret_const, steps = fitting.fixed_point_and_tree_hem(target, constant, 64, fitting.Config(n_reduction=4))
+    cases["c2_target"], cases["c2_constant"] = target.numpy(), constant.numpy()
+    cases["c2_fixed_point"], cases["c2_fitting"], cases["c2_ret_const"] = steps[1].numpy(), out.numpy(), ret_const.numpy()
+    t3 = synthetic.config4_input(2, 2004).view(1, 2, 64, 13).contiguous()
+    t3[..., 0] = t3[..., 0] * torch.where(torch.arange(64) % 3 == 0, -1.0, 1.0)
+    c3 = torch.tensor([[0.05, -0.02]])
+    for R in (4, 2):
+        out, ret_const, steps = fitting.fixed_point_and_tree_hem(t3, c3, 16, fitting.Config(n_reduction=R))
+        cases[f"d3r{R}_fitting"], cases[f"d3r{R}_ret_const"] = out.numpy(), ret_const.numpy()
+    cases["d3_target"], cases["d3_constant"] = t3.numpy(), c3.numpy()
+    return cases
+
+
+def inout_files(gm):
+    """Files written by the REFERENCE's own src/gmc/inout.py (save -> version 6, write_gm_to_ply) plus dictionaries in
+    the older layouts its load() accepts (versions 3, 4, 5), with what the reference's load / read_gm_from_ply return
+    for each of them.  Written to tests/golden/inout/."""
+    import pathlib
+    import gmc.config as ref_config
+    import gmc.inout as ref_inout
+    folder = os.path.join(HERE, "inout")
+    os.makedirs(folder, exist_ok=True)
+    ref_config.data_base_path = pathlib.Path(folder)
+    g = torch.Generator().manual_seed(77)
+    w = torch.rand(2, 1, 5, generator=g) + 0.1
+    p = torch.rand(2, 1, 5, 3, generator=g) * 2 - 1
+    A = torch.rand(2, 1, 5, 3, 3, generator=g) * 2 - 1
+    c = A @ A.transpose(-1, -2) * 0.1 + torch.eye(3) * 0.02
+    m = gm.pack_mixture(w, p, c)
+    ref_inout.save(m, "mixture_v6.torch", meta_info={"source": "reference inout.save", "n": 5})
+    amplitudes = gm.convert_priors_to_amplitudes(m)
+    torch.save({"type": "gm.Mixture", "version": 5, "data": amplitudes, "meta_info": None}, os.path.join(folder, "mixture_v5.torch"))
+    torch.save({"type": "gm.Mixture", "version": 4, "weights": gm.weights(amplitudes), "positions": gm.positions(amplitudes),
+                "covariances": gm.covariances(amplitudes), "meta_info": "v4"}, os.path.join(folder, "mixture_v4.torch"))
+    torch.save({"type": "gm.Mixture", "version": 3, "weights": gm.weights(amplitudes).view(2, 5),
+                "positions": gm.positions(amplitudes).view(2, 5, 3), "covariances": gm.covariances(amplitudes).view(2, 5, 3, 3),
+                "meta_info": None}, os.path.join(folder, "mixture_v3.torch"))
+    expected = {}
+    for v in (3, 4, 5, 6):
+        loaded, _ = ref_inout.load(f"mixture_v{v}.torch")
+        expected[f"v{v}"] = loaded.numpy()
+    ply = os.path.join(folder, "mixture.ply")
+    ref_inout.write_gm_to_ply(gm.weights(m), gm.positions(m), gm.covariances(m), 1, ply)
+    expected["ply_plain"] = ref_inout.read_gm_from_ply(ply, ismodel=False, device="cpu").numpy()
+    expected["ply_model"] = ref_inout.read_gm_from_ply(ply, ismodel=True, device="cpu").numpy()
+    expected["mixture"] = m.numpy()
+    np.savez_compressed(os.path.join(folder, "expected.npz"), **expected)
+
+
 def main():
+    if "--network" in sys.argv:
+        from oracle import build_ref
+        build_ref.build()
+        np.savez_compressed(os.path.join(HERE, "gmcn3d_forward.npz"), **gmcn3d_network_case())
+        print("wrote gmcn3d_forward.npz")
+        np.savez_compressed(os.path.join(HERE, "relu_tree_hem.npz"), **relu_tree_hem_case())
+        print("wrote relu_tree_hem.npz")
+        return
+    import subprocess
+    subprocess.run([sys.executable, os.path.abspath(__file__), "--network"], check=True)   # a process of its own
     reference_root = os.environ.get("GMC_REFERENCE_ROOT", "/root/reference")
     from oracle import build_ref
     build_ref.build()
@@ -249,6 +350,8 @@ def main():
     print("wrote relu_fit.npz")
     np.savez_compressed(os.path.join(HERE, "strategies.npz"), **strategy_cases(gm, fitting))
     print("wrote strategies.npz")
+    inout_files(gm)
+    print("wrote inout/")
 
 
 if __name__ == "__main__":

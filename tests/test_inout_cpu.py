@@ -77,3 +77,38 @@ def test_mat_tools_index_helpers():
     coords = torch.tensor([[2, 4, 6], [1, 0, 3]])
     assert mat_tools.flatten_index(coords, idx.shape).tolist() == [idx[2, 4, 6].item(), idx[1, 0, 3].item()]
     assert math.isclose(mat_tools.trace(torch.eye(3).unsqueeze(0)).item(), 3.0)
+
+
+def test_files_written_by_the_reference_load_here(monkeypatch):
+    """tests/golden/inout/ holds a version-6 file written by the reference's inout.save, dictionaries in the older
+    layouts (3, 4, 5: amplitudes) and a PLY written by the reference's write_gm_to_ply, with what the reference's own
+    load / read_gm_from_ply return for them (src/gmc/inout.py:12-141)."""
+    import os
+    import pathlib
+    import numpy as np
+    import gmc.config as config
+    import gmc.inout as inout
+    folder = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "inout")
+    expected = dict(np.load(os.path.join(folder, "expected.npz")))
+    monkeypatch.setattr(config, "data_base_path", pathlib.Path(folder))
+    for v in (3, 4, 5, 6):
+        loaded, meta = inout.load(f"mixture_v{v}.torch")
+        assert loaded.shape == (2, 1, 5, 13)
+        assert np.allclose(loaded.numpy(), expected[f"v{v}"], rtol=1e-6, atol=1e-8), v
+    assert inout.load("mixture_v6.torch")[1] == {"source": "reference inout.save", "n": 5}
+    assert np.array_equal(inout.load("mixture_v6.torch")[0].numpy(), expected["mixture"])
+    ply = os.path.join(folder, "mixture.ply")
+    assert np.allclose(inout.read_gm_from_ply(ply, ismodel=False, device="cpu").numpy(), expected["ply_plain"], rtol=1e-6)
+    assert np.allclose(inout.read_gm_from_ply(ply, ismodel=True, device="cpu").numpy(), expected["ply_model"], rtol=1e-5)
+
+
+def test_ply_written_here_equals_the_reference_file(tmp_path):
+    import os
+    import numpy as np
+    import gmc.inout as inout
+    import gmc.mixture as gm
+    folder = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "inout")
+    m = torch.from_numpy(dict(np.load(os.path.join(folder, "expected.npz")))["mixture"])
+    path = str(tmp_path / "mine.ply")
+    inout.write_gm_to_ply(gm.weights(m), gm.positions(m), gm.covariances(m), 1, path)
+    assert open(path).read() == open(os.path.join(folder, "mixture.ply")).read()
