@@ -1,15 +1,23 @@
-"""Benchmark of the mixture-evaluation hot path: evaluate_inversed forward + backward, 3D, fp32.
+"""Benchmark of the gmc operator path on B200.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config 0..4]
 
-A step is one forward + backward pass over one batch of the 3D evaluation configuration
-(B=32 per GPU, L=16, G=512 components, N=16384 query points: 2^32 Gaussian-point pairs per GPU and step).
-With N > 1 (launched under torch.distributed.run, one rank per GPU) every rank owns its own batch shard
-(weak scaling); the only inter-GPU traffic is an NCCL all-gather of the forward outputs, enqueued on a side
-stream so that it overlaps the backward kernel. Rank 0 prints one JSON line.
+Default (--config 0), one JSON line:
+  * headline: 3D mixture evaluation, evaluate_inversed forward + backward (B=32, L=16, G=512 components, N=16384 query
+    points: 2^32 Gaussian-point pairs per step). The batch of 32 is SHARDED over the N ranks (strong scaling: 32 / 16 /
+    8 / 4 mixtures-batches per GPU); the only inter-GPU traffic is an NCCL all-gather of the forward outputs, enqueued
+    so that it overlaps the backward kernel. `weak` repeats the measurement with 32 per GPU.
+  * `sustained`: the same step back to back for at least three seconds with the SM clock sampled.
+  * `secondary`: the other benchmark configurations, each with its own value, end-to-end figure, roofline and CPU
+    baseline: 2 = 2D ReLU fit with BVH-MHEM reduction, 3 = 2D convolution-fitting layer, 4 = 3D GMCN forward
+    (B=256 in total, sharded over the ranks).
+--config 1..4 prints that configuration alone (used for profiler captures).
 
---impl reference times the reference's CPU algorithm (the oracle restatement of its OpenMP path, fp32) on the
-host cores for the same metric, on a bounded batch slice of the same workload.
+Under torch.distributed.run (one rank per GPU) rank 0 prints the line. Times are CUDA-event times on the launching
+stream, maximum over ranks.
+
+--impl reference times the reference's own CPU implementation of the same configuration on the host cores (the
+library built from the reference's sources when it is present, else the restated port), on a bounded sample.
 """
 import argparse
 import json
@@ -27,9 +35,10 @@ for _p in (ROOT, PKG):
 METRIC = "gaussian_point_evals_per_s_fwd_bwd_3d"
 UNIT = "pair-evals/s"
 L, G, N, D = 16, 512, 16384, 3
-B_PER_GPU = 32
+B_TOTAL = 32
 FLOP_FWD, FLOP_BWD = 27, 52          # algorithmic FP32 flop per (Gaussian, point) pair, 3D
 N_SM_LANES = 128                      # FP32 lanes per SM
+SECONDARY_BATCH = {2: 32, 3: 64, 4: 256}
 
 
 def _args():
@@ -38,17 +47,19 @@ def _args():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--cpu-batch", type=int, default=16, help="batch slice timed on the host cores")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="host time given to one CPU baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batch", type=int, default=None,
-                    help="batch per GPU (default: the configuration's 32; smaller values are for profiler captures)")
+                    help="batch PER GPU instead of the configuration's total batch split over the ranks "
+                         "(smaller values are for profiler captures)")
     ap.add_argument("--relu-fit", choices=["fixed_point_only", "fixed_point_and_tree_hem"], default="fixed_point_only",
                     help="config 4: ReLU fitting strategy of the layers (the second one runs LBVH + BVH-MHEM in 3D)")
     ap.add_argument("--no-cuda-graph", action="store_true", help="config 4: launch the forward kernel by kernel")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiler captures)")
-    ap.add_argument("--config", type=int, default=1, choices=[1, 2, 3, 4],
-                    help="1 (default, the headline): 3D evaluation fwd+bwd; 2: 2D ReLU fit with BVH-MHEM reduction; "
-                         "3: 2D convolution fitting layer; 4: 3D GMCN forward")
+    ap.add_argument("--no-extras", action="store_true", help="--config 0: headline only (no weak / sustained / secondary)")
+    ap.add_argument("--config", type=int, default=0, choices=[0, 1, 2, 3, 4],
+                    help="0 (default): headline + sustained + secondary blocks; 1: 3D evaluation fwd+bwd alone; "
+                         "2: 2D ReLU fit with BVH-MHEM reduction; 3: 2D convolution fitting layer; 4: 3D GMCN forward")
     return ap.parse_args()
 
 
@@ -105,6 +116,7 @@ class ClockSampler:
         if self.nvml is not None:
             self._thread = threading.Thread(target=self._run, daemon=True)
             self._thread.start()
+        return self
 
     def stop(self):
         self._stop.set()
@@ -115,6 +127,34 @@ class ClockSampler:
         s = sorted(self.samples)
         reasons = sorted(r for r in self.reasons if r not in ("None", "GpuIdle", "ApplicationsClocksSetting"))
         return {"sm_mhz": s[len(s) // 2], "sm_max_mhz": self.max_mhz, "reasons": reasons, "samples": len(s)}
+
+
+def _gpu_index(local_rank):
+    """NVML index of this rank's GPU (NVML ignores CUDA_VISIBLE_DEVICES)."""
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local_rank])
+        except (ValueError, IndexError):
+            pass
+    return local_rank
+
+
+def _bind_rank_to_cores(local_rank, world):
+    """Gives every rank of a multi-rank run its own contiguous share of the host cores this process may use, before
+    any page-locked buffer is allocated, so that staging threads and first-touched pages stay put."""
+    if world <= 1 or not hasattr(os, "sched_setaffinity"):
+        return None
+    try:
+        cpus = sorted(os.sched_getaffinity(0))
+        per = len(cpus) // world
+        if per < 1:
+            return None
+        mine = cpus[local_rank * per:(local_rank + 1) * per]
+        os.sched_setaffinity(0, mine)
+        return f"{mine[0]}-{mine[-1]}"
+    except OSError:
+        return None
 
 
 def _repeat_for(fn, min_seconds=10.0, max_reps=1000):
@@ -129,52 +169,144 @@ def _repeat_for(fn, min_seconds=10.0, max_reps=1000):
             return reps, dt
 
 
-def _cpu_baseline(cpu_batch):
-    """Reference CPU algorithm (oracle restatement, fp32, OpenMP over query points) on a batch slice."""
+# ---------------------------------------------------------------------------------------------------------------
+# CPU baselines: the reference's own CPU code when its library is present, else the restated port
+# ---------------------------------------------------------------------------------------------------------------
+def _cpu_backend():
+    from oracle import cpu_oracle, ref_native
+    n = cpu_oracle.use_all_cores()       # also lifts OMP_NUM_THREADS=1 exported by torchrun for the port's loops
+    if ref_native.available():
+        try:
+            ref_native.lib()
+            return ref_native, "reference", n
+        except OSError:
+            pass
+    return cpu_oracle, "port", n
+
+
+def cpu_baseline(config, seconds):
+    """One bounded CPU sample of configuration `config` -> cpu_baseline block (value in the configuration's unit)."""
+    import numpy as np
     import synthetic_inputs as synthetic
-    from oracle import cpu_oracle
-    cpu_oracle.use_all_cores()
-    m, x, g = synthetic.config1(n_batch=cpu_batch)
-    m, x, g = m.numpy(), x.numpy(), g.numpy()
-    cpu_oracle.eval_forward(m[:1, :1], x[:1, :1])   # page in / thread pool warm-up
-    t0 = time.perf_counter()
-    cpu_oracle.eval_forward(m, x)
-    cpu_oracle.eval_backward(g, m, x)
-    dt = time.perf_counter() - t0
-    pairs = cpu_batch * L * G * N
-    return {"value": pairs / dt, "unit": UNIT, "cores": cpu_oracle.num_threads(), "kind": "port",
-            "sample": f"batch slice B={cpu_batch} of the same workload ({pairs} pairs, one fwd+bwd, {dt:.2f} s); "
-                      "fp32, OpenMP over query points"}, dt
+    backend, kind, cores = _cpu_backend()
+    how = ("the reference's own CPU path (src/gmc/cpp/extensions built by oracle/build_ref.py; its launcher runs one "
+           "OpenMP thread per CUDA-block thread)" if kind == "reference" else
+           "restated port of the reference's CPU path, gcc -O3 -march=x86-64-v3 -fopenmp")
+    if config == 1:
+        m, x, g = (t.numpy() for t in synthetic.config1(n_batch=1))
+        t0 = time.perf_counter()
+        backend.eval_forward(m[:, :1], x[:, :1])
+        backend.eval_backward(g[:, :1], m[:, :1], x[:, :1])
+        t1 = time.perf_counter() - t0                                    # one (batch, layer) mixture: 2^23 pairs
+        n_mix = int(max(1, min(16, seconds / max(t1, 1e-3))))
+        t0 = time.perf_counter()
+        backend.eval_forward(m[:, :n_mix], x[:, :n_mix])
+        backend.eval_backward(g[:, :n_mix], m[:, :n_mix], x[:, :n_mix])
+        dt = time.perf_counter() - t0
+        pairs = n_mix * G * N
+        return {"value": pairs / dt, "unit": UNIT, "cores": cores, "kind": kind,
+                "sample": f"{n_mix} of the 512 (batch, layer) mixtures of the same workload ({pairs} pairs, one fwd+bwd, "
+                          f"{dt:.2f} s), scaled linearly; fp32; {how}"}
+    if config == 2:
+        sample, _ = synthetic.config2(n_batch=1, n_layers=32)
+        flat = sample.numpy().reshape(-1, 1024, 7).copy()
+        flat[..., 0] = np.abs(flat[..., 0]) + 0.01
+        reps, dt = _repeat_for(lambda: backend.mhem_fit_forward(flat, 64, 4), seconds)
+        return {"value": reps * flat.shape[0] * 1024 / dt, "unit": "gaussians/s", "cores": cores, "kind": kind,
+                "sample": f"LBVH + BVH-MHEM fit of {flat.shape[0]} mixtures x 1024 Gaussians, {reps} passes ({dt:.2f} s); "
+                          f"the fixed-point evaluations are not included in the CPU figure; {how}"}
+    if config == 3:
+        sd, sk, K = synthetic.config3(n_batch=4)
+        sdn, skn = sd.numpy(), sk.numpy()
+        reps, dt = _repeat_for(lambda: backend.convolution_fitting_forward(sdn, skn, K), seconds)
+        return {"value": reps * 4 * 16 * 5120 / dt, "unit": "product-gaussians/s", "cores": cores, "kind": kind,
+                "sample": f"64 of the layer's 1024 trees (5120 products each), {reps} passes ({dt:.2f} s); {how}"}
+    import torch
+    g = torch.Generator().manual_seed(1)
+    layers = []
+    nb = 4
+    for (cin, gcomp, cout, kfit) in ((1, 64, 8, 64), (8, 64, 16, 32), (16, 32, 32, 16), (32, 16, 64, 8)):
+        cov, _ = synthetic.covariances_and_inverses((nb, cin, gcomp), 3, 0.03, 0.15, g)
+        data = synthetic.pack(torch.rand(nb, cin, gcomp, generator=g), torch.rand(nb, cin, gcomp, 3, generator=g) * 2 - 1, cov)
+        kcov, _ = synthetic.covariances_and_inverses((cout, cin, 5), 3, 0.1, 0.4, g)
+        kern = synthetic.pack(torch.randn(cout, cin, 5, generator=g) + 0.1, torch.randn(cout, cin, 5, 3, generator=g), kcov)
+        layers.append((data.numpy(), kern.numpy(), kfit))
+
+    def four_layers():
+        for data, kern, kfit in layers:
+            backend.convolution_fitting_forward(data, kern, kfit)
+
+    reps, dt = _repeat_for(four_layers, seconds)
+    return {"value": reps * nb / dt, "unit": "samples/s", "cores": cores, "kind": kind,
+            "sample": f"the four convolution-fitting layers only (the dominant stage) on {nb} samples, {reps} passes "
+                      f"({dt:.2f} s); ReLU fixed-point evaluations and normalisations are not included; {how}"}
+
+
+_METRICS = {1: (METRIC, UNIT), 2: ("gaussians_per_s_relu_fit_bvh_mhem_2d", "gaussians/s"),
+            3: ("product_gaussians_per_s_convolution_fitting_2d", "product-gaussians/s"),
+            4: ("samples_per_s_gmcn3d_forward", "samples/s")}
+_WORKLOADS = {1: f"config1: 3D evaluate_inversed fwd+bwd, B={B_TOTAL} L={L} G={G} N={N}",
+              2: "config2: LBVH + BVH-MHEM fit, L=32 G=1024 -> K=64, R=4",
+              3: "config3: convolution_fitting forward, Cin=8 G=128 Cout=16 Gk=5 -> K=128 (T=5120)",
+              4: "config4: the four convolution-fitting layers of the GMCN-3D forward"}
 
 
 def run_reference(args, rank):
     if rank != 0:
         return
-    times = []
-    base = None
+    config = args.config or 1
+    metric, unit = _METRICS[config]
+    values, times, base = [], [], None
+    t_start = time.perf_counter()
     for i in range(args.warmup + args.steps):
-        base, dt = _cpu_baseline(args.cpu_batch)
+        t0 = time.perf_counter()
+        base = cpu_baseline(config, args.cpu_seconds)
         if i >= args.warmup:
-            times.append(dt)
-        if sum(times) > 120:     # keep the whole run within a few minutes
+            values.append(base["value"])
+            times.append(time.perf_counter() - t0)
+        if time.perf_counter() - t_start > 150:     # keep the whole run within a few minutes
             break
-    steps = len(times)
-    pairs = args.cpu_batch * L * G * N
-    value = pairs * steps / sum(times)
+    if not values:
+        values, times = [base["value"]], [time.perf_counter() - t_start]
+    value = sum(values) / len(values)
     base["value"] = value
-    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-            "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / steps, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"config1 slice: 3D evaluate_inversed fwd+bwd, B={args.cpu_batch} L={L} G={G} N={N}"},
+    line = {"impl": "reference", "metric": metric, "value": value, "unit": unit, "n_gpus": args.gpus, "steps": len(values),
+            "warmup": args.warmup, "ms_per_step": 1e3 * sum(times) / len(times), "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": _WORKLOADS[config] + "; each step is one bounded sample of it on the host cores"},
             "cpu_baseline": base,
-            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+            "e2e": {"value": value, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     _emit(line)
 
 
+# ---------------------------------------------------------------------------------------------------------------
+# configuration 1: 3D evaluation forward + backward
+# ---------------------------------------------------------------------------------------------------------------
+def build_probe():
+    """Builds bench_probe.cu (beside this file) into bench_probe.so for sm_100a; returns the path or None."""
+    import subprocess
+    src, out = os.path.join(ROOT, "bench_probe.cu"), os.path.join(ROOT, "bench_probe.so")
+    if os.path.exists(out) and os.path.getmtime(out) >= os.path.getmtime(src):
+        return out
+    nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+    try:
+        subprocess.run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-shared", "-Xcompiler",
+                        "-fPIC", "-o", out, src], check=True, capture_output=True)
+    except (OSError, subprocess.CalledProcessError):
+        return None
+    return out
+
+
 def _measure_fp32_peak(torch, dev):
-    """FP32 FMA peak of this GPU in TFLOP/s: the library's probe kernel (FFMA chains only), best of 5 launches."""
+    """FP32 FMA peak of this GPU in TFLOP/s: a chain-of-FFMA probe kernel (bench_probe.cu beside this file, built into
+    its own small library), best of 5 launches. None when the probe library cannot be built."""
     import ctypes
-    from gmc import _native
+    path = build_probe()
+    if path is None:
+        return None
+    probe = ctypes.CDLL(path)
+    probe.gmc_bench_fp32_fma_probe.restype = ctypes.c_int
+    probe.gmc_bench_fp32_fma_probe.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_double), ctypes.c_void_p]
     sink = torch.zeros(1, device=dev)
     flop = ctypes.c_double(0.0)
     stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
@@ -182,7 +314,8 @@ def _measure_fp32_peak(torch, dev):
     for i in range(6):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        _native.check(_native.lib.gmc_fp32_fma_probe(_native.ptr(sink), 4000, ctypes.byref(flop), stream), "fp32 probe")
+        if probe.gmc_bench_fp32_fma_probe(ctypes.c_void_p(sink.data_ptr()), 4000, ctypes.byref(flop), stream) != 0:
+            return None
         e1.record()
         torch.cuda.synchronize(dev)
         if i > 0:
@@ -190,25 +323,55 @@ def _measure_fp32_peak(torch, dev):
     return best
 
 
-def run_ours(args, rank, world, local_rank):
+def _copy_ceiling(torch, dist, dev, world, h2d_bytes, d2h_bytes):
+    """Plain page-locked copies of the step's input and output sizes, both directions at once on two streams, all ranks
+    at the same time: what the host memory system gives every rank, in GB/s per direction."""
+    h_in = torch.empty(max(h2d_bytes, 4) // 4, dtype=torch.float32).pin_memory()
+    h_out = torch.empty(max(d2h_bytes, 4) // 4, dtype=torch.float32).pin_memory()
+    d_in, d_out = torch.empty_like(h_in, device=dev), torch.empty_like(h_out, device=dev)
+    s1, s2 = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    reps = 5
+
+    def once():
+        with torch.cuda.stream(s1):
+            d_in.copy_(h_in, non_blocking=True)
+        with torch.cuda.stream(s2):
+            h_out.copy_(d_out, non_blocking=True)
+
+    once()
+    torch.cuda.synchronize(dev)
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        once()
+    torch.cuda.synchronize(dev)
+    dt = (time.perf_counter() - t0) / reps
+    t = torch.tensor([dt], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dt = float(t.item())
+    return {"h2d_gbs": h2d_bytes / dt / 1e9, "d2h_gbs": d2h_bytes / dt / 1e9, "ms": dt * 1e3,
+            "how": "both directions at once, page-locked buffers of the step's sizes, all ranks together, slowest rank"}
+
+
+def config1_block(args, rank, world, local_rank, b_rank, steps, with_e2e, with_peak, sustained_seconds=0.0):
+    """Times `steps` forward+backward passes over this rank's shard of b_rank batch entries -> dict (rank 0) or None."""
     import torch
     import torch.distributed as dist
-    import gmc.mixture as gm
     from gmc import sharding
     import synthetic_inputs as synthetic
     import gmc.cpp.extensions.evaluate_inversed.evaluate_inversed as ev
 
-    if not torch.cuda.is_available():
-        raise RuntimeError("bench.py needs a CUDA device: the library has no CPU path")
-    torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
-
-    # every rank owns its own batch shard (different seed per rank)
-    B_PER_GPU = args.batch if args.batch is not None else globals()["B_PER_GPU"]
-    m_h, x_h, g_h = synthetic.config1(n_batch=B_PER_GPU, seed=1001 + rank)
-    m_h, x_h, g_h = m_h.pin_memory(), x_h.pin_memory(), g_h.pin_memory()
+    # the configuration's batch is generated whole from its seed and this rank takes its contiguous shard
+    n_gen = b_rank * world
+    m_all, x_all, g_all = synthetic.config1(n_batch=n_gen, seed=1001)
+    s, e = sharding.shard_range(n_gen, world, rank)
+    m_h, x_h, g_h = (t[s:e].contiguous().pin_memory() for t in (m_all, x_all, g_all))
+    del m_all, x_all, g_all
     m, x, g = m_h.to(dev), x_h.to(dev), g_h.to(dev)
-    pairs_rank = B_PER_GPU * L * G * N
+    pairs_rank = b_rank * L * G * N
     gather = sharding.OutputGatherer(world, dev) if world > 1 else None
 
     def step(record=None):
@@ -224,17 +387,18 @@ def run_ours(args, rank, world, local_rank):
             record[2].record()
         return out, gm_, gx_
 
-    for _ in range(max(args.warmup, 3)):
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
         step()
     torch.cuda.synchronize()
 
-    sampler = ClockSampler(torch.cuda.current_device() if "CUDA_VISIBLE_DEVICES" not in os.environ else local_rank)
-    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    sampler = ClockSampler(_gpu_index(local_rank))
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     sampler.start()
-    for i in range(args.steps):
+    for i in range(steps):
         evs[i][0].record()
         step(evs[i])
     torch.cuda.synchronize()
@@ -242,21 +406,41 @@ def run_ours(args, rank, world, local_rank):
         dist.barrier()
     clocks = sampler.stop()
     total_ms = evs[0][0].elapsed_time(evs[-1][2])
-    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in evs) / args.steps
-    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in evs) / args.steps
+    fwd_ms = sum(e_[0].elapsed_time(e_[1]) for e_ in evs) / steps
+    bwd_ms = sum(e_[1].elapsed_time(e_[2]) for e_ in evs) / steps
+
+    # ---- the same step back to back for several seconds: the clock the GPU settles at, and what the step costs there ----
+    sustained = None
+    if sustained_seconds > 0:
+        n_sus = max(steps, int(sustained_seconds * 1e3 / max(total_ms / steps, 1e-3)) + 1)
+        sus = ClockSampler(_gpu_index(local_rank))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        sus.start()
+        e0.record()
+        for _ in range(n_sus):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        sus_clocks = sus.stop()
+        sus_ms = e0.elapsed_time(e1)
+        sustained = [sus_ms, n_sus, sus_clocks]
 
     # ---- end to end through the public API with host buffers ----
-    out_h = torch.empty((B_PER_GPU, L, N), dtype=torch.float32).pin_memory()
+    out_h = torch.empty((b_rank, L, N), dtype=torch.float32).pin_memory()
     gm_h = torch.empty_like(m_h).pin_memory()
     gx_h = torch.empty_like(x_h).pin_memory()
-    e2e_steps = max(3, min(args.steps, 20))
+    h2d = (m_h.numel() + x_h.numel() + g_h.numel()) * 4
+    d2h = (out_h.numel() + gm_h.numel() + gx_h.numel()) * 4
+    e2e_steps = max(3, min(steps, 20))
+    e2e_ms, ceiling = float("nan"), None
+    if with_e2e:
+        def e2e_step():
+            # the public host-buffer call: batch slices pipelined through copy-in / kernels / copy-out streams
+            ev.host_forward_backward(m_h, x_h, g_h, out=out_h, grad_mixture=gm_h, grad_xes=gx_h)
 
-    def e2e_step():
-        # the public host-buffer call: batch slices pipelined through copy-in / kernels / copy-out streams
-        ev.host_forward_backward(m_h, x_h, g_h, out=out_h, grad_mixture=gm_h, grad_xes=gx_h)
-
-    e2e_ms = float("nan")
-    if not args.no_e2e:
         for _ in range(3):
             e2e_step()
         torch.cuda.synchronize()
@@ -269,61 +453,63 @@ def run_ours(args, rank, world, local_rank):
         e1.record()
         torch.cuda.synchronize()
         e2e_ms = e0.elapsed_time(e1) / e2e_steps
+        ceiling = _copy_ceiling(torch, dist, dev, world, h2d, d2h)
+        ev._native.lib.gmc_host_pipeline_release()
 
-    t = torch.tensor([total_ms, fwd_ms, bwd_ms, e2e_ms], dtype=torch.float64, device=dev)
+    vals = [total_ms, fwd_ms, bwd_ms, e2e_ms, sustained[0] if sustained else 0.0]
+    t = torch.tensor(vals, dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, fwd_ms, bwd_ms, e2e_ms = t.tolist()
+    total_ms, fwd_ms, bwd_ms, e2e_ms, sus_ms = t.tolist()
     if rank != 0:
-        return
+        return None
 
     peaks, peaks_kind = _measured_peaks()
     n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
     sm_max_mhz = float(peaks.get("sm_max_mhz", 1965.0))
-    fp32_nominal_tflops = n_sm * N_SM_LANES * 2 * sm_max_mhz * 1e6 / 1e12
-    fp32_peak_tflops = _measure_fp32_peak(torch, dev)     # MEASURED_PEAKS.json has no FP32 entry: measured here
-    ms_per_step = total_ms / args.steps
-    value = world * pairs_rank / (ms_per_step * 1e-3)
+    nominal = n_sm * N_SM_LANES * 2 * sm_max_mhz * 1e6 / 1e12
+    measured = _measure_fp32_peak(torch, dev) if with_peak else None
+    peak = measured if measured else nominal
+    peak_source = ("measured in this run: scalar FFMA chains (bench_probe, best of 5, CUDA events); MEASURED_PEAKS.json has "
+                   "no FP32 entry" if measured else
+                   f"nominal {n_sm} SMs x 128 lanes x 2 flop x {sm_max_mhz:.0f} MHz (MEASURED_PEAKS.json has no FP32 entry)")
+    ms_per_step = total_ms / steps
     ach_bwd = FLOP_BWD * pairs_rank / (bwd_ms * 1e-3) / 1e12
     ach_fwd = FLOP_FWD * pairs_rank / (fwd_ms * 1e-3) / 1e12
     ach_all = (FLOP_FWD + FLOP_BWD) * pairs_rank / ((fwd_ms + bwd_ms) * 1e-3) / 1e12
-    h2d = (m_h.numel() + x_h.numel() + g_h.numel()) * 4
-    d2h = (out_h.numel() + gm_h.numel() + gx_h.numel()) * 4
-    line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"config1: 3D evaluate_inversed fwd+bwd, B={B_PER_GPU}/GPU L={L} G={G} N={N} "
-                               f"({pairs_rank} pairs per GPU and step)",
-                   "l2": f"inputs ({(m_h.numel() + x_h.numel() + g_h.numel()) * 4 / 1e6:.0f} MB per step) "
-                         "are larger than L2 (126 MB) at the default batch; no explicit flush",
-                   "sharding": f"batch over {world} rank(s), all-gather of forward outputs overlapped with backward"},
-        "roofline": {"bound": "fp32", "kernel": "eval_backward_kernel<3,2>", "achieved": ach_bwd,
-                     "peak": fp32_peak_tflops, "unit": "TFLOP/s", "frac": ach_bwd / fp32_peak_tflops,
-                     # dram__bytes_read+write of one launch: 32.79 MB captured by ncu at B=4 (profiles/), scaled by B/4
+    block = {
+        "value": world * pairs_rank / (ms_per_step * 1e-3), "unit": UNIT, "ms_per_step": ms_per_step, "steps": steps,
+        "batch_per_gpu": b_rank, "pairs_per_gpu_and_step": pairs_rank,
+        "roofline": {"bound": "fp32", "kernel": "eval_backward_kernel<3,2,128>", "achieved": ach_bwd,
+                     "peak": peak, "unit": "TFLOP/s", "frac": ach_bwd / peak,
+                     # dram__bytes_read+write of one launch: captured by ncu at B=4 (profiles/), scaled by B/4
                      # because every byte of traffic belongs to one (batch, layer) mixture
-                     "traffic": 32.79e6 * B_PER_GPU / 4, "traffic_unit": "bytes (ncu capture at B=4, scaled by B/4)",
-                     "peak_source": "measured in this run: scalar FFMA chains (gmc_fp32_fma_probe, best of 5, CUDA events); "
-                                    "MEASURED_PEAKS.json has no FP32 entry",
-                     "peak_nominal": fp32_nominal_tflops, "frac_of_nominal": ach_bwd / fp32_nominal_tflops,
-                     "peak_nominal_source": f"{n_sm} SMs x 128 lanes x 2 flop x {sm_max_mhz:.0f} MHz "
-                                            f"(sm_max_mhz from {peaks_kind} MEASURED_PEAKS.json)",
+                     "traffic": 32.79e6 * b_rank / 4, "traffic_unit": "bytes (ncu capture at B=4, scaled by B/4)",
+                     "peak_source": peak_source, "peak_nominal": nominal, "frac_of_nominal": ach_bwd / nominal,
                      "algorithmic_flop_per_pair": FLOP_BWD, "ms_per_launch": bwd_ms},
         "roofline_forward": {"bound": "fp32", "kernel": "eval_forward_kernel<3,8>", "achieved": ach_fwd,
-                             "peak": fp32_peak_tflops, "unit": "TFLOP/s", "frac": ach_fwd / fp32_peak_tflops,
+                             "peak": peak, "unit": "TFLOP/s", "frac": ach_fwd / peak, "frac_of_nominal": ach_fwd / nominal,
                              "algorithmic_flop_per_pair": FLOP_FWD, "ms_per_launch": fwd_ms},
-        "roofline_fwd_bwd": {"bound": "fp32", "achieved": ach_all, "peak": fp32_peak_tflops, "unit": "TFLOP/s",
-                             "frac": ach_all / fp32_peak_tflops, "frac_of_nominal": ach_all / fp32_nominal_tflops,
+        "roofline_fwd_bwd": {"bound": "fp32", "achieved": ach_all, "peak": peak, "unit": "TFLOP/s",
+                             "frac": ach_all / peak, "frac_of_nominal": ach_all / nominal,
                              "algorithmic_flop_per_pair": FLOP_FWD + FLOP_BWD},
-        "e2e": None if args.no_e2e else
-               {"value": world * pairs_rank / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps},
-        "gpu_launches": 2 * args.steps,
+        "e2e": None if not with_e2e else
+               {"value": world * pairs_rank / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d * world,
+                "d2h_bytes_per_step": d2h * world, "ms_per_step": e2e_ms, "steps": e2e_steps,
+                "h2d_gbs_per_rank": h2d / (e2e_ms * 1e-3) / 1e9, "d2h_gbs_per_rank": d2h / (e2e_ms * 1e-3) / 1e9,
+                "copy_ceiling_per_rank": ceiling},
+        "gpu_launches": 2 * steps,
         "clocks": clocks,
     }
-    if not args.no_cpu_baseline and world == 1:
-        line["cpu_baseline"], _ = _cpu_baseline(args.cpu_batch)
-    _emit(line)
+    if sustained is not None:
+        _, n_sus, sus_clocks = sustained
+        sus_step = sus_ms / n_sus
+        block["sustained"] = {"seconds": sus_ms * 1e-3, "steps": n_sus, "ms_per_step": sus_step,
+                              "value": world * pairs_rank / (sus_step * 1e-3), "unit": UNIT, "clocks": sus_clocks,
+                              "ms_x_mhz": sus_step * (sus_clocks.get("sm_mhz") or 0),
+                              "burst_ms_x_mhz": ms_per_step * (clocks.get("sm_mhz") or 0),
+                              "frac_of_nominal_fwd_bwd": (FLOP_FWD + FLOP_BWD) * pairs_rank / (sus_step * 1e-3) / 1e12 / nominal}
+    return block
 
 
 # ---------------------------------------------------------------------------------------------------------------
@@ -342,14 +528,20 @@ def _gmcn3d(torch, model, fitting_method=None):
     return net, head
 
 
-def _secondary_setup(args, rank, dev):
-    """-> (metric, unit, units per step and rank, step(), host_inputs, workload text, algorithmic bytes, cpu_baseline())"""
+_DOMINANT = {2: "mhem_fit_forward_kernel<2,4>", 3: "convolution_fitting_tree_kernel<2>", 4: "convolution_fitting_tree_kernel<3>"}
+
+
+def _secondary_setup(args, config, rank, world, dev, n_batch):
+    """-> (units per step and rank, step(), host_inputs, workload text, algorithmic bytes per step and rank)"""
     import torch
+    from gmc import sharding
     import synthetic_inputs as synthetic
     import gmc.fitting as fitting
-    if args.config == 2:
-        n_batch = args.batch if args.batch is not None else 32
-        m_h, c_h = synthetic.config2(n_batch=n_batch, seed=1002 + rank)
+    n_gen = n_batch * world
+    s, e = sharding.shard_range(n_gen, world, rank)
+    if config == 2:
+        m_all, c_all = synthetic.config2(n_batch=n_gen, seed=1002)
+        m_h, c_h = m_all[s:e].contiguous(), c_all[s:e].contiguous()
         m, c = m_h.to(dev), c_h.to(dev)
         cfg = fitting.Config(n_reduction=4)
         units = n_batch * 32 * 1024
@@ -359,25 +551,14 @@ def _secondary_setup(args, rank, dev):
             with torch.no_grad():
                 return fitting.fixed_point_and_tree_hem(mm, cc, 64, cfg)[0]
 
-        def cpu():
-            from oracle import cpu_oracle
-            cpu_oracle.use_all_cores()
-            sample, _ = synthetic.config2(n_batch=32)
-            flat = sample.numpy().reshape(-1, 1024, 7).copy()
-            flat[..., 0] = abs(flat[..., 0]) + 0.01
-            reps, dt = _repeat_for(lambda: cpu_oracle.mhem_fit_forward(flat, 64, 4))
-            return {"value": reps * flat.shape[0] * 1024 / dt, "unit": "gaussians/s", "cores": cpu_oracle.num_threads(),
-                    "kind": "port",
-                    "sample": f"LBVH + BVH-MHEM fit of {flat.shape[0]} mixtures x 1024 Gaussians, {reps} passes "
-                              f"({dt:.2f} s); the fixed-point evaluations are not included in the CPU figure"}
         # LBVH 56 B/Gaussian + MHEM per mixture 28672 + 2*128*(2G-1) + 1792 B (node attributes written and read once)
         alg_bytes = units * 56 + n_batch * 32 * (28672 + 2 * 128 * 2047 + 1792)
-        return ("gaussians_per_s_relu_fit_bvh_mhem_2d", "gaussians/s", units, step, (m_h, c_h),
-                f"config2: fixed_point_and_tree_hem, B={n_batch}/GPU L=32 G=1024 -> K=64, R=4", alg_bytes, cpu)
-    if args.config == 3:
+        return (units, step, (m_h, c_h),
+                f"config2: fixed_point_and_tree_hem, B={n_gen} (={n_batch}/GPU) L=32 G=1024 -> K=64, R=4", alg_bytes)
+    if config == 3:
         import gmc.cpp.extensions.convolution_fitting.binding as cf
-        n_batch = args.batch if args.batch is not None else 64
-        d_h, k_h, K = synthetic.config3(n_batch=n_batch, seed=1003 + rank)
+        d_all, k_h, K = synthetic.config3(n_batch=n_gen, seed=1003)
+        d_h = d_all[s:e].contiguous()
         d, k = d_h.to(dev), k_h.to(dev)
         units = n_batch * 16 * 5120
 
@@ -385,22 +566,12 @@ def _secondary_setup(args, rank, dev):
             dd, kk = (d, k) if inputs is None else inputs
             return cf.forward(dd, kk, K)[0]
 
-        def cpu():
-            from oracle import cpu_oracle
-            cpu_oracle.use_all_cores()
-            sd, sk, _ = synthetic.config3(n_batch=64)
-            sdn, skn = sd.numpy(), sk.numpy()
-            reps, dt = _repeat_for(lambda: cpu_oracle.convolution_fitting_forward(sdn, skn, K))
-            return {"value": reps * 64 * 16 * 5120 / dt, "unit": "product-gaussians/s", "cores": cpu_oracle.num_threads(),
-                    "kind": "port",
-                    "sample": f"the whole layer (1024 trees x 5120 products), {reps} passes ({dt:.2f} s)"}
         alg_bytes = (d_h.numel() + k_h.numel()) * 4 + n_batch * 16 * (5120 * 4 + 2 * K * 4 + K * 7 * 4 + K * 4 * 4)
-        return ("product_gaussians_per_s_convolution_fitting_2d", "product-gaussians/s", units, step, (d_h, k_h),
-                f"config3: convolution_fitting forward, B={n_batch}/GPU Cin=8 G=128 Cout=16 Gk=5 -> K=128 (T=5120)",
-                alg_bytes, cpu)
+        return (units, step, (d_h, k_h),
+                f"config3: convolution_fitting forward, B={n_gen} (={n_batch}/GPU) Cin=8 G=128 Cout=16 Gk=5 -> K=128 (T=5120)",
+                alg_bytes)
     import gmc.model as model
-    n_batch = args.batch if args.batch is not None else 256
-    x_h = synthetic.config4_input(n_batch=n_batch, seed=1004 + rank)
+    x_h = synthetic.config4_input(n_batch=n_gen, seed=1004)[s:e].contiguous()
     x = x_h.to(dev)
     net, head = _gmcn3d(torch, model, getattr(fitting, args.relu_fit))
     net, head = net.to(dev), head.to(dev)
@@ -424,52 +595,25 @@ def _secondary_setup(args, rank, dev):
         return graphed(xx) if graphed is not None else eager(xx)
 
     step.uncaptured = lambda: eager(x)      # the same launches outside the graph, for the launch count
-
-    def cpu():
-        from oracle import cpu_oracle
-        cpu_oracle.use_all_cores()
-        # dominant stage on the CPU: the four convolution-fitting layers on a batch slice (random data of the layer shapes)
-        g = torch.Generator().manual_seed(1)
-        layers = []
-        for (cin, gcomp, cout, kfit) in ((1, 64, 8, 64), (8, 64, 16, 32), (16, 32, 32, 16), (32, 16, 64, 8)):
-            cov, _ = synthetic.covariances_and_inverses((32, cin, gcomp), 3, 0.03, 0.15, g)
-            data = synthetic.pack(torch.rand(32, cin, gcomp, generator=g), torch.rand(32, cin, gcomp, 3, generator=g) * 2 - 1, cov)
-            kcov, _ = synthetic.covariances_and_inverses((cout, cin, 5), 3, 0.1, 0.4, g)
-            kern = synthetic.pack(torch.randn(cout, cin, 5, generator=g) + 0.1, torch.randn(cout, cin, 5, 3, generator=g), kcov)
-            layers.append((data.numpy(), kern.numpy(), kfit))
-
-        def four_layers():
-            for data, kern, kfit in layers:
-                cpu_oracle.convolution_fitting_forward(data, kern, kfit)
-
-        reps, dt = _repeat_for(four_layers)
-        return {"value": reps * 32 / dt, "unit": "samples/s", "cores": cpu_oracle.num_threads(), "kind": "port",
-                "sample": f"the four convolution-fitting layers only (the dominant stage) on 32 samples, {reps} passes "
-                          f"({dt:.2f} s); ReLU fixed-point evaluations and normalisations are not included"}
     keys = n_batch * (8 * 320 + (16 + 32 + 64) * 2560)
-    return ("samples_per_s_gmcn3d_forward", "samples/s", n_batch, step, (x_h,),
-            f"config4: GMCN-3D forward, B={n_batch}/GPU, 64 input Gaussians, conv-fit layers 1->8->16->32->64 "
+    return (n_batch, step, (x_h,),
+            f"config4: GMCN-3D forward, B={n_gen} (={n_batch}/GPU), 64 input Gaussians, conv-fit layers 1->8->16->32->64 "
             f"(K=64/32/16/8, ReLU fit {args.relu_fit}), integrate, linear to 10 logits; "
             + ("one CUDA graph per forward" if graphed is not None else "kernel-by-kernel launches"),
-            keys * 4 + n_batch * 64 * 13 * 4, cpu)
+            keys * 4 + n_batch * 64 * 13 * 4)
 
 
-def run_secondary(args, rank, world, local_rank):
+def secondary_block(args, config, rank, world, local_rank, n_batch, steps):
     import torch
     import torch.distributed as dist
-    from gmc import sharding
-    if not torch.cuda.is_available():
-        raise RuntimeError("bench.py needs a CUDA device: the library has no CPU path")
-    torch.cuda.set_device(local_rank)
+    from gmc import sharding, _native
     dev = torch.device("cuda", local_rank)
-    metric, unit, units, step, host_inputs, workload, alg_bytes, cpu = _secondary_setup(args, rank, dev)
+    metric, unit = _METRICS[config]
+    units, step, host_inputs, workload, alg_bytes = _secondary_setup(args, config, rank, world, dev, n_batch)
     host_inputs = tuple(t.pin_memory() for t in host_inputs)
     gather = sharding.OutputGatherer(world, dev) if world > 1 else None
-    # kernels of this library per step (the library counts its launches; a graph replay repeats the captured ones)
-    from gmc import _native
-    launches_before = _native.lib.gmc_kernel_launch_count()
-    getattr(step, "uncaptured", step)()
-    launches_per_step = _native.lib.gmc_kernel_launch_count() - launches_before
+    # kernels of this library per step, counted on one uncaptured step (a graph replay repeats the captured ones)
+    launches_per_step, launches_all = _count_kernels(torch, getattr(step, "uncaptured", step))
 
     def full_step():
         out = step()
@@ -481,23 +625,23 @@ def run_secondary(args, rank, world, local_rank):
     for _ in range(max(args.warmup, 3)):
         full_step()
     torch.cuda.synchronize()
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(_gpu_index(local_rank))
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     sampler.start()
     e0.record()
-    for _ in range(args.steps):
+    for _ in range(steps):
         full_step()
     e1.record()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     clocks = sampler.stop()
-    ms = e0.elapsed_time(e1) / args.steps
+    ms = e0.elapsed_time(e1) / steps
 
-    e2e_steps = max(3, min(args.steps, 20))
+    e2e_steps = max(3, min(steps, 20))
     out_h = None
 
     def e2e_step():
@@ -511,6 +655,8 @@ def run_secondary(args, rank, world, local_rank):
     for _ in range(3):
         e2e_step()
     torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
     e0.record()
     for _ in range(e2e_steps):
         e2e_step()
@@ -522,25 +668,125 @@ def run_secondary(args, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, e2e_ms = t.tolist()
     if rank != 0:
-        return
+        return None
     peaks, peaks_kind = _measured_peaks()
     hbm = float(peaks["hbm_gbs"])
     achieved = alg_bytes / (ms * 1e-3) / 1e9
-    line = {"metric": metric, "value": world * units / (ms * 1e-3), "unit": unit, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": workload, "l2": "working set of a step is smaller than L2 for some stages; not flushed",
-                       "sharding": f"batch over {world} rank(s)" + (", all-gather of outputs" if world > 1 else "")},
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
-                         "traffic": None, "algorithmic_bytes_per_step": alg_bytes,
-                         "note": f"whole step against {peaks_kind} copy bandwidth; the stages are latency bound at these "
-                                 "sizes, see profiles/"},
+    return {"config": config, "metric": metric, "value": world * units / (ms * 1e-3), "unit": unit, "n_gpus": world,
+            "steps": steps, "ms_per_step": ms, "scaling": "strong" if args.batch is None else "weak",
+            "workload": workload,
+            "roofline": {"bound": "hbm", "kernel": _DOMINANT[config], "achieved": achieved, "peak": hbm, "unit": "GB/s",
+                         "frac": achieved / hbm, "traffic": None, "algorithmic_bytes_per_step": alg_bytes,
+                         "note": f"whole step of one rank against {peaks_kind} copy bandwidth; the stages are latency / "
+                                 "issue bound at these sizes (profiles/), the named kernel takes the largest share"},
             "e2e": {"value": world * units / (e2e_ms * 1e-3), "unit": unit,
-                    "h2d_bytes_per_step": sum(t.numel() * 4 for t in host_inputs),
-                    "d2h_bytes_per_step": out_h.numel() * 4, "ms_per_step": e2e_ms, "steps": e2e_steps},
-            "gpu_launches": launches_per_step * args.steps, "clocks": clocks}
+                    "h2d_bytes_per_step": world * sum(t.numel() * 4 for t in host_inputs),
+                    "d2h_bytes_per_step": world * out_h.numel() * 4, "ms_per_step": e2e_ms, "steps": e2e_steps},
+            "gpu_launches": launches_per_step * steps, "gpu_launches_per_step": launches_per_step,
+            "all_kernels_per_step": launches_all, "clocks": clocks}
+
+
+def _count_kernels(torch, fn):
+    """Runs fn() once under the CUDA activity tracer -> (kernels of this library, all kernels). The library's kernels
+    live in namespace gmc. Without the tracer the count falls back to the library calls made (each launches >= 1)."""
+    from gmc import _native
+    calls_before = _native.entry_calls()
+    try:
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            fn()
+            torch.cuda.synchronize()
+        names = [e.name for e in prof.events() if "cuda" in str(getattr(e, "device_type", "")).lower()
+                 and not e.name.lower().startswith(("memcpy", "memset"))]
+        ours = sum(1 for n in names if "gmc::" in n)
+        if ours > 0:
+            return ours, len(names)
+    except Exception:
+        fn()
+        torch.cuda.synchronize()
+    return max(1, _native.entry_calls() - calls_before), None
+
+
+# ---------------------------------------------------------------------------------------------------------------
+def _per_rank_batch(args, total, world):
+    if args.batch is not None:
+        return args.batch, "weak"
+    if total % world != 0:
+        raise RuntimeError(f"the configuration's batch of {total} does not split evenly over {world} ranks")
+    return total // world, "strong"
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local_rank)
+    cores = _bind_rank_to_cores(local_rank, world)
+    steps = args.steps
+
+    if args.config in (2, 3, 4):
+        n_batch, scaling = _per_rank_batch(args, SECONDARY_BATCH[args.config], world)
+        block = secondary_block(args, args.config, rank, world, local_rank, n_batch, steps)
+        if rank != 0:
+            return
+        line = {"metric": block["metric"], "value": block["value"], "unit": block["unit"], "n_gpus": world, "steps": steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": block["ms_per_step"], "higher_is_better": True,
+                "scaling": scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": block["workload"], "l2": "working set of a step is smaller than L2 for some "
+                           "stages; not flushed", "sharding": f"batch over {world} rank(s)"},
+                "roofline": block["roofline"], "e2e": block["e2e"], "gpu_launches": block["gpu_launches"],
+                "clocks": block["clocks"]}
+        if not args.no_cpu_baseline and world == 1:
+            line["cpu_baseline"] = cpu_baseline(args.config, args.cpu_seconds)
+        _emit(line)
+        return
+
+    extras = args.config == 0 and not args.no_extras
+    b_rank, scaling = _per_rank_batch(args, B_TOTAL, world)
+    head = config1_block(args, rank, world, local_rank, b_rank, steps, with_e2e=not args.no_e2e, with_peak=True,
+                         sustained_seconds=3.0 if extras else 0.0)
+    weak = None
+    if extras and world > 1:
+        weak = config1_block(args, rank, world, local_rank, B_TOTAL, max(10, min(steps, 30)), with_e2e=not args.no_e2e,
+                             with_peak=False)
+    secondary = []
+    if extras:
+        for cfg in (2, 3, 4):
+            try:
+                nb, _ = _per_rank_batch(args, SECONDARY_BATCH[cfg], world)
+                blk = secondary_block(args, cfg, rank, world, local_rank, nb, max(10, min(steps, 50)))
+                if rank == 0 and world == 1 and not args.no_cpu_baseline:
+                    blk["cpu_baseline"] = cpu_baseline(cfg, min(args.cpu_seconds, 8.0))
+            except Exception as err:                        # the headline must not be lost to a secondary failure
+                blk = {"config": cfg, "error": f"{type(err).__name__}: {str(err).splitlines()[0] if str(err) else ''}"}
+            if rank == 0:
+                secondary.append(blk)
+    if rank != 0:
+        return
+    line = {
+        "metric": METRIC, "value": head["value"], "unit": UNIT, "n_gpus": world, "steps": steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": head["ms_per_step"], "higher_is_better": True, "scaling": scaling,
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"config1: 3D evaluate_inversed fwd+bwd, B={b_rank * world} (={b_rank}/GPU) L={L} G={G} N={N} "
+                               f"({head['pairs_per_gpu_and_step']} pairs per GPU and step)",
+                   "l2": f"inputs of a step ({(head['e2e'] or {}).get('h2d_bytes_per_step', 0) / max(world, 1) / 1e6:.0f} MB per GPU) "
+                         + ("are larger than L2 (126 MB); no explicit flush" if b_rank >= 32 else
+                            "fit in L2 (126 MB) at this shard size and are re-read from it every step; the kernels are "
+                            "FP32-pipe bound (DRAM traffic under 1 % of peak), so residency does not change the time"),
+                   "sharding": f"batch of {b_rank * world} split over {world} rank(s), all-gather of forward outputs overlapped "
+                               "with backward" + (f"; rank bound to host cores {cores}" if cores else "")},
+        "roofline": head["roofline"], "roofline_forward": head["roofline_forward"], "roofline_fwd_bwd": head["roofline_fwd_bwd"],
+        "e2e": head["e2e"], "gpu_launches": head["gpu_launches"], "clocks": head["clocks"],
+    }
+    if "sustained" in head:
+        line["sustained"] = head["sustained"]
+    if weak is not None:
+        line["weak"] = {k: weak[k] for k in ("value", "unit", "ms_per_step", "steps", "batch_per_gpu", "e2e", "clocks")}
+        line["weak"]["roofline_frac_of_nominal_fwd_bwd"] = weak["roofline_fwd_bwd"]["frac_of_nominal"]
+    if secondary:
+        line["secondary"] = secondary
     if not args.no_cpu_baseline and world == 1:
-        line["cpu_baseline"] = cpu()
+        line["cpu_baseline"] = cpu_baseline(1, args.cpu_seconds)
     _emit(line)
 
 
@@ -578,10 +824,7 @@ def main():
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
-        if args.config == 1:
-            run_ours(args, rank, world, local_rank)
-        else:
-            run_secondary(args, rank, world, local_rank)
+        run_ours(args, rank, world, local_rank)
     finally:
         if world > 1:
             import torch.distributed as dist

@@ -21,14 +21,7 @@ void set_last_cuda_error(cudaError_t e);
         }                                                   \
     } while (0)
 
-// Counts kernel launches of the library (read by gmc_kernel_launch_count; benchmark bookkeeping).
-void note_kernel_launch();
-
-#define GMC_LAUNCH_CHECK()                  \
-    do {                                    \
-        ::gmc::note_kernel_launch();        \
-        GMC_CUDA_TRY(cudaGetLastError());   \
-    } while (0)
+#define GMC_LAUNCH_CHECK() GMC_CUDA_TRY(cudaGetLastError())
 
 // One word per translation unit (the library is built without relocatable device code). Kernels OR
 // a code into it when a bounded wait gives up or a self check fails; gmc_device_check_word() reads
@@ -46,12 +39,28 @@ static __device__ int g_device_check_word;
     }
 
 enum DeviceCheck : int {
-    CHECK_MBARRIER_TIMEOUT = 1,
-    CHECK_FLAG_TIMEOUT = 2,
-    CHECK_INDEX_RANGE = 4,
+    CHECK_MBARRIER_TIMEOUT = 1,     // a bounded wait for a bulk copy ran out
+    CHECK_INDEX_RANGE = 4,          // GMC_BOUNDS_CHECK builds only: a data-dependent index left its array
 };
 
 __device__ __forceinline__ void report_check(int code) { atomicOr(&g_device_check_word, code); }
+
+// Data-dependent indices (tree children, sorted object ids, subtree ranges) are checked in builds compiled with
+// -DGMC_BOUNDS_CHECK: an index outside [0, n) sets CHECK_INDEX_RANGE in the check word and is replaced by 0, so the
+// access that follows stays inside the array. Regular builds compile the macro to the index itself.
+#ifdef GMC_BOUNDS_CHECK
+template <typename I, typename N>
+__device__ __forceinline__ I checked_index(I i, N n) {
+    if (static_cast<unsigned long long>(i) >= static_cast<unsigned long long>(n)) {
+        report_check(CHECK_INDEX_RANGE);
+        return I(0);
+    }
+    return i;
+}
+#define GMC_IDX(i, n) ::gmc::checked_index((i), (n))
+#else
+#define GMC_IDX(i, n) (i)
+#endif
 
 static inline cudaStream_t as_stream(void* s) { return reinterpret_cast<cudaStream_t>(s); }
 
@@ -104,11 +113,11 @@ __device__ __forceinline__ void bulk_copy_g2s(void* dst_smem, const void* src_gm
                  : "memory");
 }
 
-// Waits for the phase with the given parity, giving up after a fixed number of polls. Returns false
+// Waits for the phase with the given parity, giving up after `max_polls` polls. Returns false
 // (after recording CHECK_MBARRIER_TIMEOUT) if the phase never completed.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity, int max_polls = (1 << 22)) {
     const uint32_t addr = smem_u32(bar);
-    for (int it = 0; it < (1 << 22); ++it) {
+    for (int it = 0; it < max_polls; ++it) {
         uint32_t done;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"

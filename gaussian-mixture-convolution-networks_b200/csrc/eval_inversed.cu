@@ -14,9 +14,9 @@
 //  backward: a CTA owns one (batch, layer), a tile of query points and a chunk of Gaussians. Every thread
 //            keeps GQ Gaussians and their 1 + D + D(D+1)/2 gradient sums in registers and streams the
 //            tile's points (x, grad_out) from shared memory, so the per-Gaussian sums need no cross-lane
-//            traffic in the pair loop. The per-point position gradient is what crosses lanes: each thread
-//            writes its D partial sums to a padded shared array and the CTA folds them once per 16 points.
-//            CTA totals go to global memory with one atomic per value.
+//            traffic in the pair loop. The per-point position gradient is what crosses lanes: each lane
+//            writes its D partial sums into its warp's own padded shared rows and the warp folds them once
+//            per 16 points (no CTA barrier in the loop). Totals go to global memory with one atomic per value.
 #include "common.cuh"
 
 namespace gmc {
@@ -37,6 +37,12 @@ namespace {
 #endif
 #ifndef GMC_BWD_MINB
 #define GMC_BWD_MINB 4
+#endif
+#ifndef GMC_BWD_GP_LARGE
+#define GMC_BWD_GP_LARGE 2          // packed Gaussian pairs per thread for mixtures of 384 components and more
+#endif
+#ifndef GMC_BWD_THREADS_LARGE
+#define GMC_BWD_THREADS_LARGE 128   // CTA size of that variant (all threads along the Gaussian axis)
 #endif
 constexpr int kFwdThreads = 128;
 constexpr int kFwdChunk = GMC_FWD_CHUNK;   // Gaussians staged per shared-memory chunk
@@ -110,7 +116,7 @@ template <int D, int P>
 __global__ void __launch_bounds__(kFwdThreads, GMC_FWD_MINB)
 eval_forward_kernel(const float* __restrict__ mixture, const float* __restrict__ xes, float* __restrict__ out,
                     int n_layers, int n_components, int n_batch_xes, int n_layers_xes, int n_xes,
-                    int tiles_per_mixture) {
+                    int tiles_per_mixture, int lose_copy) {
     constexpr int RF = Raw<D>::kFloats;
     constexpr int RC = ReadyCount<D>::value;
     constexpr int PF = 2 * RC;
@@ -174,11 +180,19 @@ eval_forward_kernel(const float* __restrict__ mixture, const float* __restrict__
             if (tid == 0) {
                 fence_proxy_async();
                 mbar_arrive_expect_tx(&sm.bar, bytes);
-                bulk_copy_g2s(sm.raw, chunk, bytes, &sm.bar);
+                // lose_copy (error-path test only): the copy is never issued, so nothing is in flight and the wait
+                // below must run out
+                if (!lose_copy) bulk_copy_g2s(sm.raw, chunk, bytes, &sm.bar);
             }
-            const bool ok = mbar_wait_bounded(&sm.bar, phase);
+            const bool ok = mbar_wait_bounded(&sm.bar, phase, lose_copy ? (1 << 10) : (1 << 22));
             phase ^= 1u;
-            if (__syncthreads_or(!ok)) return;   // CTA-wide decision, nothing else is in flight
+            if (__syncthreads_or(!ok)) {
+                // CTA-wide decision. The wait only runs out when the copy never arrives; the check word is set, and the
+                // tile's outputs become NaN so that the failure cannot pass for a result.
+                float* o_bad = out + size_t(bl) * n_xes + n0;
+                for (int i = tid; i < n_here; i += kFwdThreads) o_bad[i] = __int_as_float(0x7fc00000);
+                return;
+            }
         }
         for (int g = tid; g < gc_even; g += kFwdThreads) {
             float rdy[RC];
@@ -251,68 +265,34 @@ eval_forward_kernel(const float* __restrict__ mixture, const float* __restrict__
 // ---------------------------------------------------------------------------------------------
 // backward
 // ---------------------------------------------------------------------------------------------
-constexpr int kBwdThreads = 128;
-constexpr int kBwdPointChunk = 16;     // points folded per shared-memory round
+constexpr int kBwdPointChunk = 16;     // points between two folds of the position-gradient partial sums
 constexpr int kBwdTilePoints = 512;    // points per CTA
+constexpr int kBwdRowStride = 36;      // floats per row of a warp's partial array: 32 lanes + 4 (rows stay 16-byte aligned,
+                                       // float4 reads of consecutive rows fall on distinct banks)
 
 template <int D>
 struct BwdSmem {
     alignas(16) float4 pts[kBwdTilePoints * 2];                            // (x,x,y,y) (z,z,g,g) per point
-    alignas(16) float partial[kBwdPointChunk * D * (kBwdThreads + 4)];      // [point][dim][thread] (+pad)
+    alignas(16) float partial[1];                                          // [warp][point * D + dim][kBwdRowStride]
+    static constexpr size_t bytes(int n_warps) {
+        return sizeof(float4) * kBwdTilePoints * 2 + sizeof(float) * size_t(n_warps) * kBwdPointChunk * D * kBwdRowStride;
+    }
 };
 
-// GP = packed Gaussian pairs per thread (a thread owns 2 * GP Gaussians: g = base + tg + (2 q + h) * TG).
+// The Gaussians a thread owns (2 * GP of them, two per packed register pair) in the form the pair loop reads, and
+// their gradient sums.
 template <int D, int GP>
-__global__ void __launch_bounds__(kBwdThreads, GMC_BWD_MINB)
-eval_backward_kernel(const float* __restrict__ grad_out, const float* __restrict__ mixture,
-                     const float* __restrict__ xes, float* __restrict__ grad_mixture,
-                     float* __restrict__ grad_xes, int n_layers, int n_components, int n_batch_xes,
-                     int n_layers_xes, int n_xes, int tg_threads, int n_point_tiles, int n_gauss_chunks) {
+struct BwdOwned {
+    static constexpr int NS = D * (D + 1) / 2;
+    float2 nmu[GP][D], A[GP][NS], cw2[GP];      // -mu;  k S (symmetrised, k = -1/2 log2 e);  w norm 2 ln 2
+    float2 sa[GP], U[GP][D], M[GP][NS];         // sum a;  sum c2 t;  sum c2 t t^T (upper triangle)
+};
+
+template <int D, int GP>
+__device__ __forceinline__ void bwd_load_owned(BwdOwned<D, GP>& o, const float* __restrict__ mix, int n_components,
+                                               int gbase, int tg, int TG) {
     constexpr int RF = Raw<D>::kFloats;
     constexpr int NS = D * (D + 1) / 2;
-    extern __shared__ __align__(16) unsigned char smem_bytes[];
-    BwdSmem<D>& sm = *reinterpret_cast<BwdSmem<D>*>(smem_bytes);
-
-    const int tid = threadIdx.x;
-    int bid = blockIdx.x;
-    const int gchunk = bid % n_gauss_chunks;
-    bid /= n_gauss_chunks;
-    const int ptile = bid % n_point_tiles;
-    const int bl = bid / n_point_tiles;
-    const int b = bl / n_layers;
-    const int l = bl - b * n_layers;
-    const int bx = n_batch_xes == 1 ? 0 : b;
-    const int lx = n_layers_xes == 1 ? 0 : l;
-
-    const int TG = tg_threads;                 // threads along the Gaussian axis (32, 64 or 128)
-    const int TP = kBwdThreads / TG;           // point slices
-    const int tg = tid % TG;
-    const int slice = tid / TG;
-    const int TGP = TG + 4;                    // padded row length of the partial array
-
-    const int n0 = ptile * kBwdTilePoints;
-    const int n_here = min(kBwdTilePoints, n_xes - n0);
-    const size_t xes_row = (size_t(bx) * n_layers_xes + lx) * size_t(n_xes);
-
-    // ---- stage points: (x, grad_out), every value duplicated for the packed pair loop ----
-    for (int i = tid; i < kBwdTilePoints; i += kBwdThreads) {
-        float px = 0.f, py = 0.f, pz = 0.f, go = 0.f;
-        if (i < n_here) {
-            const float* xp = xes + (xes_row + n0 + i) * D;
-            go = __ldg(grad_out + size_t(bl) * n_xes + n0 + i);
-            px = __ldg(xp);
-            py = __ldg(xp + 1);
-            if constexpr (D == 3) pz = __ldg(xp + 2);
-        }
-        sm.pts[2 * i] = make_float4(px, px, py, py);
-        sm.pts[2 * i + 1] = make_float4(pz, pz, go, go);
-    }
-
-    // ---- my Gaussians, in ready form for the backward pair loop ----
-    float2 nmu[GP][D], A[GP][NS], cw2[GP];
-    float2 sa[GP], U[GP][D], M[GP][NS];
-    const float* mix = mixture + size_t(bl) * n_components * RF;
-    const int gbase = gchunk * TG * GP * 2;
 #pragma unroll
     for (int q = 0; q < GP; ++q) {
         float v[2][D + NS + 1];
@@ -349,125 +329,83 @@ eval_backward_kernel(const float* __restrict__ grad_out, const float* __restrict
             }
         }
 #pragma unroll
-        for (int d = 0; d < D; ++d) { nmu[q][d] = f2(v[0][d], v[1][d]); U[q][d] = f2(0.f, 0.f); }
+        for (int d = 0; d < D; ++d) { o.nmu[q][d] = f2(v[0][d], v[1][d]); o.U[q][d] = f2(0.f, 0.f); }
 #pragma unroll
-        for (int s = 0; s < NS; ++s) { A[q][s] = f2(v[0][D + s], v[1][D + s]); M[q][s] = f2(0.f, 0.f); }
-        cw2[q] = f2(v[0][D + NS], v[1][D + NS]);
-        sa[q] = f2(0.f, 0.f);
+        for (int s = 0; s < NS; ++s) { o.A[q][s] = f2(v[0][D + s], v[1][D + s]); o.M[q][s] = f2(0.f, 0.f); }
+        o.cw2[q] = f2(v[0][D + NS], v[1][D + NS]);
+        o.sa[q] = f2(0.f, 0.f);
     }
-    __syncthreads();
+}
 
-    const bool need_gx = grad_xes != nullptr;
-    constexpr int PPI = GMC_BWD_PPI;   // points in flight per loop iteration (independent dependency chains)
-    for (int c0 = 0; c0 < n_here; c0 += kBwdPointChunk) {
-        for (int pp0 = slice * PPI; pp0 < kBwdPointChunk; pp0 += TP * PPI) {
-            float2 X[PPI][3], GO[PPI], dx[PPI][D];
-#pragma unroll
-            for (int k = 0; k < PPI; ++k) {
-                const float4 pa = sm.pts[2 * (c0 + pp0 + k)];
-                const float4 pb = sm.pts[2 * (c0 + pp0 + k) + 1];
-                X[k][0] = f2(pa.x, pa.y); X[k][1] = f2(pa.z, pa.w); X[k][2] = f2(pb.x, pb.y);
-                GO[k] = f2(pb.z, pb.w);
-#pragma unroll
-                for (int d = 0; d < D; ++d) dx[k][d] = f2(0.f, 0.f);
-            }
-#pragma unroll
-            for (int q = 0; q < GP; ++q) {
-#pragma unroll
-                for (int k = 0; k < PPI; ++k) {
-                    if constexpr (D == 3) {
-                        const float2 t0 = add2(X[k][0], nmu[q][0]), t1 = add2(X[k][1], nmu[q][1]),
-                                     t2 = add2(X[k][2], nmu[q][2]);
-                        const float2 r0 = fma2(A[q][2], t2, fma2(A[q][1], t1, mul2(A[q][0], t0)));
-                        const float2 r1 = fma2(A[q][4], t2, fma2(A[q][3], t1, mul2(A[q][1], t0)));
-                        const float2 r2 = fma2(A[q][5], t2, fma2(A[q][4], t1, mul2(A[q][2], t0)));
-                        const float2 qq = fma2(t2, r2, fma2(t1, r1, mul2(t0, r0)));
-                        const float2 a = mul2(ex2_2(qq), GO[k]);
-                        sa[q] = add2(sa[q], a);
-                        const float2 c2 = mul2(a, cw2[q]);
-                        dx[k][0] = fma2(c2, r0, dx[k][0]);
-                        dx[k][1] = fma2(c2, r1, dx[k][1]);
-                        dx[k][2] = fma2(c2, r2, dx[k][2]);
-                        const float2 u0 = mul2(c2, t0), u1 = mul2(c2, t1), u2 = mul2(c2, t2);
-                        U[q][0] = add2(U[q][0], u0);
-                        U[q][1] = add2(U[q][1], u1);
-                        U[q][2] = add2(U[q][2], u2);
-                        M[q][0] = fma2(u0, t0, M[q][0]);
-                        M[q][1] = fma2(u0, t1, M[q][1]);
-                        M[q][2] = fma2(u0, t2, M[q][2]);
-                        M[q][3] = fma2(u1, t1, M[q][3]);
-                        M[q][4] = fma2(u1, t2, M[q][4]);
-                        M[q][5] = fma2(u2, t2, M[q][5]);
-                    } else {
-                        const float2 t0 = add2(X[k][0], nmu[q][0]), t1 = add2(X[k][1], nmu[q][1]);
-                        const float2 r0 = fma2(A[q][1], t1, mul2(A[q][0], t0));
-                        const float2 r1 = fma2(A[q][2], t1, mul2(A[q][1], t0));
-                        const float2 qq = fma2(t1, r1, mul2(t0, r0));
-                        const float2 a = mul2(ex2_2(qq), GO[k]);
-                        sa[q] = add2(sa[q], a);
-                        const float2 c2 = mul2(a, cw2[q]);
-                        dx[k][0] = fma2(c2, r0, dx[k][0]);
-                        dx[k][1] = fma2(c2, r1, dx[k][1]);
-                        const float2 u0 = mul2(c2, t0), u1 = mul2(c2, t1);
-                        U[q][0] = add2(U[q][0], u0);
-                        U[q][1] = add2(U[q][1], u1);
-                        M[q][0] = fma2(u0, t0, M[q][0]);
-                        M[q][1] = fma2(u0, t1, M[q][1]);
-                        M[q][2] = fma2(u1, t1, M[q][2]);
-                    }
-                }
-            }
-            if (need_gx) {
-#pragma unroll
-                for (int k = 0; k < PPI; ++k)
-#pragma unroll
-                    for (int d = 0; d < D; ++d) sm.partial[((pp0 + k) * D + d) * TGP + tg] = dx[k][d].x + dx[k][d].y;
-            }
-        }
-        if (need_gx) {
-            __syncthreads();
-            // fold: row = (point, dim); SPLIT threads share a row, each sums TG / SPLIT entries
-            constexpr int ROWS = kBwdPointChunk * D;
-            constexpr int SPLIT = (kBwdThreads / ROWS) >= 4 ? 4 : ((kBwdThreads / ROWS) >= 2 ? 2 : 1);
-            const int row = tid / SPLIT;
-            const int part = tid - row * SPLIT;
-            if (row < ROWS) {
-                const int per = TG / SPLIT;    // multiple of 4 because TG >= 32 and SPLIT <= 4
-                const float4* src = reinterpret_cast<const float4*>(sm.partial + row * TGP + part * per);
-                float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-                for (int i = 0; i < per / 4; ++i) {
-                    const float4 v = src[i];
-                    s0 += v.x; s1 += v.y; s2 += v.z; s3 += v.w;
-                }
-                const int pp = row / D;
-                const int d = row - pp * D;
-                if (c0 + pp < n_here) atomicAdd(grad_xes + (xes_row + n0 + c0 + pp) * D + d, (s0 + s1) + (s2 + s3));
-            }
-            __syncthreads();
-        }
+// One query point against packed pair q of the owned Gaussians: 33 packed operations + 2 ex2 in 3D (21 + 2 in 2D).
+template <int D, int GP>
+__device__ __forceinline__ void bwd_pair(BwdOwned<D, GP>& o, int q, const float2 (&X)[3], float2 GO, float2 (&dx)[D]) {
+    if constexpr (D == 3) {
+        const float2 t0 = add2(X[0], o.nmu[q][0]), t1 = add2(X[1], o.nmu[q][1]), t2 = add2(X[2], o.nmu[q][2]);
+        const float2 r0 = fma2(o.A[q][2], t2, fma2(o.A[q][1], t1, mul2(o.A[q][0], t0)));
+        const float2 r1 = fma2(o.A[q][4], t2, fma2(o.A[q][3], t1, mul2(o.A[q][1], t0)));
+        const float2 r2 = fma2(o.A[q][5], t2, fma2(o.A[q][4], t1, mul2(o.A[q][2], t0)));
+        const float2 qq = fma2(t2, r2, fma2(t1, r1, mul2(t0, r0)));
+        const float2 a = mul2(ex2_2(qq), GO);
+        o.sa[q] = add2(o.sa[q], a);
+        const float2 c2 = mul2(a, o.cw2[q]);
+        dx[0] = fma2(c2, r0, dx[0]);
+        dx[1] = fma2(c2, r1, dx[1]);
+        dx[2] = fma2(c2, r2, dx[2]);
+        const float2 u0 = mul2(c2, t0), u1 = mul2(c2, t1), u2 = mul2(c2, t2);
+        o.U[q][0] = add2(o.U[q][0], u0);
+        o.U[q][1] = add2(o.U[q][1], u1);
+        o.U[q][2] = add2(o.U[q][2], u2);
+        o.M[q][0] = fma2(u0, t0, o.M[q][0]);
+        o.M[q][1] = fma2(u0, t1, o.M[q][1]);
+        o.M[q][2] = fma2(u0, t2, o.M[q][2]);
+        o.M[q][3] = fma2(u1, t1, o.M[q][3]);
+        o.M[q][4] = fma2(u1, t2, o.M[q][4]);
+        o.M[q][5] = fma2(u2, t2, o.M[q][5]);
+    } else {
+        const float2 t0 = add2(X[0], o.nmu[q][0]), t1 = add2(X[1], o.nmu[q][1]);
+        const float2 r0 = fma2(o.A[q][1], t1, mul2(o.A[q][0], t0));
+        const float2 r1 = fma2(o.A[q][2], t1, mul2(o.A[q][1], t0));
+        const float2 qq = fma2(t1, r1, mul2(t0, r0));
+        const float2 a = mul2(ex2_2(qq), GO);
+        o.sa[q] = add2(o.sa[q], a);
+        const float2 c2 = mul2(a, o.cw2[q]);
+        dx[0] = fma2(c2, r0, dx[0]);
+        dx[1] = fma2(c2, r1, dx[1]);
+        const float2 u0 = mul2(c2, t0), u1 = mul2(c2, t1);
+        o.U[q][0] = add2(o.U[q][0], u0);
+        o.U[q][1] = add2(o.U[q][1], u1);
+        o.M[q][0] = fma2(u0, t0, o.M[q][0]);
+        o.M[q][1] = fma2(u0, t1, o.M[q][1]);
+        o.M[q][2] = fma2(u1, t1, o.M[q][2]);
     }
+}
 
-    if (grad_mixture == nullptr) return;
-
-    // ---- finish the per-Gaussian gradient, one atomic per value (point slices issue separate atomics) ----
+// Finishes the per-Gaussian gradient from the sums, one atomic per value (other CTAs and point slices add theirs).
+template <int D, int GP>
+__device__ __forceinline__ void bwd_store_owned(const BwdOwned<D, GP>& o, const float* __restrict__ mix,
+                                                float* __restrict__ grad_mix, int n_components, int gbase, int tg,
+                                                int TG) {
+    constexpr int RF = Raw<D>::kFloats;
+    constexpr int NS = D * (D + 1) / 2;
 #pragma unroll
     for (int q = 0; q < GP; ++q) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             const int g = gbase + tg + (2 * q + h) * TG;
             if (g >= n_components) continue;
-            const float sa_h = h ? sa[q].y : sa[q].x;
+            const float sa_h = h ? o.sa[q].y : o.sa[q].x;
             float Uh[D], Mh[NS];
 #pragma unroll
-            for (int d = 0; d < D; ++d) Uh[d] = h ? U[q][d].y : U[q][d].x;
+            for (int d = 0; d < D; ++d) Uh[d] = h ? o.U[q][d].y : o.U[q][d].x;
 #pragma unroll
-            for (int s = 0; s < NS; ++s) Mh[s] = h ? M[q][s].y : M[q][s].x;
+            for (int s = 0; s < NS; ++s) Mh[s] = h ? o.M[q][s].y : o.M[q][s].x;
             const float* r = mix + size_t(g) * RF;
             const float w = __ldg(r);
             float S[D * D];
 #pragma unroll
             for (int i = 0; i < D * D; ++i) S[i] = __ldg(r + 1 + D + i);
-            float* go = grad_mixture + (size_t(bl) * n_components + g) * RF;
+            float* go = grad_mix + size_t(g) * RF;
             constexpr float inv2ln2 = 1.f / (2.f * kLn2);
             float det, cof[D * D];
             if constexpr (D == 2) {
@@ -515,6 +453,130 @@ eval_backward_kernel(const float* __restrict__ grad_out, const float* __restrict
     }
 }
 
+// GP = packed Gaussian pairs per thread (a thread owns 2 * GP Gaussians: g = base + tg + (2 q + h) * TG).
+// THREADS = CTA size. TG threads lie along the Gaussian axis (a multiple of 32, so a warp never straddles two point
+// slices); the THREADS / TG slices take contiguous blocks of the tile's points.
+// A warp is self-contained after the staging barrier: it walks its points in chunks of 16, every lane writes its D
+// partial position-gradient sums per point into the warp's own shared rows, the warp folds the rows (one lane per
+// (point, dim) row, float4 reads) and adds the results to global memory. No CTA barrier in the loop.
+template <int D, int GP, int THREADS>
+__global__ void __launch_bounds__(THREADS, GMC_BWD_MINB)
+eval_backward_kernel(const float* __restrict__ grad_out, const float* __restrict__ mixture,
+                     const float* __restrict__ xes, float* __restrict__ grad_mixture,
+                     float* __restrict__ grad_xes, int n_layers, int n_components, int n_batch_xes,
+                     int n_layers_xes, int n_xes, int tg_threads, int n_point_tiles, int n_gauss_chunks) {
+    constexpr int RF = Raw<D>::kFloats;
+    constexpr int ROWS = kBwdPointChunk * D;
+    extern __shared__ __align__(16) unsigned char smem_bytes[];
+    BwdSmem<D>& sm = *reinterpret_cast<BwdSmem<D>*>(smem_bytes);
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    int bid = blockIdx.x;
+    const int gchunk = bid % n_gauss_chunks;
+    bid /= n_gauss_chunks;
+    const int ptile = bid % n_point_tiles;
+    const int bl = bid / n_point_tiles;
+    const int b = bl / n_layers;
+    const int l = bl - b * n_layers;
+    const int bx = n_batch_xes == 1 ? 0 : b;
+    const int lx = n_layers_xes == 1 ? 0 : l;
+
+    const int TG = tg_threads;                 // threads along the Gaussian axis (32, 64 or 128)
+    const int TP = THREADS / TG;               // point slices
+    const int tg = tid % TG;
+    const int slice = tid / TG;
+
+    const int n0 = ptile * kBwdTilePoints;
+    const int n_here = min(kBwdTilePoints, n_xes - n0);
+    const size_t xes_row = (size_t(bx) * n_layers_xes + lx) * size_t(n_xes);
+
+    // ---- stage points: (x, grad_out), every value duplicated for the packed pair loop ----
+    for (int i = tid; i < kBwdTilePoints; i += THREADS) {
+        float px = 0.f, py = 0.f, pz = 0.f, go = 0.f;
+        if (i < n_here) {
+            const float* xp = xes + (xes_row + n0 + i) * D;
+            go = __ldg(grad_out + size_t(bl) * n_xes + n0 + i);
+            px = __ldg(xp);
+            py = __ldg(xp + 1);
+            if constexpr (D == 3) pz = __ldg(xp + 2);
+        }
+        sm.pts[2 * i] = make_float4(px, px, py, py);
+        sm.pts[2 * i + 1] = make_float4(pz, pz, go, go);
+    }
+
+    BwdOwned<D, GP> own;
+    const float* mix = mixture + size_t(bl) * n_components * RF;
+    const int gbase = gchunk * TG * GP * 2;
+    bwd_load_owned<D, GP>(own, mix, n_components, gbase, tg, TG);
+    __syncthreads();
+
+    const bool need_gx = grad_xes != nullptr;
+    const int part = (tid >> 5) * ROWS * kBwdRowStride;     // first float of this warp's rows in sm.partial
+    constexpr int PPI = GMC_BWD_PPI;   // points in flight per loop iteration (independent dependency chains)
+    const int per_slice = kBwdTilePoints / TP;
+    const int p_end = min(n_here, (slice + 1) * per_slice);
+    for (int c0 = slice * per_slice; c0 < p_end; c0 += kBwdPointChunk) {
+        for (int pp0 = 0; pp0 < kBwdPointChunk; pp0 += PPI) {
+            float2 X[PPI][3], GO[PPI], dx[PPI][D];
+#pragma unroll
+            for (int k = 0; k < PPI; ++k) {
+                const float4 pa = sm.pts[2 * (c0 + pp0 + k)];
+                const float4 pb = sm.pts[2 * (c0 + pp0 + k) + 1];
+                X[k][0] = f2(pa.x, pa.y); X[k][1] = f2(pa.z, pa.w); X[k][2] = f2(pb.x, pb.y);
+                GO[k] = f2(pb.z, pb.w);
+#pragma unroll
+                for (int d = 0; d < D; ++d) dx[k][d] = f2(0.f, 0.f);
+            }
+#pragma unroll
+            for (int q = 0; q < GP; ++q) {
+#pragma unroll
+                for (int k = 0; k < PPI; ++k) bwd_pair<D, GP>(own, q, X[k], GO[k], dx[k]);
+            }
+            if (need_gx) {
+#pragma unroll
+                for (int k = 0; k < PPI; ++k)
+#pragma unroll
+                    for (int d = 0; d < D; ++d)
+                        sm.partial[part + ((pp0 + k) * D + d) * kBwdRowStride + lane] = dx[k][d].x + dx[k][d].y;
+            }
+        }
+        if (need_gx) {
+            __syncwarp();
+            // rows 0..31: one lane per row, 32 values each
+            float* gx = grad_xes + (xes_row + n0 + c0) * D;
+            {
+                const float4* src = reinterpret_cast<const float4*>(sm.partial + part + lane * kBwdRowStride);
+                float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float4 v = src[i];
+                    s0 += v.x; s1 += v.y; s2 += v.z; s3 += v.w;
+                }
+                if (c0 + lane / D < n_here) atomicAdd(gx + lane, (s0 + s1) + (s2 + s3));
+            }
+            if constexpr (ROWS > 32) {
+                // rows 32..47: two lanes per row, 16 values each
+                const int row = 32 + (lane & 15);
+                const float4* src = reinterpret_cast<const float4*>(sm.partial + part + row * kBwdRowStride + (lane >> 4) * 16);
+                float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float4 v = src[i];
+                    s0 += v.x; s1 += v.y; s2 += v.z; s3 += v.w;
+                }
+                float s = (s0 + s1) + (s2 + s3);
+                s += __shfl_xor_sync(0xffffffffu, s, 16);
+                if (lane < 16 && c0 + row / D < n_here) atomicAdd(gx + row, s);
+            }
+            __syncwarp();
+        }
+    }
+
+    if (grad_mixture == nullptr) return;
+    bwd_store_owned<D, GP>(own, mix, grad_mixture + size_t(bl) * n_components * RF, n_components, gbase, tg, TG);
+}
+
 template <typename K>
 int set_smem(K kernel, size_t bytes) {
     if (bytes > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)));
@@ -532,7 +594,7 @@ int check_eval_args(int n_batch, int n_layers, int n_components, int n_dims, int
 
 template <int D, int P>
 int launch_forward(const float* mixture, const float* xes, float* out, int n_batch, int n_layers, int n_components,
-                   int n_batch_xes, int n_layers_xes, int n_xes, cudaStream_t stream) {
+                   int n_batch_xes, int n_layers_xes, int n_xes, cudaStream_t stream, int lose_copy = 0) {
     constexpr int TILE = kFwdThreads * P;
     const long long tiles = (n_xes + TILE - 1) / TILE;
     const long long blocks = tiles * n_batch * n_layers;
@@ -541,12 +603,12 @@ int launch_forward(const float* mixture, const float* xes, float* out, int n_bat
     const size_t smem = sizeof(FwdSmem<D, P>);
     if (int s = set_smem(kernel, smem)) return s;
     kernel<<<unsigned(blocks), kFwdThreads, smem, stream>>>(mixture, xes, out, n_layers, n_components, n_batch_xes,
-                                                            n_layers_xes, n_xes, int(tiles));
+                                                            n_layers_xes, n_xes, int(tiles), lose_copy);
     GMC_LAUNCH_CHECK();
     return GMC_OK;
 }
 
-template <int D, int GP>
+template <int D, int GP, int THREADS>
 int launch_backward(const float* grad_out, const float* mixture, const float* xes, float* grad_mixture,
                     float* grad_xes, int n_batch, int n_layers, int n_components, int n_batch_xes, int n_layers_xes,
                     int n_xes, int tg, cudaStream_t stream) {
@@ -554,12 +616,12 @@ int launch_backward(const float* grad_out, const float* mixture, const float* xe
     const long long gchunks = (n_components + tg * GP * 2 - 1) / (tg * GP * 2);
     const long long blocks = ptiles * gchunks * n_batch * n_layers;
     if (blocks > 0x7fffffffLL) return GMC_ERR_BAD_DIMS;
-    auto kernel = eval_backward_kernel<D, GP>;
-    const size_t smem = sizeof(BwdSmem<D>);
+    auto kernel = eval_backward_kernel<D, GP, THREADS>;
+    const size_t smem = BwdSmem<D>::bytes(THREADS / 32);
     if (int s = set_smem(kernel, smem)) return s;
-    kernel<<<unsigned(blocks), kBwdThreads, smem, stream>>>(grad_out, mixture, xes, grad_mixture, grad_xes, n_layers,
-                                                            n_components, n_batch_xes, n_layers_xes, n_xes, tg,
-                                                            int(ptiles), int(gchunks));
+    kernel<<<unsigned(blocks), THREADS, smem, stream>>>(grad_out, mixture, xes, grad_mixture, grad_xes, n_layers,
+                                                        n_components, n_batch_xes, n_layers_xes, n_xes, tg,
+                                                        int(ptiles), int(gchunks));
     GMC_LAUNCH_CHECK();
     return GMC_OK;
 }
@@ -587,6 +649,18 @@ extern "C" int gmc_eval_inversed_forward(const float* mixture, const float* xes,
                  : launch_forward<3, kFwdPoints>(mixture, xes, out, n_batch, n_layers, n_components, n_batch_xes, n_layers_xes, n_xes, st);
 }
 
+extern "C" int gmc_debug_eval_forward_lost_copy(const float* mixture, const float* xes, float* out, int n_batch,
+                                                int n_layers, int n_components, int n_dims, int n_batch_xes,
+                                                int n_layers_xes, int n_xes, void* stream) {
+    using namespace gmc;
+    if (int s = check_eval_args(n_batch, n_layers, n_components, n_dims, n_batch_xes, n_layers_xes, n_xes)) return s;
+    if (!mixture || !xes || !out) return GMC_ERR_NULL_POINTER;
+    cudaStream_t st = as_stream(stream);
+    if (n_dims == 2)
+        return launch_forward<2, 1>(mixture, xes, out, n_batch, n_layers, n_components, n_batch_xes, n_layers_xes, n_xes, st, 1);
+    return launch_forward<3, 1>(mixture, xes, out, n_batch, n_layers, n_components, n_batch_xes, n_layers_xes, n_xes, st, 1);
+}
+
 extern "C" int gmc_eval_inversed_backward(const float* grad_out, const float* mixture, const float* xes,
                                           float* grad_mixture, float* grad_xes, int n_batch, int n_layers,
                                           int n_components, int n_dims, int n_batch_xes, int n_layers_xes, int n_xes,
@@ -602,15 +676,15 @@ extern "C" int gmc_eval_inversed_backward(const float* grad_out, const float* mi
         GMC_CUDA_TRY(cudaMemsetAsync(grad_xes, 0, sizeof(float) * size_t(n_batch_xes) * n_layers_xes * n_xes * n_dims, st));
     if (!grad_mixture && !grad_xes) return GMC_OK;
 
-    // packed Gaussian pairs per thread (2 or 4 Gaussians) and threads along the Gaussian axis
+    // packed Gaussian pairs per thread (2, 4 or 8 Gaussians), CTA size and threads along the Gaussian axis
     int gp, tg;
-    if (n_components >= 384) { gp = 2; tg = 128; }
+    if (n_components >= 384) { gp = GMC_BWD_GP_LARGE; tg = GMC_BWD_THREADS_LARGE; }
     else if (n_components > 128) { gp = 1; tg = 128; }
     else if (n_components > 64) { gp = 1; tg = 64; }
     else { gp = 1; tg = 32; }
-#define GMC_BWD(D_, GP_) launch_backward<D_, GP_>(grad_out, mixture, xes, grad_mixture, grad_xes, n_batch, n_layers, \
-                                                  n_components, n_batch_xes, n_layers_xes, n_xes, tg, st)
-    if (n_dims == 2) return gp == 2 ? GMC_BWD(2, 2) : GMC_BWD(2, 1);
-    return gp == 2 ? GMC_BWD(3, 2) : GMC_BWD(3, 1);
+#define GMC_BWD(D_, GP_, T_) launch_backward<D_, GP_, T_>(grad_out, mixture, xes, grad_mixture, grad_xes, n_batch, \
+                                                          n_layers, n_components, n_batch_xes, n_layers_xes, n_xes, tg, st)
+    if (n_dims == 2) return gp > 1 ? GMC_BWD(2, GMC_BWD_GP_LARGE, GMC_BWD_THREADS_LARGE) : GMC_BWD(2, 1, 128);
+    return gp > 1 ? GMC_BWD(3, GMC_BWD_GP_LARGE, GMC_BWD_THREADS_LARGE) : GMC_BWD(3, 1, 128);
 #undef GMC_BWD
 }

@@ -8,8 +8,9 @@
 // PCIe is full duplex, so with page-locked host buffers both copy directions hide behind the kernels and the
 // call costs about one slice of copy-in, the kernels, and one slice of copy-out.
 //
-// The device workspace, the streams and the events are created once per device and kept until
-// gmc_host_pipeline_release().
+// The device workspace (cudaMalloc, grown with cudaFree + cudaMalloc when a larger problem arrives), six streams and
+// twelve events are created once per device and kept until gmc_host_pipeline_release(). One mutex serialises the calls
+// of a process: the slots are shared. The call blocks until the host buffers are complete.
 #include <mutex>
 
 #include "common.cuh"
@@ -75,6 +76,8 @@ inline size_t round64(size_t n) { return (n + 63) & ~size_t(63); }   // keeps ev
 
 }  // namespace
 }  // namespace gmc
+
+int gmc_tu_check_eval_inversed(int* word);   // reads and clears the check word of the evaluation kernels (eval_inversed.cu)
 
 extern "C" int gmc_eval_inversed_host(const float* mixture, const float* xes, const float* grad_out, float* out,
                                       float* grad_mixture, float* grad_xes, int n_batch, int n_layers,
@@ -148,7 +151,18 @@ extern "C" int gmc_eval_inversed_host(const float* mixture, const float* xes, co
     DevicePipe& p = g_pipes[device];
     if (int s = pipe_prepare(p, need)) return s;
 
+    // Inside the loop an error is recorded and the loop left; the streams are drained below in every case, because copies
+    // already queued keep reading and writing the caller's buffers until they finish.
     int status = GMC_OK;
+#define GMC_PIPE_TRY(expr)                                    \
+    {                                                         \
+        const cudaError_t pipe_e_ = (expr);                   \
+        if (pipe_e_ != cudaSuccess) {                         \
+            set_last_cuda_error(pipe_e_);                     \
+            status = GMC_ERR_CUDA;                            \
+            break;                                            \
+        }                                                     \
+    }
     for (int i = 0; i < n_slices && status == GMC_OK; ++i) {
         const int k = i % kSlots;
         const int b0 = starts[i];
@@ -157,20 +171,20 @@ extern "C" int gmc_eval_inversed_host(const float* mixture, const float* xes, co
         const int bx0 = n_batch_xes == 1 ? 0 : b0;
         float* d = p.slot[k];
 
-        // copy-in: the slot's inputs are free once the kernels of slice i-2 are done
-        if (i >= kSlots) GMC_CUDA_TRY(cudaStreamWaitEvent(p.s_in, p.comp_done[k], 0));
-        GMC_CUDA_TRY(cudaMemcpyAsync(d + off_m, mixture + m_row * b0, m_row * nb * sizeof(float),
+        // copy-in: the slot's inputs are free once the kernels of the slice that used it before (i - kSlots) are done
+        if (i >= kSlots) GMC_PIPE_TRY(cudaStreamWaitEvent(p.s_in, p.comp_done[k], 0));
+        GMC_PIPE_TRY(cudaMemcpyAsync(d + off_m, mixture + m_row * b0, m_row * nb * sizeof(float),
                                      cudaMemcpyHostToDevice, p.s_in));
-        GMC_CUDA_TRY(cudaMemcpyAsync(d + off_x, xes + x_row * bx0, x_row * nbx * sizeof(float), cudaMemcpyHostToDevice,
+        GMC_PIPE_TRY(cudaMemcpyAsync(d + off_x, xes + x_row * bx0, x_row * nbx * sizeof(float), cudaMemcpyHostToDevice,
                                      p.s_in));
         if (grad_out)
-            GMC_CUDA_TRY(cudaMemcpyAsync(d + off_g, grad_out + o_row * b0, o_row * nb * sizeof(float),
+            GMC_PIPE_TRY(cudaMemcpyAsync(d + off_g, grad_out + o_row * b0, o_row * nb * sizeof(float),
                                          cudaMemcpyHostToDevice, p.s_in));
-        GMC_CUDA_TRY(cudaEventRecord(p.in_done[k], p.s_in));
+        GMC_PIPE_TRY(cudaEventRecord(p.in_done[k], p.s_in));
 
-        // compute: the slot's outputs are free once slice i-2 has been copied out
-        GMC_CUDA_TRY(cudaStreamWaitEvent(p.s_comp[k], p.in_done[k], 0));
-        if (i >= kSlots) GMC_CUDA_TRY(cudaStreamWaitEvent(p.s_comp[k], p.out_done[k], 0));
+        // compute: the slot's outputs are free once slice i - kSlots has been copied out
+        GMC_PIPE_TRY(cudaStreamWaitEvent(p.s_comp[k], p.in_done[k], 0));
+        if (i >= kSlots) GMC_PIPE_TRY(cudaStreamWaitEvent(p.s_comp[k], p.out_done[k], 0));
         if (out)
             status = gmc_eval_inversed_forward(d + off_m, d + off_x, d + off_o, nb, n_layers, n_components, n_dims, nbx,
                                                n_layers_xes, n_xes, p.s_comp[k]);
@@ -179,21 +193,22 @@ extern "C" int gmc_eval_inversed_host(const float* mixture, const float* xes, co
                                                 grad_xes ? d + off_gx : nullptr, nb, n_layers, n_components, n_dims,
                                                 nbx, n_layers_xes, n_xes, p.s_comp[k]);
         if (status != GMC_OK) break;
-        GMC_CUDA_TRY(cudaEventRecord(p.comp_done[k], p.s_comp[k]));
+        GMC_PIPE_TRY(cudaEventRecord(p.comp_done[k], p.s_comp[k]));
 
         // copy-out
-        GMC_CUDA_TRY(cudaStreamWaitEvent(p.s_out, p.comp_done[k], 0));
+        GMC_PIPE_TRY(cudaStreamWaitEvent(p.s_out, p.comp_done[k], 0));
         if (out)
-            GMC_CUDA_TRY(cudaMemcpyAsync(out + o_row * b0, d + off_o, o_row * nb * sizeof(float), cudaMemcpyDeviceToHost,
+            GMC_PIPE_TRY(cudaMemcpyAsync(out + o_row * b0, d + off_o, o_row * nb * sizeof(float), cudaMemcpyDeviceToHost,
                                          p.s_out));
         if (backward && grad_mixture)
-            GMC_CUDA_TRY(cudaMemcpyAsync(grad_mixture + m_row * b0, d + off_gm, m_row * nb * sizeof(float),
+            GMC_PIPE_TRY(cudaMemcpyAsync(grad_mixture + m_row * b0, d + off_gm, m_row * nb * sizeof(float),
                                          cudaMemcpyDeviceToHost, p.s_out));
         if (backward && grad_xes)
-            GMC_CUDA_TRY(cudaMemcpyAsync(grad_xes + x_row * bx0, d + off_gx, x_row * nbx * sizeof(float),
+            GMC_PIPE_TRY(cudaMemcpyAsync(grad_xes + x_row * bx0, d + off_gx, x_row * nbx * sizeof(float),
                                          cudaMemcpyDeviceToHost, p.s_out));
-        GMC_CUDA_TRY(cudaEventRecord(p.out_done[k], p.s_out));
+        GMC_PIPE_TRY(cudaEventRecord(p.out_done[k], p.s_out));
     }
+#undef GMC_PIPE_TRY
     // the host buffers are valid when the call returns; drain every stream even after an error
     cudaError_t e1 = cudaStreamSynchronize(p.s_in);
     cudaError_t e2 = cudaSuccess;
@@ -206,7 +221,10 @@ extern "C" int gmc_eval_inversed_host(const float* mixture, const float* xes, co
     GMC_CUDA_TRY(e1);
     GMC_CUDA_TRY(e2);
     GMC_CUDA_TRY(e3);
-    return GMC_OK;
+    // everything is synchronised here anyway: a kernel that gave up (bounded wait) turns into an error status
+    int word = 0;
+    if (int s = gmc_tu_check_eval_inversed(&word)) return s;
+    return word != 0 ? GMC_ERR_DEVICE_CHECK : GMC_OK;
 }
 
 extern "C" int gmc_host_pipeline_release(void) {

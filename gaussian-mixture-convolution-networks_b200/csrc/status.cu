@@ -1,18 +1,12 @@
 // Status strings, the per-thread CUDA error message and the device check word reader.
-#include <atomic>
-
 #include "common.cuh"
 
 namespace gmc {
 namespace {
 thread_local cudaError_t t_last_error = cudaSuccess;
-std::atomic<long long> g_kernel_launches{0};
 }
 void set_last_cuda_error(cudaError_t e) { t_last_error = e; }
-void note_kernel_launch() { g_kernel_launches.fetch_add(1, std::memory_order_relaxed); }
 }  // namespace gmc
-
-extern "C" long long gmc_kernel_launch_count(void) { return gmc::g_kernel_launches.load(std::memory_order_relaxed); }
 
 // one reader per translation unit that owns kernels
 int gmc_tu_check_eval_inversed(int* word);
@@ -30,10 +24,8 @@ extern "C" const char* gmc_status_string(int status) {
         case GMC_ERR_BAD_BROADCAST: return "xes must have a batch and layer extent of one or equal to the mixture's";
         case GMC_ERR_NULL_POINTER: return "a required pointer is NULL";
         case GMC_ERR_UNSUPPORTED: return "unsupported parameter value";
-        case GMC_ERR_WORKSPACE: return "scratch buffer too small";
         case GMC_ERR_CUDA: return "CUDA runtime error";
         case GMC_ERR_DEVICE_CHECK: return "a device-side check failed";
-        case GMC_ERR_ALIGNMENT: return "pointer not aligned";
         case GMC_ERR_BUILTIN_SCRATCH:
             return "problem exceeds the built-in scratch of the no-allocation entry point (n_mixtures * n_components > "
                    "2^20); use the entry point that takes caller scratch";
@@ -47,10 +39,23 @@ extern "C" const char* gmc_last_cuda_error(void) {
 
 extern "C" const char* gmc_version(void) { return "0.1"; }
 
+static int read_all_check_words(int* word_out);
+
+extern "C" int gmc_sync_and_check(void* stream) {
+    GMC_CUDA_TRY(cudaStreamSynchronize(gmc::as_stream(stream)));
+    int word = 0;
+    if (int s = read_all_check_words(&word)) return s;
+    return word != 0 ? GMC_ERR_DEVICE_CHECK : GMC_OK;
+}
+
 extern "C" int gmc_device_check_word(int* word_out) {
     if (!word_out) return GMC_ERR_NULL_POINTER;
     *word_out = 0;
     GMC_CUDA_TRY(cudaDeviceSynchronize());
+    return read_all_check_words(word_out);
+}
+
+static int read_all_check_words(int* word_out) {
     if (int s = gmc_tu_check_eval_inversed(word_out)) return s;
     if (int s = gmc_tu_check_small_ops(word_out)) return s;
     if (int s = gmc_tu_check_lbvh(word_out)) return s;

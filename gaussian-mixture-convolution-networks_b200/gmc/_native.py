@@ -29,8 +29,6 @@ lib.gmc_last_cuda_error.restype = ctypes.c_char_p
 lib.gmc_last_cuda_error.argtypes = []
 lib.gmc_version.restype = ctypes.c_char_p
 lib.gmc_version.argtypes = []
-lib.gmc_kernel_launch_count.restype = ctypes.c_longlong
-lib.gmc_kernel_launch_count.argtypes = []
 lib.gmc_device_check_word.restype = _c_int
 lib.gmc_device_check_word.argtypes = [ctypes.POINTER(_c_int)]
 
@@ -44,9 +42,10 @@ def _declare(name, argtypes):
 
 _declare("gmc_eval_inversed_forward", [_c_float_p] * 3 + [_c_int] * 7 + [_c_void_p])
 _declare("gmc_eval_inversed_backward", [_c_float_p] * 5 + [_c_int] * 7 + [_c_void_p])
+_declare("gmc_debug_eval_forward_lost_copy", [_c_float_p] * 3 + [_c_int] * 7 + [_c_void_p])
+_declare("gmc_sync_and_check", [_c_void_p])
 _declare("gmc_eval_inversed_host", [_c_float_p] * 6 + [_c_int] * 8)
 _declare("gmc_host_pipeline_release", [])
-_declare("gmc_fp32_fma_probe", [_c_float_p, _c_int, ctypes.POINTER(ctypes.c_double), _c_void_p])
 _declare("gmc_relu_fixed_point", [_c_float_p] * 5 + [ctypes.c_longlong, _c_int, _c_int, _c_void_p])
 _declare("gmc_matrix_inverse", [_c_float_p] * 2 + [ctypes.c_longlong, _c_int, _c_void_p])
 _declare("gmc_matrix_inverse_backward", [_c_float_p] * 3 + [ctypes.c_longlong, _c_int, _c_void_p])
@@ -73,7 +72,17 @@ class GmcError(RuntimeError):
     pass
 
 
+_entry_calls = 0
+
+
+def entry_calls() -> int:
+    """Number of library calls checked so far in this process (every operator call passes through check())."""
+    return _entry_calls
+
+
 def check(status: int, what: str) -> None:
+    global _entry_calls
+    _entry_calls += 1
     if status != 0:
         msg = lib.gmc_status_string(status).decode()
         cuda_msg = lib.gmc_last_cuda_error().decode()
@@ -100,6 +109,12 @@ def require_cuda_f32(t: torch.Tensor, name: str) -> None:
         raise GmcError(f"{name} must be float32 (got {t.dtype})")
     if not t.is_contiguous():
         raise GmcError(f"{name} must be contiguous")
+
+
+def sync_and_check(device=None) -> None:
+    """Waits for the current stream of `device` and raises GmcError if a kernel reported a give-up since the last check."""
+    stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    check(lib.gmc_sync_and_check(stream), "device-side check")
 
 
 def device_check_word() -> int:

@@ -73,15 +73,21 @@ class OutputGatherer:
 def all_reduce_gradients(module: torch.nn.Module, group=None, average: bool = True) -> None:
     """Data-parallel training step glue: sums (or averages) the parameter gradients of `module` over all ranks, in
     one flattened collective. Kernel mixtures are small, so one bucket is enough."""
-    params = [p for p in module.parameters() if p.grad is not None]
+    # every rank must issue a collective of the same length: the list is built from requires_grad (identical on all
+    # ranks), not from which gradients happen to exist on this rank; a missing gradient counts as zeros
+    params = [p for p in module.parameters() if p.requires_grad]
     if not params:
         return
-    flat = torch.cat([p.grad.reshape(-1) for p in params])
+    flat = torch.cat([(p.grad if p.grad is not None else torch.zeros_like(p)).reshape(-1) for p in params])
     dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group)
     if average:
         flat /= dist.get_world_size(group)
     offset = 0
     for p in params:
-        n = p.grad.numel()
-        p.grad.copy_(flat[offset:offset + n].view_as(p.grad))
+        n = p.numel()
+        piece = flat[offset:offset + n].view_as(p)
+        if p.grad is None:
+            p.grad = piece.clone()
+        else:
+            p.grad.copy_(piece)
         offset += n

@@ -31,10 +31,8 @@ enum gmc_status {
     GMC_ERR_BAD_BROADCAST = 2,   /* xes batch/layer extent is neither 1 nor the mixture's             */
     GMC_ERR_NULL_POINTER = 3,    /* a required pointer is NULL                                        */
     GMC_ERR_UNSUPPORTED = 4,     /* e.g. reduction_n not in {2,4}                                     */
-    GMC_ERR_WORKSPACE = 5,       /* caller-provided scratch is too small                              */
     GMC_ERR_CUDA = 6,            /* a CUDA runtime call failed (see gmc_last_cuda_error)              */
     GMC_ERR_DEVICE_CHECK = 7,    /* a kernel-side bounded wait or self check gave up                  */
-    GMC_ERR_ALIGNMENT = 8,       /* a pointer is not aligned to sizeof(float)                         */
     GMC_ERR_BUILTIN_SCRATCH = 9  /* problem larger than the built-in scratch of a *_noalloc entry point */
 };
 
@@ -44,11 +42,20 @@ const char* gmc_status_string(int status);
 const char* gmc_last_cuda_error(void);
 /* Library version, "major.minor". */
 const char* gmc_version(void);
-/* Reads and clears the device-side check word of the current device (synchronises the device).
- * 0 = no kernel reported a problem since the last call. */
+/* Reads and clears the device-side check word of the current device (synchronises the WHOLE device).
+ * 0 = no kernel reported a problem since the last call. Bit 1: a bounded wait for a bulk copy ran out (the kernel
+ * wrote NaN to the outputs it could not compute); bit 4: an index check of a bounds-checked build failed. */
 int gmc_device_check_word(int* word_out);
-/* Number of kernels this library has launched in the process so far (all threads, all devices). */
-long long gmc_kernel_launch_count(void);
+/* Waits for `stream` and returns GMC_ERR_DEVICE_CHECK if any kernel of this library reported a problem since the last
+ * check (the word is cleared), GMC_OK otherwise. Call it wherever the host synchronises anyway: device-side give-ups
+ * never hang and never abort, this is how they become visible. Not for use during stream capture. */
+int gmc_sync_and_check(void* stream);
+/* Error-path test aid: the forward evaluation with its bulk copy deliberately left out, so that the bounded wait runs
+ * out after about a thousand polls: every output becomes NaN and the check word gets bit 1. Nothing is in flight when
+ * the kernel gives up; the context stays usable. No reference counterpart. */
+int gmc_debug_eval_forward_lost_copy(const float* mixture, const float* xes, float* out, int n_batch, int n_layers,
+                                     int n_components, int n_dims, int n_batch_xes, int n_layers_xes, int n_xes,
+                                     void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Mixture evaluation with the matrix slot holding the INVERSE covariance S:
@@ -94,11 +101,6 @@ int gmc_eval_inversed_host(const float* mixture, const float* xes, const float* 
                            float* grad_mixture, float* grad_xes, int n_batch, int n_layers, int n_components,
                            int n_dims, int n_batch_xes, int n_layers_xes, int n_xes, int n_slices);
 int gmc_host_pipeline_release(void);
-
-/* Measurement aid: launches independent scalar FFMA chains (32 warps per SM, nothing but FFMA) on the stream and
- * returns the number of floating-point operations of the launch in *flop_out; timed with CUDA events it gives the
- * FP32 peak of the device at its current clocks. sink: one device float (never written). No reference counterpart. */
-int gmc_fp32_fma_probe(float* sink, int iterations, double* flop_out, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * ReLU approximation of mixtures (covariance form, [n_mixtures, n_components, 1+D+D*D]) with per-mixture constants by

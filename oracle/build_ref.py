@@ -1,4 +1,12 @@
-"""TEST INFRASTRUCTURE. Builds the REFERENCE's own native sources (CPU path) into oracle/_ref/libgmc_ref.so.
+"""TEST INFRASTRUCTURE. Builds the REFERENCE's own native sources (CPU path) into two libraries under oracle/_ref/:
+libgmc_ref_fit.so (LBVH, BVH-MHEM fit, evaluation) and libgmc_ref_convfit.so (convolution fitting).
+
+Two libraries because the reference builds these as separate extension modules (bvh_mhem_fit/binding.py:11-20 links
+lbvh/bvh.cu, convolution_fitting/binding.py:10-19 links Tree.cu) and relies on it: lbvh/building.h and
+convolution_fitting/building.h (likewise the two morton_code.h) define the same inline functions
+(lbvh::kernels::determine_range, find_split, lbvh::sort_morton_codes) with different bodies under the same include
+guard. Linked into one object the linker keeps one body for both users and the convolution tree silently gets the
+other variant (it differs for leaves with equal Morton codes).
 
 The sources are compiled where they lie in the reference checkout (nothing is copied): `lbvh/bvh.cu`,
 `convolution_fitting/Tree.cu`, `evaluate_inversed/parallel_implementation.cu`, `CpuSynchronisationPoint.cpp`, and the
@@ -17,7 +25,9 @@ import sysconfig
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT_DIR = os.path.join(HERE, "_ref")
-LIB_PATH = os.path.join(OUT_DIR, "libgmc_ref.so")
+LIB_FIT = os.path.join(OUT_DIR, "libgmc_ref_fit.so")
+LIB_CONVFIT = os.path.join(OUT_DIR, "libgmc_ref_convfit.so")
+LIB_PATH = LIB_FIT
 SHIMS = os.path.join(HERE, "ref_shims")
 ENTRY = os.path.join(HERE, "ref_entry.cu")
 
@@ -29,7 +39,7 @@ def reference_ext_dir():
 
 
 def available() -> bool:
-    return os.path.exists(LIB_PATH)
+    return os.path.exists(LIB_FIT) and os.path.exists(LIB_CONVFIT)
 
 
 def _torch_dirs():
@@ -39,15 +49,22 @@ def _torch_dirs():
     return [inc, os.path.join(inc, "torch", "csrc", "api", "include")], os.path.join(base, "lib")
 
 
+FIT_PARTS = ("LBVH", "MHEM_FWD", "MHEM_BWD", "EVAL")
+CONVFIT_PARTS = ("CONVFIT_FWD", "CONVFIT_BWD")
+
+
 def _units(ext):
-    # (object name, source, extra defines)
+    # (object name, source, extra defines, library)
     units = [
-        ("ref_bvh.o", os.path.join(ext, "lbvh", "bvh.cu"), []),
-        ("ref_tree.o", os.path.join(ext, "convolution_fitting", "Tree.cu"), []),
-        ("ref_eval_cpu.o", os.path.join(ext, "evaluate_inversed", "parallel_implementation.cu"), []),
+        ("ref_bvh.o", os.path.join(ext, "lbvh", "bvh.cu"), [], "fit"),
+        ("ref_eval_cpu.o", os.path.join(ext, "evaluate_inversed", "parallel_implementation.cu"), [], "fit"),
+        ("ref_tree.o", os.path.join(ext, "convolution_fitting", "Tree.cu"), [], "convfit"),
+        ("entry_common.o", ENTRY, ["-DREF_PART_COMMON"], "both"),
     ]
-    for part in ("COMMON", "LBVH", "MHEM_FWD", "MHEM_BWD", "CONVFIT_FWD", "CONVFIT_BWD", "EVAL"):
-        units.append(("entry_%s.o" % part.lower(), ENTRY, ["-DREF_PART_" + part]))
+    for part in FIT_PARTS:
+        units.append(("entry_%s.o" % part.lower(), ENTRY, ["-DREF_PART_" + part], "fit"))
+    for part in CONVFIT_PARTS:
+        units.append(("entry_%s.o" % part.lower(), ENTRY, ["-DREF_PART_" + part], "convfit"))
     return units
 
 
@@ -55,12 +72,12 @@ def build(force: bool = False, jobs: int = 0) -> str:
     """Returns the library path; builds it when the reference checkout is present and the library is stale."""
     ext = reference_ext_dir()
     if ext is None:
-        if not os.path.exists(LIB_PATH):
-            raise FileNotFoundError("no reference checkout and no prebuilt " + LIB_PATH)
+        if not available():
+            raise FileNotFoundError("no reference checkout and no prebuilt libraries under " + OUT_DIR)
         return LIB_PATH
-    deps = [ENTRY] + [os.path.join(r, f) for r, _, fs in os.walk(SHIMS) for f in fs]
+    deps = [ENTRY, os.path.abspath(__file__)] + [os.path.join(r, f) for r, _, fs in os.walk(SHIMS) for f in fs]
     newest = max(os.path.getmtime(p) for p in deps)
-    if not force and os.path.exists(LIB_PATH) and os.path.getmtime(LIB_PATH) >= newest:
+    if not force and available() and min(os.path.getmtime(LIB_FIT), os.path.getmtime(LIB_CONVFIT)) >= newest:
         return LIB_PATH
     os.makedirs(OUT_DIR, exist_ok=True)
     incs, torch_lib = _torch_dirs()
@@ -69,7 +86,7 @@ def build(force: bool = False, jobs: int = 0) -> str:
               "-Xcompiler", "-fopenmp,-fPIC", "-w", "-I" + SHIMS, "-I" + ext] + ["-I" + i for i in incs]
 
     def compile_unit(unit):
-        obj, src, defs = unit
+        obj, src, defs, _ = unit
         out = os.path.join(OUT_DIR, obj)
         if not force and os.path.exists(out) and os.path.getmtime(out) >= max(newest, os.path.getmtime(src)):
             return out
@@ -77,14 +94,21 @@ def build(force: bool = False, jobs: int = 0) -> str:
         return out
 
     jobs = jobs or max(1, min(6, (os.cpu_count() or 2) - 1))
+    units = _units(ext)
     with concurrent.futures.ThreadPoolExecutor(jobs) as pool:
-        objs = list(pool.map(compile_unit, _units(ext)))
+        objs = list(pool.map(compile_unit, units))
     sync_obj = os.path.join(OUT_DIR, "ref_sync.o")
     subprocess.run(["g++", "-std=c++17", "-O2", "-fPIC", "-I" + SHIMS, "-I" + ext, "-c",
                     os.path.join(ext, "CpuSynchronisationPoint.cpp"), "-o", sync_obj], check=True)
-    subprocess.run(["nvcc", "-shared", "-o", LIB_PATH] + objs + [sync_obj] +
-                   ["-Xcompiler", "-fopenmp", "-L" + torch_lib, "-ltorch", "-ltorch_cpu", "-lc10",
-                    "-Xlinker", "-rpath," + torch_lib], check=True)
+    for which, path in (("fit", LIB_FIT), ("convfit", LIB_CONVFIT)):
+        mine = [o for o, u in zip(objs, units) if u[3] in (which, "both")]
+        # -Bsymbolic: calls inside a library bind to that library's own definitions whatever else the process has loaded
+        subprocess.run(["nvcc", "-shared", "-o", path] + mine + [sync_obj] +
+                       ["-Xcompiler", "-fopenmp", "-L" + torch_lib, "-ltorch", "-ltorch_cpu", "-lc10",
+                        "-Xlinker", "-Bsymbolic", "-Xlinker", "-rpath," + torch_lib], check=True)
+    old = os.path.join(OUT_DIR, "libgmc_ref.so")
+    if os.path.exists(old):
+        os.remove(old)
     return LIB_PATH
 
 

@@ -1,5 +1,5 @@
 // TEST INFRASTRUCTURE: C entry points around the REFERENCE's own native sources (CPU path), built into
-// oracle/_ref/libgmc_ref.so by oracle/build_ref.py.  The reference sources are compiled where they lie (they are not
+// oracle/_ref/libgmc_ref_fit.so and libgmc_ref_convfit.so by oracle/build_ref.py.  The reference sources are compiled where they lie (they are not
 // copied); this file only converts between raw host pointers and the torch::Tensor arguments the reference functions
 // take.  Used to pin oracle/cpu/* (and through it the CUDA kernels) to the reference itself, and as the timed CPU
 // baseline.  One source, several translation units: the build compiles it once per REF_PART_* macro because the
@@ -12,14 +12,38 @@
 #include <exception>
 #include <string>
 
+#include <omp.h>
 #include <torch/types.h>
 
 std::string& gmc_ref_error_slot();  // defined in the REF_PART_COMMON unit
+bool& gmc_ref_serial_flag();        // defined in the REF_PART_COMMON unit
 
 namespace {
+// Serial mode: the reference's CPU launcher opens an OpenMP team of as many threads as a CUDA block has
+// (parallel_start.h:92-111). Called from inside an active parallel region of our own, with nested parallelism off, that
+// team has one thread and the "CUDA threads" run one after the other: race-free and reproducible. Needed because the
+// reference's convolution_fitting mass pass adds a node's mass and its count with two independent atomics
+// (convolution_fitting/Tree.cu:289-294), and the interleaving changes the masses, hence the selected subtrees.
+// Not usable for code that waits on a CPU barrier across its threads (bvh_mhem_fit backward, ParallelStack.h:20).
 template <typename Fn> int guarded(Fn&& fn) {
     try {
-        fn();
+        if (gmc_ref_serial_flag()) {
+            std::exception_ptr err;
+            omp_set_max_active_levels(1);
+#pragma omp parallel num_threads(2)
+            {
+                if (omp_get_thread_num() == 0) {
+                    try {
+                        fn();
+                    } catch (...) {
+                        err = std::current_exception();
+                    }
+                }
+            }
+            if (err) std::rethrow_exception(err);
+        } else {
+            fn();
+        }
         return 0;
     } catch (const std::exception& e) {
         gmc_ref_error_slot() = e.what();
@@ -44,7 +68,13 @@ std::string& gmc_ref_error_slot() {
     static thread_local std::string slot;
     return slot;
 }
+bool& gmc_ref_serial_flag() {
+    static bool serial = false;
+    return serial;
+}
 extern "C" const char* gmc_ref_last_error() { return gmc_ref_error_slot().c_str(); }
+// 1: run the reference's CPU "threads" one after the other (see guarded()); 0: as the reference runs them.
+extern "C" void gmc_ref_set_serial(int serial) { gmc_ref_serial_flag() = serial != 0; }
 #endif
 
 // ---------------------------------------------------------------------------------------------------------------

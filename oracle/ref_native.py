@@ -8,31 +8,57 @@ import numpy as np
 
 from . import build_ref as _build
 
-_lib = None
+_libs = {}
 
 
 def available() -> bool:
     return _build.available()
 
 
+def _load(path):
+    if path not in _libs:
+        import torch  # noqa: F401  (the libraries link against libtorch; importing torch loads it)
+        if not os.path.exists(path):
+            raise FileNotFoundError(path + " is not built (run oracle/build_ref.py beside a reference checkout)")
+        handle = ctypes.CDLL(path)          # RTLD_LOCAL: the two libraries do not see each other's symbols
+        handle.gmc_ref_last_error.restype = ctypes.c_char_p
+        _libs[path] = handle
+    return _libs[path]
+
+
 def lib():
-    global _lib
-    if _lib is None:
-        import torch  # noqa: F401  (the library links against libtorch; importing torch loads it)
-        if not os.path.exists(_build.LIB_PATH):
-            raise FileNotFoundError(_build.LIB_PATH + " is not built (run oracle/build_ref.py beside a reference checkout)")
-        _lib = ctypes.CDLL(_build.LIB_PATH)
-        _lib.gmc_ref_last_error.restype = ctypes.c_char_p
-    return _lib
+    """LBVH, BVH-MHEM fit and evaluation (the reference's bvh_mhem_fit / evaluate_inversed extension sources)."""
+    return _load(_build.LIB_FIT)
+
+
+def lib_convfit():
+    """Convolution fitting (the reference's convolution_fitting extension sources)."""
+    return _load(_build.LIB_CONVFIT)
+
+
+class serial:
+    """Context manager: the reference's CPU threads run one after the other inside (race-free, reproducible). The
+    reference's convolution_fitting mass pass is racy when its threads run concurrently
+    (src/gmc/cpp/extensions/convolution_fitting/Tree.cu:289-294). Not for mhem_fit_backward (it waits on a CPU barrier)."""
+
+    def __enter__(self):
+        for handle in (lib(), lib_convfit()):
+            handle.gmc_ref_set_serial(ctypes.c_int(1))
+        return self
+
+    def __exit__(self, *exc):
+        for handle in (lib(), lib_convfit()):
+            handle.gmc_ref_set_serial(ctypes.c_int(0))
+        return False
 
 
 def _p(a):
     return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
 
 
-def _check(rc):
+def _check(rc, handle=None):
     if rc != 0:
-        raise RuntimeError("reference raised: " + lib().gmc_ref_last_error().decode(errors="replace"))
+        raise RuntimeError("reference raised: " + (handle or lib()).gmc_ref_last_error().decode(errors="replace"))
 
 
 def _ints(*v):
@@ -111,8 +137,9 @@ def convolution_fitting_forward(data, kernels, K: int, tree: bool = False):
     mass = np.empty((B, Cout, T - 1), dtype=np.float32) if tree else None
     count = np.empty((B, Cout, T - 1), dtype=np.int32) if tree else None
     keys = np.empty((B, Cout, T), dtype=np.int64) if tree else None
-    _check(lib().gmc_ref_convolution_fitting_forward(_p(data), _p(kernels), *_ints(B, Cin, G, Cout, Gk, D, K), _p(out),
-                                                     _p(cached), _p(objs), _p(sub), _p(nodes), _p(mass), _p(count), _p(keys)))
+    _check(lib_convfit().gmc_ref_convolution_fitting_forward(_p(data), _p(kernels), *_ints(B, Cin, G, Cout, Gk, D, K), _p(out),
+                                                             _p(cached), _p(objs), _p(sub), _p(nodes), _p(mass), _p(count),
+                                                             _p(keys)), lib_convfit())
     if tree:
         return out, cached, objs, sub, dict(nodes=nodes, mass=mass, count=count, keys=keys.view(np.uint64))
     return out, cached, objs, sub
@@ -124,7 +151,8 @@ def convolution_fitting_backward(grad, data, kernels, K: int):
     g = np.ascontiguousarray(grad, dtype=np.float32).reshape(B, Cout, K, V)
     gd = np.empty_like(data)
     gk = np.empty_like(kernels)
-    _check(lib().gmc_ref_convolution_fitting_backward(_p(g), _p(data), _p(kernels), *_ints(B, Cin, G, Cout, Gk, D, K), _p(gd), _p(gk)))
+    _check(lib_convfit().gmc_ref_convolution_fitting_backward(_p(g), _p(data), _p(kernels), *_ints(B, Cin, G, Cout, Gk, D, K),
+                                                              _p(gd), _p(gk)), lib_convfit())
     return gd, gk
 
 

@@ -71,8 +71,9 @@ def load(native: bool = False):
             return torch.from_numpy(out).view(shape[0], shape[1], int(n_components), shape[3])
 
         def convfit_apply(data, kernels, n_components):
-            return torch.from_numpy(ref_native.convolution_fitting_forward(data.detach().numpy(), kernels.detach().numpy(),
-                                                                           int(n_components))[0])
+            with ref_native.serial():      # the reference's mass pass is racy when its CPU threads run concurrently
+                return torch.from_numpy(ref_native.convolution_fitting_forward(data.detach().numpy(), kernels.detach().numpy(),
+                                                                               int(n_components))[0])
 
         sys.modules["gmc.cpp.extensions.bvh_mhem_fit.binding"].apply = fit_apply
         stub("gmc.cpp.extensions.convolution_fitting.binding", apply=convfit_apply)

@@ -26,3 +26,20 @@ def rel_inf(a, ref):
 def golden_eval():
     import numpy as np
     return dict(np.load(os.path.join(ROOT, "tests", "golden", "eval_inversed.npz")))
+
+
+@pytest.fixture(scope="module", autouse=True)
+def no_device_side_give_up(request):
+    """After every GPU test module: no kernel of the library may have reported a give-up (a bounded wait that ran out,
+    or a failed index check in a bounds-checked build). Modules that provoke one on purpose clear the word themselves."""
+    yield
+    module = request.module
+    marks = getattr(module, "pytestmark", None)
+    marks = marks if isinstance(marks, (list, tuple)) else [marks]
+    if not any(getattr(m, "name", None) == "gpu" for m in marks if m is not None):
+        return
+    import torch
+    if not torch.cuda.is_available():
+        return
+    from gmc import _native
+    assert _native.device_check_word() == 0, f"a kernel reported a device-side give-up during {module.__name__}"

@@ -221,8 +221,9 @@ def reference_native_cases(reference_root):
         data = mixture(B, Cin, G, D, 1.0, 0.02, -1.0, 1.0)
         kernels = mixture(Cout, Cin, Gk, D, 0.1, 0.005, -0.3, 0.3)
         grad = torch.randn(B, Cout, K, data.shape[-1], generator=g).numpy()
-        out, cached, objs, sub, tree = ref_native.convolution_fitting_forward(data, kernels, K, tree=True)
-        gd, gk = ref_native.convolution_fitting_backward(grad, data, kernels, K)
+        with ref_native.serial():     # race-free run of the reference's mass pass (see oracle/ref_entry.cu)
+            out, cached, objs, sub, tree = ref_native.convolution_fitting_forward(data, kernels, K, tree=True)
+            gd, gk = ref_native.convolution_fitting_backward(grad, data, kernels, K)
         key = f"cf{ci}"
         cases[key + "_data"], cases[key + "_kernels"], cases[key + "_k"], cases[key + "_grad"] = data, kernels, np.array(K), grad
         cases[key + "_fitting"], cases[key + "_cached"], cases[key + "_nodesobjs"], cases[key + "_subtrees"] = out, cached, objs, sub
@@ -253,9 +254,13 @@ def gmcn3d_network_case():
         net.norms[i].register_forward_hook(lambda mod, inp, out: acts.append(out[0].detach().clone()))
         net.gmcs[i].register_forward_hook(lambda mod, inp, out: convs.append(out[0].detach().clone()))
     net.normX.register_forward_hook(lambda mod, inp, out: feats.append(inp[0].detach().clone()))
+    norm0 = []
+    net.norm0.register_forward_hook(lambda mod, inp, out: norm0.append((out[0].detach().clone(), out[1].detach().clone())))
     with torch.no_grad():
         net(x)
-    cases = {"input": x.numpy(), "features": feats[0].numpy()}
+    # the input normalisation estimates a standard deviation from RANDOM sample points (src/gmc/modules.py:374-425), so its
+    # output depends on the random stream; it is stored and fed to the layers under test instead of being recomputed
+    cases = {"input": x.numpy(), "features": feats[0].numpy(), "norm0": norm0[0][0].numpy(), "norm0_constant": norm0[0][1].numpy()}
     for i in range(4):
         cases[f"layer{i}"] = acts[i].numpy()
         cases[f"conv{i}"] = convs[i].numpy()

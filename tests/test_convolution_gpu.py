@@ -97,5 +97,8 @@ def test_convolution_fitting_backward_matches_autograd_oracle(D, B, Cin, G, Cout
                                                                objs.cpu().numpy(), sub.cpu().numpy())
     for name, a, r in (("grad_data", d.grad.cpu().numpy(), gd), ("grad_kernels", k.grad.cpu().numpy(), gk)):
         assert np.isfinite(a).all()
+        scale = max(np.abs(r).max(), 1e-30)
         for field, sl in (("weight", slice(0, 1)), ("position", slice(1, 1 + D)), ("covariance", slice(1 + D, None))):
-            assert rel_inf(a[..., sl], r[..., sl]) < 1e-3, f"{name} {field}: {rel_inf(a[..., sl], r[..., sl]):.2e}"
+            err = float(np.abs(a[..., sl] - r[..., sl]).max() / scale)
+            print(f"conv-fit backward {name} {field}: rel(tensor) {err:.2e}, rel(field) {rel_inf(a[..., sl], r[..., sl]):.2e}")
+            assert err < 1e-4, f"{name} {field}: {err:.2e}"

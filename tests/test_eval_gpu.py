@@ -126,7 +126,8 @@ def test_forward_is_deterministic_and_does_not_touch_inputs():
 
 def test_config1_full_size_identities():
     """Full benchmark size (2^32 pairs). The output is linear in the weights, so
-    sum_n grad_out[n] out[n] == sum_g w_g dL/dw_g for every (batch, layer); a CPU oracle slice pins values."""
+    sum_n grad_out[n] out[n] == sum_g w_g dL/dw_g for every (batch, layer); two whole (batch, layer) mixtures are
+    checked against the fp64 oracle (forward, grad_mixture per field, grad_xes) at 1e-4."""
     import gmc.cpp.extensions.evaluate_inversed.evaluate_inversed as ev
     import synthetic_inputs as synthetic
     m, x, g = synthetic.config1()
@@ -149,6 +150,22 @@ def test_config1_full_size_identities():
     ref = cpu_oracle.eval_forward(ms, xs)
     assert rel_inf(out[b, l, :2048].detach().cpu().numpy(), ref[0, 0]) < TOL
     assert torch.isfinite(mt.grad).all() and torch.isfinite(xt.grad).all()
+    # the backward variant used at this size, against the fp64 oracle: the whole grad_mixture of two (batch, layer)
+    # mixtures over all 16384 points (per field), and grad_xes of those mixtures' points
+    for (b, l) in ((3, 5), (31, 15)):
+        ms = m[b:b + 1, l:l + 1].numpy().astype(np.float64)
+        xs = x[b:b + 1, l:l + 1].numpy().astype(np.float64)
+        gs = g[b:b + 1, l:l + 1].numpy().astype(np.float64)
+        ref_gm, ref_gx = cpu_oracle.eval_backward(gs, ms, xs)
+        got_gm = mt.grad[b, l].cpu().numpy()
+        for name, sl in (("weight", slice(0, 1)), ("position", slice(1, 4)), ("matrix", slice(4, 13))):
+            err = rel_inf(got_gm[:, sl], ref_gm[0, 0][:, sl])
+            print(f"config1 ({b},{l}) grad_mixture {name}: rel {err:.2e}")
+            assert err < TOL, f"grad_mixture {name} at ({b},{l}): {err:.2e}"
+        err = rel_inf(xt.grad[b, l].cpu().numpy(), ref_gx[0, 0])
+        print(f"config1 ({b},{l}) grad_xes: rel {err:.2e}")
+        assert err < TOL, f"grad_xes at ({b},{l}): {err:.2e}"
+        assert rel_inf(out[b, l].detach().cpu().numpy(), cpu_oracle.eval_forward(ms, xs)[0, 0]) < TOL
 
 
 @pytest.mark.parametrize("D", [2, 3])
@@ -190,3 +207,32 @@ def test_cpu_tensors_go_through_the_operator():
     out.backward(torch.from_numpy(grad_out))
     assert not out.is_cuda and np.array_equal(out.detach().numpy(), out_d)
     assert rel_inf(m.grad.numpy(), gm_d) < 1e-5 and rel_inf(x.grad.numpy(), gx_d) < 1e-5
+
+
+def test_a_lost_bulk_copy_is_reported_and_never_hangs():
+    """The forward kernel waits for its bulk copy with a poll limit. With the copy left out on purpose (test entry
+    point; nothing is in flight) the wait runs out: the kernel returns, its outputs are NaN, the next check call returns
+    GMC_ERR_DEVICE_CHECK, and the context keeps working."""
+    import ctypes
+    from gmc import _native
+    import gmc.cpp.extensions.evaluate_inversed.evaluate_inversed as ev
+    rng = np.random.default_rng(2)
+    m, x, _ = _random_case(rng, 2, 2, 64, 300, 3, True, True, radius=1.0)     # 64 x 13 floats: a 16-byte multiple
+    mt, xt = torch.from_numpy(m).cuda(), torch.from_numpy(x).cuda()
+    assert _native.device_check_word() == 0
+    out = torch.zeros(2, 2, 300, device="cuda")
+    stream = _native.stream_of(mt)
+    status = _native.lib.gmc_debug_eval_forward_lost_copy(_native.ptr(mt), _native.ptr(xt), _native.ptr(out), 2, 2, 64, 3, 2, 2,
+                                                          300, stream)
+    assert status == 0
+    assert _native.lib.gmc_sync_and_check(stream) == 7           # GMC_ERR_DEVICE_CHECK
+    assert torch.isnan(out).all()
+    assert _native.lib.gmc_sync_and_check(stream) == 0           # the word was cleared
+    with pytest.raises(_native.GmcError, match="device-side check"):
+        _native.lib.gmc_debug_eval_forward_lost_copy(_native.ptr(mt), _native.ptr(xt), _native.ptr(out), 2, 2, 64, 3, 2, 2, 300,
+                                                     stream)
+        _native.sync_and_check()
+    good = ev.apply(mt, xt)                                      # the context is intact
+    ref = cpu_oracle.eval_forward(m.astype(np.float64), x.astype(np.float64))
+    assert rel_inf(good.cpu().numpy(), ref) < TOL
+    assert _native.device_check_word() == 0

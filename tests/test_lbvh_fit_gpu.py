@@ -135,8 +135,9 @@ def test_fit_rejects_bad_arguments():
 
 @pytest.mark.parametrize("D,G,K,R", [(2, 64, 16, 4), (2, 40, 12, 2), (3, 48, 16, 4), (3, 30, 8, 2), (2, 16, 20, 4), (2, 100, 8, 4)])
 def test_fit_backward_matches_autograd_oracle(D, G, K, R):
-    """Analytic CUDA backward against fp64 autograd through the restated forward with all discrete decisions frozen.
-    Tolerance: relative 1e-3 per field (the reference's own backward tests use 4e-5 .. 4e-3)."""
+    """Analytic CUDA backward against fp64 autograd through the restated forward with all discrete decisions frozen
+    (that oracle agrees with the reference's hand-written fp32 backward to 4e-6: tests/test_oracle_vs_reference.py).
+    Bar: relative 1e-4 of the gradient tensor's largest entry, per field; the measured error is printed."""
     import gmc.cpp.extensions.bvh_mhem_fit.binding as fit
     from conftest import rel_inf
     from oracle import autograd_oracles
@@ -151,9 +152,12 @@ def test_fit_backward_matches_autograd_oracle(D, G, K, R):
     ref_fit, dump = cpu_oracle.mhem_fit_forward(flat, K, R, dump=True)
     grad_ref, out64 = autograd_oracles.mhem_fit_backward(g.numpy().reshape(-1, K, RF), flat, dump, K, R)
     assert np.isfinite(grad_gpu).all()
+    scale = max(np.abs(grad_ref).max(), 1e-30)
     for field, sl in (("weight", slice(0, 1)), ("position", slice(1, 1 + D)), ("covariance", slice(1 + D, None))):
-        err = rel_inf(grad_gpu[..., sl], grad_ref[..., sl])
-        assert err < 1e-3, f"{field}: rel {err:.2e}"
+        err = float(np.abs(grad_gpu[..., sl] - grad_ref[..., sl]).max() / scale)
+        per_field = rel_inf(grad_gpu[..., sl], grad_ref[..., sl])
+        print(f"fit backward D={D} G={G} K={K} R={R} {field}: rel(tensor) {err:.2e}, rel(field) {per_field:.2e}")
+        assert err < 1e-4, f"{field}: rel {err:.2e}"
     # the saved tensors are not modified: a second backward gives the same gradient
     mt.grad = None
     out2 = fit.apply(mt, K, R)

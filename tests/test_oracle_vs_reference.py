@@ -155,18 +155,31 @@ def test_library_convolution_fitting_at_benchmark_shapes(reference_library, D, B
         data = np.ascontiguousarray(synthetic.config4_input(B * Cin, 1004).numpy().reshape(B, Cin, 64, 13)[:, :, :G])
         data[..., 0] *= np.where(np.arange(G) % 5 == 0, -1.0, 1.0)      # mixed signs, as after a convolution layer
     kernels = _kernels(Cout, Cin, Gk, D, 5 + Cin)
-    out_r, cached_r, objs_r, sub_r, tree = reference_library.convolution_fitting_forward(data, kernels, K, tree=True)
     out_o, cached_o, objs_o, sub_o, keys_o = cpu_oracle.convolution_fitting_forward(data, kernels, K, with_keys=True)
-    assert np.array_equal(keys_o, tree["keys"])
-    assert np.array_equal(objs_o, objs_r) and np.array_equal(sub_o, sub_r)
-    assert rel_inf(out_o, out_r) <= 1e-6 and rel_inf(cached_o, cached_r) <= 1e-5
-    grad = np.random.default_rng(K).standard_normal(out_r.shape).astype(np.float32)
-    gd_r, gk_r = reference_library.convolution_fitting_backward(grad, data, kernels, K)
+
+    def forward():
+        out_r, cached_r, objs_r, sub_r, tree = reference_library.convolution_fitting_forward(data, kernels, K, tree=True)
+        assert np.array_equal(keys_o, tree["keys"])
+        assert np.array_equal(objs_o, objs_r) and np.array_equal(sub_o, sub_r)
+        assert rel_inf(out_o, out_r) <= 1e-6 and rel_inf(cached_o, cached_r) <= 1e-5
+
+    # serial: the reference's create_attributes adds a node's mass and its count with two independent atomics
+    # (src/gmc/cpp/extensions/convolution_fitting/Tree.cu:289-294); with its CPU threads running concurrently a later
+    # child can climb with a stale mass and the run selects other subtrees. One thread at a time is race-free.
+    with reference_library.serial():
+        forward()
+    grad = np.random.default_rng(K).standard_normal(out_o.shape).astype(np.float32)
     gd_o, gk_o, _ = autograd_oracles.convolution_fitting_backward(grad, data, kernels, objs_o, sub_o)
-    for a, r in ((gd_o, gd_r), (gk_o, gk_r)):
-        scale = max(np.abs(r).max(), 1e-30)
-        for field, sl in FIELDS(D):
-            assert float(np.abs(a[..., sl] - r[..., sl]).max() / scale) <= 2e-5, field
+
+    def backward():
+        gd_r, gk_r = reference_library.convolution_fitting_backward(grad, data, kernels, K)
+        for a, r in ((gd_o, gd_r), (gk_o, gk_r)):
+            scale = max(np.abs(r).max(), 1e-30)
+            for field, sl in FIELDS(D):
+                assert float(np.abs(a[..., sl] - r[..., sl]).max() / scale) <= 2e-5, field
+
+    with reference_library.serial():
+        backward()
 
 
 @pytest.mark.parametrize("D,G,K,R", [(2, 128, 32, 4), (3, 64, 16, 2)])

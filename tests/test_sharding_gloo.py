@@ -50,6 +50,20 @@ def _worker(rank, world, port, mode, result_dir):
             assert torch.allclose(lin.weight.grad, torch.full((2, 3), 6.0))
             assert torch.allclose(lin.bias.grad, local[1])
             torch.save(torch.tensor(1), os.path.join(result_dir, f"ok{rank}"))
+        elif mode == "grads_missing":
+            # rank 1 never touches the bias: its .grad stays None, yet both ranks must issue the same collective
+            torch.manual_seed(0)
+            lin = torch.nn.Linear(3, 2)
+            x = torch.full((4, 3), float(rank + 1))
+            if rank == 0:
+                lin(x).sum().backward()
+            else:
+                (x @ lin.weight.t()).sum().backward()
+                assert lin.bias.grad is None
+            sharding.all_reduce_gradients(lin, average=False)
+            assert torch.allclose(lin.weight.grad, torch.full((2, 3), 12.0))
+            assert torch.allclose(lin.bias.grad, torch.full((2,), 4.0))
+            torch.save(torch.tensor(1), os.path.join(result_dir, f"ok{rank}"))
         elif mode == "ragged":
             bad = shard if rank == 0 else shard[:1]
             try:
@@ -104,6 +118,10 @@ def test_all_gather_two_ranks(tmp_path):
 
 def test_gradient_all_reduce_two_ranks(tmp_path):
     _run("grads", tmp_path, (0, 1))
+
+
+def test_gradient_all_reduce_when_one_rank_lacks_a_gradient(tmp_path):
+    _run("grads_missing", tmp_path, (0, 1))
 
 
 def test_unequal_shards_raise_on_every_rank(tmp_path):
