@@ -33,24 +33,38 @@ constexpr float kEpsSmall = 0.0000000000001f;
 constexpr float kEpsLarge = 0.0000001f;
 constexpr float kKlThreshold = 0.5f;
 
+// The EM step is written once on a value type T: float in the forward pass (its decisions and values are the
+// reference's fp32 ones) and double in the backward pass, where differences of nearly equal terms are scaled by squared
+// inverse covariances (fp32 there loses three to four digits on mixtures with small covariances).
 __device__ __forceinline__ float clip(float v) { return fmaxf(v, kEpsSmall); }
-__device__ __forceinline__ int sign_of(float v) { return v >= 0.f ? 1 : -1; }
+__device__ __forceinline__ double clip(double v) { return fmax(v, double(kEpsSmall)); }
+template <typename T> __device__ __forceinline__ int sign_of(T v) { return v >= T(0) ? 1 : -1; }
+__device__ __forceinline__ float g_exp(float v) { return expf(v); }
+__device__ __forceinline__ double g_exp(double v) { return exp(v); }
+__device__ __forceinline__ float g_log(float v) { return logf(v); }
+__device__ __forceinline__ double g_log(double v) { return log(v); }
+__device__ __forceinline__ float g_pow(float a, float b) { return powf(a, b); }
+__device__ __forceinline__ double g_pow(double a, double b) { return pow(a, b); }
+__device__ __forceinline__ float g_sqrt(float v) { return sqrtf(v); }
+__device__ __forceinline__ double g_sqrt(double v) { return sqrt(v); }
+template <int D, typename T> __device__ __forceinline__ T norm_factor_t() {
+    if constexpr (sizeof(T) == 4) return T(gauss_norm_factor<D>());
+    else return D == 2 ? T(0.15915494309189535) : T(0.06349363593424097);     // (2 pi)^(-D/2)
+}
 
-template <int D> __device__ __forceinline__ float det(const float* m);
-template <> __device__ __forceinline__ float det<2>(const float* m) { return m[0] * m[3] - m[1] * m[2]; }
-template <> __device__ __forceinline__ float det<3>(const float* m) {
-    return m[0] * (m[4] * m[8] - m[5] * m[7]) - m[1] * (m[3] * m[8] - m[5] * m[6]) + m[2] * (m[3] * m[7] - m[4] * m[6]);
+template <int D, typename T> __device__ __forceinline__ T det(const T* m) {
+    if constexpr (D == 2) return m[0] * m[3] - m[1] * m[2];
+    else return m[0] * (m[4] * m[8] - m[5] * m[7]) - m[1] * (m[3] * m[8] - m[5] * m[6]) + m[2] * (m[3] * m[7] - m[4] * m[6]);
 }
-template <int D> __device__ __forceinline__ void inverse(const float* m, float* o);
-template <> __device__ __forceinline__ void inverse<2>(const float* m, float* o) {
-    const float r = 1.f / det<2>(m);
-    o[0] = m[3] * r; o[1] = -m[1] * r; o[2] = -m[2] * r; o[3] = m[0] * r;
-}
-template <> __device__ __forceinline__ void inverse<3>(const float* m, float* o) {
-    const float r = 1.f / det<3>(m);
-    o[0] = (m[4] * m[8] - m[5] * m[7]) * r; o[1] = -(m[1] * m[8] - m[2] * m[7]) * r; o[2] = (m[1] * m[5] - m[2] * m[4]) * r;
-    o[3] = -(m[3] * m[8] - m[5] * m[6]) * r; o[4] = (m[0] * m[8] - m[2] * m[6]) * r; o[5] = -(m[0] * m[5] - m[2] * m[3]) * r;
-    o[6] = (m[3] * m[7] - m[4] * m[6]) * r; o[7] = -(m[0] * m[7] - m[1] * m[6]) * r; o[8] = (m[0] * m[4] - m[1] * m[3]) * r;
+template <int D, typename T> __device__ __forceinline__ void inverse(const T* m, T* o) {
+    const T r = T(1) / det<D, T>(m);
+    if constexpr (D == 2) {
+        o[0] = m[3] * r; o[1] = -m[1] * r; o[2] = -m[2] * r; o[3] = m[0] * r;
+    } else {
+        o[0] = (m[4] * m[8] - m[5] * m[7]) * r; o[1] = -(m[1] * m[8] - m[2] * m[7]) * r; o[2] = (m[1] * m[5] - m[2] * m[4]) * r;
+        o[3] = -(m[3] * m[8] - m[5] * m[6]) * r; o[4] = (m[0] * m[8] - m[2] * m[6]) * r; o[5] = -(m[0] * m[5] - m[2] * m[3]) * r;
+        o[6] = (m[3] * m[7] - m[4] * m[6]) * r; o[7] = -(m[0] * m[7] - m[1] * m[6]) * r; o[8] = (m[0] * m[4] - m[1] * m[3]) * r;
+    }
 }
 
 // Attribute record of an internal node: [R * RF floats | integral | count | initial indices (4 x uint8) | reserved]
@@ -211,94 +225,101 @@ __device__ __forceinline__ bool cluster_and_select_ranked(WarpScratch<D, R>& ws,
 
 // Reductions over the lanes of one matrix row (fixed target t, lanes t*R .. t*R+R-1) or one matrix column (fixed s,
 // lanes s, s+R, ...); every lane of the row / column ends up with the total.
-template <int R>
-__device__ __forceinline__ float row_sum(float v) {
+template <int R, typename T>
+__device__ __forceinline__ T row_sum(T v) {
 #pragma unroll
     for (int off = 1; off < R; off <<= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
     return v;
 }
-template <int R>
-__device__ __forceinline__ float col_sum(float v) {
+template <int R, typename T>
+__device__ __forceinline__ T col_sum(T v) {
 #pragma unroll
     for (int off = R; off < 2 * R * R; off <<= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
     return v;
 }
 
 // Values of matrix entry (t, s) of the EM step, one entry per lane (lanes beyond the matrix repeat the last entry).
-template <int D>
+template <int D, typename T = float>
 struct Entry {
     int t, s, fi;
-    float W, Wc, V, Vc;       // target / initial integral and their clipped versions
-    float a, b;               // weights scaled to integral one: a_t = w_t / Wc, b_s = v_s / Vc
-    float inv[D * D];         // inverse covariance of initial Gaussian s
-    float diff[D];            // mu_t - mu_initial(s)
-    float val_a, val_b, ab;   // N(mu_t; initial s), exp(-1/2 tr(inv Sigma_t)), their product
-    float lik, gate, u, x, X, r1, r2, fw, fwc, r3;
+    T W, Wc, V, Vc;       // target / initial integral and their clipped versions
+    T a, b;               // weights scaled to integral one: a_t = w_t / Wc, b_s = v_s / Vc
+    T inv[D * D];         // inverse covariance of initial Gaussian s
+    T diff[D];            // mu_t - mu_initial(s)
+    T val_a, val_b, ab;   // N(mu_t; initial s), exp(-1/2 tr(inv Sigma_t)), their product
+    T lik, gate, u, x, X, r1, r2, fw, fwc, r3;
 };
 
 // Needs ws.tgt (padded targets) and ws.idx. Sums that feed decisions run in a fixed order (as on the CPU checker).
-template <int D, int R>
-__device__ __forceinline__ Entry<D> em_entry(const WarpScratch<D, R>& ws, int lane) {
+// gate_in == nullptr: the KL gate is decided here (forward pass, T = float). Otherwise *gate_in is this entry's gate as
+// the forward pass decided it, and the values are recomputed in T around that decision (backward pass, T = double).
+template <int D, int R, typename T = float>
+__device__ __forceinline__ Entry<D, T> em_entry(const WarpScratch<D, R>& ws, int lane, const float* gate_in = nullptr) {
     constexpr int NT = 2 * R;
     constexpr int NE = NT * R;
-    Entry<D> e;
-    float W = 0.f;
+    Entry<D, T> e;
+    T W = T(0);
 #pragma unroll
-    for (int i = 0; i < NT; ++i) W += ws.tgt[i][0];
+    for (int i = 0; i < NT; ++i) W += T(ws.tgt[i][0]);
     e.W = W; e.Wc = clip(W);
-    float V = 0.f;
+    T V = T(0);
 #pragma unroll
-    for (int s = 0; s < R; ++s) V += ws.tgt[ws.idx[s] < NT ? ws.idx[s] : 0][0];
+    for (int s = 0; s < R; ++s) V += T(ws.tgt[ws.idx[s] < NT ? ws.idx[s] : 0][0]);
     e.V = V; e.Vc = clip(V);
     const int ent = lane < NE ? lane : NE - 1;
     e.t = ent / R; e.s = ent - e.t * R;
     e.fi = ws.idx[e.s] < NT ? ws.idx[e.s] : 0;
-    e.a = ws.tgt[e.t][0] / e.Wc;
-    e.b = ws.tgt[e.fi][0] / e.Vc;
-    inverse<D>(&ws.tgt[e.fi][1 + D], e.inv);
+    e.a = T(ws.tgt[e.t][0]) / e.Wc;
+    e.b = T(ws.tgt[e.fi][0]) / e.Vc;
+    T icov[D * D], tcov[D * D];
 #pragma unroll
-    for (int k = 0; k < D; ++k) e.diff[k] = ws.tgt[e.t][1 + k] - ws.tgt[e.fi][1 + k];
-    float maha = 0.f;
+    for (int k = 0; k < D * D; ++k) { icov[k] = T(ws.tgt[e.fi][1 + D + k]); tcov[k] = T(ws.tgt[e.t][1 + D + k]); }
+    inverse<D, T>(icov, e.inv);
+#pragma unroll
+    for (int k = 0; k < D; ++k) e.diff[k] = T(ws.tgt[e.t][1 + k]) - T(ws.tgt[e.fi][1 + k]);
+    T maha = T(0);
 #pragma unroll
     for (int i = 0; i < D; ++i) {
-        float acc = 0.f;
+        T acc = T(0);
 #pragma unroll
         for (int j = 0; j < D; ++j) acc += e.inv[i * D + j] * e.diff[j];
         maha += e.diff[i] * acc;
     }
-    float tr = 0.f;
+    T tr = T(0);
 #pragma unroll
     for (int i = 0; i < D; ++i)
 #pragma unroll
-        for (int j = 0; j < D; ++j) tr += e.inv[i * D + j] * ws.tgt[e.t][1 + D + j * D + i];
-    e.val_a = sqrtf(det<D>(e.inv)) * gauss_norm_factor<D>() * expf(-0.5f * maha);
-    e.val_b = expf(-0.5f * tr);
+        for (int j = 0; j < D; ++j) tr += e.inv[i * D + j] * tcov[j * D + i];
+    e.val_a = g_sqrt(det<D, T>(e.inv)) * norm_factor_t<D, T>() * g_exp(T(-0.5) * maha);
+    e.val_b = g_exp(T(-0.5) * tr);
     e.ab = e.val_a * e.val_b;
-    e.lik = powf(clip(e.ab), 4.f * e.a);
-    const float lg = logf(det<D>(&ws.tgt[e.t][1 + D]) / det<D>(&ws.tgt[e.fi][1 + D]));
-    const float kl = sign_of(e.b) == sign_of(e.a) ? 0.5f * (maha + tr - float(D) - lg) : 0.f;
-    e.gate = kl < kKlThreshold ? 1.f : 0.f;
-    // per target: the component with the smallest KL is always gated in (first strict minimum)
+    e.lik = g_pow(clip(e.ab), T(4) * e.a);
     const int row_base = e.t * R;
-    {
+    if (gate_in == nullptr) {
+        const T lg = g_log(det<D, T>(tcov) / det<D, T>(icov));
+        const T kl = sign_of(e.b) == sign_of(e.a) ? T(0.5) * (maha + tr - T(D) - lg) : T(0);
+        e.gate = kl < T(kKlThreshold) ? T(1) : T(0);
+        // per target: the component with the smallest KL is always gated in (first strict minimum)
         int best = -1;
-        float smallest = INFINITY;
+        T smallest = T(INFINITY);
 #pragma unroll
         for (int s2 = 0; s2 < R; ++s2) {
-            const float v = __shfl_sync(0xffffffffu, kl, row_base + s2);
+            const T v = __shfl_sync(0xffffffffu, kl, row_base + s2);
             if (v < smallest) { smallest = v; best = s2; }
         }
-        if (best == e.s) e.gate = 1.f;
+        if (best == e.s) e.gate = T(1);
+    } else {
+        e.gate = T(*gate_in);
     }
     e.u = e.b * e.lik;
     e.x = clip(e.u) * e.gate;
-    float X = 0.f;
+    T X = T(0);
 #pragma unroll
     for (int s2 = 0; s2 < R; ++s2) X += __shfl_sync(0xffffffffu, e.x, row_base + s2);
     e.X = X;
     e.r1 = e.x / X;
     e.r2 = e.r1 * e.a;
-    float fw = 0.f;
+    T fw = T(0);
 #pragma unroll
     for (int t2 = 0; t2 < NT; ++t2) fw += __shfl_sync(0xffffffffu, e.r2, t2 * R + e.s);
     e.fw = fw; e.fwc = clip(fw);
@@ -395,49 +416,49 @@ __device__ void fit_em_warp(WarpScratch<D, R>& ws, int n_target, float* __restri
 }
 
 // ---- reverse of fit_em_warp: ws.tgt (padded targets), ws.idx and ws.gin (gradient of the R fitted Gaussians) in,
-//      ws.tgrad (gradient of the targets) out. The KL gate and the initial indices are constants; clip() passes the
-//      gradient only above its threshold; a covariance that was replaced by the identity passes none. ----
+//      ws.tgrad (gradient of the targets) out. The KL gate, the initial indices and every threshold decision (clip,
+//      covariance replaced by the identity) are the forward pass's fp32 ones; the values around them are recomputed
+//      and differentiated in double. ----
 template <int D, int R>
 __device__ void grad_em_warp(WarpScratch<D, R>& ws) {
+    using T = double;
+    constexpr int RF = 1 + D + D * D;
     constexpr int NT = 2 * R;
     constexpr int NE = NT * R;
     const int lane = threadIdx.x & 31;
 
-    const Entry<D> e = em_entry<D, R>(ws, lane);
-    if (lane < NE) {
-        ws.r3[e.t][e.s] = e.r3;
-        if (e.t == 0) ws.fw[e.s] = e.fw;
-    }
-    __syncwarp();
-    em_positions<D, R>(ws, lane);
-    __syncwarp();
+    const Entry<D, float> f = em_entry<D, R, float>(ws, lane);          // decisions as the forward pass took them
+    const float gate = f.gate;
+    const Entry<D, T> e = em_entry<D, R, T>(ws, lane, &gate);
 
-    const float* tg = ws.tgt[e.t];
-    const float gw = ws.gin[e.s][0];
-    float gP[D], gC[D * D];
+    T tg[RF];
 #pragma unroll
-    for (int i = 0; i < D; ++i) gP[i] = ws.gin[e.s][1 + i];
+    for (int k = 0; k < RF; ++k) tg[k] = T(ws.tgt[e.t][k]);
+    const T gw = T(ws.gin[e.s][0]);
+    T gP[D], gC[D * D];
 #pragma unroll
-    for (int ij = 0; ij < D * D; ++ij) gC[ij] = e.fw < kEpsLarge ? 0.f : ws.gin[e.s][1 + D + ij];
+    for (int i = 0; i < D; ++i) gP[i] = T(ws.gin[e.s][1 + i]);
+#pragma unroll
+    for (int ij = 0; ij < D * D; ++ij) gC[ij] = f.fw < kEpsLarge ? T(0) : T(ws.gin[e.s][1 + D + ij]);
 
     // ---- moment matching ----
-    float d[D];
+    T d[D];
 #pragma unroll
-    for (int i = 0; i < D; ++i) d[i] = tg[1 + i] - ws.outp[e.s][i];
-    float g_r3 = 0.f;
+    for (int i = 0; i < D; ++i) d[i] = tg[1 + i] - col_sum<R, T>(e.r3 * tg[1 + i]);      // mu_t - fitted centre s
+    T g_r3 = T(0);
 #pragma unroll
     for (int i = 0; i < D; ++i)
 #pragma unroll
         for (int j = 0; j < D; ++j) g_r3 += gC[i * D + j] * (d[i] * d[j] + tg[1 + D + i * D + j]);
-    float t_mu[D], t_cov[D * D];     // this entry's share of the target gradient
-    float gPt[D];
+    T t_mu[D], t_cov[D * D];     // this entry's share of the target gradient
+    T gPt[D];
 #pragma unroll
     for (int i = 0; i < D; ++i) {
-        float acc = 0.f;
+        T acc = T(0);
 #pragma unroll
         for (int j = 0; j < D; ++j) acc += (gC[i * D + j] + gC[j * D + i]) * d[j];
-        const float gd = e.r3 * acc;
-        gPt[i] = gP[i] - col_sum<R>(gd);
+        const T gd = e.r3 * acc;
+        gPt[i] = gP[i] - col_sum<R, T>(gd);
         t_mu[i] = gd + e.r3 * gPt[i];
     }
 #pragma unroll
@@ -446,51 +467,53 @@ __device__ void grad_em_warp(WarpScratch<D, R>& ws) {
     for (int ij = 0; ij < D * D; ++ij) t_cov[ij] = e.r3 * gC[ij];
 
     // ---- responsibilities ----
-    float gWc = 0.f;
+    T gWc = T(0);
 #pragma unroll
-    for (int s2 = 0; s2 < R; ++s2) gWc += ws.gin[s2][0] * ws.fw[s2];
-    float gF = gw * e.Wc;
-    const float gFc = col_sum<R>(-g_r3 * e.r2 / (e.fwc * e.fwc));
-    if (e.fw > kEpsSmall) gF += gFc;
-    const float g_r2 = g_r3 / e.fwc + gF;
-    const float g_r1 = g_r2 * e.a;
-    float g_a = g_r2 * e.r1;
-    float g_x = g_r1 / e.X;
-    g_x += row_sum<R>(-g_r1 * e.x / (e.X * e.X));
-    const float g_u = e.u > kEpsSmall ? g_x * e.gate : 0.f;
-    const float g_b = col_sum<R>(g_u * e.lik);
-    const float g_L = g_u * e.b;
+    for (int s2 = 0; s2 < R; ++s2) gWc += T(ws.gin[s2][0]) * __shfl_sync(0xffffffffu, e.fw, s2);   // lane s2 = entry (0, s2)
+    T gF = gw * e.Wc;
+    const T gFc = col_sum<R, T>(-g_r3 * e.r2 / (e.fwc * e.fwc));
+    if (f.fw > kEpsSmall) gF += gFc;
+    const T g_r2 = g_r3 / e.fwc + gF;
+    const T g_r1 = g_r2 * e.a;
+    T g_a = g_r2 * e.r1;
+    T g_x = g_r1 / e.X;
+    g_x += row_sum<R, T>(-g_r1 * e.x / (e.X * e.X));
+    const T g_u = f.u > kEpsSmall ? g_x * e.gate : T(0);
+    const T g_b = col_sum<R, T>(g_u * e.lik);
+    const T g_L = g_u * e.b;
 
     // ---- likelihood: L = clip(a b)^(4 a_t) ----
-    const float abc = clip(e.ab), wbar = 4.f * e.a;
-    const float g_abc = g_L * wbar * powf(abc, wbar - 1.f);
-    g_a += 4.f * (g_L * e.lik * logf(abc));
-    const float g_ab = e.ab > kEpsSmall ? g_abc : 0.f;
-    const float c1 = e.val_a * (g_ab * e.val_b);         // val_a * dL/dval_a
-    const float gh = (g_ab * e.val_a) * e.val_b;         // dL/dh, val_b = exp(h), h = -1/2 tr(inv Sigma_t)
-    float i_mu[D], gS[D * D];                            // gradient of the initial centre / of inv
+    const T abc = clip(e.ab), wbar = T(4) * e.a;
+    const T g_abc = g_L * wbar * g_pow(abc, wbar - T(1));
+    g_a += T(4) * (g_L * e.lik * g_log(abc));
+    const T g_ab = f.ab > kEpsSmall ? g_abc : T(0);
+    const T c1 = e.val_a * (g_ab * e.val_b);             // val_a * dL/dval_a
+    const T gh = (g_ab * e.val_a) * e.val_b;             // dL/dh, val_b = exp(h), h = -1/2 tr(inv Sigma_t)
+    T i_mu[D], gS[D * D];                                // gradient of the initial centre / of inv
 #pragma unroll
     for (int i = 0; i < D; ++i) {
-        float st = 0.f;
+        T st = T(0);
 #pragma unroll
         for (int j = 0; j < D; ++j) st += e.inv[i * D + j] * e.diff[j];
         t_mu[i] -= c1 * st;
         i_mu[i] = c1 * st;
     }
-    const float* ic = &ws.tgt[e.fi][1 + D];
+    T ic[D * D];
+#pragma unroll
+    for (int k = 0; k < D * D; ++k) ic[k] = T(ws.tgt[e.fi][1 + D + k]);
 #pragma unroll
     for (int i = 0; i < D; ++i)
 #pragma unroll
         for (int j = 0; j < D; ++j) {
-            t_cov[i * D + j] += -0.5f * gh * e.inv[j * D + i];
-            gS[i * D + j] = c1 * (0.5f * ic[j * D + i] - 0.5f * e.diff[i] * e.diff[j]) - 0.5f * gh * tg[1 + D + j * D + i];
+            t_cov[i * D + j] += T(-0.5) * gh * e.inv[j * D + i];
+            gS[i * D + j] = c1 * (T(0.5) * ic[j * D + i] - T(0.5) * e.diff[i] * e.diff[j]) - T(0.5) * gh * tg[1 + D + j * D + i];
         }
-    float i_cov[D * D];                                  // d/d Sigma_initial = -inv^T gS inv^T
+    T i_cov[D * D];                                      // d/d Sigma_initial = -inv^T gS inv^T
 #pragma unroll
     for (int i = 0; i < D; ++i)
 #pragma unroll
         for (int j = 0; j < D; ++j) {
-            float acc = 0.f;
+            T acc = T(0);
 #pragma unroll
             for (int k = 0; k < D; ++k)
 #pragma unroll
@@ -499,30 +522,30 @@ __device__ void grad_em_warp(WarpScratch<D, R>& ws) {
         }
 
     // ---- fold over rows (targets) and columns (initial Gaussians) ----
-    g_a = row_sum<R>(g_a);
+    g_a = row_sum<R, T>(g_a);
 #pragma unroll
-    for (int i = 0; i < D; ++i) { t_mu[i] = row_sum<R>(t_mu[i]); i_mu[i] = col_sum<R>(i_mu[i]); }
+    for (int i = 0; i < D; ++i) { t_mu[i] = row_sum<R, T>(t_mu[i]); i_mu[i] = col_sum<R, T>(i_mu[i]); }
 #pragma unroll
-    for (int ij = 0; ij < D * D; ++ij) { t_cov[ij] = row_sum<R>(t_cov[ij]); i_cov[ij] = col_sum<R>(i_cov[ij]); }
+    for (int ij = 0; ij < D * D; ++ij) { t_cov[ij] = row_sum<R, T>(t_cov[ij]); i_cov[ij] = col_sum<R, T>(i_cov[ij]); }
     // integrals: a_t = w_t / Wc, b_s = v_s / Vc
-    gWc += col_sum<R>(-g_a * tg[0] / (e.Wc * e.Wc));
-    const float gW = e.W > kEpsSmall ? gWc : 0.f;
-    const float gVc = row_sum<R>(-g_b * ws.tgt[e.fi][0] / (e.Vc * e.Vc));
-    const float g_v = g_b / e.Vc + (e.V > kEpsSmall ? gVc : 0.f);
+    gWc += col_sum<R, T>(-g_a * tg[0] / (e.Wc * e.Wc));
+    const T gW = f.W > kEpsSmall ? gWc : T(0);
+    const T gVc = row_sum<R, T>(-g_b * T(ws.tgt[e.fi][0]) / (e.Vc * e.Vc));
+    const T g_v = g_b / e.Vc + (f.V > kEpsSmall ? gVc : T(0));
     if (lane < NE && e.s == 0) {
-        ws.tgrad[e.t][0] = g_a / e.Wc + gW;
+        ws.tgrad[e.t][0] = float(g_a / e.Wc + gW);
 #pragma unroll
-        for (int i = 0; i < D; ++i) ws.tgrad[e.t][1 + i] = t_mu[i];
+        for (int i = 0; i < D; ++i) ws.tgrad[e.t][1 + i] = float(t_mu[i]);
 #pragma unroll
-        for (int ij = 0; ij < D * D; ++ij) ws.tgrad[e.t][1 + D + ij] = t_cov[ij];
+        for (int ij = 0; ij < D * D; ++ij) ws.tgrad[e.t][1 + D + ij] = float(t_cov[ij]);
     }
     __syncwarp();
     if (lane < NE && e.t == 0) {      // the initial Gaussians are targets e.fi (distinct per s)
-        ws.tgrad[e.fi][0] += g_v;
+        ws.tgrad[e.fi][0] += float(g_v);
 #pragma unroll
-        for (int i = 0; i < D; ++i) ws.tgrad[e.fi][1 + i] += i_mu[i];
+        for (int i = 0; i < D; ++i) ws.tgrad[e.fi][1 + i] += float(i_mu[i]);
 #pragma unroll
-        for (int ij = 0; ij < D * D; ++ij) ws.tgrad[e.fi][1 + D + ij] += i_cov[ij];
+        for (int ij = 0; ij < D * D; ++ij) ws.tgrad[e.fi][1 + D + ij] += float(i_cov[ij]);
     }
     __syncwarp();
 }
