@@ -22,6 +22,26 @@ constexpr int kThreads = 128;
 constexpr int kChunk = 1024;
 constexpr float kExpScale = -0.5f * kLog2e;
 
+// Optional transforms of the layer the fit sits in, applied on load / on store (none: {1.f, nullptr, 1}):
+//   input weights are divided by weight_divisor (the network divides a convolution's output by its input channels);
+//   output centres are multiplied by f and output covariances by f * f, f = spatial_scale[mixture % n_channels]
+//   (the covariance-scale normalisation that follows the fit in evaluation mode).
+struct LayerTransform {
+    float weight_divisor;
+    const float* spatial_scale;
+    int n_channels;
+};
+
+template <int D>
+__device__ __forceinline__ void store_geometry(float* dst, const float* __restrict__ src, float f) {
+    constexpr int RF = 1 + D + D * D;
+    const float ff = f * f;
+#pragma unroll
+    for (int k = 1; k <= D; ++k) dst[k] = __ldg(src + k) * f;
+#pragma unroll
+    for (int k = 1 + D; k < RF; ++k) dst[k] = ff * __ldg(src + k);
+}
+
 template <int D>
 struct Ready {
     static constexpr int kFloats = D + D * (D + 1) / 2 + 3;    // -mu | A | norm, w, x0: 8 (2D) or 12 (3D) floats
@@ -36,9 +56,10 @@ __host__ __device__ inline int stage_stride_floats(int floats) {
 }
 
 template <int D>
-__device__ __forceinline__ void make_ready(const float* r, float constant, float relu_constant, float* out) {
+__device__ __forceinline__ void make_ready(const float* r, float constant, float relu_constant, float weight_divisor,
+                                           float* out) {
     constexpr int NS = D * (D + 1) / 2;
-    const float w = r[0];
+    const float w = r[0] / weight_divisor;
 #pragma unroll
     for (int d = 0; d < D; ++d) out[d] = -r[1 + d];
     const float* C = r + 1 + D;
@@ -73,7 +94,8 @@ template <int D>
 __global__ void __launch_bounds__(kThreads)
 relu_fixed_point_kernel(const float* __restrict__ mixtures, const float* __restrict__ constants,
                         float* __restrict__ out_mixtures, float* __restrict__ out_constants,
-                        float* __restrict__ out_initial, long long n_mixtures, int G, int mixtures_per_cta) {
+                        float* __restrict__ out_initial, long long n_mixtures, int G, int mixtures_per_cta,
+                        LayerTransform tf) {
     constexpr int RF = 1 + D + D * D;
     constexpr int NS = D * (D + 1) / 2;
     constexpr int RD = Ready<D>::kFloats;
@@ -83,8 +105,9 @@ relu_fixed_point_kernel(const float* __restrict__ mixtures, const float* __restr
     const int local = mixtures_per_cta > 1 ? tid / G : 0;            // which of the CTA's mixtures
     const long long mix = first + local;
     const bool mixture_ok = local < mixtures_per_cta && mix < n_mixtures;
-    const float constant = mixture_ok ? __ldg(constants + mix) : 0.f;
+    const float constant = (mixture_ok && constants != nullptr) ? __ldg(constants + mix) : 0.f;
     const float relu_constant = fmaxf(constant, 0.f);
+    const float out_scale = (mixture_ok && tf.spatial_scale != nullptr) ? __ldg(tf.spatial_scale + mix % tf.n_channels) : 1.f;
     const float* src = mixtures + mix * (long long)G * RF;
     const int stage_stride = stage_stride_floats(min(G, kChunk) * RD);
     const bool single_chunk = G <= kChunk;
@@ -107,14 +130,14 @@ relu_fixed_point_kernel(const float* __restrict__ mixtures, const float* __restr
                     float r[RF];
 #pragma unroll
                     for (int f = 0; f < RF; ++f) r[f] = __ldg(src + (size_t)(j0 + row0) * RF + f);
-                    make_ready<D>(r, constant, relu_constant, ready + local * stage_stride + row0 * RD);
+                    make_ready<D>(r, constant, relu_constant, tf.weight_divisor, ready + local * stage_stride + row0 * RD);
                 }
             } else {
                 for (int j = tid; j < jc; j += kThreads) {
                     float r[RF];
 #pragma unroll
                     for (int f = 0; f < RF; ++f) r[f] = __ldg(src + (size_t)(j0 + j) * RF + f);
-                    make_ready<D>(r, constant, relu_constant, ready + j * RD);
+                    make_ready<D>(r, constant, relu_constant, tf.weight_divisor, ready + j * RD);
                 }
             }
             __syncthreads();
@@ -144,15 +167,19 @@ relu_fixed_point_kernel(const float* __restrict__ mixtures, const float* __restr
             }
         }
         if (row_ok) {
-            const float w = __ldg(src + (size_t)i * RF);
+            const float w = __ldg(src + (size_t)i * RF) / tf.weight_divisor;
             const float initial = (w + constant > 0.f) ? w : -relu_constant;
             const float x0 = fabsf(initial) + 0.1f;
             const float b = fmaxf(sum_w + constant, 0.f) - relu_constant;
             const float x = x0 * (b + 0.05f) / (sum_x + 0.05f);
             float* dst = out_mixtures + (mix * (long long)G + i) * RF;
             dst[0] = x;
+            if (tf.spatial_scale != nullptr) {
+                store_geometry<D>(dst, src + (size_t)i * RF, out_scale);
+            } else {
 #pragma unroll
-            for (int f = 1; f < RF; ++f) dst[f] = __ldg(src + (size_t)i * RF + f);
+                for (int f = 1; f < RF; ++f) dst[f] = __ldg(src + (size_t)i * RF + f);
+            }
             if (out_initial) {
                 float* ini = out_initial + (mix * (long long)G + i) * RF;
                 ini[0] = initial;
@@ -186,7 +213,7 @@ template <int D, int P>
 __global__ void __launch_bounds__(kThreads)
 relu_fixed_point_large_kernel(const float* __restrict__ mixtures, const float* __restrict__ constants,
                               float* __restrict__ out_mixtures, float* __restrict__ out_constants,
-                              float* __restrict__ out_initial, int G) {
+                              float* __restrict__ out_initial, int G, LayerTransform tf) {
     constexpr int RF = 1 + D + D * D;
     constexpr int NS = D * (D + 1) / 2;
     constexpr int RD = Ready<D>::kFloats;
@@ -195,8 +222,9 @@ relu_fixed_point_large_kernel(const float* __restrict__ mixtures, const float* _
     extern __shared__ __align__(16) float ready[];    // [kChunk / 2][PF]
     const int tid = threadIdx.x;
     const long long mix = blockIdx.x;
-    const float constant = __ldg(constants + mix);
+    const float constant = constants != nullptr ? __ldg(constants + mix) : 0.f;
     const float relu_constant = fmaxf(constant, 0.f);
+    const float out_scale = tf.spatial_scale != nullptr ? __ldg(tf.spatial_scale + mix % tf.n_channels) : 1.f;
     const float* src = mixtures + mix * (long long)G * RF;
     const bool single_chunk = G <= kChunk;
 
@@ -224,7 +252,7 @@ relu_fixed_point_large_kernel(const float* __restrict__ mixtures, const float* _
                         float r[RF];
 #pragma unroll
                         for (int f = 0; f < RF; ++f) r[f] = __ldg(src + (size_t)(j0 + j) * RF + f);
-                        make_ready<D>(r, constant, relu_constant, rdy);
+                        make_ready<D>(r, constant, relu_constant, tf.weight_divisor, rdy);
                     } else {
 #pragma unroll
                         for (int f = 0; f < RD; ++f) rdy[f] = 0.f;      // padding Gaussian: both weights 0
@@ -287,14 +315,18 @@ relu_fixed_point_large_kernel(const float* __restrict__ mixtures, const float* _
         for (int p = 0; p < P; ++p) {
             const int i = base + tid + p * kThreads;
             if (i >= G) continue;
-            const float w = __ldg(src + (size_t)i * RF);
+            const float w = __ldg(src + (size_t)i * RF) / tf.weight_divisor;
             const float initial = (w + constant > 0.f) ? w : -relu_constant;
             const float x0 = fabsf(initial) + 0.1f;
             const float b = fmaxf(sum_w[p].x + sum_w[p].y + constant, 0.f) - relu_constant;
             float* dst = out_mixtures + (mix * (long long)G + i) * RF;
             dst[0] = x0 * (b + 0.05f) / (sum_x[p].x + sum_x[p].y + 0.05f);
+            if (tf.spatial_scale != nullptr) {
+                store_geometry<D>(dst, src + (size_t)i * RF, out_scale);
+            } else {
 #pragma unroll
-            for (int f = 1; f < RF; ++f) dst[f] = __ldg(src + (size_t)i * RF + f);
+                for (int f = 1; f < RF; ++f) dst[f] = __ldg(src + (size_t)i * RF + f);
+            }
             if (out_initial) {
                 float* ini = out_initial + (mix * (long long)G + i) * RF;
                 ini[0] = initial;
@@ -308,14 +340,14 @@ relu_fixed_point_large_kernel(const float* __restrict__ mixtures, const float* _
 
 template <int D>
 int launch_relu_fixed_point(const float* mixtures, const float* constants, float* out_mixtures, float* out_constants,
-                            float* out_initial, long long n_mixtures, int G, cudaStream_t st) {
+                            float* out_initial, long long n_mixtures, int G, LayerTransform tf, cudaStream_t st) {
     if (G >= kLargeMin) {
         if (n_mixtures > 0x7fffffffLL) return GMC_ERR_BAD_DIMS;
         const int staged_pairs = (min(G, kChunk) + 1) / 2;
         const size_t smem = sizeof(float) * size_t(staged_pairs) * ReadyLarge<D>::kPairFloats;
         auto kernel = relu_fixed_point_large_kernel<D, kLargePoints>;
         if (smem > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-        kernel<<<unsigned(n_mixtures), kThreads, smem, st>>>(mixtures, constants, out_mixtures, out_constants, out_initial, G);
+        kernel<<<unsigned(n_mixtures), kThreads, smem, st>>>(mixtures, constants, out_mixtures, out_constants, out_initial, G, tf);
         GMC_LAUNCH_CHECK();
         return GMC_OK;
     }
@@ -326,7 +358,7 @@ int launch_relu_fixed_point(const float* mixtures, const float* constants, float
     auto kernel = relu_fixed_point_kernel<D>;
     if (smem > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
     kernel<<<unsigned(blocks), kThreads, smem, st>>>(mixtures, constants, out_mixtures, out_constants, out_initial,
-                                                    n_mixtures, G, per_cta);
+                                                    n_mixtures, G, per_cta, tf);
     GMC_LAUNCH_CHECK();
     return GMC_OK;
 }
@@ -336,18 +368,29 @@ int launch_relu_fixed_point(const float* mixtures, const float* constants, float
 
 GMC_DEFINE_TU_CHECK_READER(relu_fixed_point)
 
-extern "C" int gmc_relu_fixed_point(const float* mixtures, const float* constants, float* out_mixtures,
-                                    float* out_constants, float* out_initial, long long n_mixtures, int n_components,
-                                    int n_dims, void* stream) {
+extern "C" int gmc_relu_fixed_point_layer(const float* mixtures, const float* constants, float* out_mixtures,
+                                          float* out_constants, float* out_initial, long long n_mixtures,
+                                          int n_components, int n_dims, float weight_divisor,
+                                          const float* spatial_scale, int n_channels, void* stream) {
     using namespace gmc;
     if (n_dims != 2 && n_dims != 3) return GMC_ERR_BAD_DIMS;
     if (n_mixtures < 0 || n_components <= 0) return GMC_ERR_BAD_DIMS;
+    if (!(weight_divisor != 0.f)) return GMC_ERR_UNSUPPORTED;
+    if (spatial_scale != nullptr && n_channels <= 0) return GMC_ERR_BAD_DIMS;
     if (n_mixtures == 0) return GMC_OK;
-    if (!mixtures || !constants || !out_mixtures || !out_constants) return GMC_ERR_NULL_POINTER;
+    if (!mixtures || !out_mixtures || !out_constants) return GMC_ERR_NULL_POINTER;
     cudaStream_t st = as_stream(stream);
+    const LayerTransform tf{weight_divisor, spatial_scale, spatial_scale ? n_channels : 1};
     return n_dims == 2 ? launch_relu_fixed_point<2>(mixtures, constants, out_mixtures, out_constants, out_initial,
-                                                    n_mixtures, n_components, st)
+                                                    n_mixtures, n_components, tf, st)
                        : launch_relu_fixed_point<3>(mixtures, constants, out_mixtures, out_constants, out_initial,
-                                                    n_mixtures, n_components, st);
+                                                    n_mixtures, n_components, tf, st);
 }
 
+extern "C" int gmc_relu_fixed_point(const float* mixtures, const float* constants, float* out_mixtures,
+                                    float* out_constants, float* out_initial, long long n_mixtures, int n_components,
+                                    int n_dims, void* stream) {
+    if (n_mixtures > 0 && !constants) return GMC_ERR_NULL_POINTER;
+    return gmc_relu_fixed_point_layer(mixtures, constants, out_mixtures, out_constants, out_initial, n_mixtures,
+                                      n_components, n_dims, 1.f, nullptr, 1, stream);
+}

@@ -47,6 +47,8 @@ _declare("gmc_sync_and_check", [_c_void_p])
 _declare("gmc_eval_inversed_host", [_c_float_p] * 6 + [_c_int] * 8)
 _declare("gmc_host_pipeline_release", [])
 _declare("gmc_relu_fixed_point", [_c_float_p] * 5 + [ctypes.c_longlong, _c_int, _c_int, _c_void_p])
+_declare("gmc_relu_fixed_point_layer", [_c_float_p] * 5 + [ctypes.c_longlong, _c_int, _c_int, ctypes.c_float, _c_float_p,
+                                        _c_int, _c_void_p])
 _declare("gmc_matrix_inverse", [_c_float_p] * 2 + [ctypes.c_longlong, _c_int, _c_void_p])
 _declare("gmc_matrix_inverse_backward", [_c_float_p] * 3 + [ctypes.c_longlong, _c_int, _c_void_p])
 _declare("gmc_lbvh_build", [_c_float_p, ctypes.c_longlong, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p])

@@ -114,6 +114,35 @@ def fused_relu_fixed_point(mixture: Tensor, constant: Tensor) -> typing.Tuple[Te
     return initial, fp, ret_const
 
 
+def fused_relu_layer(mixture: Tensor, constant: typing.Optional[Tensor], weight_divisor: float = 1.0,
+                     channel_scale: typing.Optional[Tensor] = None) -> typing.Tuple[Tensor, Tensor]:
+    """The middle of a network layer in evaluation mode, one kernel (gmc_relu_fixed_point_layer):
+    (mixture with weights / weight_divisor, constant or zero) -> ReLU fixed-point fit -> centres * f and covariances * f^2
+    with f = channel_scale[layer] -> (mixture, constant). No gradient is recorded."""
+    from gmc import _native
+    m = mixture.detach().contiguous()
+    _native.require_cuda_f32(m, "mixture")
+    c = None
+    if constant is not None:
+        c = constant.detach().contiguous()
+        _native.require_cuda_f32(c, "constant")
+    f = None
+    if channel_scale is not None:
+        f = channel_scale.detach().contiguous()
+        _native.require_cuda_f32(f, "channel_scale")
+        if f.numel() != gm.n_layers(m):
+            raise RuntimeError("channel_scale needs one factor per layer")
+    out = torch.empty_like(m)
+    ret_const = torch.empty((gm.n_batch(m), gm.n_layers(m)), dtype=torch.float32, device=m.device)
+    if m.numel() > 0:
+        with torch.cuda.device_of(m):
+            _native.check(_native.lib.gmc_relu_fixed_point_layer(
+                _native.ptr(m), _native.ptr(c), _native.ptr(out), _native.ptr(ret_const), _native.ptr(None),
+                gm.n_batch(m) * gm.n_layers(m), gm.n_components(m), gm.n_dimensions(m), float(weight_divisor),
+                _native.ptr(f), gm.n_layers(m), _native.stream_of(m)), "relu fixed point (layer)")
+    return out, ret_const
+
+
 def _fixed_point_stage(mixture, constant, log, target=None):
     needs_grad = torch.is_grad_enabled() and (mixture.requires_grad or constant.requires_grad)
     if (target is None and not needs_grad and mixture.is_cuda and mixture.dtype == torch.float32

@@ -183,18 +183,28 @@ class CovScaleNorm(torch.nn.modules.Module):
         self.batch_norm = batch_norm
         self.register_buffer("averaged_cov_trace", torch.ones(n_layers))
 
+    def inference_scale(self, n_dims: int) -> Tensor:
+        """Per-channel factor of the batch variant in evaluation mode, sqrt(n_dims / averaged_cov_trace): the value
+        forward() multiplies centres with (covariances get its square). Cached until the buffer changes."""
+        key = (self.averaged_cov_trace.data_ptr(), self.averaged_cov_trace._version, n_dims)
+        cached = getattr(self, "_scale_cache", None)
+        if cached is None or cached[0] != key:
+            cached = (key, torch.sqrt(n_dims / self.averaged_cov_trace.detach()).contiguous())
+            self._scale_cache = cached
+        return cached[1]
+
     def forward(self, x: typing.Tuple[Tensor, typing.Optional[Tensor]]) -> typing.Tuple[Tensor, Tensor]:
         x_gm, x_constant = x
-        traces = mat_tools.trace(gm.covariances(x_gm))
         n_batch = gm.n_batch(x_gm)
         if self.batch_norm:
             if self.training:
+                traces = mat_tools.trace(gm.covariances(x_gm))
                 alpha = min(n_batch / 1000, 0.2)
                 self.averaged_cov_trace = ((1.0 - alpha) * self.averaged_cov_trace + alpha * traces.mean(dim=(0, 2))).detach()
             n_batch = 1
             avg_trace = self.averaged_cov_trace.detach()
         else:
-            avg_trace = traces.mean(dim=2)
+            avg_trace = mat_tools.trace(gm.covariances(x_gm)).mean(dim=2)
         factor = torch.sqrt(gm.n_dimensions(x_gm) / avg_trace).view(n_batch, gm.n_layers(x_gm), 1)
         y_gm = gm.spatial_scale(x_gm, factor)
         if x_constant is None:

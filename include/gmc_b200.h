@@ -114,6 +114,15 @@ int gmc_host_pipeline_release(void);
  * ---------------------------------------------------------------------------------------------- */
 int gmc_relu_fixed_point(const float* mixtures, const float* constants, float* out_mixtures, float* out_constants,
                          float* out_initial, long long n_mixtures, int n_components, int n_dims, void* stream);
+/* The same step with the two element-wise stages that surround it in a network layer folded in (evaluation mode):
+ *   input weights are divided by weight_divisor first
+ *       (src/gmc/model.py:189-190: a convolution's output is divided by its number of input channels);
+ *   output centres are multiplied by f and output covariances by f * f, f = spatial_scale[mixture % n_channels]
+ *       (src/gmc/modules.py:313-351, CovScaleNorm in evaluation mode: f = sqrt(D / averaged_cov_trace) per channel).
+ * constants == NULL means all zero; spatial_scale == NULL means no scaling. weight_divisor must not be 0. */
+int gmc_relu_fixed_point_layer(const float* mixtures, const float* constants, float* out_mixtures, float* out_constants,
+                               float* out_initial, long long n_mixtures, int n_components, int n_dims,
+                               float weight_divisor, const float* spatial_scale, int n_channels, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Batched inverse of n_matrices contiguous row-major DxD matrices (D in {2,3}); `inverses` holds the

@@ -388,3 +388,34 @@ def test_convolution_kernel_cache_follows_the_parameters():
     conv.train()
     with torch.no_grad():
         assert conv.kernels() is not conv.kernels()
+
+
+@pytest.mark.parametrize("D", [2, 3])
+def test_fused_inference_layers_equal_the_module_path(D):
+    """Net.features in evaluation mode runs each layer as convolution fit + one fused kernel (weights / n_in, ReLU
+    fixed-point fit, covariance-scale normalisation); it must return what the module-by-module path returns, also with
+    normalisation buffers that are not all one."""
+    import gmc.model as model
+    cfg = model.Config(n_dims=D)
+    cfg.layers = [model.Layer(6, 1, 12, 12), model.Layer(5, 1, 8, 8), model.Layer(7, 1, 4, 4)]
+    torch.manual_seed(3)
+    net = model.Net(config=cfg).cuda().eval()
+    for i, norm in enumerate(net.norms):
+        norm.averaged_cov_trace.copy_(torch.rand_like(norm.averaged_cov_trace) + 0.5 + i)
+    g = torch.Generator().manual_seed(5)
+    cov, _ = synthetic.covariances_and_inverses((3, 1, 20), D, 0.05, 0.3, g)
+    x = synthetic.pack(torch.rand(3, 1, 20, generator=g) + 0.2, torch.rand(3, 1, 20, D, generator=g) * 2 - 1, cov).cuda()
+    torch.manual_seed(11)       # the input normalisation draws sample points
+    with torch.no_grad():
+        assert net._fused_inference_layers(x)
+        fused = net.features(x)
+    net._fused_inference_layers = lambda t: False
+    torch.manual_seed(11)
+    with torch.no_grad():
+        plain = net.features(x)
+    assert torch.isfinite(fused).all()
+    assert rel_inf(fused.cpu().numpy(), plain.cpu().numpy()) <= 1e-6
+    # with autograd on, the general path is taken
+    del net._fused_inference_layers
+    xg = x.clone().requires_grad_(True)
+    assert not net._fused_inference_layers(xg) or not torch.is_grad_enabled()

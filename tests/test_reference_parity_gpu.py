@@ -133,8 +133,13 @@ def test_network_forward_layer_by_layer_against_the_reference_network():
     for i in range(4):
         net.norms[i].register_forward_hook(lambda mod, inp, out: acts.append(out[0].detach()))
         net.gmcs[i].register_forward_hook(lambda mod, inp, out: convs.append(out[0].detach()))
+    x_in = torch.from_numpy(golden["input"]).cuda()
     with torch.no_grad():
-        feats = net.features(torch.from_numpy(golden["input"]).cuda())
+        fused = net.features(x_in)                       # per layer: convolution fit + one fused kernel
+        assert not acts, "the fused inference path does not call the layer modules"
+        net._fused_inference_layers = lambda x: False    # module by module, so that the hooks see every layer
+        feats = net.features(x_in)
+    assert rel_inf(fused.cpu().numpy(), feats.cpu().numpy()) <= 1e-6
     for i in range(4):
         for what, got, ref in (("conv", convs[i], golden[f"conv{i}"]), ("layer", acts[i], golden[f"layer{i}"])):
             got = got.cpu().numpy()
