@@ -37,12 +37,17 @@ def _headers_mtime():
     return newest
 
 
-def _compile(src, verbose):
-    obj = os.path.join(BUILD_DIR, src[:-3] + ".o")
+CHECKED_LIB_PATH = os.path.join(OUT_DIR, "libgmc_b200_checked.so")
+
+
+def _compile(src, verbose, bounds_check=False):
+    obj = os.path.join(BUILD_DIR + ("_checked" if bounds_check else ""), src[:-3] + ".o")
     src_path = os.path.join(CSRC, src)
     if os.path.exists(obj) and os.path.getmtime(obj) >= max(os.path.getmtime(src_path), _headers_mtime()):
         return obj
     flags = list(COMMON_FLAGS)
+    if bounds_check:
+        flags += ["-DGMC_BOUNDS_CHECK"]
     if src in IEEE_FILES:
         flags += ["--fmad=false"]
     else:
@@ -58,19 +63,22 @@ def _compile(src, verbose):
     return obj
 
 
-def build(verbose: bool = False) -> str:
+def build(verbose: bool = False, bounds_check: bool = False) -> str:
+    """bounds_check=True builds libgmc_b200_checked.so instead: the same sources with -DGMC_BOUNDS_CHECK (indices read from
+    data are range-checked on the device; used by the tests in place of a memory checker)."""
+    lib_path = CHECKED_LIB_PATH if bounds_check else LIB_PATH
     os.makedirs(OUT_DIR, exist_ok=True)
-    os.makedirs(BUILD_DIR, exist_ok=True)
+    os.makedirs(BUILD_DIR + ("_checked" if bounds_check else ""), exist_ok=True)
     srcs = _sources()
     with concurrent.futures.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as pool:
-        objs = list(pool.map(lambda s: _compile(s, verbose), srcs))
-    if (not os.path.exists(LIB_PATH)) or any(os.path.getmtime(o) > os.path.getmtime(LIB_PATH) for o in objs):
-        cmd = [NVCC] + ARCH_FLAGS + ["-shared", "-o", LIB_PATH] + objs + ["-lcudart"]
+        objs = list(pool.map(lambda s: _compile(s, verbose, bounds_check), srcs))
+    if (not os.path.exists(lib_path)) or any(os.path.getmtime(o) > os.path.getmtime(lib_path) for o in objs):
+        cmd = [NVCC] + ARCH_FLAGS + ["-shared", "-o", lib_path] + objs + ["-lcudart"]
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
-    return LIB_PATH
+    return lib_path
 
 
 if __name__ == "__main__":
-    print(build(verbose="-v" in sys.argv))
+    print(build(verbose="-v" in sys.argv, bounds_check="--checked" in sys.argv))

@@ -232,7 +232,7 @@ convolution_fitting_tree_kernel(const float* __restrict__ data, const float* __r
         float m = 0.f;
         if (leaf < T) {
             int gi, ci, ki;
-            product_parts(nodesobjs[leaf], gi, ci, ki);
+            product_parts(GMC_IDX(nodesobjs[leaf], T), gi, ci, ki);
             m = __fmul_rn(__ldg(data_b + (size_t(ci) * G + gi) * RF), __ldg(kernels_o + (size_t(ci) * Gk + ki) * RF));
         }
         arrive(leaf < T, uint32_t(n_internal + leaf), leaf, leaf, m, queues, &queue_count[1]);
@@ -357,6 +357,7 @@ __device__ __forceinline__ void aggregate_output(const float* data_b, const floa
     }
     auto records = [&](int t, float* dg, float* kg) {
         int ki, rem, ci, gi;
+        t = GMC_IDX(t, by_gc.d * Gk);              // product index below Cin * G * Gk
         by_gc.split(t, ki, rem);
         by_g.split(rem, ci, gi);
         load_gaussian<D, STAGED>(data_b, ci * G + gi, dg);
@@ -622,7 +623,7 @@ convolution_fitting_backward_kernel(const float* __restrict__ grad, const float*
     for (int k = warp; k < K; k += kWarps) {
         const int start = subtrees[2 * k], end = subtrees[2 * k + 1];
         if (start < 0) continue;
-        for (int j = start - n_internal + lane; j < end - n_internal; j += 32) slot_of[nodesobjs[j]] = uint16_t(k);
+        for (int j = start - n_internal + lane; j < end - n_internal; j += 32) slot_of[GMC_IDX(nodesobjs[GMC_IDX(j, T)], T)] = uint16_t(k);
     }
     __syncthreads();
 

@@ -23,6 +23,10 @@ int lbvh_build_launch(const float* mixture, long long n_mixtures, int n_componen
 
 namespace {
 
+// Child and object indices read from the node array (checked in GMC_BOUNDS_CHECK builds, see common.cuh)
+#define GMC_NODE(i, n_internal) GMC_IDX(int(i), 2 * (n_internal) + 1)
+#define GMC_OBJ(i, n_internal) GMC_IDX(int(i), (n_internal) + 1)
+
 #ifndef GMC_FIT_THREADS
 #define GMC_FIT_THREADS 256
 #endif
@@ -570,7 +574,7 @@ __device__ __forceinline__ void compute_levels(const uint16_t* __restrict__ node
             __threadfence_block();
             if (atomicAdd(&arrive[parent], 1) == 0) break;
             __threadfence_block();
-            const int l = nodes[size_t(parent) * 4 + 1], r = nodes[size_t(parent) * 4 + 2];
+            const int l = GMC_NODE(nodes[size_t(parent) * 4 + 1], n_internal), r = GMC_NODE(nodes[size_t(parent) * 4 + 2], n_internal);
             const int lv = 1 + max(int(((volatile unsigned char*)level)[l]), int(((volatile unsigned char*)level)[r]));
             ((volatile unsigned char*)level)[parent] = (unsigned char)lv;
             atomicMax(max_level, lv);
@@ -613,14 +617,14 @@ __device__ __forceinline__ int gather_children(WarpScratch<D, R>& ws, const floa
                                                int& child_slot, bool& in_range, bool& valid, int& pos) {
     constexpr int RF = 1 + D + D * D;
     constexpr int AF = Attr<D, R>::kFloats;
-    const int l = nodes[size_t(id) * 4 + 1], r = nodes[size_t(id) * 4 + 2];
+    const int l = GMC_NODE(nodes[size_t(id) * 4 + 1], n_internal), r = GMC_NODE(nodes[size_t(id) * 4 + 2], n_internal);
     auto count_of = [&](int n) -> int { return n >= n_internal ? 1 : __float_as_int(attrs[size_t(n) * AF + R * RF + 1]); };
     const int cl = count_of(l), cr = count_of(r);
     child = lane < R ? l : r;
     child_slot = lane < R ? lane : lane - R;
     in_range = lane < 2 * R && child_slot < (lane < R ? cl : cr);
     const float* src = nullptr;
-    if (in_range) src = child >= n_internal ? mix + size_t(nodes[size_t(child) * 4 + 3]) * RF
+    if (in_range) src = child >= n_internal ? mix + size_t(GMC_OBJ(nodes[size_t(child) * 4 + 3], n_internal)) * RF
                                             : attrs + size_t(child) * AF + size_t(child_slot) * RF;
     valid = in_range && fabsf(src[0]) >= kEpsLarge;
     const unsigned vmask = __ballot_sync(0xffffffffu, valid);
@@ -651,7 +655,7 @@ __device__ __forceinline__ int select_nodes(const float* __restrict__ mix, const
     constexpr int AF = Attr<D, R>::kFloats;
     auto count_of = [&](int n) -> int { return n >= n_internal ? 1 : __float_as_int(attrs[size_t(n) * AF + R * RF + 1]); };
     auto integral_of = [&](int n) -> float {
-        return n >= n_internal ? mix[size_t(nodes[size_t(n) * 4 + 3]) * RF] : attrs[size_t(n) * AF + R * RF];
+        return n >= n_internal ? mix[size_t(GMC_OBJ(nodes[size_t(n) * 4 + 3], n_internal)) * RF] : attrs[size_t(n) * AF + R * RF];
     };
     auto rating_of = [&](int n) -> float { return count_of(n) < R ? -2.f : fabsf(integral_of(n)); };
     if (lane == 0) { sel_node[0] = 0; sel_rating[0] = rating_of(0); }
@@ -671,7 +675,7 @@ __device__ __forceinline__ int select_nodes(const float* __restrict__ mix, const
         }
         if (best == 0x7fffffff) break;   // no full node left
         const int id = sel_node[best];
-        const int l = nodes[size_t(id) * 4 + 1], r = nodes[size_t(id) * 4 + 2];
+        const int l = GMC_NODE(nodes[size_t(id) * 4 + 1], n_internal), r = GMC_NODE(nodes[size_t(id) * 4 + 2], n_internal);
         __syncwarp();
         if (lane == 0) {
             sel_node[best] = l; sel_rating[best] = rating_of(l);
@@ -720,7 +724,7 @@ mhem_fit_forward_kernel(const float* __restrict__ mixture, const uint16_t* __res
 
     auto child_count = [&](int id) -> int { return id >= n_internal ? 1 : __float_as_int(attrs[size_t(id) * AF + R * RF + 1]); };
     auto child_integral = [&](int id) -> float {
-        return id >= n_internal ? mix[size_t(nodes[size_t(id) * 4 + 3]) * RF] : attrs[size_t(id) * AF + R * RF];
+        return id >= n_internal ? mix[size_t(GMC_OBJ(nodes[size_t(id) * 4 + 3], n_internal)) * RF] : attrs[size_t(id) * AF + R * RF];
     };
 
     // ---- node ids grouped by level (arrive[] is dead after compute_levels and holds the list) ----
@@ -740,7 +744,7 @@ mhem_fit_forward_kernel(const float* __restrict__ mixture, const uint16_t* __res
                 const int n_target = gather_children<D, R>(ws, mix, nodes, attrs, n_internal, id, lane, child, child_slot, in_range, valid, pos);
                 float* rec = attrs + size_t(id) * AF;
                 if (lane == 0) {
-                    rec[R * RF] = child_integral(nodes[size_t(id) * 4 + 1]) + child_integral(nodes[size_t(id) * 4 + 2]);
+                    rec[R * RF] = child_integral(GMC_NODE(nodes[size_t(id) * 4 + 1], n_internal)) + child_integral(GMC_NODE(nodes[size_t(id) * 4 + 2], n_internal));
                     rec[R * RF + 1] = __int_as_float(n_target > R ? R : n_target);
                     rec[R * RF + 3] = 0.f;
                 }
@@ -771,7 +775,7 @@ mhem_fit_forward_kernel(const float* __restrict__ mixture, const uint16_t* __res
     for (int i = warp; i < n_list; i += kWarps) {
         const int id = sel_node[i];
         const int cnt = child_count(id);
-        const float* src = id >= n_internal ? mix + size_t(nodes[size_t(id) * 4 + 3]) * RF : attrs + size_t(id) * AF;
+        const float* src = id >= n_internal ? mix + size_t(GMC_OBJ(nodes[size_t(id) * 4 + 3], n_internal)) * RF : attrs + size_t(id) * AF;
         for (int o = lane; o < cnt * RF; o += 32) {
             const int slot = sel_offset[i] + o / RF;
             if (slot < K) out[size_t(sel_offset[i]) * RF + o] = src[o];
@@ -833,7 +837,7 @@ mhem_fit_backward_kernel(const float* __restrict__ grad_all, const float* __rest
         const int id = sel_node[i];
         const int cnt = count_of(id);
         if (id >= n_internal) {      // a selected leaf hands its gradient straight to its Gaussian
-            const int obj = nodes[size_t(id) * 4 + 3];
+            const int obj = GMC_OBJ(nodes[size_t(id) * 4 + 3], n_internal);
             if (sel_offset[i] < K && fabsf(mix[size_t(obj) * RF]) >= kEpsLarge)
                 for (int f = lane; f < RF; f += 32) grad_target[size_t(obj) * RF + f] = grad[size_t(sel_offset[i]) * RF + f];
         } else {
@@ -877,7 +881,7 @@ mhem_fit_backward_kernel(const float* __restrict__ grad_all, const float* __rest
                 if (in_range) {
                     if (child >= n_internal) {
                         if (valid) {
-                            float* dst = grad_target + size_t(nodes[size_t(child) * 4 + 3]) * RF;
+                            float* dst = grad_target + size_t(GMC_OBJ(nodes[size_t(child) * 4 + 3], n_internal)) * RF;
 #pragma unroll
                             for (int f = 0; f < RF; ++f) dst[f] = ws.tgrad[pos][f];
                         }

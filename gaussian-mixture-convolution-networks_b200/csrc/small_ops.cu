@@ -187,6 +187,16 @@ __global__ void __launch_bounds__(kThreads) symeig_kernel(const float* __restric
 }  // namespace
 }  // namespace gmc
 
+namespace gmc {
+namespace {
+#ifdef GMC_BOUNDS_CHECK
+__global__ void index_check_probe_kernel(const float* one, long long index, long long n, float* out) {
+    *out = one[GMC_IDX(index, n)];      // an index outside [0, n) is reported and replaced by 0
+}
+#endif
+}  // namespace
+}  // namespace gmc
+
 GMC_DEFINE_TU_CHECK_READER(small_ops)
 
 extern "C" int gmc_symeig(const float* matrices, float* eigenvalues, float* eigenvectors, long long n_matrices,
@@ -249,4 +259,19 @@ extern "C" int gmc_integrate(const float* mixture, float* integrals, long long n
                                                                           1 + n_dims + n_dims * n_dims);
     GMC_LAUNCH_CHECK();
     return GMC_OK;
+}
+
+extern "C" int gmc_debug_index_check(const float* one_float, float* out, long long index, long long n, void* stream) {
+    using namespace gmc;
+    if (!one_float || !out) return GMC_ERR_NULL_POINTER;
+#ifdef GMC_BOUNDS_CHECK
+    if (index < 0 || n <= 0) return GMC_ERR_BAD_DIMS;
+    if (index < n && index != 0) return GMC_ERR_BAD_DIMS;   // the buffer holds one float: in-range means index 0
+    index_check_probe_kernel<<<1, 1, 0, as_stream(stream)>>>(one_float, index, n, out);
+    GMC_LAUNCH_CHECK();
+    return GMC_OK;
+#else
+    (void)index; (void)n; (void)stream;
+    return GMC_ERR_UNSUPPORTED;                              // this build carries no index checks
+#endif
 }

@@ -44,6 +44,7 @@ _declare("gmc_eval_inversed_forward", [_c_float_p] * 3 + [_c_int] * 7 + [_c_void
 _declare("gmc_eval_inversed_backward", [_c_float_p] * 5 + [_c_int] * 7 + [_c_void_p])
 _declare("gmc_debug_eval_forward_lost_copy", [_c_float_p] * 3 + [_c_int] * 7 + [_c_void_p])
 _declare("gmc_sync_and_check", [_c_void_p])
+_declare("gmc_debug_index_check", [_c_float_p, _c_float_p, ctypes.c_longlong, ctypes.c_longlong, _c_void_p])
 _declare("gmc_eval_inversed_host", [_c_float_p] * 6 + [_c_int] * 8)
 _declare("gmc_host_pipeline_release", [])
 _declare("gmc_relu_fixed_point", [_c_float_p] * 5 + [ctypes.c_longlong, _c_int, _c_int, _c_void_p])

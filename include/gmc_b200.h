@@ -53,6 +53,11 @@ int gmc_sync_and_check(void* stream);
 /* Error-path test aid: the forward evaluation with its bulk copy deliberately left out, so that the bounded wait runs
  * out after about a thousand polls: every output becomes NaN and the check word gets bit 1. Nothing is in flight when
  * the kernel gives up; the context stays usable. No reference counterpart. */
+/* Test aid of the bounds-checked build (libgmc_b200_checked.so, compiled with -DGMC_BOUNDS_CHECK: every index that a
+ * kernel reads from data -- tree children, object ids, sorted product indices -- is range-checked; a bad one sets bit 4
+ * of the check word and is replaced by 0, so the access stays inside its array). Runs the check itself once on a
+ * one-float buffer: index >= n must set the word and read element 0. Regular builds return GMC_ERR_UNSUPPORTED. */
+int gmc_debug_index_check(const float* one_float, float* out, long long index, long long n, void* stream);
 int gmc_debug_eval_forward_lost_copy(const float* mixture, const float* xes, float* out, int n_batch, int n_layers,
                                      int n_components, int n_dims, int n_batch_xes, int n_layers_xes, int n_xes,
                                      void* stream);
@@ -261,7 +266,9 @@ int gmc_convolution_fitting_backward(const float* grad, const float* data, const
  * Limit: n_mixtures * n_components <= gmc_mhem_fit_forward_noalloc_capacity() (2^20 keys); larger problems are
  * refused with GMC_ERR_BUILTIN_SCRATCH before any GPU work is issued -- use gmc_mhem_fit_forward for those.
  * Set-up: the first call on each device looks up the device address of the built-in array (once per device, with
- * that device current); make that first call before starting any stream capture.
+ * that device current); make that first call before starting any stream capture. The address is remembered per
+ * device ordinal for the life of the process: after a cudaDeviceReset() in the same process it is stale and the
+ * library must be reloaded. Pointers and stream must belong to the device that is current when the call is made.
  * Sharing: all calls on a device use the same array and it keeps whatever the previous call left in it. Nothing in
  * it has to start at zero (every slot read is written first), but two calls that run concurrently on the GPU -- on
  * different streams or from different threads -- would overwrite each other's keys: order such calls yourself.

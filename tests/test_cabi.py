@@ -62,6 +62,19 @@ def test_argument_checks_of_the_added_entry_points():
     assert h(one, one, null, one, one, null, 1, 1, 1, 2, 1, 1, 1, 0) == 3           # gradient without grad_out
 
 
+def test_argument_checks_of_the_no_allocation_entry_point():
+    from gmc import _native
+    null = ctypes.c_void_p(0)
+    one = ctypes.c_void_p(16)  # never dereferenced: argument checks come first
+    f = _native.lib.gmc_mhem_fit_forward_noalloc
+    assert f(one, 0, 8, 2, 8, 4, one, one, one, null) == 0            # nothing to do
+    assert f(one, 1, 8, 2, 8, 4, null, one, one, null) == 3           # NULL output
+    assert f(null, 1, 8, 2, 8, 4, one, one, one, null) == 3           # NULL input
+    assert f(one, 1, 8, 4, 8, 4, one, one, one, null) == 1            # D = 4
+    assert f(one, 1, 8, 2, 8, 3, one, one, one, null) == 4            # reduction_n = 3
+    assert f(one, (1 << 20) // 8 + 1, 8, 2, 8, 4, one, one, one, null) == 9   # beyond the built-in scratch
+
+
 def test_cpu_tensors_are_rejected_loudly():
     import gmc.cpp.extensions.evaluate_inversed.evaluate_inversed as ev
     with pytest.raises(RuntimeError, match="no CPU implementation"):

@@ -14,20 +14,27 @@ import synthetic_inputs as synthetic
 pytestmark = pytest.mark.gpu
 
 
-def _mixture(n_batch, n_layers, n_components, seed):
-    m = synthetic.fit_target_2d(n_batch, n_layers, n_components, seed)
-    m[..., 0] = m[..., 0].abs() + 0.01
+def _mixture(n_batch, n_layers, n_components, seed, n_dims=2):
+    if n_dims == 2:
+        m = synthetic.fit_target_2d(n_batch, n_layers, n_components, seed)
+        m[..., 0] = m[..., 0].abs() + 0.01
+    else:
+        g = torch.Generator().manual_seed(seed)
+        shape = (n_batch, n_layers, n_components)
+        cov, _ = synthetic.covariances_and_inverses(shape, 3, 0.03, 0.15, g)
+        m = synthetic.pack(torch.rand(shape, generator=g) * 0.8 + 0.2, torch.rand(*shape, 3, generator=g) * 2 - 1, cov)
     return m.cuda().contiguous()
 
 
 def _call(name, mixture, K, R, with_scratch):
     from gmc import _native
     b, l, g, v = mixture.shape
+    n_dims = {7: 2, 13: 3}[v]
     dev = mixture.device
     fitting = torch.full((b, l, K, v), float("nan"), device=dev)
     nodes = torch.full((b, l, 2 * g - 1, 4), -7, dtype=torch.int16, device=dev)
-    attribs = torch.full((b * l, _native.lib.gmc_mhem_fit_attribute_floats(g, 2, R)), float("nan"), device=dev)
-    args = [_native.ptr(mixture), b * l, g, 2, K, R, _native.ptr(fitting), _native.ptr(nodes), _native.ptr(attribs)]
+    attribs = torch.full((b * l, _native.lib.gmc_mhem_fit_attribute_floats(g, n_dims, R)), float("nan"), device=dev)
+    args = [_native.ptr(mixture), b * l, g, n_dims, K, R, _native.ptr(fitting), _native.ptr(nodes), _native.ptr(attribs)]
     keys = None
     if with_scratch:
         keys = torch.empty((b * l, g), dtype=torch.int64, device=dev)
@@ -40,8 +47,8 @@ def _call(name, mixture, K, R, with_scratch):
 
 def test_noalloc_entry_point_matches_the_regular_one_on_two_calls_in_a_row():
     # second call: smaller problem, so stale keys of the first call sit behind and between the new ones
-    for (b, l, g, K, R, seed) in ((3, 4, 1024, 64, 4, 21), (2, 3, 100, 32, 2, 22)):
-        m = _mixture(b, l, g, seed)
+    for (b, l, g, K, R, seed, n_dims) in ((3, 4, 1024, 64, 4, 21, 2), (2, 3, 100, 32, 2, 22, 2), (2, 2, 64, 16, 2, 23, 3)):
+        m = _mixture(b, l, g, seed, n_dims)
         s0, fit_ref, nodes_ref, attr_ref = _call("gmc_mhem_fit_forward", m, K, R, True)
         s1, fit_new, nodes_new, attr_new = _call("gmc_mhem_fit_forward_noalloc", m, K, R, False)
         assert s0 == 0 and s1 == 0
