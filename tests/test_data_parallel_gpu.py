@@ -114,7 +114,10 @@ def test_two_rank_training_step_equals_the_single_gpu_step(tmp_path):
     params = {k: v.detach().cpu() for k, v in net.named_parameters()}
     for r in range(2):
         got = torch.load(os.path.join(str(tmp_path), f"rank{r}.pt"))
-        assert set(got["grads"]) == set(grads)
+        # parameters the loss does not reach get no gradient on one GPU and an all-zero one from the all-reduce
+        assert set(grads) <= set(got["grads"])
+        for name in set(got["grads"]) - set(grads):
+            assert got["grads"][name].abs().max().item() == 0, name
         for name, g in grads.items():
             scale = max(g.abs().max().item(), 1e-12)
             err = (got["grads"][name] - g.cpu()).abs().max().item() / scale
