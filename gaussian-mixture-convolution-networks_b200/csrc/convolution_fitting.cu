@@ -301,6 +301,194 @@ convolution_fitting_tree_kernel(const float* __restrict__ data, const float* __r
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Trees of more than kMaxProducts products (up to 65535): the same construction with every array in global scratch
+// instead of shared memory, one CTA of 1024 threads per tree. Per tree the scratch holds (T = number of products):
+//   keys A, keys B [T] uint64 | left, right, first, last [T-1] int32 | parent [2T-1] int32 | mass [2T-1] fp32 |
+//   arrivals [T-1] int32                                      (convfit_large_scratch_bytes(T) bytes, 16-byte aligned)
+// Steps: bounding box and keys as in the shared-memory kernel; stable radix sort of the keys in global memory; Karras
+// range / split search per internal node on (sign | Morton code, sorted position); masses bottom-up, the second child to
+// arrive adds mass(left) + mass(right); greedy selection by warp 0.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kLargeTreeThreads = 1024;
+constexpr int kMaxProductsLarge = 65535;      // ranks and digit offsets of the sort are 16 bit
+
+__host__ __device__ inline size_t convfit_large_scratch_bytes(long long T) {
+    const size_t t = size_t(T);
+    return ((16 * t + 4 * 4 * (t - 1) + 4 * (2 * t - 1) + 4 * (2 * t - 1) + 4 * (t - 1)) + 15) & ~size_t(15);
+}
+
+template <int D>
+__global__ void __launch_bounds__(kLargeTreeThreads)
+convolution_fitting_tree_large_kernel(const float* __restrict__ data, const float* __restrict__ kernels, Dims n,
+                                      int* __restrict__ nodesobjs_all, int* __restrict__ subtrees_all,
+                                      unsigned char* __restrict__ scratch_all) {
+    constexpr int RF = 1 + D + D * D;
+    constexpr int NW = kLargeTreeThreads / 32;
+    extern __shared__ __align__(16) unsigned char smem_bytes[];
+    const int Cin = n.n_channels_in, G = n.n_components, Gk = n.n_kernel_components, K = n.n_fitting;
+    const int T = Cin * G * Gk;
+    const int n_internal = T - 1;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int b = blockIdx.x / n.n_channels_out, o = blockIdx.x - b * n.n_channels_out;
+    const float* data_b = data + size_t(b) * Cin * G * RF;
+    const float* kernels_o = kernels + size_t(o) * Cin * Gk * RF;
+    int* nodesobjs = nodesobjs_all + size_t(blockIdx.x) * T;
+    int* subtrees = subtrees_all + size_t(blockIdx.x) * 2 * K;
+    unsigned char* scratch = scratch_all + size_t(blockIdx.x) * convfit_large_scratch_bytes(T);
+    uint64_t* keys_a = reinterpret_cast<uint64_t*>(scratch);
+    uint64_t* keys_b = keys_a + T;
+    int* left = reinterpret_cast<int*>(keys_b + T);
+    int* right = left + n_internal;
+    int* first = right + n_internal;
+    int* last = first + n_internal;
+    int* parent = last + n_internal;                     // [2T-1]
+    float* mass = reinterpret_cast<float*>(parent + (2 * T - 1));   // [2T-1]
+    int* arrivals = reinterpret_cast<int*>(mass + (2 * T - 1));     // [T-1]
+    // shared: ranks of the sort [T] uint16 (later the selection list), then the sort's histograms
+    uint16_t* ranks = reinterpret_cast<uint16_t*>(smem_bytes);
+    const size_t list_bytes = size_t(K) * 8 > size_t(T) * 2 ? size_t(K) * 8 : size_t(T) * 2;
+    void* sort_scratch = smem_bytes + ((list_bytes + 15) & ~size_t(15));
+    int* sel_node = reinterpret_cast<int*>(smem_bytes);
+    unsigned* sel_rating = reinterpret_cast<unsigned*>(sel_node + K);
+    __shared__ float s_hi[NW][D], s_lo[NW][D], box_hi[D], box_lo[D];
+
+    // ---- bounding box: max over channels of (data max + kernel max), min likewise ----
+    {
+        float hi[D], lo[D];
+#pragma unroll
+        for (int d = 0; d < D; ++d) { hi[d] = -INFINITY; lo[d] = INFINITY; }
+        for (int ci = warp; ci < Cin; ci += NW) {
+            float dh[D], dl[D], kh[D], kl[D];
+#pragma unroll
+            for (int d = 0; d < D; ++d) { dh[d] = kh[d] = -INFINITY; dl[d] = kl[d] = INFINITY; }
+            for (int g = lane; g < G; g += 32) {
+#pragma unroll
+                for (int d = 0; d < D; ++d) {
+                    const float v = __ldg(data_b + (size_t(ci) * G + g) * RF + 1 + d);
+                    dh[d] = fmaxf(dh[d], v); dl[d] = fminf(dl[d], v);
+                }
+            }
+            for (int g = lane; g < Gk; g += 32) {
+#pragma unroll
+                for (int d = 0; d < D; ++d) {
+                    const float v = __ldg(kernels_o + (size_t(ci) * Gk + g) * RF + 1 + d);
+                    kh[d] = fmaxf(kh[d], v); kl[d] = fminf(kl[d], v);
+                }
+            }
+#pragma unroll
+            for (int d = 0; d < D; ++d) {
+                hi[d] = fmaxf(hi[d], __fadd_rn(warp_max(dh[d]), warp_max(kh[d])));
+                lo[d] = fminf(lo[d], __fadd_rn(warp_min(dl[d]), warp_min(kl[d])));
+            }
+        }
+        if (lane == 0) {
+#pragma unroll
+            for (int d = 0; d < D; ++d) { s_hi[warp][d] = hi[d]; s_lo[warp][d] = lo[d]; }
+        }
+        __syncthreads();
+        if (tid < D) {
+            float h = s_hi[0][tid], l = s_lo[0][tid];
+            for (int w = 1; w < NW; ++w) { h = fmaxf(h, s_hi[w][tid]); l = fminf(l, s_lo[w][tid]); }
+            box_hi[tid] = h; box_lo[tid] = l;
+        }
+        __syncthreads();
+    }
+    auto product_parts = [&](int t, int& comp_in, int& ch_in, int& comp_k) {
+        comp_k = t / (G * Cin);
+        const int rem = t - comp_k * (G * Cin);
+        ch_in = rem / G;
+        comp_in = rem - ch_in * G;
+    };
+    // ---- keys; leaf masses ----
+    for (int t = tid; t < T; t += kLargeTreeThreads) {
+        int gi, ci, ki;
+        product_parts(t, gi, ci, ki);
+        const float* dg = data_b + (size_t(ci) * G + gi) * RF;
+        const float* kg = kernels_o + (size_t(ci) * Gk + ki) * RF;
+        uint32_t q[3] = {0u, 0u, 0u};
+#pragma unroll
+        for (int d = 0; d < D; ++d) q[d] = lbvh::quantise(__fadd_rn(__ldg(dg + 1 + d), __ldg(kg + 1 + d)), box_lo[d], box_hi[d]);
+        const uint64_t sign = __fmul_rn(__ldg(dg), __ldg(kg)) > 0.f ? 1ull : 0ull;
+        keys_a[t] = (sign << 62) | (uint64_t(lbvh::morton30(q[0], q[1], q[2])) << 32) | uint64_t(uint32_t(t));
+    }
+    for (int i = tid; i < n_internal; i += kLargeTreeThreads) arrivals[i] = 0;
+    __threadfence_block();
+    __syncthreads();
+    const uint64_t* keys = lbvh::radix_sort_global(keys_a, keys_b, T, 32, 4, ranks, sort_scratch);   // back in A
+    for (int j = tid; j < T; j += kLargeTreeThreads) {
+        const int t = int(uint32_t(keys[j]));
+        nodesobjs[j] = t;
+        int gi, ci, ki;
+        product_parts(t, gi, ci, ki);
+        mass[n_internal + j] = __fmul_rn(__ldg(data_b + (size_t(ci) * G + gi) * RF), __ldg(kernels_o + (size_t(ci) * Gk + ki) * RF));
+    }
+    // ---- internal nodes ----
+    {
+        const lbvh::PositionTieBreakCode code{keys};
+        for (int i = tid; i < n_internal; i += kLargeTreeThreads) {
+            const int2 r = lbvh::determine_range(code, T, i);
+            const int gamma = lbvh::find_split(code, r.x, r.y);
+            int l = gamma, rr = gamma + 1;
+            if (min(r.x, r.y) == gamma) l += n_internal;
+            if (max(r.x, r.y) == gamma + 1) rr += n_internal;
+            left[i] = l; right[i] = rr; first[i] = r.x; last[i] = r.y;
+            parent[l] = i; parent[rr] = i;
+            if (i == 0) parent[0] = -1;
+        }
+    }
+    __threadfence_block();
+    __syncthreads();
+    // ---- masses, bottom-up: the second child to arrive at a node completes it and climbs on ----
+    for (int leaf = tid; leaf < T; leaf += kLargeTreeThreads) {
+        int node = parent[n_internal + leaf];
+        for (int guard = 0; guard < 4 * kMaxLevels && node >= 0; ++guard) {
+            __threadfence_block();
+            if (atomicAdd(&arrivals[node], 1) == 0) break;
+            __threadfence_block();
+            const float ml = ((volatile float*)mass)[left[node]], mr = ((volatile float*)mass)[right[node]];
+            ((volatile float*)mass)[node] = __fadd_rn(ml, mr);
+            node = parent[node];
+        }
+    }
+    __threadfence_block();
+    __syncthreads();
+    // ---- greedy selection of K subtree roots (warp 0); the list replaces the sort's ranks ----
+    if (warp == 0) {
+        auto rating_of = [&](int id) -> unsigned { return id >= n_internal ? 0u : __float_as_uint(fabsf(mass[id])) + 1u; };
+        if (lane == 0) { sel_node[0] = 0; sel_rating[0] = 1u; }       // the root is expanded first whatever its mass
+        __syncwarp();
+        int n_sel = 1;
+        while (n_sel < K) {
+            unsigned best_rating = 0u;
+            int best = 0x7fffffff;
+            for (int i = lane; i < n_sel; i += 32)
+                if (sel_rating[i] > best_rating) { best_rating = sel_rating[i]; best = i; }
+            const unsigned top = __reduce_max_sync(0xffffffffu, best_rating);
+            if (top == 0u) break;
+            best = __reduce_min_sync(0xffffffffu, best_rating == top ? best : 0x7fffffff);
+            if (lane == 0) {
+                const int id = sel_node[best];
+                const int l = left[id], r = right[id];
+                sel_node[best] = l; sel_rating[best] = rating_of(l);
+                sel_node[n_sel] = r; sel_rating[n_sel] = rating_of(r);
+            }
+            ++n_sel;
+            __syncwarp();
+        }
+        for (int k = lane; k < K; k += 32) {
+            int start = -1, end = -1;
+            if (k < n_sel) {
+                const int id = sel_node[k];
+                start = id >= n_internal ? id : n_internal + first[id];
+                end = id >= n_internal ? id + 1 : n_internal + last[id] + 1;
+            }
+            subtrees[2 * k] = start;
+            subtrees[2 * k + 1] = end;
+        }
+    }
+}
+
 // Staged input record. 3D: the 13 floats of a Gaussian are read as 4 float4; records are 20 floats apart, an odd
 // number of float4, so that arbitrary records spread evenly over the 8 groups of 4 banks (a stride of 16 floats would
 // put all records on two of them). 2D: the 7 floats are read one by one at their natural (odd) stride, which measured
@@ -767,6 +955,69 @@ extern "C" int gmc_convolution_fitting_forward(const float* data, const float* k
                                               blocks, smem, agg_blocks, groups_per_tree, staged, staged_bytes, st))
             return s;
     }
+    return GMC_OK;
+}
+
+extern "C" size_t gmc_convolution_fitting_large_scratch_bytes(int n_batch, int n_channels_in, int n_components,
+                                                              int n_channels_out, int n_kernel_components) {
+    const long long T = (long long)n_channels_in * n_components * n_kernel_components;
+    if (n_batch <= 0 || n_channels_out <= 0 || T < 2 || T > gmc::kMaxProductsLarge) return 0;
+    return size_t(n_batch) * size_t(n_channels_out) * gmc::convfit_large_scratch_bytes(T);
+}
+
+extern "C" int gmc_convolution_fitting_forward_large(const float* data, const float* kernels, int n_batch,
+                                                     int n_channels_in, int n_components, int n_channels_out,
+                                                     int n_kernel_components, int n_dims, int n_components_fitting,
+                                                     float* fitting, float* cached_pos_covs, int32_t* nodesobjs,
+                                                     int32_t* fitting_subtrees, void* scratch, size_t scratch_bytes,
+                                                     void* stream) {
+    using namespace gmc;
+    if (n_dims != 2 && n_dims != 3) return GMC_ERR_BAD_DIMS;
+    if (n_batch <= 0 || n_channels_in <= 0 || n_components <= 0 || n_channels_out <= 0 || n_kernel_components <= 0)
+        return GMC_ERR_BAD_DIMS;
+    const long long T = (long long)n_channels_in * n_components * n_kernel_components;
+    if (T < 2 || T > kMaxProductsLarge) return GMC_ERR_BAD_DIMS;
+    if (n_components_fitting <= 0 || n_components_fitting > 8192) return GMC_ERR_BAD_DIMS;
+    if (!data || !kernels || !fitting || !cached_pos_covs || !nodesobjs || !fitting_subtrees || !scratch) return GMC_ERR_NULL_POINTER;
+    const long long blocks = (long long)n_batch * n_channels_out;
+    if (blocks > 0x7fffffffLL) return GMC_ERR_BAD_DIMS;
+    if (scratch_bytes < size_t(blocks) * convfit_large_scratch_bytes(T)) return GMC_ERR_BAD_DIMS;
+    if ((reinterpret_cast<uintptr_t>(scratch) & 15u) != 0) return GMC_ERR_BAD_DIMS;
+    const Dims n{n_batch, n_channels_in, n_components, n_channels_out, n_kernel_components, n_components_fitting};
+    cudaStream_t st = as_stream(stream);
+    const size_t list = size_t(n_components_fitting) * 8 > size_t(T) * 2 ? size_t(n_components_fitting) * 8 : size_t(T) * 2;
+    const size_t smem = ((list + 15) & ~size_t(15)) + 2 * size_t((kLargeTreeThreads / 32) + 1) * 256 + 32;
+    if (smem > 220 * 1024) return GMC_ERR_BAD_DIMS;
+    unsigned char* sc = static_cast<unsigned char*>(scratch);
+    if (n_dims == 2) {
+        GMC_CUDA_TRY(cudaFuncSetAttribute(convolution_fitting_tree_large_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        convolution_fitting_tree_large_kernel<2><<<unsigned(blocks), kLargeTreeThreads, smem, st>>>(data, kernels, n, nodesobjs, fitting_subtrees, sc);
+    } else {
+        GMC_CUDA_TRY(cudaFuncSetAttribute(convolution_fitting_tree_large_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        convolution_fitting_tree_large_kernel<3><<<unsigned(blocks), kLargeTreeThreads, smem, st>>>(data, kernels, n, nodesobjs, fitting_subtrees, sc);
+    }
+    GMC_LAUNCH_CHECK();
+    // aggregation: the kernel of the regular path, reading the sorted products and the subtree ranges from global memory
+    const int groups_per_tree = (n_components_fitting + kAggOutputsPerCta - 1) / kAggOutputsPerCta;
+    const long long agg_blocks = blocks * groups_per_tree;
+    if (agg_blocks > 0x7fffffffLL) return GMC_ERR_BAD_DIMS;
+    const size_t staged_bytes = sizeof(float) * size_t(n_channels_in) * (n_components + n_kernel_components) *
+                                size_t(n_dims == 2 ? StagedRecord<2>::kStride : StagedRecord<3>::kStride);
+    const bool staged = staged_bytes <= kAggMaxStagedBytes;
+#define GMC_AGG(D_)                                                                                                        \
+    if (staged) {                                                                                                          \
+        if (staged_bytes > 48 * 1024)                                                                                      \
+            GMC_CUDA_TRY(cudaFuncSetAttribute(convolution_fitting_aggregate_kernel<D_, true>,                              \
+                                              cudaFuncAttributeMaxDynamicSharedMemorySize, int(staged_bytes)));            \
+        convolution_fitting_aggregate_kernel<D_, true><<<unsigned(agg_blocks), 256, staged_bytes, st>>>(                   \
+            data, kernels, n, nodesobjs, fitting_subtrees, fitting, cached_pos_covs, groups_per_tree);                     \
+    } else {                                                                                                               \
+        convolution_fitting_aggregate_kernel<D_, false><<<unsigned(agg_blocks), 256, 0, st>>>(                             \
+            data, kernels, n, nodesobjs, fitting_subtrees, fitting, cached_pos_covs, groups_per_tree);                     \
+    }
+    if (n_dims == 2) { GMC_AGG(2) } else { GMC_AGG(3) }
+#undef GMC_AGG
+    GMC_LAUNCH_CHECK();
     return GMC_OK;
 }
 

@@ -137,6 +137,80 @@ __device__ __forceinline__ uint64_t* radix_sort_shared(uint64_t* a, uint64_t* b,
     return a;
 }
 
+// The same stable LSD radix sort for keys that live in GLOBAL memory (trees too large for shared memory): `a` and `b`
+// are global buffers of n keys, the rank that a key carries between the counting and the scatter loop sits in the
+// shared array `ranks` (n uint16) instead of in key bits, `scratch` as above. n < 65536. Sorted keys end up in `a` for an
+// even number of passes. One CTA sorts one segment; all its threads must call.
+__device__ __forceinline__ uint64_t* radix_sort_global(uint64_t* a, uint64_t* b, int n, int first_bit, int n_passes,
+                                                       uint16_t* ranks, void* scratch) {
+    const int n_warps = blockDim.x >> 5;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int chunk = (((n + n_warps - 1) / n_warps) + 31) & ~31;
+    const int begin = min(n, warp * chunk), end = min(n, begin + chunk);
+    uint16_t* hist = reinterpret_cast<uint16_t*>(scratch);
+    uint16_t* my_hist = hist + warp * 256;
+    uint16_t* totals = hist + n_warps * 256;
+    unsigned* warp_sums = reinterpret_cast<unsigned*>(totals + 256);
+    const unsigned lt_mask = (1u << lane) - 1u;
+    for (int pass = 0; pass < n_passes; ++pass) {
+        const int shift = first_bit + 8 * pass;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) reinterpret_cast<unsigned*>(my_hist)[lane + 32 * k] = 0u;
+        __syncwarp();
+        for (int i0 = begin; i0 < end; i0 += 32) {
+            const int i = i0 + lane;
+            const bool active = i < end;
+            const unsigned act = __ballot_sync(0xffffffffu, active);
+            if (active) {
+                const unsigned digit = unsigned(a[i] >> shift) & 0xFFu;
+                const unsigned peers = __match_any_sync(act, digit);
+                const int leader = __ffs(peers) - 1;
+                unsigned before = 0u;
+                if (lane == leader) {
+                    before = my_hist[digit];
+                    my_hist[digit] = uint16_t(before + __popc(peers));
+                }
+                before = __shfl_sync(act, before, leader);
+                ranks[i] = uint16_t(before + __popc(peers & lt_mask));
+            }
+            __syncwarp();
+        }
+        __syncthreads();
+        if (threadIdx.x < 256) {
+            unsigned run = 0u;
+            for (int w = 0; w < n_warps; ++w) {
+                const unsigned c = hist[w * 256 + threadIdx.x];
+                hist[w * 256 + threadIdx.x] = uint16_t(run);
+                run += c;
+            }
+            unsigned incl = run;
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const unsigned o = __shfl_up_sync(0xffffffffu, incl, off);
+                if (lane >= off) incl += o;
+            }
+            totals[threadIdx.x] = uint16_t(incl - run);
+            if (lane == 31) warp_sums[warp] = incl;
+        }
+        __syncthreads();
+        unsigned group_base = 0u;
+#pragma unroll
+        for (int k = 0; k < 7; ++k) group_base += k < lane ? warp_sums[k] : 0u;
+        for (int i0 = begin; i0 < end; i0 += 32) {
+            const int i = i0 + lane;
+            const bool active = i < end;
+            const uint64_t key = active ? a[i] : 0ull;
+            const unsigned digit = unsigned(key >> shift) & 0xFFu;
+            const unsigned base = __shfl_sync(0xffffffffu, group_base, int(digit >> 5));
+            if (active) b[base + unsigned(totals[digit]) + unsigned(my_hist[digit]) + unsigned(ranks[i])] = key;
+        }
+        __threadfence_block();
+        __syncthreads();
+        uint64_t* t = a; a = b; b = t;
+    }
+    return a;
+}
+
 __device__ __forceinline__ int common_upper_bits(uint64_t a, uint64_t b) { return __clzll(int64_t(a ^ b)); }
 
 // Code functor: plain key (BVH fit) or (key & high 32 bits) + sorted position (convolution fit).

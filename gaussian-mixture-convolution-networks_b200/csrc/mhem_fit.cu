@@ -33,6 +33,11 @@ namespace {
 constexpr int kThreads = GMC_FIT_THREADS;
 constexpr int kWarps = kThreads / 32;
 constexpr int kMaxLevels = 72;
+constexpr int kSharedBookkeepingMax = 8192;   // above this many components the per-node arrays go to global scratch
+// bytes of global bookkeeping per mixture: level [2G-1 -> 16] + arrive / order [4 (G-1)] + has_grad [G], at most 8 G
+__host__ __device__ inline size_t big_scratch_bytes(int G) {
+    return ((size_t(2 * G - 1) + 15) & ~size_t(15)) + 4 * size_t(G - 1) + ((size_t(G) + 15) & ~size_t(15));
+}
 constexpr float kEpsSmall = 0.0000000000001f;
 constexpr float kEpsLarge = 0.0000001f;
 constexpr float kKlThreshold = 0.5f;
@@ -698,17 +703,19 @@ __device__ __forceinline__ int select_nodes(const float* __restrict__ mix, const
 template <int D, int R>
 __global__ void __launch_bounds__(kThreads)
 mhem_fit_forward_kernel(const float* __restrict__ mixture, const uint16_t* __restrict__ nodes_all, float* __restrict__ attrs_all,
-                        float* __restrict__ out_all, int n_components, int n_fitting) {
+                        float* __restrict__ out_all, int n_components, int n_fitting, unsigned char* big_scratch) {
     constexpr int RF = 1 + D + D * D;
     constexpr int AF = Attr<D, R>::kFloats;
     extern __shared__ __align__(16) unsigned char smem_bytes[];
     FitSmem<D, R>& sm = *reinterpret_cast<FitSmem<D, R>*>(smem_bytes);
     const int G = n_components, K = n_fitting;
     const int n_internal = G - 1, n_nodes = 2 * G - 1;
-    unsigned char* level = smem_bytes + sizeof(FitSmem<D, R>);
+    // per-node bookkeeping: in shared memory, or (mixtures too large for that) in this mixture's slice of big_scratch
+    unsigned char* small = smem_bytes + sizeof(FitSmem<D, R>);
+    unsigned char* level = big_scratch ? big_scratch + size_t(blockIdx.x) * big_scratch_bytes(G) : small;
     int* arrive = reinterpret_cast<int*>(level + ((n_nodes + 15) & ~15));
     const int sel_cap = K > 1024 ? K : 1024;   // capacity of the selection list (the reference holds 1024 entries)
-    int* sel_node = arrive + n_internal;
+    int* sel_node = big_scratch ? reinterpret_cast<int*>(small) : arrive + n_internal;
     float* sel_rating = reinterpret_cast<float*>(sel_node + sel_cap);
     int* sel_offset = reinterpret_cast<int*>(sel_rating + sel_cap);
     __shared__ int s_max_level, s_n_selected_nodes, s_written;
@@ -797,7 +804,7 @@ __global__ void __launch_bounds__(kThreads)
 mhem_fit_backward_kernel(const float* __restrict__ grad_all, const float* __restrict__ mixture,
                          const uint16_t* __restrict__ nodes_all, const float* __restrict__ attrs_all,
                          float* __restrict__ node_grad_all, float* __restrict__ grad_target_all, int n_components,
-                         int n_fitting) {
+                         int n_fitting, unsigned char* big_scratch) {
     constexpr int RF = 1 + D + D * D;
     constexpr int AF = Attr<D, R>::kFloats;
     constexpr int NT = 2 * R;
@@ -805,13 +812,15 @@ mhem_fit_backward_kernel(const float* __restrict__ grad_all, const float* __rest
     FitSmem<D, R>& sm = *reinterpret_cast<FitSmem<D, R>*>(smem_bytes);
     const int G = n_components, K = n_fitting;
     const int n_internal = G - 1, n_nodes = 2 * G - 1;
-    unsigned char* level = smem_bytes + sizeof(FitSmem<D, R>);
+    unsigned char* small = smem_bytes + sizeof(FitSmem<D, R>);
+    unsigned char* level = big_scratch ? big_scratch + size_t(blockIdx.x) * big_scratch_bytes(G) : small;
     int* arrive = reinterpret_cast<int*>(level + ((n_nodes + 15) & ~15));
     const int sel_cap = K > 1024 ? K : 1024;
-    int* sel_node = arrive + n_internal;
+    int* sel_node = big_scratch ? reinterpret_cast<int*>(small) : arrive + n_internal;
     float* sel_rating = reinterpret_cast<float*>(sel_node + sel_cap);
     int* sel_offset = reinterpret_cast<int*>(sel_rating + sel_cap);
-    unsigned char* has_grad = reinterpret_cast<unsigned char*>(sel_offset + sel_cap);
+    unsigned char* has_grad = big_scratch ? reinterpret_cast<unsigned char*>(arrive + n_internal)
+                                          : reinterpret_cast<unsigned char*>(sel_offset + sel_cap);
     __shared__ int s_max_level, s_n_selected_nodes, s_written;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -903,18 +912,21 @@ mhem_fit_backward_kernel(const float* __restrict__ grad_all, const float* __rest
 template <int D, int R>
 size_t fit_smem_bytes(int G, int K) {
     const int n_nodes = 2 * G - 1;
-    return sizeof(FitSmem<D, R>) + size_t((n_nodes + 15) & ~15) + sizeof(int) * size_t(G - 1) +
-           size_t(K > 1024 ? K : 1024) * 12 + size_t((G + 15) & ~15);
+    const size_t fixed = sizeof(FitSmem<D, R>) + size_t(K > 1024 ? K : 1024) * 12;
+    if (G > kSharedBookkeepingMax) return fixed;                  // per-node arrays live in global scratch
+    return fixed + size_t((n_nodes + 15) & ~15) + sizeof(int) * size_t(G - 1) + size_t((G + 15) & ~15);
 }
 
 template <int D, int R>
 int launch_fit(const float* mixture, long long n_mixtures, int G, int K, const uint16_t* nodes, float* attrs, float* out,
-               cudaStream_t stream) {
+               cudaStream_t stream, unsigned char* big_scratch = nullptr) {
     auto kernel = mhem_fit_forward_kernel<D, R>;
     const size_t smem = fit_smem_bytes<D, R>(G, K);
     if (smem > 200 * 1024) return GMC_ERR_BAD_DIMS;
     if (smem > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-    kernel<<<unsigned(n_mixtures), kThreads, smem, stream>>>(mixture, nodes, attrs, out, G, K);
+    if (G > kSharedBookkeepingMax && big_scratch == nullptr) return GMC_ERR_NULL_POINTER;
+    kernel<<<unsigned(n_mixtures), kThreads, smem, stream>>>(mixture, nodes, attrs, out, G, K,
+                                                            G > kSharedBookkeepingMax ? big_scratch : nullptr);
     GMC_LAUNCH_CHECK();
     return GMC_OK;
 }
@@ -926,7 +938,11 @@ int launch_fit_backward(const float* grad, const float* mixture, long long n_mix
     const size_t smem = fit_smem_bytes<D, R>(G, K);
     if (smem > 200 * 1024) return GMC_ERR_BAD_DIMS;
     if (smem > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-    kernel<<<unsigned(n_mixtures), kThreads, smem, stream>>>(grad, mixture, nodes, attrs, node_grad, grad_target, G, K);
+    // large mixtures: the per-node bookkeeping follows the node gradients in the caller's scratch
+    unsigned char* big = G > kSharedBookkeepingMax
+                             ? reinterpret_cast<unsigned char*>(node_grad + size_t(n_mixtures) * size_t(G - 1) * R * (1 + D + D * D))
+                             : nullptr;
+    kernel<<<unsigned(n_mixtures), kThreads, smem, stream>>>(grad, mixture, nodes, attrs, node_grad, grad_target, G, K, big);
     GMC_LAUNCH_CHECK();
     return GMC_OK;
 }
@@ -954,7 +970,10 @@ extern "C" int gmc_mhem_fit_forward(const float* mixture, long long n_mixtures, 
     cudaStream_t st = as_stream(stream);
     uint16_t* nodes = reinterpret_cast<uint16_t*>(bvh_nodes);
     if (int s = lbvh_build_launch(mixture, n_mixtures, n_components, n_dims, scratch_keys, nodes, st)) return s;
-#define GMC_FIT(D_, R_) launch_fit<D_, R_>(mixture, n_mixtures, n_components, n_components_fitting, nodes, bvh_attributes, fitting, st)
+    // the Morton keys are dead once the nodes exist: for large mixtures their buffer (8 bytes per component) takes the
+    // per-node bookkeeping of the fit kernel (at most 8 bytes per component, see big_scratch_bytes)
+    unsigned char* big = reinterpret_cast<unsigned char*>(scratch_keys);
+#define GMC_FIT(D_, R_) launch_fit<D_, R_>(mixture, n_mixtures, n_components, n_components_fitting, nodes, bvh_attributes, fitting, st, big)
     if (n_dims == 2) return reduction_n == 2 ? GMC_FIT(2, 2) : GMC_FIT(2, 4);
     return reduction_n == 2 ? GMC_FIT(3, 2) : GMC_FIT(3, 4);
 #undef GMC_FIT
@@ -1042,12 +1061,13 @@ extern "C" int gmc_mhem_fit_forward_noalloc(const float* mixture, long long n_mi
     uint16_t* nodes = reinterpret_cast<uint16_t*>(bvh_nodes);
     // every key slot that is read is written first by the build kernel, so the array needs no clearing between calls
     if (int s = lbvh_build_launch(mixture, n_mixtures, n_components, n_dims, keys, nodes, st)) return s;
+    unsigned char* big = reinterpret_cast<unsigned char*>(keys);     // dead keys = bookkeeping of large mixtures
     if (n_dims == 2) {
         return reduction_n == 2
-                   ? launch_fit<2, 2>(mixture, n_mixtures, n_components, n_components_fitting, nodes, bvh_attributes, fitting, st)
-                   : launch_fit<2, 4>(mixture, n_mixtures, n_components, n_components_fitting, nodes, bvh_attributes, fitting, st);
+                   ? launch_fit<2, 2>(mixture, n_mixtures, n_components, n_components_fitting, nodes, bvh_attributes, fitting, st, big)
+                   : launch_fit<2, 4>(mixture, n_mixtures, n_components, n_components_fitting, nodes, bvh_attributes, fitting, st, big);
     }
     return reduction_n == 2
-               ? launch_fit<3, 2>(mixture, n_mixtures, n_components, n_components_fitting, nodes, bvh_attributes, fitting, st)
-               : launch_fit<3, 4>(mixture, n_mixtures, n_components, n_components_fitting, nodes, bvh_attributes, fitting, st);
+               ? launch_fit<3, 2>(mixture, n_mixtures, n_components, n_components_fitting, nodes, bvh_attributes, fitting, st, big)
+               : launch_fit<3, 4>(mixture, n_mixtures, n_components, n_components_fitting, nodes, bvh_attributes, fitting, st, big);
 }

@@ -65,6 +65,9 @@ _declare("gmc_convolution_forward", [_c_float_p] * 3 + [_c_int] * 6 + [_c_void_p
 _declare("gmc_convolution_backward", [_c_float_p] * 5 + [_c_int] * 6 + [_c_void_p])
 _declare("gmc_convolution_fitting_forward", [_c_float_p] * 2 + [_c_int] * 7 + [_c_void_p] * 5)
 _declare("gmc_convolution_fitting_backward", [_c_float_p] * 3 + [_c_int] * 7 + [_c_void_p] * 7)
+_declare("gmc_convolution_fitting_forward_large", [_c_float_p] * 2 + [_c_int] * 7 + [_c_void_p] * 5 + [ctypes.c_size_t, _c_void_p])
+lib.gmc_convolution_fitting_large_scratch_bytes.restype = ctypes.c_size_t
+lib.gmc_convolution_fitting_large_scratch_bytes.argtypes = [_c_int] * 5
 _declare("gmc_mhem_fit_backward", [_c_float_p, _c_float_p, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_int, _c_void_p,
                                    _c_void_p, _c_void_p, _c_void_p, _c_void_p])
 _declare("gmc_symeig", [_c_float_p] * 3 + [ctypes.c_longlong, _c_int, _c_void_p])

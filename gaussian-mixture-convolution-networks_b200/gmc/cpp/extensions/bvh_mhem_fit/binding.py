@@ -52,7 +52,8 @@ def backward(grad: torch.Tensor, fitting_mixture: torch.Tensor, target_mixture: 
         raise RuntimeError("grad has the wrong shape")
     n_mix = n_batch * n_layers
     grad_target = torch.empty_like(target_mixture)
-    scratch = torch.empty((n_mix, (n_components - 1) * reduction_n * target_mixture.shape[-1]), dtype=torch.float32,
+    extra = 2 * n_components if n_components > 8192 else 0      # per-node bookkeeping of large mixtures (see gmc_b200.h)
+    scratch = torch.empty((n_mix, (n_components - 1) * reduction_n * target_mixture.shape[-1] + extra), dtype=torch.float32,
                           device=target_mixture.device)
     with torch.cuda.device_of(target_mixture):
         _native.check(_native.lib.gmc_mhem_fit_backward(

@@ -10,6 +10,9 @@ from gmc import _native
 from gmc.cpp.extensions.convolution.binding import _dims
 
 
+SHARED_MEMORY_TREE_MAX = 8192      # products per tree that gmc_convolution_fitting_forward builds in shared memory
+
+
 def forward(data: torch.Tensor, kernels: torch.Tensor, n_components_fitting: int):
     """-> (fitting [B, Cout, K, V], cached_pos_covs [B, Cout, K, D*D], nodesobjs int32 [B, Cout, T],
     fitting_subtrees int32 [B, Cout, 2K])."""
@@ -25,9 +28,20 @@ def forward(data: torch.Tensor, kernels: torch.Tensor, n_components_fitting: int
     nodesobjs = torch.empty((n_batch, n_out, T), dtype=torch.int32, device=dev)
     subtrees = torch.empty((n_batch, n_out, 2 * K), dtype=torch.int32, device=dev)
     with torch.cuda.device_of(data):
-        _native.check(_native.lib.gmc_convolution_fitting_forward(
-            _native.ptr(data), _native.ptr(kernels), *dims, K, _native.ptr(fitting), _native.ptr(cached),
-            _native.ptr(nodesobjs), _native.ptr(subtrees), _native.stream_of(data)), "convolution_fitting forward")
+        if T > SHARED_MEMORY_TREE_MAX:
+            # trees too large for shared memory are built in global scratch
+            n_bytes = _native.lib.gmc_convolution_fitting_large_scratch_bytes(n_batch, n_in, n_comp, n_out, n_kcomp)
+            if n_bytes == 0:
+                raise _native.GmcError(f"convolution_fitting: {T} products per tree are beyond the limit of 65535")
+            scratch = torch.empty((n_bytes + 15) // 16 * 2, dtype=torch.int64, device=dev)
+            _native.check(_native.lib.gmc_convolution_fitting_forward_large(
+                _native.ptr(data), _native.ptr(kernels), *dims, K, _native.ptr(fitting), _native.ptr(cached),
+                _native.ptr(nodesobjs), _native.ptr(subtrees), _native.ptr(scratch), scratch.numel() * 8,
+                _native.stream_of(data)), "convolution_fitting forward (large trees)")
+        else:
+            _native.check(_native.lib.gmc_convolution_fitting_forward(
+                _native.ptr(data), _native.ptr(kernels), *dims, K, _native.ptr(fitting), _native.ptr(cached),
+                _native.ptr(nodesobjs), _native.ptr(subtrees), _native.stream_of(data)), "convolution_fitting forward")
     return fitting, cached, nodesobjs, subtrees
 
 

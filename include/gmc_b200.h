@@ -166,8 +166,10 @@ int gmc_integrate(const float* mixture, float* integrals, long long n_mixtures, 
  *   nodes    [n_mixtures, 2*n_components-1, 4] uint16 {parent, left, right, object}: internal nodes first
  *            (root = 0, object = own id), leaves at n_components-1 .. in sorted order (object = component id);
  *            fields without a value hold 0xFFFF.
- * 2 <= n_components <= 8192. Integer results are bit-identical to an IEEE fp32 evaluation of the reference
- * formulas; a box axis with zero extent (always z in 2D) contributes Morton cell 0.
+ * 2 <= n_components <= 32768 (node indices are 16 bit with 0xFFFF = none; the reference lets up to 65534 through, but
+ * its uint16 node indices wrap beyond 32768). Up to 8192 components the tree is built in shared memory, above that in
+ * global memory (the node buffer doubles as sort scratch before it is written). Integer results are bit-identical to an
+ * IEEE fp32 evaluation of the reference formulas; a box axis with zero extent (always z in 2D) contributes Morton cell 0.
  *
  * Replaces lbvh::Bvh<D,float>::construct with make_aabbs=false
  * (src/gmc/cpp/extensions/lbvh/bvh.cu:23-144, 241-299, 373-458; lbvh/morton_code.h; lbvh/building.h).
@@ -177,12 +179,13 @@ int gmc_lbvh_build(const float* mixture, long long n_mixtures, int n_components,
 
 /* ------------------------------------------------------------------------------------------------
  * BVH-MHEM reduction: fits n_components_fitting (K, a multiple of reduction_n) Gaussians to each covariance-form
- * mixture of n_components Gaussians (2 <= n_components <= 8192, reduction_n R in {2,4}).
+ * mixture of n_components Gaussians (2 <= n_components <= 32768, reduction_n R in {2,4}).
  *   fitting        [n_mixtures, K, 1+D+D*D]            out; unused slots are (0, 0, identity)
  *   bvh_nodes      [n_mixtures, 2*n_components-1, 4]   out; as gmc_lbvh_build
  *   bvh_attributes [n_mixtures, gmc_mhem_fit_attribute_floats(...)] fp32, out; per internal node
  *                  [R Gaussians | integral | count | R initial indices (uint8) | reserved]; input of the backward
- *   scratch_keys   [n_mixtures, n_components] uint64   scratch (sorted Morton keys on return)
+ *   scratch_keys   [n_mixtures, n_components] uint64   scratch (sorted Morton keys on return for n_components <= 8192;
+ *                  larger mixtures reuse it for the fit's per-node bookkeeping, so its content is undefined then)
  * Weights are expected non-negative (the network applies the fit after the ReLU fixed-point step).
  *
  * Replaces bvh_mhem_fit_forward (src/gmc/cpp/extensions/bvh_mhem_fit/bindings.cpp:11-22,
@@ -195,8 +198,9 @@ int gmc_mhem_fit_forward(const float* mixture, long long n_mixtures, int n_compo
 
 /* Gradient of gmc_mhem_fit_forward with the tree, the node selection, the initial representatives and the KL gate
  * held fixed. grad is [n_mixtures, K, V]; mixture, bvh_nodes and bvh_attributes are the forward's input / outputs (not
- * modified); scratch_node_grad is [n_mixtures, (n_components-1) * reduction_n * V] floats of scratch;
- * grad_mixture [n_mixtures, n_components, V] is fully overwritten.
+ * modified); scratch_node_grad is [n_mixtures, (n_components-1) * reduction_n * V] floats of scratch, followed for
+ * n_components > 8192 by 2 * n_components more floats per mixture (per-node bookkeeping that no longer fits in shared
+ * memory); grad_mixture [n_mixtures, n_components, V] is fully overwritten.
  *
  * Replaces bvh_mhem_fit_backward (src/gmc/cpp/extensions/bvh_mhem_fit/bindings.cpp:24-40,
  * implementation_backward.h:41-594). Unlike the reference, the saved attributes are not overwritten, so the same
@@ -238,6 +242,19 @@ int gmc_convolution_fitting_forward(const float* data, const float* kernels, int
                                     int n_components, int n_channels_out, int n_kernel_components, int n_dims,
                                     int n_components_fitting, float* fitting, float* cached_pos_covs,
                                     int32_t* nodesobjs, int32_t* fitting_subtrees, void* stream);
+/* The same operator for trees of more than 8192 products (up to 65535; the reference indexes products with 32 bits,
+ * src/gmc/cpp/extensions/convolution_fitting/Tree.cu:29-30): the tree is built in caller-provided global scratch instead
+ * of shared memory (one CTA per tree; slower per product). scratch must be 16-byte aligned and hold
+ * gmc_convolution_fitting_large_scratch_bytes(...) bytes (0 = sizes out of range); its content is undefined afterwards.
+ * Results obey the same rules as gmc_convolution_fitting_forward, whose outputs it fills. */
+size_t gmc_convolution_fitting_large_scratch_bytes(int n_batch, int n_channels_in, int n_components, int n_channels_out,
+                                                   int n_kernel_components);
+int gmc_convolution_fitting_forward_large(const float* data, const float* kernels, int n_batch, int n_channels_in,
+                                          int n_components, int n_channels_out, int n_kernel_components, int n_dims,
+                                          int n_components_fitting, float* fitting, float* cached_pos_covs,
+                                          int32_t* nodesobjs, int32_t* fitting_subtrees, void* scratch,
+                                          size_t scratch_bytes, void* stream);
+
 
 /* Gradient of gmc_convolution_fitting_forward with the tree frozen. grad is [n_batch, n_channels_out, K, V]; fitting,
  * cached_pos_covs, nodesobjs and fitting_subtrees are the forward's outputs (not modified). grad_data (like data) and

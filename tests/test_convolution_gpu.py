@@ -64,6 +64,36 @@ def test_convolution_fitting_forward_matches_oracle(D, B, Cin, G, Cout, Gk, K):
     assert err.max() <= 1e-3
 
 
+@pytest.mark.parametrize("D,B,Cin,G,Cout,Gk,K", [(2, 2, 8, 1024, 2, 5, 128),      # T = 40960
+                                                 (3, 1, 4, 512, 3, 5, 64),        # T = 10240
+                                                 (2, 1, 1, 8193, 1, 1, 16)])      # just above the shared-memory size
+def test_convolution_fitting_of_large_trees_matches_oracle(D, B, Cin, G, Cout, Gk, K):
+    """More than 8192 products per tree: the tree is built in global scratch (gmc_convolution_fitting_forward_large).
+    Same permutation, same subtree ranges, same values; the backward runs on the same outputs."""
+    import gmc.cpp.extensions.convolution_fitting.binding as cf
+    from oracle import autograd_oracles
+    data, kernels = _inputs(D, B, Cin, G, Cout, Gk, 1000 + G + K)
+    data[0, 0, 10:20, 1:1 + D] = data[0, 0, 9:10, 1:1 + D]          # equal Morton codes: ties keep ascending product index
+    d = data.cuda().requires_grad_(True)
+    k = kernels.cuda().requires_grad_(True)
+    fitting, cached, nodesobjs, subtrees = cf.forward(d.detach(), k.detach(), K)
+    ref, ref_cached, ref_objs, ref_sub = cpu_oracle.convolution_fitting_forward(data.numpy(), kernels.numpy(), K)
+    assert np.array_equal(nodesobjs.cpu().numpy(), ref_objs)
+    assert np.array_equal(subtrees.cpu().numpy(), ref_sub)
+    out = fitting.cpu().numpy()
+    for name, sl in (("weight", slice(0, 1)), ("position", slice(1, 1 + D)), ("covariance", slice(1 + D, None))):
+        assert rel_inf(out[..., sl], ref[..., sl]) < 1e-4, name
+    res = cf.apply(d, k, K)
+    g = torch.randn(res.shape, generator=torch.Generator().manual_seed(4))
+    res.backward(g.cuda())
+    gd, gk, _ = autograd_oracles.convolution_fitting_backward(g.numpy(), data.numpy(), kernels.numpy(), ref_objs, ref_sub)
+    for a, r in ((d.grad.cpu().numpy(), gd), (k.grad.cpu().numpy(), gk)):
+        scale = max(np.abs(r).max(), 1e-30)
+        assert float(np.abs(a - r).max() / scale) < 1e-4
+    with pytest.raises(RuntimeError):
+        cf.forward(torch.zeros(1, 1, 65536, 1 + D + D * D).cuda(), torch.zeros(1, 1, 1, 1 + D + D * D).cuda(), 4)
+
+
 def test_convolution_fitting_with_k_equal_t_is_the_exact_convolution():
     # the reference's own criterion (src/gmc/test_cpp_convolution_fitting.py:60-68, test_modules.py:89-108)
     import gmc.cpp.extensions.convolution_fitting.binding as cf

@@ -38,6 +38,52 @@ def test_lbvh_bit_exact(D, G):
     assert torch.equal(keys, keys2) and torch.equal(nodes, nodes2)      # deterministic
 
 
+@pytest.mark.parametrize("D,G", [(2, 8193), (2, 20000), (3, 20000), (2, 32768)])
+def test_lbvh_bit_exact_beyond_the_shared_memory_size(D, G):
+    """More than 8192 components per mixture: the tree is built in global memory. Same keys, same nodes."""
+    from gmc import lbvh
+    m = _mixture(D, 2, 1, G, 300 + G)
+    m[0, 0, 100:164, 1:1 + D] = m[0, 0, 99:100, 1:1 + D]          # equal Morton cells: the component id breaks the tie
+    keys, nodes = lbvh.build(m.cuda())
+    ref_keys, ref_nodes = cpu_oracle.lbvh_build(m.numpy())
+    assert np.array_equal(keys.cpu().numpy().view(np.uint64).reshape(-1, G), ref_keys)
+    assert np.array_equal(nodes.cpu().numpy().view(np.uint16).reshape(-1, 2 * G - 1, 4), ref_nodes)
+    with pytest.raises(RuntimeError):
+        lbvh.build(_mixture(D, 1, 1, 32769, 1).cuda())
+
+
+@pytest.mark.parametrize("D,G,K,R", [(2, 20000, 64, 4), (3, 9000, 32, 2)])
+def test_fit_of_large_mixtures_matches_oracle(D, G, K, R):
+    """The reference plans for mixtures of 2 000 to 20 000 components
+    (src/gmc/cpp/extensions/evaluate_inversed/parallel_implementation_optimised_backward.cu:121-125); above 8192 the
+    fit keeps its per-node bookkeeping in global scratch. Forward against the oracle, backward against the reference
+    library where it is present."""
+    import gmc.cpp.extensions.bvh_mhem_fit.binding as fit
+    from oracle import ref_native
+    m = _mixture(D, 1, 2, G, 5 * G + K)
+    RF = m.shape[-1]
+    mt = m.cuda().requires_grad_(True)
+    out = fit.apply(mt, K, R)
+    fitting, nodes, attribs = fit.forward(m.cuda(), K, R)
+    flat = m.numpy().reshape(-1, G, RF)
+    ref, dump = cpu_oracle.mhem_fit_forward(flat, K, R, dump=True)
+    assert np.array_equal(nodes.cpu().numpy().view(np.uint16).reshape(-1, 2 * G - 1, 4), dump["nodes"])
+    gaussians, integrals, counts, initial = _unpack_attrs(attribs, G, R, RF)
+    assert np.array_equal(counts, dump["counts"][:, :G - 1])
+    got = out.detach().cpu().numpy().reshape(-1, K, RF)
+    np.testing.assert_allclose(got, ref, rtol=5e-3, atol=1e-5)
+    err = cpu_oracle.density_rel_l2(got, ref, ref, res=64 if D == 2 else 24)
+    assert err.max() <= 1e-3
+    g = torch.randn(out.shape, generator=torch.Generator().manual_seed(2))
+    out.backward(g.cuda())
+    grad = mt.grad.cpu().numpy().reshape(-1, G, RF)
+    assert np.isfinite(grad).all() and np.abs(grad).max() > 0
+    if ref_native.available():
+        gref = ref_native.mhem_fit_backward(g.numpy(), m.numpy(), K, R)
+        scale = max(np.abs(gref).max(), 1e-30)
+        assert float(np.abs(grad - gref).max() / scale) <= 1e-4
+
+
 def test_lbvh_degenerate_axes_and_duplicate_positions():
     from gmc import lbvh
     m = _mixture(2, 1, 2, 33, 5)
