@@ -34,6 +34,43 @@ __device__ __forceinline__ uint32_t morton30(uint32_t qx, uint32_t qy, uint32_t 
     return (expand_bits3(qx) << 2) + (expand_bits3(qy) << 1) + expand_bits3(qz);
 }
 
+// Spreads the low 32 bits of v over the even bit positions of a 64-bit word.
+__device__ __forceinline__ uint64_t expand_bits2(uint32_t v) {
+    uint64_t t = v;
+    t = ((t << 16) | t) & 0x0000FFFF0000FFFFull;
+    t = ((t << 8) | t) & 0x00FF00FF00FF00FFull;
+    t = ((t << 4) | t) & 0x0F0F0F0F0F0F0F0Full;
+    t = ((t << 2) | t) & 0x3333333333333333ull;
+    t = ((t << 1) | t) & 0x5555555555555555ull;
+    return t;
+}
+
+// 10-bit cell of a value in [0, 1] (diagonal entry of the matrix slot over its per-mixture maximum).
+__device__ __forceinline__ uint32_t quantise_unit(float v) {
+    const float scaled = __fmul_rn(v, 1024.0f);
+    const uint32_t q = scaled > 0.0f ? __float2uint_rz(scaled) : 0u;
+    return min(q, 1023u);
+}
+
+// Sort key of one component from the 30-bit Morton codes of its position and of its matrix diagonal and its index:
+// layout 0 = position << 16 | id; 1 = 12 position bits, 36 bits position / diagonal interleaved, 16 bits id;
+// 2 = 54 interleaved bits, 10 bits id; 3 = 27 position, 27 diagonal, 10 id; 4 = 27 diagonal, 27 position, 10 id
+// (the reference's lbvh/morton_code.h:170-252; only layouts 0 and 1 keep the whole id in the low 16 bits).
+__device__ __forceinline__ uint64_t component_key(int layout, uint32_t pos, uint32_t cov, uint32_t id) {
+    switch (layout) {
+        case 0: return (uint64_t(pos) << 16) | uint64_t(id & 0xFFFFu);
+        case 1: {
+            uint64_t result = pos >> 18;
+            const uint64_t poscov = (expand_bits2(pos & 0x3FFFFu) << 1) | expand_bits2(cov >> 12);
+            result = (result << 36) | poscov;
+            return (result << 16) | uint64_t(id & 0xFFFFu);
+        }
+        case 2: return ((((expand_bits2(pos) << 1) | expand_bits2(cov)) << 4) & 0xFFFFFFFFFFFFFC00ull) | uint64_t(id & 0xFFFFu);
+        case 3: return (uint64_t(pos & ~0x7u) << 34) | (uint64_t(cov & ~0x7u) << 7) | uint64_t(id & 0x3FFu);
+        default: return (uint64_t(cov & ~0x7u) << 34) | (uint64_t(pos & ~0x7u) << 7) | uint64_t(id & 0x3FFu);
+    }
+}
+
 // Sorts keys[0 .. n_pow2) ascending; n_pow2 is a power of two, entries beyond the real count hold ~0ull.
 // All threads of the CTA must call it.
 __device__ __forceinline__ void bitonic_sort_shared(uint64_t* keys, int n_pow2) {

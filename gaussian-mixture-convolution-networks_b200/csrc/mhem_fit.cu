@@ -18,7 +18,7 @@
 
 namespace gmc {
 
-int lbvh_build_launch(const float* mixture, long long n_mixtures, int n_components, int n_dims, uint64_t* sorted_keys,
+int lbvh_build_launch(const float* mixture, long long n_mixtures, int n_components, int n_dims, int layout, uint64_t* sorted_keys,
                       uint16_t* nodes, cudaStream_t stream);
 
 namespace {
@@ -969,7 +969,7 @@ extern "C" int gmc_mhem_fit_forward(const float* mixture, long long n_mixtures, 
     if (!mixture || !fitting || !bvh_nodes || !bvh_attributes || !scratch_keys) return GMC_ERR_NULL_POINTER;
     cudaStream_t st = as_stream(stream);
     uint16_t* nodes = reinterpret_cast<uint16_t*>(bvh_nodes);
-    if (int s = lbvh_build_launch(mixture, n_mixtures, n_components, n_dims, scratch_keys, nodes, st)) return s;
+    if (int s = lbvh_build_launch(mixture, n_mixtures, n_components, n_dims, 0, scratch_keys, nodes, st)) return s;
     // the Morton keys are dead once the nodes exist: for large mixtures their buffer (8 bytes per component) takes the
     // per-node bookkeeping of the fit kernel (at most 8 bytes per component, see big_scratch_bytes)
     unsigned char* big = reinterpret_cast<unsigned char*>(scratch_keys);
@@ -1060,7 +1060,7 @@ extern "C" int gmc_mhem_fit_forward_noalloc(const float* mixture, long long n_mi
     cudaStream_t st = as_stream(stream);
     uint16_t* nodes = reinterpret_cast<uint16_t*>(bvh_nodes);
     // every key slot that is read is written first by the build kernel, so the array needs no clearing between calls
-    if (int s = lbvh_build_launch(mixture, n_mixtures, n_components, n_dims, keys, nodes, st)) return s;
+    if (int s = lbvh_build_launch(mixture, n_mixtures, n_components, n_dims, 0, keys, nodes, st)) return s;
     unsigned char* big = reinterpret_cast<unsigned char*>(keys);     // dead keys = bookkeeping of large mixtures
     if (n_dims == 2) {
         return reduction_n == 2

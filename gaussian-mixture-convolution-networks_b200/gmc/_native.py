@@ -53,6 +53,8 @@ _declare("gmc_relu_fixed_point_layer", [_c_float_p] * 5 + [ctypes.c_longlong, _c
 _declare("gmc_matrix_inverse", [_c_float_p] * 2 + [ctypes.c_longlong, _c_int, _c_void_p])
 _declare("gmc_matrix_inverse_backward", [_c_float_p] * 3 + [ctypes.c_longlong, _c_int, _c_void_p])
 _declare("gmc_lbvh_build", [_c_float_p, ctypes.c_longlong, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p])
+_declare("gmc_lbvh_build_ex", [_c_float_p, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_int, ctypes.c_float, _c_void_p,
+                               _c_void_p, _c_void_p, _c_void_p])
 lib.gmc_mhem_fit_attribute_floats.restype = ctypes.c_size_t
 lib.gmc_mhem_fit_attribute_floats.argtypes = [_c_int, _c_int, _c_int]
 _declare("gmc_mhem_fit_forward", [_c_float_p, ctypes.c_longlong, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,

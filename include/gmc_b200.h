@@ -177,6 +177,24 @@ int gmc_integrate(const float* mixture, float* integrals, long long n_mixtures, 
 int gmc_lbvh_build(const float* mixture, long long n_mixtures, int n_components, int n_dims,
                    uint64_t* sorted_keys, int16_t* nodes, void* stream);
 
+/* The same build with the options of lbvh::Config (src/gmc/cpp/extensions/lbvh/Config.h).
+ *   morton_code_algorithm  0 Old (gmc_lbvh_build), 1 Cov1_12p36pc16i, 2 Cov2_54pc10i, 3 Cov3_27p27c10i, 4 Cov4_27c27p10i:
+ *                          key layouts that mix the 30-bit Morton code of the diagonal of the matrix slot (each axis
+ *                          divided by its maximum over the mixture) into the key (lbvh/morton_code.h:170-252,
+ *                          lbvh/bvh.cu:254-276). The object of a leaf is the low 16 bits of its key, as in the reference;
+ *                          layouts 2..4 keep only 10 index bits there.
+ *   make_aabbs != 0        also writes aabbs [n_mixtures, 2*n_components-1, 8] fp32 = {upper.x,y,z,0, lower.x,y,z,0}
+ *                          (z = 0 in 2D): leaves = box of the ellipsoid where the component's density falls to
+ *                          aabb_threshold (> 0), at least the 95 % ellipsoid; internal nodes = union of their children
+ *                          (lbvh/bvh.cu:164-231, 460-510). The matrix slot must then hold INVERSE covariances
+ *                          (lbvh/bvh.cu:204). Only with algorithms 0 and 1 (the leaf must name its component);
+ *                          others return GMC_ERR_UNSUPPORTED. aabbs may be NULL when make_aabbs == 0.
+ * Keys and nodes are bit-identical to the reference's; boxes agree to fp32 rounding of the closed-form
+ * eigen-decomposition (math/symeig_detail.h). */
+int gmc_lbvh_build_ex(const float* mixture, long long n_mixtures, int n_components, int n_dims,
+                      int morton_code_algorithm, int make_aabbs, float aabb_threshold, uint64_t* sorted_keys,
+                      int16_t* nodes, float* aabbs, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * BVH-MHEM reduction: fits n_components_fitting (K, a multiple of reduction_n) Gaussians to each covariance-form
  * mixture of n_components Gaussians (2 <= n_components <= 32768, reduction_n R in {2,4}).

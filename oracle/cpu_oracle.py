@@ -92,6 +92,60 @@ def lbvh_build(mixture: np.ndarray):
     return keys, nodes
 
 
+def lbvh_build_ex(mixture: np.ndarray, algorithm: int = 0, make_aabbs: bool = False, aabb_threshold: float = 0.001):
+    """LBVH build with the options of lbvh::Config -> (keys, nodes[, aabbs fp32 [n, 2G-1, 8]]). With make_aabbs the
+    matrix slot of the mixture must hold inverse covariances."""
+    flat, G, D = _flat_mixtures(mixture)
+    n = flat.shape[0]
+    keys = np.empty((n, G), dtype=np.uint64)
+    nodes = np.empty((n, 2 * G - 1, 4), dtype=np.uint16)
+    aabbs = np.empty((n, 2 * G - 1, 8), dtype=np.float32) if make_aabbs else None
+    rc = lib().oracle_lbvh_build_ex(_p(flat), ctypes.c_int(n), ctypes.c_int(G), ctypes.c_int(D), ctypes.c_int(algorithm),
+                                    ctypes.c_int(int(make_aabbs)), ctypes.c_float(aabb_threshold), _p(keys), _p(nodes), _p(aabbs))
+    assert rc == 0
+    return (keys, nodes, aabbs) if make_aabbs else (keys, nodes)
+
+
+def compare_lbvh_boxes(mixture: np.ndarray, nodes: np.ndarray, boxes: np.ndarray, expected: np.ndarray, threshold: float,
+                       tolerance: float = 1e-3, min_gap: float = 0.05):
+    """Checks LBVH boxes `boxes` [n, 2G-1, 8] of inverse-covariance mixtures against `expected`.
+
+    The reference's leaf half-extents delta[r]^2 = factor^2 * sum_k lambda_k v_r[k]^2 depend on the eigenVECTORS of the
+    covariance, so two close eigenvalues make them a function of the rounding (any basis of the shared eigenspace is
+    valid). Hence: (1) leaves whose eigenvalues are separated by more than min_gap (relative) agree within `tolerance`
+    of the largest coordinate; (2) every leaf keeps 0 < delta^2 <= factor^2 lambda_max (the closed form's third
+    vector is a cross product of two unit vectors, shorter than 1 when those are not orthogonal) and is centred on its mean; (3) every internal box is EXACTLY the union of its children's boxes. Returns the worst error of (1)."""
+    flat, G, D = _flat_mixtures(mixture)
+    n = flat.shape[0]
+    nodes = nodes.reshape(n, 2 * G - 1, 4).astype(np.int64)
+    boxes = boxes.reshape(n, 2 * G - 1, 8)
+    expected = expected.reshape(n, 2 * G - 1, 8)
+    scale = np.abs(expected).max()
+    leaves = nodes[:, G - 1:, 3]                                          # component of every leaf
+    comp = np.take_along_axis(flat, leaves[..., None], axis=1)            # [n, G, RF]
+    cov = np.linalg.inv(comp[..., 1 + D:].reshape(n, G, D, D).astype(np.float64))
+    lam = np.linalg.eigvalsh(0.5 * (cov + np.swapaxes(cov, -1, -2)))
+    gap = (np.diff(lam, axis=-1) / lam[..., -1:]).min(-1)
+    factor2 = np.maximum(-2.0 * np.log(threshold / np.abs(comp[..., 0].astype(np.float64))), 5.991464547107982)
+    lb, le = boxes[:, G - 1:], expected[:, G - 1:]
+    err = np.abs(lb - le).max(-1)
+    well = gap > min_gap
+    assert well.mean() > 0.5, "test mixtures must mostly have separated eigenvalues"
+    worst = float(err[well].max() / scale)
+    assert worst <= tolerance, f"leaf boxes off by {worst:.2e} of the extent"
+    half = 0.5 * (lb[..., :D] - lb[..., 4:4 + D]).astype(np.float64)
+    centre = 0.5 * (lb[..., :D] + lb[..., 4:4 + D]).astype(np.float64)
+    assert np.abs(centre - comp[..., 1:1 + D]).max() <= 1e-5 * scale
+    hi = factor2[..., None] * lam[..., -1:] * (1 + 1e-3)
+    assert ((half > 0) & (half ** 2 <= hi)).all(), "leaf half-extents outside (0, lambda_max * factor^2]"
+    assert (boxes[..., 3] == 0).all() and (boxes[..., 7] == 0).all() and (boxes[..., D:3] == 0).all()
+    left = np.take_along_axis(boxes, nodes[:, :G - 1, 1:2], axis=1)
+    right = np.take_along_axis(boxes, nodes[:, :G - 1, 2:3], axis=1)
+    union = np.concatenate((np.maximum(left[..., :4], right[..., :4]), np.minimum(left[..., 4:], right[..., 4:])), -1)
+    assert np.array_equal(boxes[:, :G - 1], union), "internal boxes are not the union of their children"
+    return worst
+
+
 def mhem_fit_forward(mixture: np.ndarray, K: int, R: int, nodes: np.ndarray = None, dump: bool = False):
     """Restated BVH-MHEM fit: mixture [..., G, V] (covariance form) -> fitting [n, K, V]
     (+ per-node Gaussians / counts / integrals / initial indices when dump=True)."""

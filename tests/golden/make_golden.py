@@ -328,7 +328,43 @@ def inout_files(gm):
     np.savez_compressed(os.path.join(folder, "expected.npz"), **expected)
 
 
+def lbvh_option_cases():
+    """LBVH builds of the reference's native CPU code with the options of lbvh::Config: the five key layouts, and
+    make_aabbs with layouts 0 and 1 (mixtures in inverse-covariance form, as lbvh/bvh.cu:204 expects)."""
+    from oracle import ref_native
+    cases = {}
+    idx = 0
+    for mi, (D, G) in enumerate(((2, 50), (3, 50), (2, 333), (3, 600))):
+        g = torch.Generator().manual_seed(9000 + 10 * D + G)
+        w = torch.rand(2, 2, G, generator=g) * 2 - 1
+        w = torch.where(w.abs() < 0.05, torch.full_like(w, 0.05), w)
+        p = torch.rand(2, 2, G, D, generator=g) * 2 - 1
+        A = torch.rand(2, 2, G, D, D, generator=g) * 2 - 1
+        cov = (A @ A.transpose(-1, -2) + torch.eye(D) * 0.2) * 0.05
+        inv = torch.linalg.inv(cov.double())
+        inv = (0.5 * (inv + inv.transpose(-1, -2))).float()
+        m = torch.cat((w.unsqueeze(-1), p, inv.reshape(2, 2, G, D * D)), -1).contiguous().numpy()
+        for algorithm in range(5):
+            for make_aabbs in ((False, True) if algorithm < 2 else (False,)):
+                out = ref_native.lbvh_build(m, algorithm, make_aabbs, 0.001)
+                key = f"lbvh{idx:02d}"
+                cases[f"mixture{mi}"] = m
+                cases[key + "_options"] = np.array([mi, algorithm, int(make_aabbs)])
+                cases[key + "_keys"], cases[key + "_nodes"] = out[0], out[1]
+                if make_aabbs:
+                    cases[key + "_aabbs"] = out[2]
+                idx += 1
+    cases["n_cases"] = np.array(idx)
+    return cases
+
+
 def main():
+    if "--lbvh-options" in sys.argv:
+        from oracle import build_ref
+        build_ref.build()
+        np.savez_compressed(os.path.join(HERE, "reference_lbvh_options.npz"), **lbvh_option_cases())
+        print("wrote reference_lbvh_options.npz")
+        return
     if "--network" in sys.argv:
         from oracle import build_ref
         build_ref.build()
@@ -344,6 +380,8 @@ def main():
     build_ref.build()
     np.savez_compressed(os.path.join(HERE, "reference_native.npz"), **reference_native_cases(reference_root))
     print("wrote reference_native.npz")
+    np.savez_compressed(os.path.join(HERE, "reference_lbvh_options.npz"), **lbvh_option_cases())
+    print("wrote reference_lbvh_options.npz")
     gm, fitting, mat_tools = ref_python.load()
     np.savez_compressed(os.path.join(HERE, "eval_inversed.npz"), **eval_cases(gm))
     print("wrote eval_inversed.npz")

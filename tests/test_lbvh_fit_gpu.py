@@ -1,9 +1,12 @@
 """GPU parity of the LBVH build (bit-exact keys / permutation / topology) and of the BVH-MHEM fit forward (node
 level and relative L2 density error <= 1e-3 on a 64^D grid) against the CPU oracle."""
+import os
+
 import numpy as np
 import pytest
 import torch
 
+from conftest import ROOT
 from oracle import cpu_oracle
 import synthetic_inputs as synthetic
 
@@ -50,6 +53,68 @@ def test_lbvh_bit_exact_beyond_the_shared_memory_size(D, G):
     assert np.array_equal(nodes.cpu().numpy().view(np.uint16).reshape(-1, 2 * G - 1, 4), ref_nodes)
     with pytest.raises(RuntimeError):
         lbvh.build(_mixture(D, 1, 1, 32769, 1).cuda())
+
+
+def _inverse_form_mixture(D, B, L, G, seed):
+    g = torch.Generator().manual_seed(seed)
+    _, inv = synthetic.covariances_and_inverses((B, L, G), D, 0.05, 0.5, g)
+    w = torch.rand(B, L, G, generator=g) * 2 - 1
+    w = torch.where(w.abs() < 0.05, torch.full_like(w, 0.05), w)
+    p = torch.rand(B, L, G, D, generator=g) * 2 - 1
+    return synthetic.pack(w, p, inv)
+
+
+@pytest.mark.parametrize("D,G", [(2, 50), (3, 333), (2, 4000), (3, 9000)])
+@pytest.mark.parametrize("algorithm", [0, 1, 2, 3, 4])
+def test_lbvh_key_layouts_bit_exact(D, G, algorithm):
+    """The covariance-aware key layouts of lbvh::Config::MortonCodeAlgorithm: keys and nodes bit-exact against the
+    oracle (itself bit-exact against the reference library, tests/test_oracle_vs_reference.py), shared-memory and
+    global-memory build."""
+    from gmc import lbvh
+    m = _inverse_form_mixture(D, 2, 2, G, 500 + G + algorithm)
+    keys, nodes = lbvh.build(m.cuda(), morton_code_algorithm=algorithm)
+    ref_keys, ref_nodes = cpu_oracle.lbvh_build_ex(m.numpy(), algorithm)
+    assert np.array_equal(keys.cpu().numpy().view(np.uint64).reshape(-1, G), ref_keys)
+    assert np.array_equal(nodes.cpu().numpy().view(np.uint16).reshape(-1, 2 * G - 1, 4), ref_nodes)
+
+
+@pytest.mark.parametrize("D,G,algorithm,threshold", [(2, 50, 0, 0.001), (3, 333, 1, 0.001), (3, 64, 0, 0.05), (2, 9000, 1, 0.01)])
+def test_lbvh_boxes(D, G, algorithm, threshold):
+    """make_aabbs: ellipsoid boxes of the leaves and their unions (lbvh/bvh.cu:164-231, 460-510), see
+    cpu_oracle.compare_lbvh_boxes for the bars. Repeated launches give identical boxes."""
+    from gmc import lbvh
+    m = _inverse_form_mixture(D, 2, 3, G, 700 + G)
+    keys, nodes, boxes = lbvh.build(m.cuda(), algorithm, True, threshold)
+    ref_keys, ref_nodes, ref_boxes = cpu_oracle.lbvh_build_ex(m.numpy(), algorithm, True, threshold)
+    assert np.array_equal(keys.cpu().numpy().view(np.uint64).reshape(-1, G), ref_keys)
+    nodes_np = nodes.cpu().numpy().view(np.uint16).reshape(-1, 2 * G - 1, 4)
+    assert np.array_equal(nodes_np, ref_nodes)
+    worst = cpu_oracle.compare_lbvh_boxes(m.numpy(), nodes_np, boxes.cpu().numpy(), ref_boxes, threshold)
+    print(f"lbvh boxes D={D} G={G}: worst leaf error {worst:.2e} of the extent")
+    _, _, again = lbvh.build(m.cuda(), algorithm, True, threshold)
+    assert torch.equal(boxes, again)
+    with pytest.raises(RuntimeError):
+        lbvh.build(m.cuda(), 2, True, threshold)      # the leaf of layouts 2..4 does not name its component
+
+
+def test_lbvh_boxes_against_reference_fixture():
+    """The boxes of the reference library itself (tests/golden/reference_lbvh_options.npz)."""
+    from gmc import lbvh
+    gold = dict(np.load(os.path.join(ROOT, "tests", "golden", "reference_lbvh_options.npz")))
+    checked = 0
+    for i in range(int(gold["n_cases"])):
+        key = f"lbvh{i:02d}"
+        mi, algorithm, make_aabbs = (int(v) for v in gold[key + "_options"])
+        m = gold[f"mixture{mi}"]
+        G = m.shape[-2]
+        out = lbvh.build(torch.from_numpy(m).cuda(), algorithm, bool(make_aabbs), 0.001)
+        assert np.array_equal(out[0].cpu().numpy().view(np.uint64).reshape(-1, G), gold[key + "_keys"])
+        nodes_np = out[1].cpu().numpy().view(np.uint16).reshape(-1, 2 * G - 1, 4)
+        assert np.array_equal(nodes_np, gold[key + "_nodes"])
+        if make_aabbs:
+            cpu_oracle.compare_lbvh_boxes(m, nodes_np, out[2].cpu().numpy(), gold[key + "_aabbs"], 0.001)
+            checked += 1
+    assert checked >= 8
 
 
 @pytest.mark.parametrize("D,G,K,R", [(2, 20000, 64, 4), (3, 9000, 32, 2)])

@@ -208,3 +208,47 @@ def test_library_evaluation(reference_library):
         gm_o, gx_o = cpu_oracle.eval_backward(g, m, x)
         gm_r, gx_r = reference_library.eval_backward(g, m, x)
         assert rel_inf(gm_o, gm_r) <= 5e-6 and rel_inf(gx_o, gx_r) <= 5e-6
+
+
+def test_golden_lbvh_options():
+    """Key layouts 0..4 and make_aabbs of lbvh::Config: the oracle against tests/golden/reference_lbvh_options.npz
+    (reference library outputs). Keys and nodes bit-exact; boxes by cpu_oracle.compare_lbvh_boxes (1e-3 of the extent for
+    leaves with separated eigenvalues, exact union for internal nodes)."""
+    gold = dict(np.load(os.path.join(ROOT, "tests", "golden", "reference_lbvh_options.npz")))
+    n = int(gold["n_cases"])
+    assert n >= 20
+    worst = 0.0
+    for i in range(n):
+        key = f"lbvh{i:02d}"
+        mi, algorithm, make_aabbs = (int(v) for v in gold[key + "_options"])
+        m = gold[f"mixture{mi}"]
+        out = cpu_oracle.lbvh_build_ex(m, algorithm, bool(make_aabbs), 0.001)
+        assert np.array_equal(out[0], gold[key + "_keys"]), f"{key}: keys, layout {algorithm}"
+        assert np.array_equal(out[1], gold[key + "_nodes"]), f"{key}: nodes, layout {algorithm}"
+        if make_aabbs:
+            worst = max(worst, cpu_oracle.compare_lbvh_boxes(m, out[1], out[2], gold[key + "_aabbs"], 0.001))
+            # the reference's own boxes pass the same structural checks
+            cpu_oracle.compare_lbvh_boxes(m, gold[key + "_nodes"], gold[key + "_aabbs"], gold[key + "_aabbs"], 0.001)
+    print(f"lbvh boxes oracle vs reference native: worst {worst:.2e} of the extent")
+
+
+def test_library_lbvh_options(reference_library):
+    m = synthetic_inverse_mixture(3, 2, 3, 200, 77)
+    for algorithm in range(5):
+        a = cpu_oracle.lbvh_build_ex(m, algorithm)
+        b = reference_library.lbvh_build(m, algorithm)
+        assert np.array_equal(a[0], b[0]) and np.array_equal(a[1], b[1])
+    a = cpu_oracle.lbvh_build_ex(m, 1, True, 0.01)
+    b = reference_library.lbvh_build(m, 1, True, 0.01)
+    assert np.array_equal(a[1], b[1])
+    cpu_oracle.compare_lbvh_boxes(m, a[1], a[2], b[2], 0.01)
+
+
+def synthetic_inverse_mixture(D, B, L, G, seed):
+    import torch
+    import synthetic_inputs as synthetic
+    g = torch.Generator().manual_seed(seed)
+    _, inv = synthetic.covariances_and_inverses((B, L, G), D, 0.05, 0.5, g)
+    w = torch.rand(B, L, G, generator=g) * 2 - 1
+    p = torch.rand(B, L, G, D, generator=g) * 2 - 1
+    return synthetic.pack(w, p, inv).numpy()
