@@ -170,6 +170,9 @@ convolution_fitting_tree_kernel(const float* __restrict__ data, const float* __r
         keys_a[t] = (sign << 62) | (uint64_t(lbvh::morton30(q[0], q[1], q[2])) << 32) | uint64_t(uint32_t(t));
     }
     __syncthreads();
+    // (sorting on the top 16 or 24 code bits first and ordering the runs of equal top bits afterwards was measured: the
+    // products of the deeper network layers crowd into few Morton cells, runs of 128 equal top-16 prefixes per tree, and
+    // with 24 bits the run pass costs what the saved radix pass did)
     const uint64_t* keys = lbvh::radix_sort_shared(keys_a, keys_b, T, 32, 4, radix_scratch);   // 4 passes: back in A
 
     // ---- leaves; common prefix lengths of neighbouring codes; empty slots ----
@@ -241,6 +244,29 @@ convolution_fitting_tree_kernel(const float* __restrict__ data, const float* __r
     for (int round = 1; round < kMaxLevels; ++round) {
         const int n_in = queue_count[round];
         if (n_in == 0) break;
+        if (n_in <= 32) {
+            // the number of completed nodes never grows from round to round (every arrival completes at most one node):
+            // warp 0, which also runs the selection, finishes the narrow top of the tree without CTA barriers
+            if (warp == 0) {
+                for (int tail = round; tail < kMaxLevels; ++tail) {
+                    const int n_tail = queue_count[tail];
+                    if (n_tail == 0) break;
+                    const uint16_t* queue_in = queues + ((tail - 1) & 1) * queue_stride;
+                    uint32_t node = 0u, lr = 0u;
+                    float m = 0.f;
+                    if (lane < n_tail) {
+                        node = queue_in[lane];
+                        lr = ranges[node];
+                        const float2 masses = *reinterpret_cast<const float2*>(slots + node);
+                        m = __fadd_rn(masses.x, masses.y);
+                    }
+                    arrive(lane < n_tail, node, int(lr & 0xffffu), int(lr >> 16), m, queues + (tail & 1) * queue_stride,
+                           &queue_count[tail + 1]);
+                    __syncwarp();
+                }
+            }
+            break;
+        }
         const uint16_t* queue_in = queues + ((round - 1) & 1) * queue_stride;
         for (int i0 = 0; i0 < n_in; i0 += kThreads) {
             if (i0 + warp * 32 >= n_in) break;               // nothing queued for this warp (warp-uniform)

@@ -87,6 +87,7 @@ lbvh_build_kernel(const float* __restrict__ mixture, int n_components, int layou
     extern __shared__ __align__(16) unsigned char smem_bytes[];
     uint64_t* keys = reinterpret_cast<uint64_t*>(smem_bytes);
     __shared__ Extent<D> ext;
+    __shared__ int s_sort_fallback;
 
     const int G = n_components;
     const int tid = threadIdx.x;
@@ -94,11 +95,28 @@ lbvh_build_kernel(const float* __restrict__ mixture, int n_components, int layou
 
     mixture_extent<D, kThreads>(mix, G, layout, ext);
 
-    // ---- Morton keys ----
-    const int P = lbvh::next_pow2(G);
-    for (int g = tid; g < P; g += kThreads) keys[g] = g < G ? key_of_component<D>(mix, g, layout, ext) : ~0ull;
-    __syncthreads();
-    lbvh::bitonic_sort_shared(keys, P);
+    // ---- Morton keys, ascending ----
+    if (layout == 0) {
+        // sorted as (Morton code << 32 | id) by the radix sort that the convolution fit uses (its rank bits 16..31 must
+        // be free), then shifted back to the output format (code << 16 | id)
+        uint64_t* keys_b = keys + G;
+        for (int g = tid; g < G; g += kThreads) {
+            const uint64_t k = key_of_component<D>(mix, g, 0, ext);
+            keys[g] = ((k >> 16) << 32) | (k & 0xFFFFull);
+        }
+        __syncthreads();
+        const uint64_t* sorted = lbvh::sort_codes_shared<3>(keys, keys_b, G, keys_b + G, &s_sort_fallback);
+        for (int g = tid; g < G; g += kThreads) {             // element-wise, so in place or across the buffers alike
+            const uint64_t k = sorted[g];
+            keys[g] = ((k >> 32) << 16) | (k & 0xFFFFull);
+        }
+        __syncthreads();
+    } else {
+        const int P = lbvh::next_pow2(G);
+        for (int g = tid; g < P; g += kThreads) keys[g] = g < G ? key_of_component<D>(mix, g, layout, ext) : ~0ull;
+        __syncthreads();
+        lbvh::bitonic_sort_shared(keys, P);
+    }
 
     // ---- leaves and internal nodes ----
     uint64_t* out_keys = sorted_keys + size_t(blockIdx.x) * G;
@@ -277,7 +295,9 @@ int lbvh_build_launch(const float* mixture, long long n_mixtures, int n_componen
         GMC_LAUNCH_CHECK();
         return GMC_OK;
     }
-    const size_t smem = sizeof(uint64_t) * size_t(lbvh::next_pow2(n_components));
+    // layout 0: two key buffers + the radix scratch; other layouts: one power-of-two buffer for the bitonic network
+    const size_t smem = layout == 0 ? sizeof(uint64_t) * 2 * size_t(n_components) + 2 * ((kThreads / 32) * 256 + 256) + 32
+                                    : sizeof(uint64_t) * size_t(lbvh::next_pow2(n_components));
     if (n_dims == 2) {
         if (smem > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(lbvh_build_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
         lbvh_build_kernel<2><<<unsigned(n_mixtures), kThreads, smem, stream>>>(mixture, n_components, layout, sorted_keys, nodes);

@@ -174,6 +174,41 @@ __device__ __forceinline__ uint64_t* radix_sort_shared(uint64_t* a, uint64_t* b,
     return a;
 }
 
+// Ascending order of n unique keys whose bits 32..62 hold a code and whose low bits hold the input position (bit 63 and
+// bits 16..31 zero, n <= 8192; the input must already be in ascending position order among equal codes, which key
+// generation by position gives): the result equals a stable sort on the code bits.
+// TOP_PASSES stable 8-bit passes order the keys on their top 8 * TOP_PASSES code bits; a run of keys that share those
+// bits is then in input order, and each of its members finds its place by counting the smaller keys of the run (runs
+// are short when the codes spread over the top bits: Morton codes of scattered positions). A run longer than
+// kMaxRun makes the whole CTA fall back to the plain four passes over all 32 code bits, from the partially sorted
+// state (still in position order among equal codes). `flag` is one shared int. Returns the buffer with the result.
+constexpr int kMaxRun = 64;
+
+template <int TOP_PASSES>
+__device__ __forceinline__ uint64_t* sort_codes_shared(uint64_t* a, uint64_t* b, int n, void* scratch, int* flag) {
+    constexpr int kFirstBit = 63 - 8 * TOP_PASSES;
+    if (threadIdx.x == 0) *flag = 0;
+    uint64_t* cur = radix_sort_shared(a, b, n, kFirstBit, TOP_PASSES, scratch);      // ends with a CTA barrier
+    uint64_t* other = cur == a ? b : a;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const uint64_t key = cur[i];
+        const uint64_t top = key >> kFirstBit;
+        const bool left_same = i > 0 && (cur[i - 1] >> kFirstBit) == top;
+        const bool right_same = i + 1 < n && (cur[i + 1] >> kFirstBit) == top;
+        if (!left_same && !right_same) { other[i] = key; continue; }
+        int s = i, e = i + 1;
+        while (s > 0 && i - s <= kMaxRun && (cur[s - 1] >> kFirstBit) == top) --s;
+        while (e < n && e - i <= kMaxRun && (cur[e] >> kFirstBit) == top) ++e;
+        if (e - s > kMaxRun) { *flag = 1; continue; }
+        int rank = 0;
+        for (int j = s; j < e; ++j) rank += cur[j] < key ? 1 : 0;
+        other[s + rank] = key;
+    }
+    __syncthreads();
+    if (*flag == 0) return other;
+    return radix_sort_shared(cur, other, n, 32, 4, scratch);
+}
+
 // The same stable LSD radix sort for keys that live in GLOBAL memory (trees too large for shared memory): `a` and `b`
 // are global buffers of n keys, the rank that a key carries between the counting and the scatter loop sits in the
 // shared array `ranks` (n uint16) instead of in key bits, `scratch` as above. n < 65536. Sorted keys end up in `a` for an
