@@ -1,11 +1,22 @@
 /*
  * gmc_b200.h -- C ABI of the B200 (sm_100a) Gaussian-mixture operator library.
  *
- * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as void*,
- * nullptr = the legacy default stream) and returns an int status (GMC_OK == 0). The library
- * allocates nothing: outputs and scratch are owned by the caller. All kernels are enqueued on
- * the given stream and the call returns without synchronising. There is no CPU code path: a
+ * Every entry point takes plain pointers, sizes and a CUDA stream (passed as void*, nullptr = the
+ * legacy default stream) and returns an int status (GMC_OK == 0). There is no CPU code path: a
  * call on a machine without a CUDA device returns GMC_ERR_CUDA.
+ *
+ * Allocation, state and synchronisation, exactly:
+ *  - The device-pointer entry points (everything except the three named below) allocate nothing and keep
+ *    no state: outputs and scratch are owned by the caller, all kernels are enqueued on the given stream
+ *    and the call returns without synchronising. They may set function attributes (dynamic shared memory
+ *    size) on first use and can be captured in a CUDA graph.
+ *  - gmc_eval_inversed_host (HOST buffers) owns per-device state: four device slots (cudaMalloc on first
+ *    use, re-allocated when a larger problem arrives), six streams and twelve events, kept until
+ *    gmc_host_pipeline_release(). It blocks until the host outputs are complete; one mutex serialises the
+ *    calls of a process.
+ *  - gmc_device_check_word synchronises the whole device, gmc_sync_and_check the given stream; both read
+ *    and clear a per-device __device__ word that kernels set instead of hanging or trapping.
+ *  - gmc_mhem_fit_forward_noalloc uses an 8 MiB __device__ array inside the library as its scratch.
  *
  * Data layout (identical to the reference's packed mixtures, src/gmc/mixture.py:37-67 and
  * src/gmc/cpp/extensions/util/gaussian.h:14-46): a mixture is a contiguous fp32 array
@@ -50,14 +61,14 @@ int gmc_device_check_word(int* word_out);
  * check (the word is cleared), GMC_OK otherwise. Call it wherever the host synchronises anyway: device-side give-ups
  * never hang and never abort, this is how they become visible. Not for use during stream capture. */
 int gmc_sync_and_check(void* stream);
-/* Error-path test aid: the forward evaluation with its bulk copy deliberately left out, so that the bounded wait runs
- * out after about a thousand polls: every output becomes NaN and the check word gets bit 1. Nothing is in flight when
- * the kernel gives up; the context stays usable. No reference counterpart. */
 /* Test aid of the bounds-checked build (libgmc_b200_checked.so, compiled with -DGMC_BOUNDS_CHECK: every index that a
  * kernel reads from data -- tree children, object ids, sorted product indices -- is range-checked; a bad one sets bit 4
  * of the check word and is replaced by 0, so the access stays inside its array). Runs the check itself once on a
  * one-float buffer: index >= n must set the word and read element 0. Regular builds return GMC_ERR_UNSUPPORTED. */
 int gmc_debug_index_check(const float* one_float, float* out, long long index, long long n, void* stream);
+/* Error-path test aid: the forward evaluation with its bulk copy deliberately left out, so that the bounded wait runs
+ * out after about a thousand polls: every output becomes NaN and the check word gets bit 1. Nothing is in flight when
+ * the kernel gives up; the context stays usable. No reference counterpart. */
 int gmc_debug_eval_forward_lost_copy(const float* mixture, const float* xes, float* out, int n_batch, int n_layers,
                                      int n_components, int n_dims, int n_batch_xes, int n_layers_xes, int n_xes,
                                      void* stream);
