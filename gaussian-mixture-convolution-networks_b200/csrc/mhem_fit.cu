@@ -8,9 +8,11 @@
 //
 // Organisation on the GPU: one CTA per mixture. Tree levels (height above the leaves) are computed in shared memory
 // with the "second arriver continues" pass; levels are then processed in order, one warp per node, with the 2R x R
-// likelihood / KL / responsibility matrices spread one entry per lane. The heap-driven clustering of fit_initial is
-// sequential by nature and runs on lane 0. Node results live in a global attribute array that is also what the
-// backward pass reads: per internal node R Gaussians, the integral, the Gaussian count, the R initial indices.
+// likelihood / KL / responsibility matrices spread one entry per lane. The single-linkage clustering of fit_initial:
+// when all finite centre distances of a node differ, the heap's pop order is the rank of the distance, so the warp ranks
+// the pairs with shuffles and every lane merges the sub-graphs in registers; with equal distances the order among equal
+// keys is the heap's own, and lane 0 runs the restated heap. Node results live in a global attribute array that is also
+// what the backward pass reads: per internal node R Gaussians, the integral, the Gaussian count, the R initial indices.
 #include <mutex>
 
 #include "common.cuh"
