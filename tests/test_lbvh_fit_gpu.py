@@ -160,6 +160,26 @@ def test_lbvh_degenerate_axes_and_duplicate_positions():
     assert np.array_equal(nodes.cpu().numpy().view(np.uint16).reshape(-1, 65, 4), ref_nodes)
 
 
+@pytest.mark.parametrize("D", [2, 3])
+def test_lbvh_sort_with_crowded_cells(D):
+    """The shared-memory build orders the keys by their top code bits first and fixes runs of equal top bits afterwards;
+    runs longer than 64 fall back to full radix passes. Three mixtures: tight clusters (runs of 2..60 equal prefixes),
+    200 identical means (fall-back path), all means identical."""
+    from gmc import lbvh
+    G = 700
+    m = _mixture(D, 3, 1, G, 77)
+    g = torch.Generator().manual_seed(5)
+    centres = torch.rand(20, D, generator=g) * 2 - 1
+    m[0, 0, :, 1:1 + D] = centres[torch.randint(0, 20, (G,), generator=g)] + torch.randn(G, D, generator=g) * 1e-4
+    m[0, 0, :2, 1:1 + D] = torch.tensor([[-1.0] * D, [1.0] * D])          # keeps the box wide, the clusters narrow
+    m[1, 0, 100:300, 1:1 + D] = m[1, 0, 99:100, 1:1 + D]
+    m[2, 0, :, 1:1 + D] = m[2, 0, :1, 1:1 + D]
+    keys, nodes = lbvh.build(m.cuda())
+    ref_keys, ref_nodes = cpu_oracle.lbvh_build(m.numpy())
+    assert np.array_equal(keys.cpu().numpy().view(np.uint64).reshape(-1, G), ref_keys)
+    assert np.array_equal(nodes.cpu().numpy().view(np.uint16).reshape(-1, 2 * G - 1, 4), ref_nodes)
+
+
 def _unpack_attrs(attribs, G, R, RF):
     a = attribs.cpu().numpy().reshape(attribs.shape[0], G - 1, R * RF + 4)
     gaussians = a[..., :R * RF].reshape(a.shape[0], G - 1, R, RF)
