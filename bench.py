@@ -687,24 +687,32 @@ def secondary_block(args, config, rank, world, local_rank, n_batch, steps):
 
 
 def _count_kernels(torch, fn):
-    """Runs fn() once under the CUDA activity tracer -> (kernels of this library, all kernels). The library's kernels
-    live in namespace gmc. Without the tracer the count falls back to the library calls made (each launches >= 1)."""
+    """Runs fn() under the CUDA activity tracer -> (kernels of this library, all kernels) per call of fn. The library's
+    kernels live in namespace gmc. Without the tracer the count falls back to the library calls made (each launches
+    at least one kernel)."""
     from gmc import _native
     calls_before = _native.entry_calls()
+    runs = 0
     try:
         from torch.profiler import ProfilerActivity, profile
+        repeats = 3          # a single short step can end before the tracer has attached
         with profile(activities=[ProfilerActivity.CUDA]) as prof:
-            fn()
+            for _ in range(repeats):
+                fn()
+                runs += 1
             torch.cuda.synchronize()
         names = [e.name for e in prof.events() if "cuda" in str(getattr(e, "device_type", "")).lower()
                  and not e.name.lower().startswith(("memcpy", "memset"))]
         ours = sum(1 for n in names if "gmc::" in n)
-        if ours > 0:
-            return ours, len(names)
+        if ours >= repeats:
+            return ours // repeats, len(names) // repeats
     except Exception:
+        pass
+    if runs == 0:
         fn()
-        torch.cuda.synchronize()
-    return max(1, _native.entry_calls() - calls_before), None
+        runs = 1
+    torch.cuda.synchronize()
+    return max(1, (_native.entry_calls() - calls_before) // runs), None
 
 
 # ---------------------------------------------------------------------------------------------------------------
