@@ -487,7 +487,7 @@ def config1_block(args, rank, world, local_rank, b_rank, steps, with_e2e, with_p
                      "traffic": 32.79e6 * b_rank / 4, "traffic_unit": "bytes (ncu capture at B=4, scaled by B/4)",
                      "peak_source": peak_source, "peak_nominal": nominal, "frac_of_nominal": ach_bwd / nominal,
                      "algorithmic_flop_per_pair": FLOP_BWD, "ms_per_launch": bwd_ms},
-        "roofline_forward": {"bound": "fp32", "kernel": "eval_forward_kernel<3,8>", "achieved": ach_fwd,
+        "roofline_forward": {"bound": "fp32", "kernel": "eval_forward_kernel<3,4>", "achieved": ach_fwd,
                              "peak": peak, "unit": "TFLOP/s", "frac": ach_fwd / peak, "frac_of_nominal": ach_fwd / nominal,
                              "algorithmic_flop_per_pair": FLOP_FWD, "ms_per_launch": fwd_ms},
         "roofline_fwd_bwd": {"bound": "fp32", "achieved": ach_all, "peak": peak, "unit": "TFLOP/s",

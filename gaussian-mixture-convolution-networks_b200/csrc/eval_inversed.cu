@@ -9,7 +9,11 @@
 //            chunk-wise in shared memory (raw records arrive by one non-multicast bulk copy when the
 //            chunk is 16-byte aligned) and rewritten once per CTA into "ready" form
 //                c = w (2 pi)^(-D/2) sqrt(det S),  mu,  A = -1/2 log2(e) S  (off-diagonals folded)
-//            so the pair loop is   t = x - mu;  q = t^T A t;  acc += c * ex2(q)   (FMA pipe + one MUFU).
+//            so the pair loop is   t = x - mu;  q = t^T A t;  acc += c * ex2(q)   (FMA pipe + one MUFU),
+//            or, where its rounding allows (decided per chunk, see make_triangular), into "triangular" form
+//                c,  L with 1/2 log2(e) S = L L^T,  nb = -L^T mu
+//            with the shorter loop   y = L^T x + nb;  acc += c * ex2(-|y|^2)   (no subtraction per pair).
+//            Both loops work on coordinates relative to the centre of the tile's points.
 //            Every thread keeps P query points in registers and reads Gaussians as broadcast float4.
 //  backward: a CTA owns one (batch, layer), a tile of query points and a chunk of Gaussians. Every thread
 //            keeps GQ Gaussians and their 1 + D + D(D+1)/2 gradient sums in registers and streams the
@@ -27,10 +31,10 @@ namespace {
 #define GMC_FWD_CHUNK 256
 #endif
 #ifndef GMC_FWD_P
-#define GMC_FWD_P 8
+#define GMC_FWD_P 4
 #endif
 #ifndef GMC_FWD_MINB
-#define GMC_FWD_MINB 1
+#define GMC_FWD_MINB 6
 #endif
 #ifndef GMC_BWD_PPI
 #define GMC_BWD_PPI 2
@@ -66,6 +70,30 @@ __device__ __forceinline__ float2 ex2_2(float2 q) { return make_float2(ex2_appro
 
 constexpr float kExpScale = -0.5f * kLog2e;
 
+// 2^(-|y|^2) for the packed pair (y0, y1[, y2]). The packed instructions have no operand negation, the scalar FFMA has:
+// the last term is added by two scalar FFMAs that flip both signs on the way, instead of a packed FFMA plus two negations.
+#ifndef GMC_FWD_NEG
+#define GMC_FWD_NEG 1
+#endif
+__device__ __forceinline__ float2 ex2_of_minus_square(float2 y0, float2 y1) {
+#if GMC_FWD_NEG
+    const float2 w = mul2(y0, y0);
+    return make_float2(ex2_approx(fmaf(-y1.x, y1.x, -w.x)), ex2_approx(fmaf(-y1.y, y1.y, -w.y)));
+#else
+    const float2 z = fma2(y1, y1, mul2(y0, y0));
+    return make_float2(ex2_approx(-z.x), ex2_approx(-z.y));
+#endif
+}
+__device__ __forceinline__ float2 ex2_of_minus_square(float2 y0, float2 y1, float2 y2) {
+#if GMC_FWD_NEG
+    const float2 w = fma2(y1, y1, mul2(y0, y0));
+    return make_float2(ex2_approx(fmaf(-y2.x, y2.x, -w.x)), ex2_approx(fmaf(-y2.y, y2.y, -w.y)));
+#else
+    const float2 z = fma2(y2, y2, fma2(y1, y1, mul2(y0, y0)));
+    return make_float2(ex2_approx(-z.x), ex2_approx(-z.y));
+#endif
+}
+
 __device__ __forceinline__ float det2(const float* S) { return S[0] * S[3] - S[1] * S[2]; }
 __device__ __forceinline__ float det3(const float* S) {
     return S[0] * (S[4] * S[8] - S[5] * S[7]) - S[1] * (S[3] * S[8] - S[5] * S[6]) +
@@ -81,20 +109,68 @@ struct ReadyCount {
 };
 
 template <int D>
-__device__ __forceinline__ void make_ready(const float* r, float* out) {
+__device__ __forceinline__ void make_ready(const float* r, const float* origin, float* out) {
     if constexpr (D == 2) {
         const float* S = r + 3;
-        out[0] = -r[1]; out[1] = -r[2];
+        out[0] = origin[0] - r[1]; out[1] = origin[1] - r[2];
         out[2] = r[0] * kInv2Pi * sqrtf(det2(S));
         out[3] = kExpScale * S[0]; out[4] = kExpScale * (S[1] + S[2]); out[5] = kExpScale * S[3];
     } else {
         const float* S = r + 4;
-        out[0] = -r[1]; out[1] = -r[2]; out[2] = -r[3];
+        out[0] = origin[0] - r[1]; out[1] = origin[1] - r[2]; out[2] = origin[2] - r[3];
         out[3] = r[0] * kInv2Pi15 * sqrtf(det3(S));
         out[4] = kExpScale * S[0]; out[5] = kExpScale * (S[1] + S[3]); out[6] = kExpScale * (S[2] + S[6]);
         out[7] = kExpScale * S[4]; out[8] = kExpScale * (S[5] + S[7]); out[9] = kExpScale * S[8];
     }
 }
+
+// "triangular" form of one Gaussian for the short pair loop: with A = 1/2 log2(e) sym(S) = L L^T (Cholesky, L lower
+// triangular) the exponent is -|L^T (x - mu)|^2 in base 2, and y = L^T x' + nb with x' = x - origin,
+// nb = -L^T (mu - origin) needs no separate subtraction per pair: 9 multiply-adds for y and |y|^2 in 3D instead of 12.
+// 2D: nb0 nb1 c l00 l10 l11; 3D: nb0 nb1 nb2 c l00 l10 l20 l11 l21 l22 (the same record sizes as the ready form).
+// The price is rounding: y is a difference of terms of size |L| |x'|, so the form is only used where that size, bounded
+// by the largest absolute row sum of L^T (returned here; +inf if S is not positive definite) times the half extent of
+// the tile's points, keeps the error of the exponent far below the tolerance (see kTriangularLimit).
+template <int D>
+__device__ __forceinline__ float make_triangular(const float* r, const float* origin, float* out) {
+    constexpr float k = 0.5f * kLog2e;
+    if constexpr (D == 2) {
+        const float* S = r + 3;
+        const float a00 = k * S[0], a01 = 0.5f * k * (S[1] + S[2]), a11 = k * S[3];
+        const float l00 = sqrtf(a00), l10 = a01 / l00;
+        const float d1 = a11 - l10 * l10;
+        const float l11 = sqrtf(d1);
+        const float m0 = r[1] - origin[0], m1 = r[2] - origin[1];
+        out[0] = -(l00 * m0 + l10 * m1);
+        out[1] = -(l11 * m1);
+        out[2] = r[0] * kInv2Pi * sqrtf(det2(S));
+        out[3] = l00; out[4] = l10; out[5] = l11;
+        const float bound = fmaxf(fabsf(l00) + fabsf(l10), fabsf(l11));
+        return (a00 > 0.f && d1 > 0.f) ? bound : INFINITY;
+    } else {
+        const float* S = r + 4;
+        const float a00 = k * S[0], a01 = 0.5f * k * (S[1] + S[3]), a02 = 0.5f * k * (S[2] + S[6]);
+        const float a11 = k * S[4], a12 = 0.5f * k * (S[5] + S[7]), a22 = k * S[8];
+        const float l00 = sqrtf(a00), l10 = a01 / l00, l20 = a02 / l00;
+        const float d1 = a11 - l10 * l10;
+        const float l11 = sqrtf(d1), l21 = (a12 - l20 * l10) / l11;
+        const float d2 = a22 - l20 * l20 - l21 * l21;
+        const float l22 = sqrtf(d2);
+        const float m0 = r[1] - origin[0], m1 = r[2] - origin[1], m2 = r[3] - origin[2];
+        out[0] = -(l00 * m0 + l10 * m1 + l20 * m2);
+        out[1] = -(l11 * m1 + l21 * m2);
+        out[2] = -(l22 * m2);
+        out[3] = r[0] * kInv2Pi15 * sqrtf(det3(S));
+        out[4] = l00; out[5] = l10; out[6] = l20; out[7] = l11; out[8] = l21; out[9] = l22;
+        const float bound = fmaxf(fabsf(l00) + fabsf(l10) + fabsf(l20), fmaxf(fabsf(l11) + fabsf(l21), fabsf(l22)));
+        return (a00 > 0.f && d1 > 0.f && d2 > 0.f) ? bound : INFINITY;
+    }
+}
+
+// Largest (row sum of |L^T|) x (half extent of the tile's points) for which a chunk of Gaussians takes the triangular
+// loop. The rounding error of y is at most 2 eps x that product for a pair that matters (a Gaussian within reach of
+// the tile), which changes the pair's value by at most 0.71 x that much of the Gaussian's peak: 350 -> 3e-5 of the peak.
+constexpr float kTriangularLimit = 350.f;
 
 // ---------------------------------------------------------------------------------------------
 // forward
@@ -110,6 +186,10 @@ struct FwdSmem {
     alignas(16) float ready[(kFwdChunk / 2) * kPairFloats];
     alignas(16) float xs[kTile * D];
     alignas(8) uint64_t bar;
+    float box_lo[D][kFwdThreads / 32], box_hi[D][kFwdThreads / 32];
+    float origin[D];
+    float half_extent;
+    int row_sum_bits;      // largest row-sum bound of the chunk, as the bit pattern of a non-negative float
 };
 
 template <int D, int P>
@@ -155,13 +235,60 @@ eval_forward_kernel(const float* __restrict__ mixture, const float* __restrict__
     }
     __syncthreads();
 
-    float2 x[P][D];    // every coordinate duplicated into both halves
+    // ---- origin = centre of the box of the tile's points; the pair loops work on x' = x - origin ----
+    {
+        float lo[D], hi[D];
+#pragma unroll
+        for (int d = 0; d < D; ++d) { lo[d] = INFINITY; hi[d] = -INFINITY; }
+#pragma unroll
+        for (int p = 0; p < P; ++p) {
+            const int i = tid + p * kFwdThreads;
+            if (i < n_here) {
+#pragma unroll
+                for (int d = 0; d < D; ++d) {
+                    const float v = sm.xs[i * D + d];
+                    lo[d] = fminf(lo[d], v);
+                    hi[d] = fmaxf(hi[d], v);
+                }
+            }
+        }
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                lo[d] = fminf(lo[d], __shfl_xor_sync(0xffffffffu, lo[d], o));
+                hi[d] = fmaxf(hi[d], __shfl_xor_sync(0xffffffffu, hi[d], o));
+            }
+            if ((tid & 31) == 0) { sm.box_lo[d][tid >> 5] = lo[d]; sm.box_hi[d][tid >> 5] = hi[d]; }
+        }
+        __syncthreads();
+        if (tid == 0) {
+            float half = 0.f;
+#pragma unroll
+            for (int d = 0; d < D; ++d) {
+                float l = sm.box_lo[d][0], h = sm.box_hi[d][0];
+                for (int w = 1; w < kFwdThreads / 32; ++w) { l = fminf(l, sm.box_lo[d][w]); h = fmaxf(h, sm.box_hi[d][w]); }
+                const float centre = 0.5f * l + 0.5f * h;
+                sm.origin[d] = centre;
+                half = fmaxf(half, fmaxf(h - centre, centre - l));
+            }
+            sm.half_extent = half;
+            sm.row_sum_bits = 0;
+        }
+        __syncthreads();
+    }
+    float origin[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) origin[d] = sm.origin[d];
+    const float half_extent = sm.half_extent;
+
+    float2 x[P][D];    // x - origin, every coordinate duplicated into both halves
     float2 acc[P];
 #pragma unroll
     for (int p = 0; p < P; ++p) {
 #pragma unroll
         for (int d = 0; d < D; ++d) {
-            const float v = sm.xs[(tid + p * kFwdThreads) * D + d];
+            const float v = sm.xs[(tid + p * kFwdThreads) * D + d] - origin[d];
             x[p][d] = f2(v, v);
         }
         acc[p] = f2(0.f, 0.f);
@@ -194,18 +321,35 @@ eval_forward_kernel(const float* __restrict__ mixture, const float* __restrict__
                 return;
             }
         }
+        auto raw_record = [&](int g, float* r) {
+            if (bulk) {
+#pragma unroll
+                for (int i = 0; i < RF; ++i) r[i] = sm.raw[g * RF + i];
+            } else {
+#pragma unroll
+                for (int i = 0; i < RF; ++i) r[i] = __ldg(chunk + g * RF + i);
+            }
+        };
+        // ---- which loop for this chunk: the largest row-sum bound of its Gaussians against the tile's extent ----
+        {
+            float bound = 0.f;
+            for (int g = tid; g < gc; g += kFwdThreads) {
+                float r[RF], tri[RC];
+                raw_record(g, r);
+                const float b = make_triangular<D>(r, origin, tri);
+                bound = (b >= bound) ? b : (b == b ? bound : INFINITY);      // NaN counts as "not usable"
+            }
+            atomicMax(&sm.row_sum_bits, __float_as_int(bound));
+        }
+        __syncthreads();
+        const bool triangular = __int_as_float(sm.row_sum_bits) * half_extent <= kTriangularLimit;
         for (int g = tid; g < gc_even; g += kFwdThreads) {
             float rdy[RC];
             if (g < gc) {
                 float r[RF];
-                if (bulk) {
-#pragma unroll
-                    for (int i = 0; i < RF; ++i) r[i] = sm.raw[g * RF + i];
-                } else {
-#pragma unroll
-                    for (int i = 0; i < RF; ++i) r[i] = __ldg(chunk + g * RF + i);
-                }
-                make_ready<D>(r, rdy);
+                raw_record(g, r);
+                if (triangular) make_triangular<D>(r, origin, rdy);
+                else make_ready<D>(r, origin, rdy);
             } else {
 #pragma unroll
                 for (int i = 0; i < RC; ++i) rdy[i] = 0.f;   // padding Gaussian: c = 0
@@ -215,40 +359,74 @@ eval_forward_kernel(const float* __restrict__ mixture, const float* __restrict__
             for (int i = 0; i < RC; ++i) dst[2 * i] = rdy[i];
         }
         __syncthreads();
+        if (tid == 0) sm.row_sum_bits = 0;          // for the next chunk (read again only after two more barriers)
 
         const float4* rp = reinterpret_cast<const float4*>(sm.ready);
         const int n_pairs = gc_even >> 1;
         if constexpr (D == 3) {
+            if (triangular) {
 #pragma unroll 2
-            for (int j = 0; j < n_pairs; ++j) {
-                const float4 v0 = rp[j * 5 + 0], v1 = rp[j * 5 + 1], v2 = rp[j * 5 + 2], v3 = rp[j * 5 + 3],
-                             v4 = rp[j * 5 + 4];
-                const float2 nm0 = f2(v0.x, v0.y), nm1 = f2(v0.z, v0.w), nm2 = f2(v1.x, v1.y), c = f2(v1.z, v1.w);
-                const float2 a00 = f2(v2.x, v2.y), a01 = f2(v2.z, v2.w), a02 = f2(v3.x, v3.y), a11 = f2(v3.z, v3.w);
-                const float2 a12 = f2(v4.x, v4.y), a22 = f2(v4.z, v4.w);
+                for (int j = 0; j < n_pairs; ++j) {
+                    const float4 v0 = rp[j * 5 + 0], v1 = rp[j * 5 + 1], v2 = rp[j * 5 + 2], v3 = rp[j * 5 + 3],
+                                 v4 = rp[j * 5 + 4];
+                    const float2 nb0 = f2(v0.x, v0.y), nb1 = f2(v0.z, v0.w), nb2 = f2(v1.x, v1.y), c = f2(v1.z, v1.w);
+                    const float2 l00 = f2(v2.x, v2.y), l10 = f2(v2.z, v2.w), l20 = f2(v3.x, v3.y), l11 = f2(v3.z, v3.w);
+                    const float2 l21 = f2(v4.x, v4.y), l22 = f2(v4.z, v4.w);
 #pragma unroll
-                for (int p = 0; p < P; ++p) {
-                    const float2 t0 = add2(x[p][0], nm0), t1 = add2(x[p][1], nm1), t2 = add2(x[p][2], nm2);
-                    const float2 r0 = fma2(a02, t2, fma2(a01, t1, mul2(a00, t0)));
-                    const float2 r1 = fma2(a12, t2, mul2(a11, t1));
-                    const float2 r2 = mul2(a22, t2);
-                    const float2 q = fma2(t2, r2, fma2(t1, r1, mul2(t0, r0)));
-                    acc[p] = fma2(c, ex2_2(q), acc[p]);
+                    for (int p = 0; p < P; ++p) {
+                        const float2 y2 = fma2(l22, x[p][2], nb2);
+                        const float2 y1 = fma2(l11, x[p][1], fma2(l21, x[p][2], nb1));
+                        const float2 y0 = fma2(l00, x[p][0], fma2(l10, x[p][1], fma2(l20, x[p][2], nb0)));
+                        acc[p] = fma2(c, ex2_of_minus_square(y0, y1, y2), acc[p]);
+                    }
+                }
+            } else {
+#pragma unroll 2
+                for (int j = 0; j < n_pairs; ++j) {
+                    const float4 v0 = rp[j * 5 + 0], v1 = rp[j * 5 + 1], v2 = rp[j * 5 + 2], v3 = rp[j * 5 + 3],
+                                 v4 = rp[j * 5 + 4];
+                    const float2 nm0 = f2(v0.x, v0.y), nm1 = f2(v0.z, v0.w), nm2 = f2(v1.x, v1.y), c = f2(v1.z, v1.w);
+                    const float2 a00 = f2(v2.x, v2.y), a01 = f2(v2.z, v2.w), a02 = f2(v3.x, v3.y), a11 = f2(v3.z, v3.w);
+                    const float2 a12 = f2(v4.x, v4.y), a22 = f2(v4.z, v4.w);
+#pragma unroll
+                    for (int p = 0; p < P; ++p) {
+                        const float2 t0 = add2(x[p][0], nm0), t1 = add2(x[p][1], nm1), t2 = add2(x[p][2], nm2);
+                        const float2 r0 = fma2(a02, t2, fma2(a01, t1, mul2(a00, t0)));
+                        const float2 r1 = fma2(a12, t2, mul2(a11, t1));
+                        const float2 r2 = mul2(a22, t2);
+                        const float2 q = fma2(t2, r2, fma2(t1, r1, mul2(t0, r0)));
+                        acc[p] = fma2(c, ex2_2(q), acc[p]);
+                    }
                 }
             }
         } else {
+            if (triangular) {
 #pragma unroll 2
-            for (int j = 0; j < n_pairs; ++j) {
-                const float4 v0 = rp[j * 3 + 0], v1 = rp[j * 3 + 1], v2 = rp[j * 3 + 2];
-                const float2 nm0 = f2(v0.x, v0.y), nm1 = f2(v0.z, v0.w), c = f2(v1.x, v1.y), a00 = f2(v1.z, v1.w);
-                const float2 a01 = f2(v2.x, v2.y), a11 = f2(v2.z, v2.w);
+                for (int j = 0; j < n_pairs; ++j) {
+                    const float4 v0 = rp[j * 3 + 0], v1 = rp[j * 3 + 1], v2 = rp[j * 3 + 2];
+                    const float2 nb0 = f2(v0.x, v0.y), nb1 = f2(v0.z, v0.w), c = f2(v1.x, v1.y), l00 = f2(v1.z, v1.w);
+                    const float2 l10 = f2(v2.x, v2.y), l11 = f2(v2.z, v2.w);
 #pragma unroll
-                for (int p = 0; p < P; ++p) {
-                    const float2 t0 = add2(x[p][0], nm0), t1 = add2(x[p][1], nm1);
-                    const float2 r0 = fma2(a01, t1, mul2(a00, t0));
-                    const float2 r1 = mul2(a11, t1);
-                    const float2 q = fma2(t1, r1, mul2(t0, r0));
-                    acc[p] = fma2(c, ex2_2(q), acc[p]);
+                    for (int p = 0; p < P; ++p) {
+                        const float2 y1 = fma2(l11, x[p][1], nb1);
+                        const float2 y0 = fma2(l00, x[p][0], fma2(l10, x[p][1], nb0));
+                        acc[p] = fma2(c, ex2_of_minus_square(y0, y1), acc[p]);
+                    }
+                }
+            } else {
+#pragma unroll 2
+                for (int j = 0; j < n_pairs; ++j) {
+                    const float4 v0 = rp[j * 3 + 0], v1 = rp[j * 3 + 1], v2 = rp[j * 3 + 2];
+                    const float2 nm0 = f2(v0.x, v0.y), nm1 = f2(v0.z, v0.w), c = f2(v1.x, v1.y), a00 = f2(v1.z, v1.w);
+                    const float2 a01 = f2(v2.x, v2.y), a11 = f2(v2.z, v2.w);
+#pragma unroll
+                    for (int p = 0; p < P; ++p) {
+                        const float2 t0 = add2(x[p][0], nm0), t1 = add2(x[p][1], nm1);
+                        const float2 r0 = fma2(a01, t1, mul2(a00, t0));
+                        const float2 r1 = mul2(a11, t1);
+                        const float2 q = fma2(t1, r1, mul2(t0, r0));
+                        acc[p] = fma2(c, ex2_2(q), acc[p]);
+                    }
                 }
             }
         }

@@ -87,6 +87,51 @@ def test_every_kernel_variant(D, G, N):
         _check(m, x, g, what=f"G{G} N{N} D{D} bx{bx} lx{lx}")
 
 
+def _mixture_of_scale(rng, B, L, G, D, centre, spread, s_lo, s_hi):
+    w = rng.uniform(-1, 1, (B, L, G)).astype(np.float32)
+    p = (centre + rng.uniform(-spread, spread, (B, L, G, D))).astype(np.float32)
+    Q = np.linalg.qr(rng.standard_normal((B, L, G, D, D)))[0]
+    s = np.exp(rng.uniform(np.log(s_lo), np.log(s_hi), (B, L, G, D)))
+    inv = Q @ (np.eye(D) / (s ** 2)[..., None]) @ np.swapaxes(Q, -1, -2)
+    inv = 0.5 * (inv + np.swapaxes(inv, -1, -2))
+    return np.ascontiguousarray(np.concatenate((w[..., None], p, inv.reshape(B, L, G, D * D).astype(np.float32)), -1))
+
+
+@pytest.mark.parametrize("D", [2, 3])
+def test_forward_loop_selection(D):
+    """The forward kernel has a short pair loop on a triangular factor of the matrix, chosen per chunk of 256 Gaussians
+    when (largest entry sum of the factor) x (extent of the tile's points) is small enough for its rounding, and the
+    general loop otherwise. Regimes: benchmark-like (short loop); Gaussians a thousand times narrower than the domain
+    (general loop); one narrow Gaussian in the second chunk only (both loops in one launch); a domain far from the
+    origin (the loops work relative to the tile's centre); a matrix that is not positive definite (general loop; 2D
+    only, where det > 0 leaves the norm factor real)."""
+    rng = np.random.default_rng(90 + D)
+    N = 1500
+
+    def check(m, x, what, tol=TOL):
+        out = _gpu_eval(m, x, np.ones((m.shape[0], m.shape[1], x.shape[2]), np.float32))[0]
+        ref = cpu_oracle.eval_forward(m.astype(np.float64), x.astype(np.float64))
+        assert np.isfinite(out).all(), what
+        assert rel_inf(out, ref) < tol, f"{what}: rel {rel_inf(out, ref):.3e}"
+
+    x = rng.uniform(-1.2, 1.2, (2, 3, N, D)).astype(np.float32)
+    check(_mixture_of_scale(rng, 2, 3, 512, D, 0.0, 1.0, 0.03, 0.25), x, "benchmark-like")
+    check(_mixture_of_scale(rng, 2, 3, 300, D, 0.0, 1.0, 0.0005, 0.002), np.ascontiguousarray(x[:, :, :400]), "narrow Gaussians")
+    m = _mixture_of_scale(rng, 2, 3, 512, D, 0.0, 1.0, 0.05, 0.25)
+    m[:, :, 400] = _mixture_of_scale(rng, 2, 3, 1, D, 0.0, 0.1, 0.0005, 0.001)[:, :, 0]
+    m[:, :, 400, 0] = 1e-4                      # its peak is 1 / s^D times the weight: keep it comparable to the rest
+    x_near = x.copy()
+    x_near[:, :, :64] = m[:, :, 400, None, 1:1 + D] + rng.uniform(-0.002, 0.002, (2, 3, 64, D)).astype(np.float32)
+    check(m, x_near, "one narrow Gaussian in the second chunk")
+    far = 1000.0
+    xf = (far + rng.uniform(-1.2, 1.2, (2, 3, N, D))).astype(np.float32)
+    check(_mixture_of_scale(rng, 2, 3, 512, D, far, 1.0, 0.1, 0.5), xf, "domain far from the origin")
+    if D == 2:
+        m = _mixture_of_scale(rng, 2, 3, 64, D, 0.0, 1.0, 0.5, 1.0)
+        m[:, :, ::2, 3:] *= -1.0                 # negative definite: det > 0, the exponent grows with the distance
+        check(m, x, "matrix not positive definite")
+
+
 def test_large_n_uses_the_four_points_per_thread_forward():
     rng = np.random.default_rng(5)
     for D in (2, 3):
