@@ -21,6 +21,9 @@
 //            traffic in the pair loop. The per-point position gradient is what crosses lanes: each lane
 //            writes its D partial sums into its warp's own padded shared rows and the warp folds them once
 //            per 16 points (no CTA barrier in the loop). Totals go to global memory with one atomic per value.
+#include <cstddef>
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace gmc {
@@ -171,6 +174,9 @@ __device__ __forceinline__ float make_triangular(const float* r, const float* or
 // loop. The rounding error of y is at most 2 eps x that product for a pair that matters (a Gaussian within reach of
 // the tile), which changes the pair's value by at most 0.71 x that much of the Gaussian's peak: 350 -> 3e-5 of the peak.
 constexpr float kTriangularLimit = 350.f;
+// The backward pass sums gradients, which feel an error of y more than the value does (a term's relative error is about
+// (2 ln 2 |y| + 2 / |y|) times it): a tighter limit, still twice what the 3D benchmark configuration needs.
+constexpr float kTriangularLimitBackward = 120.f;
 
 // ---------------------------------------------------------------------------------------------
 // forward
@@ -450,25 +456,51 @@ constexpr int kBwdRowStride = 36;      // floats per row of a warp's partial arr
 
 template <int D>
 struct BwdSmem {
-    alignas(16) float4 pts[kBwdTilePoints * 2];                            // (x,x,y,y) (z,z,g,g) per point
+    alignas(16) float4 pts[kBwdTilePoints * 2];                            // (x,x,y,y) (z,z,g,g) per point, x - origin
+    float box_lo[D][8], box_hi[D][8];                                      // per-warp box of the tile's points
+    float origin[D];                                                       // centre of that box
+    float half_extent;
+    int bound_bits;                                                        // largest row-sum bound of the CTA's Gaussians
     alignas(16) float partial[1];                                          // [warp][point * D + dim][kBwdRowStride]
     static constexpr size_t bytes(int n_warps) {
-        return sizeof(float4) * kBwdTilePoints * 2 + sizeof(float) * size_t(n_warps) * kBwdPointChunk * D * kBwdRowStride;
+        return offsetof(BwdSmem, partial) + sizeof(float) * size_t(n_warps) * kBwdPointChunk * D * kBwdRowStride;
     }
 };
 
 // The Gaussians a thread owns (2 * GP of them, two per packed register pair) in the form the pair loop reads, and
-// their gradient sums.
+// their gradient sums. Two forms (see make_ready / make_triangular of the forward pass):
+//   general:     nmu = origin - mu, A = k S (symmetrised, k = -1/2 log2 e), sums over t = x - mu
+//   triangular:  nmu = nb = -L^T (mu - origin), A = L (l00 l10 l20 l11 l21 l22; -k S = L L^T), sums over y = L^T t
 template <int D, int GP>
 struct BwdOwned {
     static constexpr int NS = D * (D + 1) / 2;
-    float2 nmu[GP][D], A[GP][NS], cw2[GP];      // -mu;  k S (symmetrised, k = -1/2 log2 e);  w norm 2 ln 2
-    float2 sa[GP], U[GP][D], M[GP][NS];         // sum a;  sum c2 t;  sum c2 t t^T (upper triangle)
+    float2 nmu[GP][D], A[GP][NS], cw2[GP];      // see above;  cw2 = w norm 2 ln 2
+    float2 sa[GP], U[GP][D], M[GP][NS];         // sum a;  sum c2 t (or y);  sum c2 t t^T (or y y^T), upper triangle
 };
 
+// Largest row-sum bound (make_triangular) of the Gaussians this thread owns.
 template <int D, int GP>
+__device__ __forceinline__ float bwd_owned_bound(const float* __restrict__ mix, int n_components, int gbase, int tg, int TG,
+                                                 const float* origin) {
+    constexpr int RF = Raw<D>::kFloats;
+    float bound = 0.f;
+#pragma unroll
+    for (int i = 0; i < 2 * GP; ++i) {
+        const int g = gbase + tg + i * TG;
+        if (g < n_components) {
+            float r[RF], tri[ReadyCount<D>::value];
+#pragma unroll
+            for (int f = 0; f < RF; ++f) r[f] = __ldg(mix + size_t(g) * RF + f);
+            const float b = make_triangular<D>(r, origin, tri);
+            bound = (b >= bound) ? b : (b == b ? bound : INFINITY);
+        }
+    }
+    return bound;
+}
+
+template <int D, int GP, bool TRI>
 __device__ __forceinline__ void bwd_load_owned(BwdOwned<D, GP>& o, const float* __restrict__ mix, int n_components,
-                                               int gbase, int tg, int TG) {
+                                               int gbase, int tg, int TG, const float* origin) {
     constexpr int RF = Raw<D>::kFloats;
     constexpr int NS = D * (D + 1) / 2;
 #pragma unroll
@@ -480,30 +512,40 @@ __device__ __forceinline__ void bwd_load_owned(BwdOwned<D, GP>& o, const float* 
             for (int i = 0; i < D + NS + 1; ++i) v[h][i] = 0.f;
             const int g = gbase + tg + (2 * q + h) * TG;
             if (g < n_components) {
-                const float* r = mix + size_t(g) * RF;
-                const float w = __ldg(r);
+                float r[RF];
 #pragma unroll
-                for (int d = 0; d < D; ++d) v[h][d] = -__ldg(r + 1 + d);
-                float S[D * D];
+                for (int f = 0; f < RF; ++f) r[f] = __ldg(mix + size_t(g) * RF + f);
+                if constexpr (TRI) {
+                    float tri[ReadyCount<D>::value];            // nb[D], w norm, L[NS]
+                    make_triangular<D>(r, origin, tri);
 #pragma unroll
-                for (int i = 0; i < D * D; ++i) S[i] = __ldg(r + 1 + D + i);
-                float det;
-                if constexpr (D == 2) {
-                    det = det2(S);
-                    v[h][D + 0] = kExpScale * S[0];
-                    v[h][D + 1] = kExpScale * 0.5f * (S[1] + S[2]);
-                    v[h][D + 2] = kExpScale * S[3];
+                    for (int d = 0; d < D; ++d) v[h][d] = tri[d];
+#pragma unroll
+                    for (int e = 0; e < NS; ++e) v[h][D + e] = tri[D + 1 + e];
+                    v[h][D + NS] = tri[D] * (2.f * kLn2);
                 } else {
-                    det = det3(S);
-                    v[h][D + 0] = kExpScale * S[0];
-                    v[h][D + 1] = kExpScale * 0.5f * (S[1] + S[3]);
-                    v[h][D + 2] = kExpScale * 0.5f * (S[2] + S[6]);
-                    v[h][D + 3] = kExpScale * S[4];
-                    v[h][D + 4] = kExpScale * 0.5f * (S[5] + S[7]);
-                    v[h][D + 5] = kExpScale * S[8];
+                    const float w = r[0];
+#pragma unroll
+                    for (int d = 0; d < D; ++d) v[h][d] = origin[d] - r[1 + d];
+                    const float* S = r + 1 + D;
+                    float det;
+                    if constexpr (D == 2) {
+                        det = det2(S);
+                        v[h][D + 0] = kExpScale * S[0];
+                        v[h][D + 1] = kExpScale * 0.5f * (S[1] + S[2]);
+                        v[h][D + 2] = kExpScale * S[3];
+                    } else {
+                        det = det3(S);
+                        v[h][D + 0] = kExpScale * S[0];
+                        v[h][D + 1] = kExpScale * 0.5f * (S[1] + S[3]);
+                        v[h][D + 2] = kExpScale * 0.5f * (S[2] + S[6]);
+                        v[h][D + 3] = kExpScale * S[4];
+                        v[h][D + 4] = kExpScale * 0.5f * (S[5] + S[7]);
+                        v[h][D + 5] = kExpScale * S[8];
+                    }
+                    // c2 = w * norm * (2 ln 2): folds the 1/k of "S t = (A t) / k" and the sign of d/dx
+                    v[h][D + NS] = w * gauss_norm_factor<D>() * sqrtf(det) * (2.f * kLn2);
                 }
-                // c2 = w * norm * (2 ln 2): folds the 1/k of "S t = (A t) / k" and the sign of d/dx
-                v[h][D + NS] = w * gauss_norm_factor<D>() * sqrtf(det) * (2.f * kLn2);
             }
         }
 #pragma unroll
@@ -515,10 +557,49 @@ __device__ __forceinline__ void bwd_load_owned(BwdOwned<D, GP>& o, const float* 
     }
 }
 
-// One query point against packed pair q of the owned Gaussians: 33 packed operations + 2 ex2 in 3D (21 + 2 in 2D).
-template <int D, int GP>
+// One query point against packed pair q of the owned Gaussians.
+// General form: 33 packed operations + 2 ex2 in 3D (21 + 2 in 2D); dx accumulates c2 (A t) = the position gradient.
+// Triangular form: 29 packed + 2 scalar operations + 2 ex2 in 3D (18 + 2 + 2 in 2D): y = L^T x' + nb without a
+// subtraction, sums over y, and dx accumulates L (c2 y) = MINUS the position gradient (the caller flips the sign).
+template <int D, int GP, bool TRI>
 __device__ __forceinline__ void bwd_pair(BwdOwned<D, GP>& o, int q, const float2 (&X)[3], float2 GO, float2 (&dx)[D]) {
-    if constexpr (D == 3) {
+    if constexpr (TRI && D == 3) {
+        const float2 (&L)[6] = o.A[q];
+        const float2 y2 = fma2(L[5], X[2], o.nmu[q][2]);
+        const float2 y1 = fma2(L[3], X[1], fma2(L[4], X[2], o.nmu[q][1]));
+        const float2 y0 = fma2(L[0], X[0], fma2(L[1], X[1], fma2(L[2], X[2], o.nmu[q][0])));
+        const float2 a = mul2(ex2_of_minus_square(y0, y1, y2), GO);
+        o.sa[q] = add2(o.sa[q], a);
+        const float2 c2 = mul2(a, o.cw2[q]);
+        const float2 u0 = mul2(c2, y0), u1 = mul2(c2, y1), u2 = mul2(c2, y2);
+        dx[0] = fma2(L[0], u0, dx[0]);
+        dx[1] = fma2(L[3], u1, fma2(L[1], u0, dx[1]));
+        dx[2] = fma2(L[5], u2, fma2(L[4], u1, fma2(L[2], u0, dx[2])));
+        o.U[q][0] = add2(o.U[q][0], u0);
+        o.U[q][1] = add2(o.U[q][1], u1);
+        o.U[q][2] = add2(o.U[q][2], u2);
+        o.M[q][0] = fma2(u0, y0, o.M[q][0]);
+        o.M[q][1] = fma2(u0, y1, o.M[q][1]);
+        o.M[q][2] = fma2(u0, y2, o.M[q][2]);
+        o.M[q][3] = fma2(u1, y1, o.M[q][3]);
+        o.M[q][4] = fma2(u1, y2, o.M[q][4]);
+        o.M[q][5] = fma2(u2, y2, o.M[q][5]);
+    } else if constexpr (TRI) {
+        const float2 (&L)[3] = o.A[q];                   // l00 l10 l11
+        const float2 y1 = fma2(L[2], X[1], o.nmu[q][1]);
+        const float2 y0 = fma2(L[0], X[0], fma2(L[1], X[1], o.nmu[q][0]));
+        const float2 a = mul2(ex2_of_minus_square(y0, y1), GO);
+        o.sa[q] = add2(o.sa[q], a);
+        const float2 c2 = mul2(a, o.cw2[q]);
+        const float2 u0 = mul2(c2, y0), u1 = mul2(c2, y1);
+        dx[0] = fma2(L[0], u0, dx[0]);
+        dx[1] = fma2(L[2], u1, fma2(L[1], u0, dx[1]));
+        o.U[q][0] = add2(o.U[q][0], u0);
+        o.U[q][1] = add2(o.U[q][1], u1);
+        o.M[q][0] = fma2(u0, y0, o.M[q][0]);
+        o.M[q][1] = fma2(u0, y1, o.M[q][1]);
+        o.M[q][2] = fma2(u1, y1, o.M[q][2]);
+    } else if constexpr (D == 3) {
         const float2 t0 = add2(X[0], o.nmu[q][0]), t1 = add2(X[1], o.nmu[q][1]), t2 = add2(X[2], o.nmu[q][2]);
         const float2 r0 = fma2(o.A[q][2], t2, fma2(o.A[q][1], t1, mul2(o.A[q][0], t0)));
         const float2 r1 = fma2(o.A[q][4], t2, fma2(o.A[q][3], t1, mul2(o.A[q][1], t0)));
@@ -560,7 +641,9 @@ __device__ __forceinline__ void bwd_pair(BwdOwned<D, GP>& o, int q, const float2
 }
 
 // Finishes the per-Gaussian gradient from the sums, one atomic per value (other CTAs and point slices add theirs).
-template <int D, int GP>
+// Triangular form: with Z = L^-1 the sums over y turn into the sums over t: sum c2 t = Z^T U, sum c2 t t^T = Z^T M Z,
+// and d/d mu = S sum(c t) = L U.
+template <int D, int GP, bool TRI>
 __device__ __forceinline__ void bwd_store_owned(const BwdOwned<D, GP>& o, const float* __restrict__ mix,
                                                 float* __restrict__ grad_mix, int n_components, int gbase, int tg,
                                                 int TG) {
@@ -604,26 +687,80 @@ __device__ __forceinline__ void bwd_store_owned(const BwdOwned<D, GP>& o, const 
             const float root = sqrtf(det);
             const float norm = gauss_norm_factor<D>() * root;
             atomicAdd(go, norm * sa_h);
-            // d/d mu = S * sum(c t);  U holds sum(c2 t) with c2 = c * 2 ln 2
+            float Mfull[D * D];                      // sum c2 t t^T
+            if constexpr (TRI) {
+                float Lh[NS];
 #pragma unroll
-            for (int i = 0; i < D; ++i) {
-                float s = 0.f;
+                for (int s = 0; s < NS; ++s) Lh[s] = h ? o.A[q][s].y : o.A[q][s].x;
+                float Lm[D][D], Z[D][D], My[D][D];   // L (lower), its inverse, the symmetric sum over y
 #pragma unroll
-                for (int j = 0; j < D; ++j) s = fmaf(0.5f * (S[i * D + j] + S[j * D + i]), Uh[j] * inv2ln2, s);
-                atomicAdd(go + 1 + i, s);
+                for (int i = 0; i < D; ++i)
+#pragma unroll
+                    for (int j = 0; j < D; ++j) { Lm[i][j] = 0.f; Z[i][j] = 0.f; }
+                if constexpr (D == 2) {
+                    Lm[0][0] = Lh[0]; Lm[1][0] = Lh[1]; Lm[1][1] = Lh[2];
+                    Z[0][0] = 1.f / Lh[0]; Z[1][1] = 1.f / Lh[2];
+                    Z[1][0] = -Lh[1] * Z[0][0] * Z[1][1];
+                } else {
+                    Lm[0][0] = Lh[0]; Lm[1][0] = Lh[1]; Lm[2][0] = Lh[2]; Lm[1][1] = Lh[3]; Lm[2][1] = Lh[4]; Lm[2][2] = Lh[5];
+                    Z[0][0] = 1.f / Lh[0]; Z[1][1] = 1.f / Lh[3]; Z[2][2] = 1.f / Lh[5];
+                    Z[1][0] = -Lh[1] * Z[0][0] * Z[1][1];
+                    Z[2][1] = -Lh[4] * Z[1][1] * Z[2][2];
+                    Z[2][0] = (Lh[1] * Lh[4] - Lh[2] * Lh[3]) * Z[0][0] * Z[1][1] * Z[2][2];
+                }
+                int s_idx = 0;
+#pragma unroll
+                for (int i = 0; i < D; ++i)
+#pragma unroll
+                    for (int j = i; j < D; ++j) { My[i][j] = Mh[s_idx]; My[j][i] = Mh[s_idx]; ++s_idx; }
+                // d/d mu = L U
+#pragma unroll
+                for (int i = 0; i < D; ++i) {
+                    float acc = 0.f;
+#pragma unroll
+                    for (int j = 0; j <= i; ++j) acc = fmaf(Lm[i][j], Uh[j], acc);
+                    atomicAdd(go + 1 + i, acc);
+                }
+                float B[D][D];                        // My Z
+#pragma unroll
+                for (int i = 0; i < D; ++i)
+#pragma unroll
+                    for (int j = 0; j < D; ++j) {
+                        float acc = 0.f;
+#pragma unroll
+                        for (int m = j; m < D; ++m) acc = fmaf(My[i][m], Z[m][j], acc);
+                        B[i][j] = acc;
+                    }
+#pragma unroll
+                for (int i = 0; i < D; ++i)
+#pragma unroll
+                    for (int j = 0; j < D; ++j) {
+                        float acc = 0.f;
+#pragma unroll
+                        for (int m = i; m < D; ++m) acc = fmaf(Z[m][i], B[m][j], acc);
+                        Mfull[i * D + j] = acc;
+                    }
+            } else {
+                // d/d mu = S * sum(c t);  U holds sum(c2 t) with c2 = c * 2 ln 2
+#pragma unroll
+                for (int i = 0; i < D; ++i) {
+                    float s = 0.f;
+#pragma unroll
+                    for (int j = 0; j < D; ++j) s = fmaf(0.5f * (S[i * D + j] + S[j * D + i]), Uh[j] * inv2ln2, s);
+                    atomicAdd(go + 1 + i, s);
+                }
+                int s_idx = 0;
+#pragma unroll
+                for (int i = 0; i < D; ++i)
+#pragma unroll
+                    for (int j = i; j < D; ++j) {
+                        Mfull[i * D + j] = Mh[s_idx];
+                        Mfull[j * D + i] = Mh[s_idx];
+                        ++s_idx;
+                    }
             }
             // d/d S = -1/2 sum(c t t^T) + (w sum(a) factor / (2 sqrt(det))) cof(S)
             const float gdet = w * sa_h * gauss_norm_factor<D>() / (2.f * root);
-            int s_idx = 0;
-            float Mfull[D * D];
-#pragma unroll
-            for (int i = 0; i < D; ++i)
-#pragma unroll
-                for (int j = i; j < D; ++j) {
-                    Mfull[i * D + j] = Mh[s_idx];
-                    Mfull[j * D + i] = Mh[s_idx];
-                    ++s_idx;
-                }
 #pragma unroll
             for (int i = 0; i < D * D; ++i)
                 atomicAdd(go + 1 + D + i, fmaf(-0.5f * inv2ln2, Mfull[i], gdet * cof[i]));
@@ -669,90 +806,150 @@ eval_backward_kernel(const float* __restrict__ grad_out, const float* __restrict
     const int n_here = min(kBwdTilePoints, n_xes - n0);
     const size_t xes_row = (size_t(bx) * n_layers_xes + lx) * size_t(n_xes);
 
-    // ---- stage points: (x, grad_out), every value duplicated for the packed pair loop ----
-    for (int i = tid; i < kBwdTilePoints; i += THREADS) {
-        float px = 0.f, py = 0.f, pz = 0.f, go = 0.f;
-        if (i < n_here) {
-            const float* xp = xes + (xes_row + n0 + i) * D;
-            go = __ldg(grad_out + size_t(bl) * n_xes + n0 + i);
-            px = __ldg(xp);
-            py = __ldg(xp + 1);
-            if constexpr (D == 3) pz = __ldg(xp + 2);
+    // ---- stage points: (x - origin, grad_out), every value duplicated for the packed pair loop; origin = centre of the
+    //      box of the tile's points ----
+    {
+        constexpr int PER = (kBwdTilePoints + THREADS - 1) / THREADS;
+        float px[PER], py[PER], pz[PER], go[PER];
+        float lo[D], hi[D];
+#pragma unroll
+        for (int d = 0; d < D; ++d) { lo[d] = INFINITY; hi[d] = -INFINITY; }
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            const int i = tid + k * THREADS;
+            px[k] = py[k] = pz[k] = go[k] = 0.f;
+            if (i < n_here) {
+                const float* xp = xes + (xes_row + n0 + i) * D;
+                go[k] = __ldg(grad_out + size_t(bl) * n_xes + n0 + i);
+                px[k] = __ldg(xp);
+                py[k] = __ldg(xp + 1);
+                if constexpr (D == 3) pz[k] = __ldg(xp + 2);
+                lo[0] = fminf(lo[0], px[k]); hi[0] = fmaxf(hi[0], px[k]);
+                lo[1] = fminf(lo[1], py[k]); hi[1] = fmaxf(hi[1], py[k]);
+                if constexpr (D == 3) { lo[2] = fminf(lo[2], pz[k]); hi[2] = fmaxf(hi[2], pz[k]); }
+            }
         }
-        sm.pts[2 * i] = make_float4(px, px, py, py);
-        sm.pts[2 * i + 1] = make_float4(pz, pz, go, go);
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                lo[d] = fminf(lo[d], __shfl_xor_sync(0xffffffffu, lo[d], o));
+                hi[d] = fmaxf(hi[d], __shfl_xor_sync(0xffffffffu, hi[d], o));
+            }
+            if (lane == 0) { sm.box_lo[d][tid >> 5] = lo[d]; sm.box_hi[d][tid >> 5] = hi[d]; }
+        }
+        __syncthreads();
+        if (tid == 0) {
+            float half = 0.f;
+#pragma unroll
+            for (int d = 0; d < D; ++d) {
+                float l = sm.box_lo[d][0], h = sm.box_hi[d][0];
+                for (int w = 1; w < THREADS / 32; ++w) { l = fminf(l, sm.box_lo[d][w]); h = fmaxf(h, sm.box_hi[d][w]); }
+                const float centre = 0.5f * l + 0.5f * h;
+                sm.origin[d] = centre;
+                half = fmaxf(half, fmaxf(h - centre, centre - l));
+            }
+            sm.half_extent = half;
+            sm.bound_bits = 0;
+        }
+        __syncthreads();
+        const float ox = sm.origin[0], oy = sm.origin[1], oz = D == 3 ? sm.origin[D - 1] : 0.f;
+#pragma unroll
+        for (int k = 0; k < PER; ++k) {
+            const int i = tid + k * THREADS;
+            if (i < kBwdTilePoints) {
+                const bool live = i < n_here;
+                const float x0 = live ? px[k] - ox : 0.f, x1 = live ? py[k] - oy : 0.f, x2 = live ? pz[k] - oz : 0.f;
+                sm.pts[2 * i] = make_float4(x0, x0, x1, x1);
+                sm.pts[2 * i + 1] = make_float4(x2, x2, go[k], go[k]);
+            }
+        }
     }
+    float origin[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) origin[d] = sm.origin[d];
 
-    BwdOwned<D, GP> own;
     const float* mix = mixture + size_t(bl) * n_components * RF;
     const int gbase = gchunk * TG * GP * 2;
-    bwd_load_owned<D, GP>(own, mix, n_components, gbase, tg, TG);
+    // ---- which pair loop: the largest row-sum bound of the CTA's Gaussians against the extent of its points ----
+    atomicMax(&sm.bound_bits, __float_as_int(bwd_owned_bound<D, GP>(mix, n_components, gbase, tg, TG, origin)));
     __syncthreads();
+    const bool triangular = __int_as_float(sm.bound_bits) * sm.half_extent <= kTriangularLimitBackward;
 
     const bool need_gx = grad_xes != nullptr;
     const int part = (tid >> 5) * ROWS * kBwdRowStride;     // first float of this warp's rows in sm.partial
     constexpr int PPI = GMC_BWD_PPI;   // points in flight per loop iteration (independent dependency chains)
     const int per_slice = kBwdTilePoints / TP;
     const int p_end = min(n_here, (slice + 1) * per_slice);
-    for (int c0 = slice * per_slice; c0 < p_end; c0 += kBwdPointChunk) {
-        for (int pp0 = 0; pp0 < kBwdPointChunk; pp0 += PPI) {
-            float2 X[PPI][3], GO[PPI], dx[PPI][D];
+
+    auto run = [&](auto form) {
+        constexpr bool TRI = decltype(form)::value;
+        BwdOwned<D, GP> own;
+        bwd_load_owned<D, GP, TRI>(own, mix, n_components, gbase, tg, TG, origin);
+        for (int c0 = slice * per_slice; c0 < p_end; c0 += kBwdPointChunk) {
+            for (int pp0 = 0; pp0 < kBwdPointChunk; pp0 += PPI) {
+                float2 X[PPI][3], GO[PPI], dx[PPI][D];
 #pragma unroll
-            for (int k = 0; k < PPI; ++k) {
-                const float4 pa = sm.pts[2 * (c0 + pp0 + k)];
-                const float4 pb = sm.pts[2 * (c0 + pp0 + k) + 1];
-                X[k][0] = f2(pa.x, pa.y); X[k][1] = f2(pa.z, pa.w); X[k][2] = f2(pb.x, pb.y);
-                GO[k] = f2(pb.z, pb.w);
+                for (int k = 0; k < PPI; ++k) {
+                    const float4 pa = sm.pts[2 * (c0 + pp0 + k)];
+                    const float4 pb = sm.pts[2 * (c0 + pp0 + k) + 1];
+                    X[k][0] = f2(pa.x, pa.y); X[k][1] = f2(pa.z, pa.w); X[k][2] = f2(pb.x, pb.y);
+                    GO[k] = f2(pb.z, pb.w);
 #pragma unroll
-                for (int d = 0; d < D; ++d) dx[k][d] = f2(0.f, 0.f);
-            }
+                    for (int d = 0; d < D; ++d) dx[k][d] = f2(0.f, 0.f);
+                }
 #pragma unroll
-            for (int q = 0; q < GP; ++q) {
+                for (int q = 0; q < GP; ++q) {
 #pragma unroll
-                for (int k = 0; k < PPI; ++k) bwd_pair<D, GP>(own, q, X[k], GO[k], dx[k]);
+                    for (int k = 0; k < PPI; ++k) bwd_pair<D, GP, TRI>(own, q, X[k], GO[k], dx[k]);
+                }
+                if (need_gx) {
+#pragma unroll
+                    for (int k = 0; k < PPI; ++k)
+#pragma unroll
+                        for (int d = 0; d < D; ++d) {
+                            // the triangular loop accumulates minus the gradient
+                            const float v = TRI ? (-dx[k][d].x) - dx[k][d].y : dx[k][d].x + dx[k][d].y;
+                            sm.partial[part + ((pp0 + k) * D + d) * kBwdRowStride + lane] = v;
+                        }
+                }
             }
             if (need_gx) {
+                __syncwarp();
+                // rows 0..31: one lane per row, 32 values each
+                float* gx = grad_xes + (xes_row + n0 + c0) * D;
+                {
+                    const float4* src = reinterpret_cast<const float4*>(sm.partial + part + lane * kBwdRowStride);
+                    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
-                for (int k = 0; k < PPI; ++k)
+                    for (int i = 0; i < 8; ++i) {
+                        const float4 v = src[i];
+                        s0 += v.x; s1 += v.y; s2 += v.z; s3 += v.w;
+                    }
+                    if (c0 + lane / D < n_here) atomicAdd(gx + lane, (s0 + s1) + (s2 + s3));
+                }
+                if constexpr (ROWS > 32) {
+                    // rows 32..47: two lanes per row, 16 values each
+                    const int row = 32 + (lane & 15);
+                    const float4* src = reinterpret_cast<const float4*>(sm.partial + part + row * kBwdRowStride + (lane >> 4) * 16);
+                    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
 #pragma unroll
-                    for (int d = 0; d < D; ++d)
-                        sm.partial[part + ((pp0 + k) * D + d) * kBwdRowStride + lane] = dx[k][d].x + dx[k][d].y;
+                    for (int i = 0; i < 4; ++i) {
+                        const float4 v = src[i];
+                        s0 += v.x; s1 += v.y; s2 += v.z; s3 += v.w;
+                    }
+                    float s = (s0 + s1) + (s2 + s3);
+                    s += __shfl_xor_sync(0xffffffffu, s, 16);
+                    if (lane < 16 && c0 + row / D < n_here) atomicAdd(gx + row, s);
+                }
+                __syncwarp();
             }
         }
-        if (need_gx) {
-            __syncwarp();
-            // rows 0..31: one lane per row, 32 values each
-            float* gx = grad_xes + (xes_row + n0 + c0) * D;
-            {
-                const float4* src = reinterpret_cast<const float4*>(sm.partial + part + lane * kBwdRowStride);
-                float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float4 v = src[i];
-                    s0 += v.x; s1 += v.y; s2 += v.z; s3 += v.w;
-                }
-                if (c0 + lane / D < n_here) atomicAdd(gx + lane, (s0 + s1) + (s2 + s3));
-            }
-            if constexpr (ROWS > 32) {
-                // rows 32..47: two lanes per row, 16 values each
-                const int row = 32 + (lane & 15);
-                const float4* src = reinterpret_cast<const float4*>(sm.partial + part + row * kBwdRowStride + (lane >> 4) * 16);
-                float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float4 v = src[i];
-                    s0 += v.x; s1 += v.y; s2 += v.z; s3 += v.w;
-                }
-                float s = (s0 + s1) + (s2 + s3);
-                s += __shfl_xor_sync(0xffffffffu, s, 16);
-                if (lane < 16 && c0 + row / D < n_here) atomicAdd(gx + row, s);
-            }
-            __syncwarp();
-        }
-    }
-
-    if (grad_mixture == nullptr) return;
-    bwd_store_owned<D, GP>(own, mix, grad_mixture + size_t(bl) * n_components * RF, n_components, gbase, tg, TG);
+        if (grad_mixture != nullptr)
+            bwd_store_owned<D, GP, TRI>(own, mix, grad_mixture + size_t(bl) * n_components * RF, n_components, gbase, tg, TG);
+    };
+    if (triangular) run(std::true_type{});
+    else run(std::false_type{});
 }
 
 template <typename K>
