@@ -477,6 +477,15 @@ def config1_block(args, rank, world, local_rank, b_rank, steps, with_e2e, with_p
     ach_bwd = FLOP_BWD * pairs_rank / (bwd_ms * 1e-3) / 1e12
     ach_fwd = FLOP_FWD * pairs_rank / (fwd_ms * 1e-3) / 1e12
     ach_all = (FLOP_FWD + FLOP_BWD) * pairs_rank / ((fwd_ms + bwd_ms) * 1e-3) / 1e12
+    # What the kernels execute for the algorithmic flop above (triangular pair loops, which config 1 takes): FP32 lane
+    # slots on the FMA pipe per (Gaussian, point) pair -- forward 9 packed + 2 scalar instructions per two pairs = 10
+    # slots (19 flop + 1 ex2 instead of the formula's 27), backward 29 packed + 2 scalar = 30 slots -- and the share
+    # of the pipe's slots (SMs x 128 lanes x clock) they fill. A fraction of the flop peak above 1 for the forward
+    # kernel is therefore not an error: the kernel needs fewer operations than the reference formula counts.
+    slots = n_sm * N_SM_LANES * sm_max_mhz * 1e6
+    executed = {"forward": 10.0, "backward": 30.0}
+    pipe_fwd = executed["forward"] * pairs_rank / (fwd_ms * 1e-3) / slots
+    pipe_bwd = executed["backward"] * pairs_rank / (bwd_ms * 1e-3) / slots
     block = {
         "value": world * pairs_rank / (ms_per_step * 1e-3), "unit": UNIT, "ms_per_step": ms_per_step, "steps": steps,
         "batch_per_gpu": b_rank, "pairs_per_gpu_and_step": pairs_rank,
@@ -484,12 +493,16 @@ def config1_block(args, rank, world, local_rank, b_rank, steps, with_e2e, with_p
                      "peak": peak, "unit": "TFLOP/s", "frac": ach_bwd / peak,
                      # dram__bytes_read+write of one launch: captured by ncu at B=4 (profiles/), scaled by B/4
                      # because every byte of traffic belongs to one (batch, layer) mixture
-                     "traffic": 32.79e6 * b_rank / 4, "traffic_unit": "bytes (ncu capture at B=4, scaled by B/4)",
+                     "traffic": 32.82e6 * b_rank / 4, "traffic_unit": "bytes (ncu capture at B=4, scaled by B/4)",
                      "peak_source": peak_source, "peak_nominal": nominal, "frac_of_nominal": ach_bwd / nominal,
-                     "algorithmic_flop_per_pair": FLOP_BWD, "ms_per_launch": bwd_ms},
+                     "algorithmic_flop_per_pair": FLOP_BWD, "ms_per_launch": bwd_ms,
+                     "executed_fma_pipe_slots_per_pair": executed["backward"], "fma_pipe_slots_filled": pipe_bwd},
         "roofline_forward": {"bound": "fp32", "kernel": "eval_forward_kernel<3,4>", "achieved": ach_fwd,
                              "peak": peak, "unit": "TFLOP/s", "frac": ach_fwd / peak, "frac_of_nominal": ach_fwd / nominal,
-                             "algorithmic_flop_per_pair": FLOP_FWD, "ms_per_launch": fwd_ms},
+                             "algorithmic_flop_per_pair": FLOP_FWD, "ms_per_launch": fwd_ms,
+                             "executed_fma_pipe_slots_per_pair": executed["forward"], "fma_pipe_slots_filled": pipe_fwd,
+                             "note": "the kernel evaluates the exponent through a triangular factor: 19 flop + 1 ex2 per "
+                                     "pair instead of the 27 the formula counts, so achieved can exceed the flop peak"},
         "roofline_fwd_bwd": {"bound": "fp32", "achieved": ach_all, "peak": peak, "unit": "TFLOP/s",
                              "frac": ach_all / peak, "frac_of_nominal": ach_all / nominal,
                              "algorithmic_flop_per_pair": FLOP_FWD + FLOP_BWD},
