@@ -413,6 +413,11 @@ def config1_block(args, rank, world, local_rank, b_rank, steps, with_e2e, with_p
     sustained = None
     if sustained_seconds > 0:
         n_sus = max(steps, int(sustained_seconds * 1e3 / max(total_ms / steps, 1e-3)) + 1)
+        if world > 1:
+            # every step holds a collective: all ranks must run the same number of steps, whatever each one measured
+            n_all = torch.tensor([n_sus], dtype=torch.int64, device=dev)
+            dist.all_reduce(n_all, op=dist.ReduceOp.MAX)
+            n_sus = int(n_all.item())
         sus = ClockSampler(_gpu_index(local_rank))
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         if world > 1:
