@@ -99,6 +99,45 @@ __global__ void __launch_bounds__(kThreads) integrate_kernel(const float* __rest
     if (lane == 0) out[warp] = s;
 }
 
+// One warp per mixture: scale = mean trace of the matrix slot / D; writes 1 / sqrt(scale) and sqrt(scale).
+__global__ void __launch_bounds__(kThreads) trace_scale_kernel(const float* __restrict__ mixture, float* __restrict__ forth,
+                                                               float* __restrict__ back, long long n_mixtures,
+                                                               int n_components, int n_dims) {
+    const long long warp = ((long long)blockIdx.x * kThreads + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= n_mixtures) return;
+    const int record = 1 + n_dims + n_dims * n_dims;
+    const float* m = mixture + warp * (long long)n_components * record + 1 + n_dims;
+    float s = 0.f;
+    for (int g = lane; g < n_components; g += 32) {
+        float t = 0.f;
+        for (int d = 0; d < n_dims; ++d) t += __ldg(m + (size_t)g * record + d * n_dims + d);
+        s += t;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) {
+        const float scale = s / float(n_components) / float(n_dims);
+        const float root = sqrtf(scale);
+        back[warp] = root;
+        forth[warp] = 1.f / root;
+    }
+}
+
+// Positions times f, matrices times f * f, weights unchanged; f per mixture. One thread per float of the output.
+__global__ void __launch_bounds__(kThreads) spatial_scale_kernel(const float* __restrict__ mixture,
+                                                                 const float* __restrict__ factors, float* __restrict__ out,
+                                                                 long long n_floats, int n_components, int n_dims) {
+    const long long i = (long long)blockIdx.x * kThreads + threadIdx.x;
+    if (i >= n_floats) return;
+    const int record = 1 + n_dims + n_dims * n_dims;
+    const long long gaussian = i / record;
+    const int field = int(i - gaussian * record);
+    const float f = __ldg(factors + gaussian / n_components);
+    const float v = __ldg(mixture + i);
+    out[i] = field == 0 ? v : (field <= n_dims ? v * f : (f * f) * v);
+}
+
 // One matrix per thread; the decomposition itself is symeig_device (symeig_device.cuh).
 template <int D>
 __global__ void __launch_bounds__(kThreads) symeig_kernel(const float* __restrict__ in, float* __restrict__ values,
@@ -181,6 +220,35 @@ extern "C" int gmc_integrate(const float* mixture, float* integrals, long long n
     if (blocks > 0x7fffffffLL) return GMC_ERR_BAD_DIMS;
     integrate_kernel<<<unsigned(blocks), kThreads, 0, as_stream(stream)>>>(mixture, integrals, n_mixtures, n_components,
                                                                           1 + n_dims + n_dims * n_dims);
+    GMC_LAUNCH_CHECK();
+    return GMC_OK;
+}
+
+extern "C" int gmc_trace_scale(const float* mixture, float* forth, float* back, long long n_mixtures, int n_components,
+                               int n_dims, void* stream) {
+    using namespace gmc;
+    if (n_dims != 2 && n_dims != 3) return GMC_ERR_BAD_DIMS;
+    if (n_mixtures < 0 || n_components <= 0) return GMC_ERR_BAD_DIMS;
+    if (n_mixtures == 0) return GMC_OK;
+    if (!mixture || !forth || !back) return GMC_ERR_NULL_POINTER;
+    const long long blocks = (n_mixtures * 32 + kThreads - 1) / kThreads;
+    if (blocks > 0x7fffffffLL) return GMC_ERR_BAD_DIMS;
+    trace_scale_kernel<<<unsigned(blocks), kThreads, 0, as_stream(stream)>>>(mixture, forth, back, n_mixtures, n_components, n_dims);
+    GMC_LAUNCH_CHECK();
+    return GMC_OK;
+}
+
+extern "C" int gmc_spatial_scale(const float* mixture, const float* factors, float* out, long long n_mixtures,
+                                 int n_components, int n_dims, void* stream) {
+    using namespace gmc;
+    if (n_dims != 2 && n_dims != 3) return GMC_ERR_BAD_DIMS;
+    if (n_mixtures < 0 || n_components <= 0) return GMC_ERR_BAD_DIMS;
+    if (n_mixtures == 0) return GMC_OK;
+    if (!mixture || !factors || !out) return GMC_ERR_NULL_POINTER;
+    const long long n_floats = n_mixtures * n_components * (1 + n_dims + n_dims * n_dims);
+    const long long blocks = (n_floats + kThreads - 1) / kThreads;
+    if (blocks > 0x7fffffffLL) return GMC_ERR_BAD_DIMS;
+    spatial_scale_kernel<<<unsigned(blocks), kThreads, 0, as_stream(stream)>>>(mixture, factors, out, n_floats, n_components, n_dims);
     GMC_LAUNCH_CHECK();
     return GMC_OK;
 }

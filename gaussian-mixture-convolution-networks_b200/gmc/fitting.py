@@ -256,8 +256,32 @@ def solver(mixture: Tensor, constant: Tensor, n_components: int, config: Config 
 # ---------------------------------------------------------------------------------------------
 # reductions (reference fitting.py:243-276, 342-530)
 # ---------------------------------------------------------------------------------------------
+def _fused_tree_hem_scaling(m: Tensor) -> bool:
+    return m.is_cuda and m.dtype == torch.float32 and not (torch.is_grad_enabled() and m.requires_grad)
+
+
 def tree_hem(m: Tensor, n_components: int, n_reduction: int, check_inputs: bool = False) -> Tensor:
-    """BVH-MHEM reduction; the mixture is scaled per (batch, layer) to a mean covariance trace of D first."""
+    """BVH-MHEM reduction; the mixture is scaled per (batch, layer) to a mean covariance trace of D first
+    (the reference's src/gmc/fitting.py:342-358). Without a gradient the scaling runs as two small kernels of the
+    library (gmc_trace_scale, gmc_spatial_scale) instead of a chain of tensor operations."""
+    if _fused_tree_hem_scaling(m) and not check_inputs:
+        from gmc import _native
+        m = m.contiguous()
+        b, l, g, v = m.shape
+        d = gm.n_dimensions(m)
+        forth = torch.empty((b, l), dtype=torch.float32, device=m.device)
+        back = torch.empty_like(forth)
+        scaled = torch.empty_like(m)
+        with torch.cuda.device_of(m):
+            st = _native.stream_of(m)
+            _native.check(_native.lib.gmc_trace_scale(_native.ptr(m), _native.ptr(forth), _native.ptr(back), b * l, g, d, st),
+                          "trace scale")
+            _native.check(_native.lib.gmc_spatial_scale(_native.ptr(m), _native.ptr(forth), _native.ptr(scaled), b * l, g, d, st),
+                          "spatial scale")
+            fitted = cppBvhMhemFit.apply(scaled, n_components, n_reduction).contiguous()
+            _native.check(_native.lib.gmc_spatial_scale(_native.ptr(fitted), _native.ptr(back), _native.ptr(fitted), b * l,
+                                                        fitted.shape[2], d, st), "spatial scale")
+        return fitted
     scale = mat_tools.trace(gm.covariances(m)).mean(-1, keepdim=True) / gm.n_dimensions(m)
     back = torch.sqrt(scale)
     forth = 1 / back

@@ -171,6 +171,19 @@ int gmc_integrate(const float* mixture, float* integrals, long long n_mixtures, 
                   void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * The scaling around the BVH-MHEM fit (src/gmc/fitting.py:342-358: the mixture is scaled per (batch, layer) so that the
+ * mean trace of its covariances is D, fitted, and scaled back) as two small kernels instead of a chain of tensor ops.
+ * gmc_trace_scale: per mixture scale = mean over components of trace(matrix) / D;
+ *                  forth[m] = 1 / sqrt(scale), back[m] = sqrt(scale)                     (forth, back: [n_mixtures])
+ * gmc_spatial_scale: out = (weight, position * f, matrix * f * f) with f = factors[m]     (gm.spatial_scale,
+ *                  src/gmc/mixture.py:281-292, isotropic factor); out may be the input buffer.
+ * ---------------------------------------------------------------------------------------------- */
+int gmc_trace_scale(const float* mixture, float* forth, float* back, long long n_mixtures, int n_components,
+                    int n_dims, void* stream);
+int gmc_spatial_scale(const float* mixture, const float* factors, float* out, long long n_mixtures, int n_components,
+                      int n_dims, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Linear BVH over the component means of each mixture (the tree of the BVH-MHEM fit).
  *   key      = (30-bit Morton code of the mean inside the mixture's own min/max box) << 16 | component id
  *   sorted_keys [n_mixtures, n_components] uint64, ascending per mixture

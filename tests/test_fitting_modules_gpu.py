@@ -419,3 +419,20 @@ def test_fused_inference_layers_equal_the_module_path(D):
     del net._fused_inference_layers
     xg = x.clone().requires_grad_(True)
     assert not net._fused_inference_layers(xg) or not torch.is_grad_enabled()
+
+
+@pytest.mark.parametrize("D", [2, 3])
+def test_tree_hem_scaling_kernels_equal_the_tensor_path(D):
+    """tree_hem without a gradient scales through gmc_trace_scale / gmc_spatial_scale; with a gradient through the
+    tensor operations of the reference (src/gmc/fitting.py:342-358). Same result up to the rounding of the mean."""
+    import gmc.fitting as fitting
+    import synthetic_inputs as synthetic
+    g = torch.Generator().manual_seed(40 + D)
+    cov, _ = synthetic.covariances_and_inverses((3, 4, 96), D, 0.02, 0.3, g)
+    w = torch.rand(3, 4, 96, generator=g) + 0.05
+    p = torch.rand(3, 4, 96, D, generator=g) * 4 - 2
+    m = synthetic.pack(w, p, cov).cuda()
+    fused = fitting.tree_hem(m, 16, 4)
+    tensor_path = fitting.tree_hem(m.clone().requires_grad_(True), 16, 4).detach()
+    assert fused.shape == tensor_path.shape == (3, 4, 16, 1 + D + D * D)
+    assert torch.allclose(fused, tensor_path, rtol=2e-5, atol=1e-6)
