@@ -138,6 +138,184 @@ __global__ void __launch_bounds__(kThreads) spatial_scale_kernel(const float* __
     out[i] = field == 0 ? v : (field <= n_dims ? v * f : (f * f) * v);
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+// Input normalisation of a one-channel mixture per sample, the two per-sample normalisations the network applies to its
+// input in one kernel (the reference's CovScaleNorm(batch_norm=False) followed by BatchNorm(batch_norm=False),
+// src/gmc/modules.py:313-351 and 354-420):
+//   f  = sqrt(D / mean_g trace(C_g));  positions *= f, covariances *= f * f
+//   values of the scaled mixture at n_samples uniform points of the box of its centres (2D: the box widened by 15 %),
+//   weights *= scaling / max(sd, 0.001) with the unbiased standard deviation sd of those values, constant = -mean.
+// One CTA per sample. The uniform numbers come from `uniforms` ([n_batch, n_samples, D], for tests) or from a
+// counter-based hash of *seed (drawn by the caller from its own generator, so a seeded run repeats).
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kNormThreads = 256;
+
+__device__ __forceinline__ float uniform_from_counter(unsigned long long seed, unsigned long long counter) {
+    unsigned long long z = seed + (counter + 1ull) * 0x9E3779B97F4A7C15ull;      // splitmix64
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    return float(unsigned(z >> 40)) * (1.0f / 16777216.0f);                       // 24 bits -> [0, 1)
+}
+
+template <int D>
+__global__ void __launch_bounds__(kNormThreads)
+input_normalise_kernel(const float* __restrict__ mixture, const long long* __restrict__ seed, const float* __restrict__ uniforms,
+                       const float* __restrict__ scaling, int n_components, int n_samples, float* __restrict__ out,
+                       float* __restrict__ out_constants) {
+    constexpr int RF = 1 + D + D * D;
+    constexpr int RD = D + D * D + 1;                  // centre, inverse covariance, weight * norm
+    extern __shared__ __align__(16) float smem[];
+    float* ready = smem;                               // [G][RD]
+    float* values = smem + size_t(n_components) * RD;  // [n_samples]
+    __shared__ float red[kNormThreads / 32][2 * D + 1];
+    __shared__ float s_f, s_lo[D], s_hi[D], s_mean, s_factor;
+    const int G = n_components;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* src = mixture + size_t(blockIdx.x) * G * RF;
+
+    // ---- mean trace, box of the centres ----
+    float tr = 0.f, lo[D], hi[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) { lo[d] = INFINITY; hi[d] = -INFINITY; }
+    for (int g = tid; g < G; g += kNormThreads) {
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+            tr += __ldg(src + size_t(g) * RF + 1 + D + d * D + d);
+            const float p = __ldg(src + size_t(g) * RF + 1 + d);
+            lo[d] = fminf(lo[d], p);
+            hi[d] = fmaxf(hi[d], p);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        tr += __shfl_xor_sync(0xffffffffu, tr, o);
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+            lo[d] = fminf(lo[d], __shfl_xor_sync(0xffffffffu, lo[d], o));
+            hi[d] = fmaxf(hi[d], __shfl_xor_sync(0xffffffffu, hi[d], o));
+        }
+    }
+    if (lane == 0) {
+        red[warp][0] = tr;
+#pragma unroll
+        for (int d = 0; d < D; ++d) { red[warp][1 + d] = lo[d]; red[warp][1 + D + d] = hi[d]; }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float t = 0.f;
+        for (int w = 0; w < kNormThreads / 32; ++w) t += red[w][0];
+        const float f = sqrtf(float(D) / (t / float(G)));
+        s_f = f;
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+            float l = red[0][1 + d], h = red[0][1 + D + d];
+            for (int w = 1; w < kNormThreads / 32; ++w) { l = fminf(l, red[w][1 + d]); h = fmaxf(h, red[w][1 + D + d]); }
+            // the box of the SCALED centres, with the ordering a negative-free factor keeps
+            s_lo[d] = l * f;
+            s_hi[d] = h * f;
+        }
+    }
+    __syncthreads();
+    const float f = s_f;
+
+    // ---- scaled Gaussians in evaluation form ----
+    for (int g = tid; g < G; g += kNormThreads) {
+        float C[D * D], inv[D * D];
+#pragma unroll
+        for (int k = 0; k < D * D; ++k) C[k] = (f * f) * __ldg(src + size_t(g) * RF + 1 + D + k);
+        float det;
+        if constexpr (D == 2) {
+            det = C[0] * C[3] - C[1] * C[2];
+            const float r = 1.f / det;
+            inv[0] = C[3] * r; inv[1] = -C[1] * r; inv[2] = -C[2] * r; inv[3] = C[0] * r;
+        } else {
+            const float c0 = C[4] * C[8] - C[5] * C[7], c1 = C[3] * C[8] - C[5] * C[6], c2 = C[3] * C[7] - C[4] * C[6];
+            det = C[0] * c0 - C[1] * c1 + C[2] * c2;
+            const float r = 1.f / det;
+            inv[0] = c0 * r; inv[1] = -(C[1] * C[8] - C[2] * C[7]) * r; inv[2] = (C[1] * C[5] - C[2] * C[4]) * r;
+            inv[3] = -c1 * r; inv[4] = (C[0] * C[8] - C[2] * C[6]) * r; inv[5] = -(C[0] * C[5] - C[2] * C[3]) * r;
+            inv[6] = c2 * r; inv[7] = -(C[0] * C[7] - C[1] * C[6]) * r; inv[8] = (C[0] * C[4] - C[1] * C[3]) * r;
+        }
+        float* r = ready + size_t(g) * RD;
+#pragma unroll
+        for (int d = 0; d < D; ++d) r[d] = f * __ldg(src + size_t(g) * RF + 1 + d);
+#pragma unroll
+        for (int k = 0; k < D * D; ++k) r[D + k] = inv[k];
+        // weight * (2 pi)^(-D/2) / sqrt(det C)
+        r[D + D * D] = __ldg(src + size_t(g) * RF) * (D == 2 ? 0.15915494309189535f : 0.06349363593424097f) * rsqrtf(det);
+    }
+    __syncthreads();
+
+    // ---- values at the sample points ----
+    const unsigned long long sd_bits = seed != nullptr ? (unsigned long long)(*seed) : 0ull;
+    float sum = 0.f;
+    for (int i = tid; i < n_samples; i += kNormThreads) {
+        float x[D];
+#pragma unroll
+        for (int d = 0; d < D; ++d) {
+            float u = uniforms != nullptr ? __ldg(uniforms + (size_t(blockIdx.x) * n_samples + i) * D + d)
+                                          : uniform_from_counter(sd_bits, (size_t(blockIdx.x) * n_samples + i) * D + d);
+            if constexpr (D == 2) u = u * 1.3f - 0.15f;
+            x[d] = u * (s_hi[d] - s_lo[d]) + s_lo[d];
+        }
+        float v = 0.f;
+        for (int g = 0; g < G; ++g) {
+            const float* r = ready + size_t(g) * RD;
+            float t[D];
+#pragma unroll
+            for (int d = 0; d < D; ++d) t[d] = x[d] - r[d];
+            float q = 0.f;
+#pragma unroll
+            for (int a = 0; a < D; ++a) {
+                float acc = 0.f;
+#pragma unroll
+                for (int c = 0; c < D; ++c) acc = fmaf(r[D + a * D + c], t[c], acc);
+                q = fmaf(t[a], acc, q);
+            }
+            v = fmaf(r[D + D * D], __expf(-0.5f * q), v);
+        }
+        values[i] = v;
+        sum += v;
+    }
+    // ---- mean and unbiased standard deviation (two passes over the stored values) ----
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    __syncthreads();
+    if (lane == 0) red[warp][0] = sum;
+    __syncthreads();
+    if (tid == 0) {
+        float t = 0.f;
+        for (int w = 0; w < kNormThreads / 32; ++w) t += red[w][0];
+        s_mean = t / float(n_samples);
+    }
+    __syncthreads();
+    const float mean = s_mean;
+    float sq = 0.f;
+    for (int i = tid; i < n_samples; i += kNormThreads) { const float dv = values[i] - mean; sq = fmaf(dv, dv, sq); }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+    __syncthreads();
+    if (lane == 0) red[warp][0] = sq;
+    __syncthreads();
+    if (tid == 0) {
+        float t = 0.f;
+        for (int w = 0; w < kNormThreads / 32; ++w) t += red[w][0];
+        const float sd = sqrtf(t / float(n_samples - 1));
+        s_factor = (scaling != nullptr ? __ldg(scaling) : 1.f) / fmaxf(sd, 0.001f);
+        out_constants[blockIdx.x] = -mean;
+    }
+    __syncthreads();
+    const float wf = s_factor;
+    float* dst = out + size_t(blockIdx.x) * G * RF;
+    for (int i = tid; i < G * RF; i += kNormThreads) {
+        const int field = i % RF;
+        const float v = __ldg(src + i);
+        dst[i] = field == 0 ? v * wf : (field <= D ? v * f : (f * f) * v);
+    }
+}
+
 // One matrix per thread; the decomposition itself is symeig_device (symeig_device.cuh).
 template <int D>
 __global__ void __launch_bounds__(kThreads) symeig_kernel(const float* __restrict__ in, float* __restrict__ values,
@@ -249,6 +427,29 @@ extern "C" int gmc_spatial_scale(const float* mixture, const float* factors, flo
     const long long blocks = (n_floats + kThreads - 1) / kThreads;
     if (blocks > 0x7fffffffLL) return GMC_ERR_BAD_DIMS;
     spatial_scale_kernel<<<unsigned(blocks), kThreads, 0, as_stream(stream)>>>(mixture, factors, out, n_floats, n_components, n_dims);
+    GMC_LAUNCH_CHECK();
+    return GMC_OK;
+}
+
+extern "C" int gmc_input_normalise(const float* mixture, const long long* seed, const float* uniforms, const float* scaling,
+                                   long long n_batch, int n_components, int n_dims, int n_samples, float* out_mixture,
+                                   float* out_constants, void* stream) {
+    using namespace gmc;
+    if (n_dims != 2 && n_dims != 3) return GMC_ERR_BAD_DIMS;
+    if (n_batch < 0 || n_components <= 0 || n_samples < 2) return GMC_ERR_BAD_DIMS;
+    if (n_batch == 0) return GMC_OK;
+    if (n_batch > 0x7fffffffLL) return GMC_ERR_BAD_DIMS;
+    if (!mixture || !out_mixture || !out_constants || (!seed && !uniforms)) return GMC_ERR_NULL_POINTER;
+    const size_t smem = sizeof(float) * (size_t(n_components) * (n_dims + n_dims * n_dims + 1) + size_t(n_samples));
+    if (smem > 200 * 1024) return GMC_ERR_BAD_DIMS;
+    cudaStream_t st = as_stream(stream);
+    if (n_dims == 2) {
+        if (smem > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(input_normalise_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        input_normalise_kernel<2><<<unsigned(n_batch), kNormThreads, smem, st>>>(mixture, seed, uniforms, scaling, n_components, n_samples, out_mixture, out_constants);
+    } else {
+        if (smem > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(input_normalise_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+        input_normalise_kernel<3><<<unsigned(n_batch), kNormThreads, smem, st>>>(mixture, seed, uniforms, scaling, n_components, n_samples, out_mixture, out_constants);
+    }
     GMC_LAUNCH_CHECK();
     return GMC_OK;
 }

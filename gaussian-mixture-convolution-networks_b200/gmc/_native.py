@@ -76,6 +76,8 @@ _declare("gmc_symeig", [_c_float_p] * 3 + [ctypes.c_longlong, _c_int, _c_void_p]
 _declare("gmc_integrate", [_c_float_p] * 2 + [ctypes.c_longlong, _c_int, _c_int, _c_void_p])
 _declare("gmc_trace_scale", [_c_float_p] * 3 + [ctypes.c_longlong, _c_int, _c_int, _c_void_p])
 _declare("gmc_spatial_scale", [_c_float_p] * 3 + [ctypes.c_longlong, _c_int, _c_int, _c_void_p])
+_declare("gmc_input_normalise", [_c_float_p, _c_void_p, _c_float_p, _c_float_p, ctypes.c_longlong, _c_int, _c_int, _c_int,
+                                 _c_void_p, _c_void_p, _c_void_p])
 
 
 class GmcError(RuntimeError):

@@ -212,6 +212,38 @@ class CovScaleNorm(torch.nn.modules.Module):
         return y_gm, x_constant
 
 
+def fused_input_normalisation(x_gm: Tensor, scaling: typing.Optional[Tensor] = None, n_samples: int = 1000,
+                              uniforms: typing.Optional[Tensor] = None) -> typing.Tuple[Tensor, Tensor]:
+    """CovScaleNorm(1, batch_norm=False) followed by BatchNorm(1, batch_norm=False) on a one-channel mixture
+    [B, 1, G, V] in one kernel (gmc_input_normalise), without autograd. `scaling` is the BatchNorm's learnable factor
+    (a one-element CUDA tensor) or None. The sample positions come from `uniforms`
+    ([B, n_samples, D] in [0, 1)) or from a hash of a seed drawn from torch's generator of the device."""
+    from gmc import _native
+    _native.require_cuda_f32(x_gm, "mixture")
+    b, l, g, v = x_gm.shape
+    if l != 1:
+        raise RuntimeError("fused_input_normalisation handles one-channel mixtures")
+    d = gm.n_dimensions(x_gm)
+    x_gm = x_gm.contiguous()
+    out = torch.empty_like(x_gm)
+    constants = torch.empty((b, 1), dtype=torch.float32, device=x_gm.device)
+    if scaling is not None:
+        scaling = scaling.detach().reshape(1).contiguous()
+        _native.require_cuda_f32(scaling, "scaling")
+    seed = None
+    if uniforms is None:
+        seed = torch.randint(0, 2 ** 62, (1,), dtype=torch.int64, device=x_gm.device)
+    else:
+        uniforms = uniforms.contiguous()
+        _native.require_cuda_f32(uniforms, "uniforms")
+        n_samples = uniforms.shape[1]
+    with torch.cuda.device_of(x_gm):
+        _native.check(_native.lib.gmc_input_normalise(
+            _native.ptr(x_gm), _native.ptr(seed), _native.ptr(uniforms), _native.ptr(scaling), b, g, d, int(n_samples),
+            _native.ptr(out), _native.ptr(constants), _native.stream_of(x_gm)), "input normalisation")
+    return out, constants
+
+
 class BatchNorm(torch.nn.modules.Module):
     """Scales the weights so that the standard deviation of the mixture's values, sampled at random positions inside
     the box of the centres, becomes one; the sampled mean is subtracted from the constant."""

@@ -184,6 +184,22 @@ int gmc_spatial_scale(const float* mixture, const float* factors, float* out, lo
                       int n_dims, void* stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Per-sample normalisation of a one-channel input mixture [n_batch, 1, n_components, 1+D+D*D] (covariance form), the
+ * two steps the network applies to its input in evaluation mode in one kernel: CovScaleNorm(batch_norm=False) followed
+ * by BatchNorm(batch_norm=False) of the reference (src/gmc/modules.py:313-351, 354-420):
+ *   f = sqrt(D / mean trace);  positions *= f, covariances *= f*f;
+ *   the scaled mixture is evaluated at n_samples (>= 2) uniform points of the box of its centres (2D: widened by 15 %);
+ *   weights *= scaling / max(sd, 0.001) (unbiased sd of the values; scaling = device pointer to the channel's learnable
+ *   factor, NULL = 1), out_constants[b] = -mean.
+ * The uniform numbers are `uniforms` [n_batch, n_samples, D] in [0, 1) if given (tests), else a counter-based hash of
+ * *seed (device pointer to one int64 that the caller draws from its own generator).
+ * n_components * (D + D*D + 1) + n_samples floats must fit in 200 KB of shared memory.
+ * ---------------------------------------------------------------------------------------------- */
+int gmc_input_normalise(const float* mixture, const long long* seed, const float* uniforms, const float* scaling,
+                        long long n_batch, int n_components, int n_dims, int n_samples, float* out_mixture,
+                        float* out_constants, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Linear BVH over the component means of each mixture (the tree of the BVH-MHEM fit).
  *   key      = (30-bit Morton code of the mean inside the mixture's own min/max box) << 16 | component id
  *   sorted_keys [n_mixtures, n_components] uint64, ascending per mixture

@@ -217,7 +217,8 @@ def test_net_training_step_runs_every_backward_kernel(method):
 
 def test_graphed_forward_equals_eager_forward(monkeypatch):
     """The GMCN forward captured as a CUDA graph returns the eager result, also for a second input. The normalisation
-    layers sample random positions, so the sampler is replaced by a fixed sequence for the comparison."""
+    layers sample random positions, so the samplers (torch.rand of the module path, the seed that the fused input
+    normalisation draws with torch.randint) are replaced by fixed values for the comparison."""
     import math
     import gmc.model as model
     from gmc.cuda_graph import GraphedForward
@@ -234,6 +235,8 @@ def test_graphed_forward_equals_eager_forward(monkeypatch):
     net = model.Net(config=cfg).cuda().eval()
     xs = [synthetic.config4_input(n_batch=3, seed=s).cuda() for s in (1, 2)]
     monkeypatch.setattr(torch, "rand", fixed_rand)
+    monkeypatch.setattr(torch, "randint", lambda low, high, size, **kw: torch.full(tuple(size), 12345, dtype=kw.get("dtype"),
+                                                                                   device=kw.get("device")))
 
     def fn(x):
         return net.features(x)
@@ -405,12 +408,21 @@ def test_fused_inference_layers_equal_the_module_path(D):
     g = torch.Generator().manual_seed(5)
     cov, _ = synthetic.covariances_and_inverses((3, 1, 20), D, 0.05, 0.3, g)
     x = synthetic.pack(torch.rand(3, 1, 20, generator=g) + 0.2, torch.rand(3, 1, 20, D, generator=g) * 2 - 1, cov).cuda()
-    torch.manual_seed(11)       # the input normalisation draws sample points
+    # the input normalisation draws sample points, by different samplers on the two paths (it has its own test):
+    # both paths get its module-path result, computed once
+    torch.manual_seed(11)
+    with torch.no_grad():
+        stored = net.norm0((x, None))
+
+    class StoredInputNorm(torch.nn.Module):
+        def forward(self, _):
+            return stored
+
+    net.norm0 = StoredInputNorm()
     with torch.no_grad():
         assert net._fused_inference_layers(x)
         fused = net.features(x)
     net._fused_inference_layers = lambda t: False
-    torch.manual_seed(11)
     with torch.no_grad():
         plain = net.features(x)
     assert torch.isfinite(fused).all()
@@ -436,3 +448,39 @@ def test_tree_hem_scaling_kernels_equal_the_tensor_path(D):
     tensor_path = fitting.tree_hem(m.clone().requires_grad_(True), 16, 4).detach()
     assert fused.shape == tensor_path.shape == (3, 4, 16, 1 + D + D * D)
     assert torch.allclose(fused, tensor_path, rtol=2e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("D", [2, 3])
+def test_fused_input_normalisation_equals_the_two_modules(D):
+    """gmc_input_normalise against CovScaleNorm(1, batch_norm=False) + BatchNorm(1, batch_norm=False) fed with the same
+    uniform numbers (torch.rand patched), and the seeded path: repeatable, statistics near the sampled ones."""
+    import gmc.modules as modules
+    import gmc.mixture as gm
+    g = torch.Generator().manual_seed(60 + D)
+    B, G, n = 5, 64, 1000
+    cov, _ = synthetic.covariances_and_inverses((B, 1, G), D, 0.03, 0.15, g)
+    w = torch.rand(B, 1, G, generator=g) * 0.8 + 0.2
+    p = torch.rand(B, 1, G, D, generator=g) * 2 - 1
+    m = synthetic.pack(w, p, cov).cuda()
+    uniforms = torch.rand(B, n, D, generator=g).cuda()
+    norm = torch.nn.Sequential(modules.CovScaleNorm(1, batch_norm=False), modules.BatchNorm(1, batch_norm=False)).cuda().eval()
+    with torch.no_grad():
+        norm[1].learnable_scaling.fill_(1.7)
+        real_rand = torch.rand
+        torch.rand = lambda *shape, **kw: uniforms.view(B, 1, n, D)
+        try:
+            ref_m, ref_c = norm((m, None))
+        finally:
+            torch.rand = real_rand
+        out_m, out_c = modules.fused_input_normalisation(m, norm[1].learnable_scaling, uniforms=uniforms)
+    assert torch.allclose(out_m, ref_m, rtol=2e-4, atol=1e-6), float((out_m - ref_m).abs().max())
+    assert torch.allclose(out_c, ref_c, rtol=2e-4, atol=1e-5)
+    torch.manual_seed(3)
+    a_m, a_c = modules.fused_input_normalisation(m, None)
+    torch.manual_seed(3)
+    b_m, b_c = modules.fused_input_normalisation(m, None)
+    assert torch.equal(a_m, b_m) and torch.equal(a_c, b_c)
+    # another thousand sample points give the same statistics up to the sampling error (large for narrow Gaussians in 3D)
+    ratio = gm.weights(a_m) * 1.7 / gm.weights(out_m)
+    assert (ratio > 0.5).all() and (ratio < 2.0).all()
+    assert torch.equal(gm.positions(a_m), gm.positions(out_m)) and torch.equal(gm.covariances(a_m), gm.covariances(out_m))
