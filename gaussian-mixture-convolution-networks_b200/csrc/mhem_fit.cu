@@ -30,10 +30,13 @@ namespace {
 #define GMC_OBJ(i, n_internal) GMC_IDX(int(i), (n_internal) + 1)
 
 #ifndef GMC_FIT_THREADS
-#define GMC_FIT_THREADS 256
+#define GMC_FIT_THREADS 384
 #endif
-constexpr int kThreads = GMC_FIT_THREADS;
+constexpr int kThreads = GMC_FIT_THREADS;      // largest CTA; the launch picks the size by the mixture's size
 constexpr int kWarps = kThreads / 32;
+// One warp fits one node: mixtures of 512 components and more keep twelve warps busy (1.41 -> 1.37 ms at 1024 components,
+// 1024 mixtures), small ones are faster with eight (more mixtures resident per SM).
+inline int fit_threads(int n_components) { return n_components >= 512 ? kThreads : (kThreads < 256 ? kThreads : 256); }
 constexpr int kMaxLevels = 72;
 constexpr int kSharedBookkeepingMax = 8192;   // above this many components the per-node arrays go to global scratch
 // bytes of global bookkeeping per mixture: level [2G-1 -> 16] + arrive / order [4 (G-1)] + has_grad [G], at most 8 G
@@ -571,11 +574,11 @@ struct FitSmem {
 __device__ __forceinline__ void compute_levels(const uint16_t* __restrict__ nodes, int G, unsigned char* level, int* arrive,
                                                int* max_level) {
     const int n_internal = G - 1, n_nodes = 2 * G - 1;
-    for (int i = threadIdx.x; i < n_internal; i += kThreads) arrive[i] = 0;
-    for (int i = threadIdx.x; i < n_nodes; i += kThreads) level[i] = 0;
+    for (int i = threadIdx.x; i < n_internal; i += int(blockDim.x)) arrive[i] = 0;
+    for (int i = threadIdx.x; i < n_nodes; i += int(blockDim.x)) level[i] = 0;
     if (threadIdx.x == 0) *max_level = 0;
     __syncthreads();
-    for (int leaf = threadIdx.x; leaf < G; leaf += kThreads) {
+    for (int leaf = threadIdx.x; leaf < G; leaf += int(blockDim.x)) {
         int parent = nodes[size_t(n_internal + leaf) * 4];
         for (int guard = 0; guard < kMaxLevels && parent != 0xFFFF; ++guard) {
             __threadfence_block();
@@ -597,9 +600,9 @@ __device__ __forceinline__ void compute_levels(const uint16_t* __restrict__ node
 __device__ __forceinline__ void group_by_level(const unsigned char* level, int n_internal, int max_level, uint16_t* order,
                                                int* level_start, int* level_cursor) {
     const int tid = threadIdx.x;
-    for (int i = tid; i < 258; i += kThreads) level_start[i] = 0;
+    for (int i = tid; i < 258; i += int(blockDim.x)) level_start[i] = 0;
     __syncthreads();
-    for (int i = tid; i < n_internal; i += kThreads) atomicAdd(&level_start[level[i]], 1);
+    for (int i = tid; i < n_internal; i += int(blockDim.x)) atomicAdd(&level_start[level[i]], 1);
     __syncthreads();
     if (tid == 0) {
         int run = 0;
@@ -611,7 +614,7 @@ __device__ __forceinline__ void group_by_level(const unsigned char* level, int n
         }
     }
     __syncthreads();
-    for (int i = tid; i < n_internal; i += kThreads) order[atomicAdd(&level_cursor[level[i]], 1)] = uint16_t(i);
+    for (int i = tid; i < n_internal; i += int(blockDim.x)) order[atomicAdd(&level_cursor[level[i]], 1)] = uint16_t(i);
     __syncthreads();
 }
 
@@ -713,7 +716,7 @@ mhem_fit_forward_kernel(const float* __restrict__ mixture, const uint16_t* __res
     const int G = n_components, K = n_fitting;
     const int n_internal = G - 1, n_nodes = 2 * G - 1;
     // per-node bookkeeping: in shared memory, or (mixtures too large for that) in this mixture's slice of big_scratch
-    unsigned char* small = smem_bytes + sizeof(FitSmem<D, R>);
+    unsigned char* small = smem_bytes + sizeof(WarpScratch<D, R>) * (blockDim.x >> 5);
     unsigned char* level = big_scratch ? big_scratch + size_t(blockIdx.x) * big_scratch_bytes(G) : small;
     int* arrive = reinterpret_cast<int*>(level + ((n_nodes + 15) & ~15));
     const int sel_cap = K > 1024 ? K : 1024;   // capacity of the selection list (the reference holds 1024 entries)
@@ -746,7 +749,7 @@ mhem_fit_forward_kernel(const float* __restrict__ mixture, const uint16_t* __res
     for (int lv = 1; lv <= max_level; ++lv) {
         {
             const int level_end = level_start[lv + 1];
-            for (int at = level_start[lv] + warp; at < level_end; at += kWarps) {
+            for (int at = level_start[lv] + warp; at < level_end; at += int(blockDim.x >> 5)) {
                 const int id = order[at];
                 int child, child_slot, pos;
                 bool in_range, valid;
@@ -781,7 +784,7 @@ mhem_fit_forward_kernel(const float* __restrict__ mixture, const uint16_t* __res
     __syncthreads();
     const int n_list = s_n_selected_nodes;
     const int written = min(s_written, K);
-    for (int i = warp; i < n_list; i += kWarps) {
+    for (int i = warp; i < n_list; i += int(blockDim.x >> 5)) {
         const int id = sel_node[i];
         const int cnt = child_count(id);
         const float* src = id >= n_internal ? mix + size_t(GMC_OBJ(nodes[size_t(id) * 4 + 3], n_internal)) * RF : attrs + size_t(id) * AF;
@@ -790,7 +793,7 @@ mhem_fit_forward_kernel(const float* __restrict__ mixture, const uint16_t* __res
             if (slot < K) out[size_t(sel_offset[i]) * RF + o] = src[o];
         }
     }
-    for (int o = written * RF + tid; o < K * RF; o += kThreads) {
+    for (int o = written * RF + tid; o < K * RF; o += int(blockDim.x)) {
         const int f = o % RF;
         float v = 0.f;
         if (f > D && ((f - 1 - D) / D == (f - 1 - D) % D)) v = 1.f;
@@ -802,7 +805,7 @@ mhem_fit_forward_kernel(const float* __restrict__ mixture, const uint16_t* __res
 // from the top; a node that holds a gradient passes it to the Gaussians of its children (through grad_em_warp if the
 // node was fitted, unchanged otherwise). node_grad [n_internal, R * RF] is scratch; grad_target starts zeroed.
 template <int D, int R>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads < 256 ? kThreads : 256)
 mhem_fit_backward_kernel(const float* __restrict__ grad_all, const float* __restrict__ mixture,
                          const uint16_t* __restrict__ nodes_all, const float* __restrict__ attrs_all,
                          float* __restrict__ node_grad_all, float* __restrict__ grad_target_all, int n_components,
@@ -814,7 +817,7 @@ mhem_fit_backward_kernel(const float* __restrict__ grad_all, const float* __rest
     FitSmem<D, R>& sm = *reinterpret_cast<FitSmem<D, R>*>(smem_bytes);
     const int G = n_components, K = n_fitting;
     const int n_internal = G - 1, n_nodes = 2 * G - 1;
-    unsigned char* small = smem_bytes + sizeof(FitSmem<D, R>);
+    unsigned char* small = smem_bytes + sizeof(WarpScratch<D, R>) * (blockDim.x >> 5);
     unsigned char* level = big_scratch ? big_scratch + size_t(blockIdx.x) * big_scratch_bytes(G) : small;
     int* arrive = reinterpret_cast<int*>(level + ((n_nodes + 15) & ~15));
     const int sel_cap = K > 1024 ? K : 1024;
@@ -833,7 +836,7 @@ mhem_fit_backward_kernel(const float* __restrict__ grad_all, const float* __rest
     float* node_grad = node_grad_all + size_t(blockIdx.x) * n_internal * R * RF;
     float* grad_target = grad_target_all + size_t(blockIdx.x) * G * RF;
 
-    for (int i = tid; i < n_internal; i += kThreads) has_grad[i] = 0;
+    for (int i = tid; i < n_internal; i += int(blockDim.x)) has_grad[i] = 0;
     compute_levels(nodes, G, level, arrive, &s_max_level);
     const int max_level = s_max_level;
     auto count_of = [&](int n) -> int { return n >= n_internal ? 1 : __float_as_int(attrs[size_t(n) * AF + R * RF + 1]); };
@@ -844,7 +847,7 @@ mhem_fit_backward_kernel(const float* __restrict__ grad_all, const float* __rest
     }
     __syncthreads();
     const int n_list = s_n_selected_nodes;
-    for (int i = warp; i < n_list; i += kWarps) {
+    for (int i = warp; i < n_list; i += int(blockDim.x >> 5)) {
         const int id = sel_node[i];
         const int cnt = count_of(id);
         if (id >= n_internal) {      // a selected leaf hands its gradient straight to its Gaussian
@@ -870,7 +873,7 @@ mhem_fit_backward_kernel(const float* __restrict__ grad_all, const float* __rest
     for (int lv = max_level; lv >= 1; --lv) {
         {
             const int level_end = level_start[lv + 1];
-            for (int at = level_start[lv] + warp; at < level_end; at += kWarps) {
+            for (int at = level_start[lv] + warp; at < level_end; at += int(blockDim.x >> 5)) {
                 const int id = order[at];
                 if (!has_grad[id]) continue;
                 int child, child_slot, pos;
@@ -912,9 +915,9 @@ mhem_fit_backward_kernel(const float* __restrict__ grad_all, const float* __rest
 }
 
 template <int D, int R>
-size_t fit_smem_bytes(int G, int K) {
+size_t fit_smem_bytes(int G, int K, int threads) {
     const int n_nodes = 2 * G - 1;
-    const size_t fixed = sizeof(FitSmem<D, R>) + size_t(K > 1024 ? K : 1024) * 12;
+    const size_t fixed = sizeof(WarpScratch<D, R>) * size_t(threads / 32) + size_t(K > 1024 ? K : 1024) * 12;
     if (G > kSharedBookkeepingMax) return fixed;                  // per-node arrays live in global scratch
     return fixed + size_t((n_nodes + 15) & ~15) + sizeof(int) * size_t(G - 1) + size_t((G + 15) & ~15);
 }
@@ -923,11 +926,11 @@ template <int D, int R>
 int launch_fit(const float* mixture, long long n_mixtures, int G, int K, const uint16_t* nodes, float* attrs, float* out,
                cudaStream_t stream, unsigned char* big_scratch = nullptr) {
     auto kernel = mhem_fit_forward_kernel<D, R>;
-    const size_t smem = fit_smem_bytes<D, R>(G, K);
+    const size_t smem = fit_smem_bytes<D, R>(G, K, fit_threads(G));
     if (smem > 200 * 1024) return GMC_ERR_BAD_DIMS;
     if (smem > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
     if (G > kSharedBookkeepingMax && big_scratch == nullptr) return GMC_ERR_NULL_POINTER;
-    kernel<<<unsigned(n_mixtures), kThreads, smem, stream>>>(mixture, nodes, attrs, out, G, K,
+    kernel<<<unsigned(n_mixtures), fit_threads(G), smem, stream>>>(mixture, nodes, attrs, out, G, K,
                                                             G > kSharedBookkeepingMax ? big_scratch : nullptr);
     GMC_LAUNCH_CHECK();
     return GMC_OK;
@@ -937,14 +940,15 @@ template <int D, int R>
 int launch_fit_backward(const float* grad, const float* mixture, long long n_mixtures, int G, int K, const uint16_t* nodes,
                         const float* attrs, float* node_grad, float* grad_target, cudaStream_t stream) {
     auto kernel = mhem_fit_backward_kernel<D, R>;
-    const size_t smem = fit_smem_bytes<D, R>(G, K);
+    constexpr int kBackwardThreads = kThreads < 256 ? kThreads : 256;     // 128 registers: two CTAs of 256 per SM
+    const size_t smem = fit_smem_bytes<D, R>(G, K, kBackwardThreads);
     if (smem > 200 * 1024) return GMC_ERR_BAD_DIMS;
     if (smem > 48 * 1024) GMC_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
     // large mixtures: the per-node bookkeeping follows the node gradients in the caller's scratch
     unsigned char* big = G > kSharedBookkeepingMax
                              ? reinterpret_cast<unsigned char*>(node_grad + size_t(n_mixtures) * size_t(G - 1) * R * (1 + D + D * D))
                              : nullptr;
-    kernel<<<unsigned(n_mixtures), kThreads, smem, stream>>>(grad, mixture, nodes, attrs, node_grad, grad_target, G, K, big);
+    kernel<<<unsigned(n_mixtures), kBackwardThreads, smem, stream>>>(grad, mixture, nodes, attrs, node_grad, grad_target, G, K, big);
     GMC_LAUNCH_CHECK();
     return GMC_OK;
 }
