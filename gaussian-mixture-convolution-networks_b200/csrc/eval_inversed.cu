@@ -42,6 +42,9 @@ namespace {
 #ifndef GMC_BWD_PPI
 #define GMC_BWD_PPI 2
 #endif
+#ifndef GMC_BWD_UNROLL
+#define GMC_BWD_UNROLL 2            // iterations of the point loop unrolled (1, 4, 8 measured within 1 %)
+#endif
 #ifndef GMC_BWD_MINB
 #define GMC_BWD_MINB 4
 #endif
@@ -437,6 +440,7 @@ eval_forward_kernel(const float* __restrict__ mixture, const float* __restrict__
 // ---------------------------------------------------------------------------------------------
 // backward
 // ---------------------------------------------------------------------------------------------
+constexpr int kBwdUnroll = GMC_BWD_UNROLL;
 constexpr int kBwdPointChunk = 16;     // points between two folds of the position-gradient partial sums
 constexpr int kBwdTilePoints = 512;    // points per CTA
 constexpr int kBwdRowStride = 36;      // floats per row of a warp's partial array: 32 lanes + 4 (rows stay 16-byte aligned,
@@ -875,6 +879,7 @@ eval_backward_kernel(const float* __restrict__ grad_out, const float* __restrict
         BwdOwned<D, GP> own;
         bwd_load_owned<D, GP, TRI>(own, mix, n_components, gbase, tg, TG, origin);
         for (int c0 = slice * per_slice; c0 < p_end; c0 += kBwdPointChunk) {
+#pragma unroll kBwdUnroll
             for (int pp0 = 0; pp0 < kBwdPointChunk; pp0 += PPI) {
                 float2 X[PPI][3], GO[PPI], dx[PPI][D];
 #pragma unroll
