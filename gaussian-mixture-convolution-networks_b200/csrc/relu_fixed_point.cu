@@ -203,6 +203,54 @@ constexpr int kLargePoints = 4;
 __device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
 __device__ __forceinline__ float2 ex2_2(float2 q) { return make_float2(ex2_approx(q.x), ex2_approx(q.y)); }
 
+// 2^(-|y|^2) with the sign flipped by two scalar FFMAs (the packed instructions have no operand negation).
+__device__ __forceinline__ float2 ex2_of_minus_square(float2 y0, float2 y1) {
+    const float2 w = __fmul2_rn(y0, y0);
+    return make_float2(ex2_approx(fmaf(-y1.x, y1.x, -w.x)), ex2_approx(fmaf(-y1.y, y1.y, -w.y)));
+}
+__device__ __forceinline__ float2 ex2_of_minus_square(float2 y0, float2 y1, float2 y2) {
+    const float2 w = __ffma2_rn(y1, y1, __fmul2_rn(y0, y0));
+    return make_float2(ex2_approx(fmaf(-y2.x, y2.x, -w.x)), ex2_approx(fmaf(-y2.y, y2.y, -w.y)));
+}
+
+// Triangular form of a Gaussian from its ready form (make_ready: -mu | A = -1/2 log2(e) sym(S) | ...): with
+// -A = L L^T (Cholesky) the exponent is -|L^T (x - mu)|^2, and y = L^T x' + nb with x' = x - origin and
+// nb = -L^T (mu - origin) needs no subtraction per pair (the evaluation kernels use the same form; see their note on its
+// rounding). tri: nb[D] | L (l00 l10 [l20] l11 [l21 l22]). Returns the largest absolute row sum of L^T, +inf if the
+// matrix is not positive definite.
+template <int D>
+__device__ __forceinline__ float triangular_from_ready(const float* rdy, const float* origin, float* tri) {
+    if constexpr (D == 2) {
+        const float a00 = -rdy[2], a01 = -rdy[3], a11 = -rdy[4];
+        const float l00 = sqrtf(a00), l10 = a01 / l00;
+        const float d1 = a11 - l10 * l10;
+        const float l11 = sqrtf(d1);
+        const float m0 = -rdy[0] - origin[0], m1 = -rdy[1] - origin[1];
+        tri[0] = -(l00 * m0 + l10 * m1);
+        tri[1] = -(l11 * m1);
+        tri[2] = l00; tri[3] = l10; tri[4] = l11;
+        return (a00 > 0.f && d1 > 0.f) ? fmaxf(fabsf(l00) + fabsf(l10), fabsf(l11)) : INFINITY;
+    } else {
+        const float a00 = -rdy[3], a01 = -rdy[4], a02 = -rdy[5], a11 = -rdy[6], a12 = -rdy[7], a22 = -rdy[8];
+        const float l00 = sqrtf(a00), l10 = a01 / l00, l20 = a02 / l00;
+        const float d1 = a11 - l10 * l10;
+        const float l11 = sqrtf(d1), l21 = (a12 - l20 * l10) / l11;
+        const float d2 = a22 - l20 * l20 - l21 * l21;
+        const float l22 = sqrtf(d2);
+        const float m0 = -rdy[0] - origin[0], m1 = -rdy[1] - origin[1], m2 = -rdy[2] - origin[2];
+        tri[0] = -(l00 * m0 + l10 * m1 + l20 * m2);
+        tri[1] = -(l11 * m1 + l21 * m2);
+        tri[2] = -(l22 * m2);
+        tri[3] = l00; tri[4] = l10; tri[5] = l20; tri[6] = l11; tri[7] = l21; tri[8] = l22;
+        const float bound = fmaxf(fabsf(l00) + fabsf(l10) + fabsf(l20), fmaxf(fabsf(l11) + fabsf(l21), fabsf(l22)));
+        return (a00 > 0.f && d1 > 0.f && d2 > 0.f) ? bound : INFINITY;
+    }
+}
+
+// (row-sum bound) x (half extent of the mixture's centres) up to which the triangular loop is used: the error of a
+// pair's value stays below 3e-5 of the Gaussian's peak (the forward evaluation kernel uses the same limit).
+constexpr float kTriangularLimit = 350.f;
+
 template <int D>
 struct ReadyLarge {
     // per Gaussian: -mu | A (off-diagonals doubled) | norm w, norm x0 | pad = 8 (2D) or 12 (3D) floats, whole float4
@@ -228,6 +276,60 @@ relu_fixed_point_large_kernel(const float* __restrict__ mixtures, const float* _
     const float* src = mixtures + mix * (long long)G * RF;
     const bool single_chunk = G <= kChunk;
 
+    // ---- box of the centres and the largest row-sum bound of the mixture: which pair loop ----
+    __shared__ float s_red[kThreads / 32][2 * D + 1];
+    __shared__ float s_origin[D];
+    __shared__ int s_triangular;
+    {
+        float lo[D], hi[D], bound = 0.f;
+        float zero[D];
+#pragma unroll
+        for (int d = 0; d < D; ++d) { lo[d] = INFINITY; hi[d] = -INFINITY; zero[d] = 0.f; }
+        for (int j = tid; j < G; j += kThreads) {
+            float r[RF], rdy[RD], tri[D + NS];
+#pragma unroll
+            for (int f = 0; f < RF; ++f) r[f] = __ldg(src + (size_t)j * RF + f);
+            make_ready<D>(r, constant, relu_constant, tf.weight_divisor, rdy);
+            const float b = triangular_from_ready<D>(rdy, zero, tri);
+            bound = (b >= bound) ? b : (b == b ? bound : INFINITY);
+#pragma unroll
+            for (int d = 0; d < D; ++d) { lo[d] = fminf(lo[d], r[1 + d]); hi[d] = fmaxf(hi[d], r[1 + d]); }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            bound = fmaxf(bound, __shfl_xor_sync(0xffffffffu, bound, o));
+#pragma unroll
+            for (int d = 0; d < D; ++d) {
+                lo[d] = fminf(lo[d], __shfl_xor_sync(0xffffffffu, lo[d], o));
+                hi[d] = fmaxf(hi[d], __shfl_xor_sync(0xffffffffu, hi[d], o));
+            }
+        }
+        if ((tid & 31) == 0) {
+            s_red[tid >> 5][0] = bound;
+#pragma unroll
+            for (int d = 0; d < D; ++d) { s_red[tid >> 5][1 + d] = lo[d]; s_red[tid >> 5][1 + D + d] = hi[d]; }
+        }
+        __syncthreads();
+        if (tid == 0) {
+            float bmax = 0.f, half = 0.f;
+            for (int w = 0; w < kThreads / 32; ++w) bmax = fmaxf(bmax, s_red[w][0]);     // fmaxf keeps +inf; NaN became +inf above
+#pragma unroll
+            for (int d = 0; d < D; ++d) {
+                float l = s_red[0][1 + d], h = s_red[0][1 + D + d];
+                for (int w = 1; w < kThreads / 32; ++w) { l = fminf(l, s_red[w][1 + d]); h = fmaxf(h, s_red[w][1 + D + d]); }
+                const float centre = 0.5f * l + 0.5f * h;
+                s_origin[d] = centre;
+                half = fmaxf(half, fmaxf(h - centre, centre - l));
+            }
+            s_triangular = (bmax * half <= kTriangularLimit) ? 1 : 0;
+        }
+        __syncthreads();
+    }
+    const bool triangular = s_triangular != 0;
+    float origin[D];
+#pragma unroll
+    for (int d = 0; d < D; ++d) origin[d] = s_origin[d];
+
     for (int base = 0; base < G; base += kThreads * P) {
         float2 x[P][D], sum_w[P], sum_x[P];
 #pragma unroll
@@ -235,7 +337,7 @@ relu_fixed_point_large_kernel(const float* __restrict__ mixtures, const float* _
             const int i = base + tid + p * kThreads;
 #pragma unroll
             for (int d = 0; d < D; ++d) {
-                const float v = i < G ? __ldg(src + (size_t)i * RF + 1 + d) : 0.f;
+                const float v = i < G ? __ldg(src + (size_t)i * RF + 1 + d) - origin[d] : 0.f;
                 x[p][d] = f2(v, v);
             }
             sum_w[p] = f2(0.f, 0.f);
@@ -248,6 +350,7 @@ relu_fixed_point_large_kernel(const float* __restrict__ mixtures, const float* _
             if (!(single_chunk && base > 0)) {
                 for (int j = tid; j < jc_even; j += kThreads) {
                     float rdy[RD];
+                    float* dst = ready + (j >> 1) * PF + (j & 1);
                     if (j < jc) {
                         float r[RF];
 #pragma unroll
@@ -257,14 +360,25 @@ relu_fixed_point_large_kernel(const float* __restrict__ mixtures, const float* _
 #pragma unroll
                         for (int f = 0; f < RD; ++f) rdy[f] = 0.f;      // padding Gaussian: both weights 0
                     }
-                    float* dst = ready + (j >> 1) * PF + (j & 1);
+                    if (triangular) {
+                        float tri[D + NS];
+                        if (j < jc) {
+                            triangular_from_ready<D>(rdy, origin, tri);
+                        } else {
 #pragma unroll
-                    for (int f = 0; f < D; ++f) dst[2 * f] = rdy[f];
-                    if constexpr (D == 2) {
-                        dst[2 * 2] = rdy[2]; dst[2 * 3] = 2.f * rdy[3]; dst[2 * 4] = rdy[4];
+                            for (int f = 0; f < D + NS; ++f) tri[f] = 0.f;
+                        }
+#pragma unroll
+                        for (int f = 0; f < D + NS; ++f) dst[2 * f] = tri[f];
                     } else {
-                        dst[2 * 3] = rdy[3]; dst[2 * 4] = 2.f * rdy[4]; dst[2 * 5] = 2.f * rdy[5];
-                        dst[2 * 6] = rdy[6]; dst[2 * 7] = 2.f * rdy[7]; dst[2 * 8] = rdy[8];
+#pragma unroll
+                        for (int f = 0; f < D; ++f) dst[2 * f] = rdy[f] + origin[f];        // origin - mu
+                        if constexpr (D == 2) {
+                            dst[2 * 2] = rdy[2]; dst[2 * 3] = 2.f * rdy[3]; dst[2 * 4] = rdy[4];
+                        } else {
+                            dst[2 * 3] = rdy[3]; dst[2 * 4] = 2.f * rdy[4]; dst[2 * 5] = 2.f * rdy[5];
+                            dst[2 * 6] = rdy[6]; dst[2 * 7] = 2.f * rdy[7]; dst[2 * 8] = rdy[8];
+                        }
                     }
                     dst[2 * (D + NS)] = rdy[D + NS] * rdy[D + NS + 1];          // norm * w
                     dst[2 * (D + NS + 1)] = rdy[D + NS] * rdy[D + NS + 2];      // norm * x0
@@ -274,39 +388,75 @@ relu_fixed_point_large_kernel(const float* __restrict__ mixtures, const float* _
             __syncthreads();
             const float4* rp = reinterpret_cast<const float4*>(ready);
             const int n_pairs = jc_even >> 1;
+            if (triangular) {
 #pragma unroll 2
-            for (int j = 0; j < n_pairs; ++j) {
-                float4 v[PV];
+                for (int j = 0; j < n_pairs; ++j) {
+                    float4 v[PV];
 #pragma unroll
-                for (int k = 0; k < PV; ++k) v[k] = rp[j * PV + k];
-                if constexpr (D == 2) {
-                    const float2 nm0 = f2(v[0].x, v[0].y), nm1 = f2(v[0].z, v[0].w), a00 = f2(v[1].x, v[1].y),
-                                 a01 = f2(v[1].z, v[1].w), a11 = f2(v[2].x, v[2].y), cw = f2(v[2].z, v[2].w),
-                                 cx = f2(v[3].x, v[3].y);
+                    for (int k = 0; k < PV; ++k) v[k] = rp[j * PV + k];
+                    if constexpr (D == 2) {
+                        const float2 nb0 = f2(v[0].x, v[0].y), nb1 = f2(v[0].z, v[0].w), l00 = f2(v[1].x, v[1].y),
+                                     l10 = f2(v[1].z, v[1].w), l11 = f2(v[2].x, v[2].y), cw = f2(v[2].z, v[2].w),
+                                     cx = f2(v[3].x, v[3].y);
 #pragma unroll
-                    for (int p = 0; p < P; ++p) {
-                        const float2 t0 = __fadd2_rn(x[p][0], nm0), t1 = __fadd2_rn(x[p][1], nm1);
-                        const float2 r0 = __ffma2_rn(a01, t1, __fmul2_rn(a00, t0));
-                        const float2 r1 = __fmul2_rn(a11, t1);
-                        const float2 e = ex2_2(__ffma2_rn(t1, r1, __fmul2_rn(t0, r0)));
-                        sum_w[p] = __ffma2_rn(cw, e, sum_w[p]);
-                        sum_x[p] = __ffma2_rn(cx, e, sum_x[p]);
+                        for (int p = 0; p < P; ++p) {
+                            const float2 y1 = __ffma2_rn(l11, x[p][1], nb1);
+                            const float2 y0 = __ffma2_rn(l00, x[p][0], __ffma2_rn(l10, x[p][1], nb0));
+                            const float2 e = ex2_of_minus_square(y0, y1);
+                            sum_w[p] = __ffma2_rn(cw, e, sum_w[p]);
+                            sum_x[p] = __ffma2_rn(cx, e, sum_x[p]);
+                        }
+                    } else {
+                        const float2 nb0 = f2(v[0].x, v[0].y), nb1 = f2(v[0].z, v[0].w), nb2 = f2(v[1].x, v[1].y),
+                                     l00 = f2(v[1].z, v[1].w), l10 = f2(v[2].x, v[2].y), l20 = f2(v[2].z, v[2].w),
+                                     l11 = f2(v[3].x, v[3].y), l21 = f2(v[3].z, v[3].w), l22 = f2(v[4].x, v[4].y),
+                                     cw = f2(v[4].z, v[4].w), cx = f2(v[5].x, v[5].y);
+#pragma unroll
+                        for (int p = 0; p < P; ++p) {
+                            const float2 y2 = __ffma2_rn(l22, x[p][2], nb2);
+                            const float2 y1 = __ffma2_rn(l11, x[p][1], __ffma2_rn(l21, x[p][2], nb1));
+                            const float2 y0 = __ffma2_rn(l00, x[p][0], __ffma2_rn(l10, x[p][1], __ffma2_rn(l20, x[p][2], nb0)));
+                            const float2 e = ex2_of_minus_square(y0, y1, y2);
+                            sum_w[p] = __ffma2_rn(cw, e, sum_w[p]);
+                            sum_x[p] = __ffma2_rn(cx, e, sum_x[p]);
+                        }
                     }
-                } else {
-                    const float2 nm0 = f2(v[0].x, v[0].y), nm1 = f2(v[0].z, v[0].w), nm2 = f2(v[1].x, v[1].y),
-                                 a00 = f2(v[1].z, v[1].w), a01 = f2(v[2].x, v[2].y), a02 = f2(v[2].z, v[2].w),
-                                 a11 = f2(v[3].x, v[3].y), a12 = f2(v[3].z, v[3].w), a22 = f2(v[4].x, v[4].y),
-                                 cw = f2(v[4].z, v[4].w), cx = f2(v[5].x, v[5].y);
+                }
+            } else {
+#pragma unroll 2
+                for (int j = 0; j < n_pairs; ++j) {
+                    float4 v[PV];
 #pragma unroll
-                    for (int p = 0; p < P; ++p) {
-                        const float2 t0 = __fadd2_rn(x[p][0], nm0), t1 = __fadd2_rn(x[p][1], nm1),
-                                     t2 = __fadd2_rn(x[p][2], nm2);
-                        const float2 r0 = __ffma2_rn(a02, t2, __ffma2_rn(a01, t1, __fmul2_rn(a00, t0)));
-                        const float2 r1 = __ffma2_rn(a12, t2, __fmul2_rn(a11, t1));
-                        const float2 r2 = __fmul2_rn(a22, t2);
-                        const float2 e = ex2_2(__ffma2_rn(t2, r2, __ffma2_rn(t1, r1, __fmul2_rn(t0, r0))));
-                        sum_w[p] = __ffma2_rn(cw, e, sum_w[p]);
-                        sum_x[p] = __ffma2_rn(cx, e, sum_x[p]);
+                    for (int k = 0; k < PV; ++k) v[k] = rp[j * PV + k];
+                    if constexpr (D == 2) {
+                        const float2 nm0 = f2(v[0].x, v[0].y), nm1 = f2(v[0].z, v[0].w), a00 = f2(v[1].x, v[1].y),
+                                     a01 = f2(v[1].z, v[1].w), a11 = f2(v[2].x, v[2].y), cw = f2(v[2].z, v[2].w),
+                                     cx = f2(v[3].x, v[3].y);
+#pragma unroll
+                        for (int p = 0; p < P; ++p) {
+                            const float2 t0 = __fadd2_rn(x[p][0], nm0), t1 = __fadd2_rn(x[p][1], nm1);
+                            const float2 r0 = __ffma2_rn(a01, t1, __fmul2_rn(a00, t0));
+                            const float2 r1 = __fmul2_rn(a11, t1);
+                            const float2 e = ex2_2(__ffma2_rn(t1, r1, __fmul2_rn(t0, r0)));
+                            sum_w[p] = __ffma2_rn(cw, e, sum_w[p]);
+                            sum_x[p] = __ffma2_rn(cx, e, sum_x[p]);
+                        }
+                    } else {
+                        const float2 nm0 = f2(v[0].x, v[0].y), nm1 = f2(v[0].z, v[0].w), nm2 = f2(v[1].x, v[1].y),
+                                     a00 = f2(v[1].z, v[1].w), a01 = f2(v[2].x, v[2].y), a02 = f2(v[2].z, v[2].w),
+                                     a11 = f2(v[3].x, v[3].y), a12 = f2(v[3].z, v[3].w), a22 = f2(v[4].x, v[4].y),
+                                     cw = f2(v[4].z, v[4].w), cx = f2(v[5].x, v[5].y);
+#pragma unroll
+                        for (int p = 0; p < P; ++p) {
+                            const float2 t0 = __fadd2_rn(x[p][0], nm0), t1 = __fadd2_rn(x[p][1], nm1),
+                                         t2 = __fadd2_rn(x[p][2], nm2);
+                            const float2 r0 = __ffma2_rn(a02, t2, __ffma2_rn(a01, t1, __fmul2_rn(a00, t0)));
+                            const float2 r1 = __ffma2_rn(a12, t2, __fmul2_rn(a11, t1));
+                            const float2 r2 = __fmul2_rn(a22, t2);
+                            const float2 e = ex2_2(__ffma2_rn(t2, r2, __ffma2_rn(t1, r1, __fmul2_rn(t0, r0))));
+                            sum_w[p] = __ffma2_rn(cw, e, sum_w[p]);
+                            sum_x[p] = __ffma2_rn(cx, e, sum_x[p]);
+                        }
                     }
                 }
             }
