@@ -15,8 +15,8 @@ entry points.  The third-party headers the reference expects beside its tree (gl
 there, none installed) are replaced by the small stand-ins in oracle/ref_shims/.  nvcc compiles the .cu files, so their
 host code is built the way the reference builds it (no host fast-math for .cu units; its CPU launcher is OpenMP).
 
-The recipe needs the reference checkout (path in GMC_REFERENCE_ROOT, default /root/reference); where that is absent
-the prebuilt library is used as it is.
+The recipe needs the reference checkout (its path comes from GMC_REFERENCE_ROOT or the default below); where that is
+absent the prebuilt library is used as it is.
 """
 import concurrent.futures
 import os
