@@ -62,6 +62,31 @@ def test_argument_checks_of_the_added_entry_points():
     assert h(one, one, null, one, one, null, 1, 1, 1, 2, 1, 1, 1, 0) == 3           # gradient without grad_out
 
 
+def test_argument_checks_of_the_lbvh_options_and_the_normalisation_entry_points():
+    from gmc import _native
+    null = ctypes.c_void_p(0)
+    one = ctypes.c_void_p(16)  # never dereferenced: argument checks come first
+    f = _native.lib.gmc_lbvh_build_ex
+    assert f(one, 1, 8, 4, 0, 0, 0.001, one, one, null, null) == 1               # D = 4
+    assert f(one, 1, 8, 2, 5, 0, 0.001, one, one, null, null) == 4               # no such key layout
+    assert f(one, 1, 8, 2, 2, 1, 0.001, one, one, one, null) == 4                # boxes need the component id in the key
+    assert f(one, 1, 1, 2, 0, 0, 0.001, one, one, null, null) == 1               # a tree needs two leaves
+    assert f(one, 1, 32769, 2, 0, 0, 0.001, one, one, null, null) == 1           # beyond the 16-bit node indices
+    assert f(null, 1, 8, 2, 0, 0, 0.001, one, one, null, null) == 3              # NULL mixture
+    assert f(one, 0, 8, 2, 1, 0, 0.001, one, one, null, null) == 0               # nothing to do
+    t = _native.lib.gmc_trace_scale
+    assert t(one, one, one, 1, 4, 5, null) == 1 and t(null, one, one, 1, 4, 2, null) == 3 and t(one, one, one, 0, 4, 2, null) == 0
+    sc = _native.lib.gmc_spatial_scale
+    assert sc(one, one, one, 1, 0, 2, null) == 1 and sc(one, null, one, 1, 4, 2, null) == 3 and sc(one, one, one, 0, 4, 3, null) == 0
+    n = _native.lib.gmc_input_normalise
+    assert n(one, one, null, null, 1, 8, 4, 1000, one, one, null) == 1            # D = 4
+    assert n(one, one, null, null, 1, 8, 3, 1, one, one, null) == 1               # a standard deviation needs two samples
+    assert n(one, null, null, null, 1, 8, 3, 1000, one, one, null) == 3           # neither seed nor uniform numbers
+    assert n(one, one, null, null, 1, 8, 3, 1000, null, one, null) == 3           # NULL output
+    assert n(one, one, null, null, 1, 20000, 3, 1000, one, one, null) == 1        # beyond the shared-memory size
+    assert n(one, one, null, null, 0, 8, 3, 1000, one, one, null) == 0            # nothing to do
+
+
 def test_argument_checks_of_the_no_allocation_entry_point():
     from gmc import _native
     null = ctypes.c_void_p(0)
