@@ -675,7 +675,10 @@ __device__ __forceinline__ void aggregate_output(const float* data_b, const floa
 // A CTA (8 warps) serves up to kAggOutputsPerCta outputs of ONE tree. When the tree's input records (Cin * (G + Gk)
 // Gaussians) fit, they are staged in shared memory first (STAGED): the leaves of a subtree name arbitrary records,
 // and gathering 26 floats per leaf from global memory is bound by L1 wavefronts.
-constexpr int kAggOutputsPerCta = 32;
+#ifndef GMC_AGG_OUTPUTS_PER_CTA
+#define GMC_AGG_OUTPUTS_PER_CTA 128
+#endif
+constexpr int kAggOutputsPerCta = GMC_AGG_OUTPUTS_PER_CTA;
 constexpr size_t kAggMaxStagedBytes = 96 * 1024;
 
 template <int D, bool STAGED>
