@@ -118,6 +118,54 @@ convolution_fitting_tree_kernel(const float* __restrict__ data, const float* __r
         float hi[D], lo[D];
 #pragma unroll
         for (int d = 0; d < D; ++d) { hi[d] = -INFINITY; lo[d] = INFINITY; }
+        if (staged && G <= 32 && (G & (G - 1)) == 0 && Cin <= 256) {
+            // the channels' data records are segments of G lanes: one record per thread, a shuffle reduction inside the
+            // segment, the segment's first lane keeps the channel's extremes (in the radix scratch, free until the sort)
+            float* chan = reinterpret_cast<float*>(radix_scratch);          // [Cin][max D | min D]
+            for (int i0 = 0; i0 < n_data; i0 += kThreads) {
+                const int i = i0 + tid;
+                float vh[D], vl[D];
+#pragma unroll
+                for (int d = 0; d < D; ++d) { vh[d] = -INFINITY; vl[d] = INFINITY; }
+                if (i < n_data) {
+                    const float4 v = records[i];
+#pragma unroll
+                    for (int d = 0; d < D; ++d) vh[d] = vl[d] = coordinate(v, d);
+                }
+                for (int o = G >> 1; o > 0; o >>= 1) {
+#pragma unroll
+                    for (int d = 0; d < D; ++d) {
+                        vh[d] = fmaxf(vh[d], __shfl_xor_sync(0xffffffffu, vh[d], o));
+                        vl[d] = fminf(vl[d], __shfl_xor_sync(0xffffffffu, vl[d], o));
+                    }
+                }
+                if (i < n_data && (i & (G - 1)) == 0) {
+                    float* c = chan + (i / G) * 2 * D;
+#pragma unroll
+                    for (int d = 0; d < D; ++d) { c[d] = vh[d]; c[D + d] = vl[d]; }
+                }
+            }
+            __syncthreads();
+            for (int ci = tid; ci < Cin; ci += kThreads) {
+                float kh[D], kl[D];
+#pragma unroll
+                for (int d = 0; d < D; ++d) { kh[d] = -INFINITY; kl[d] = INFINITY; }
+                for (int g = 0; g < Gk; ++g) {
+                    const float4 v = records[n_data + ci * Gk + g];
+#pragma unroll
+                    for (int d = 0; d < D; ++d) { kh[d] = fmaxf(kh[d], coordinate(v, d)); kl[d] = fminf(kl[d], coordinate(v, d)); }
+                }
+                const float* c = chan + ci * 2 * D;
+#pragma unroll
+                for (int d = 0; d < D; ++d) {
+                    hi[d] = fmaxf(hi[d], __fadd_rn(c[d], kh[d]));
+                    lo[d] = fminf(lo[d], __fadd_rn(c[D + d], kl[d]));
+                }
+            }
+#pragma unroll
+            for (int d = 0; d < D; ++d) { hi[d] = warp_max(hi[d]); lo[d] = warp_min(lo[d]); }
+            __syncthreads();             // the scratch is handed back before the sort uses it
+        } else
         for (int ci = warp; ci < Cin; ci += kWarps) {
             float dh[D], dl[D], kh[D], kl[D];
 #pragma unroll
